@@ -1,0 +1,319 @@
+/*
+ * kapyb.h -- C ABI of the B200 (sm_100a) backend for kapy-lang's matmul /
+ * elementwise / reduce operator surface.
+ *
+ * The reference turns a kernel built through python/src/ir.cc (Builder.create_*)
+ * into a PTX string (python/src/passes.cc:69-262, PassManager.run ->
+ * translate_llvm_to_ptx) and has no launcher.  A binding that wants the kernel
+ * to *run* calls the entry points below instead of that pipeline: the operands
+ * are the same seven-field global tensor descriptors kapy.mk_global builds
+ * (python/src/ir.cc:1013-1025), the enums carry the numeric values of
+ * include/kapy/Dialect/Kapy/IR/Enums.td:42-109, and errors come back as status
+ * codes instead of C++ exceptions (python/src/passes.cc:72-75).
+ *
+ * Conventions
+ *   - plain C, no torch / CUDA types in signatures; `stream` is a cudaStream_t
+ *     passed as void* (NULL = the legacy default stream);
+ *   - every pointer inside a kapyb_tensor2d is a DEVICE pointer unless the
+ *     function name ends in `_host`;
+ *   - calls are asynchronous with respect to the host and ordered on `stream`,
+ *     except the `_host` variants, which return after the result is in the host
+ *     buffer;
+ *   - nothing here throws, aborts or traps the device; device-side waits are
+ *     bounded and surface as KAPYB_TIMEOUT on the next kapyb_check().
+ */
+#ifndef KAPYB_H_
+#define KAPYB_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(_WIN32)
+#define KAPYB_API
+#else
+#define KAPYB_API __attribute__((visibility("default")))
+#endif
+
+/* ------------------------------------------------------------------ enums */
+
+typedef enum {
+  KAPYB_OK = 0,
+  KAPYB_INVALID_ARG = 1, /* verifier-equivalent rejection (Kapy.cpp:451-574) */
+  KAPYB_UNSUPPORTED = 2,
+  KAPYB_CUDA_ERROR = 3,
+  KAPYB_NCCL_ERROR = 4,
+  KAPYB_TIMEOUT = 5      /* a bounded device-side wait gave up */
+} kapyb_status;
+
+/* Element types on the path (ir.cc get_*_type, :598-640). */
+typedef enum {
+  KAPYB_F16 = 0,
+  KAPYB_BF16 = 1,
+  KAPYB_F32 = 2
+} kapyb_dtype;
+
+/* Enums.td:52-61 -- value returned for out-of-bounds lanes of ld_global. */
+typedef enum {
+  KAPYB_PAD_ZERO = 0,
+  KAPYB_PAD_QNAN = 1,
+  KAPYB_PAD_PINF = 2,
+  KAPYB_PAD_NINF = 3
+} kapyb_padding;
+
+/* Enums.td:90-100.  Names an sm_80 instruction; validated against the operand
+ * dtypes exactly as MatmulOp::verify does (Kapy.cpp:491-565) and otherwise
+ * ignored: scheduling on sm_100a is tcgen05. */
+typedef enum {
+  KAPYB_MMA_ANY = 0,
+  KAPYB_MMA_M16N8K8_F16 = 1,
+  KAPYB_MMA_M16N8K16_F16 = 2,
+  KAPYB_MMA_M16N8K8_TF32 = 3,
+  KAPYB_MMA_M16N8K16_F8 = 4
+} kapyb_matmul_impl_way;
+
+/* Enums.td:102-109. */
+typedef enum {
+  KAPYB_RZ = 0,
+  KAPYB_RN = 1
+} kapyb_rounding;
+
+/* Activation fused into the GEMM epilogue.  GELU_TANH is the composite
+ * u / (1 + exp(-2k)), k = 0.7978845608f * fma(0.044715f*u*u, u, u), built from
+ * the ops kapy has (exp -> ex2.approx, ElementwiseOpToLLVM.cpp:1039-1073;
+ * divf -> div.full.f32, :730-769). */
+typedef enum {
+  KAPYB_ACT_NONE = 0,
+  KAPYB_ACT_RELU = 1,
+  KAPYB_ACT_GELU_TANH = 2,
+  KAPYB_ACT_SILU = 3
+} kapyb_activation;
+
+/* Combiner of kapy.reduce's lambda region (Ops.td:441-457, Kapy.cpp:628-649);
+ * the four single-op lambdas are recognised. */
+typedef enum {
+  KAPYB_RED_ADD = 0,
+  KAPYB_RED_MUL = 1,
+  KAPYB_RED_MAX = 2, /* arith.maximumf: NaN propagates */
+  KAPYB_RED_MIN = 3  /* arith.minimumf */
+} kapyb_combiner;
+
+/* ------------------------------------------------------------ descriptors */
+
+/* kapy.mk_global (Ops.td:95-111; lowered struct {ptr,start0,start1,end0,end1,
+ * stride0,stride1}, TypeConverter.cpp:64-73).  Element (i, j) lives at
+ * ptr + (offset_elems + i*stride0 + j*stride1) * sizeof(dtype).  Sizes and
+ * strides are i32 as in the reference; a size of 1 broadcasts when the tensor
+ * is an elementwise input. */
+typedef struct {
+  void *ptr;
+  int64_t offset_elems;
+  int32_t size0, size1;
+  int32_t stride0, stride1;
+  int32_t dtype; /* kapyb_dtype */
+  int32_t padding; /* kapyb_padding, used by elementwise loads only */
+} kapyb_tensor2d;
+
+/* result = downcast(act(alpha * (lhs . rhs) + bias [+ acc])).
+ * The product accumulates in fp32 (bf16 operands require it, Kapy.cpp:479-482);
+ * bias enters in the accumulator type, which is what kapy-combine makes of
+ * add(matmul(a,b,0), broadcast(bias)) (Combine.td:38-88); the downcast is
+ * kapy.fptofp with a mandatory rounding mode (Kapy.cpp:272-287). */
+typedef struct {
+  float alpha;        /* 1.0f for plain matmul */
+  const void *bias;   /* NULL, or device vector */
+  int32_t bias_dtype; /* kapyb_dtype */
+  int32_t bias_axis;  /* 1: one value per column ([1,N] broadcast over rows);
+                         0: one value per row ([M,1]) */
+  int32_t activation; /* kapyb_activation */
+  int32_t rounding;   /* kapyb_rounding for the final downcast */
+} kapyb_epilogue;
+
+/* ----------------------------------------------- elementwise programs */
+
+/* One op of a recorded elementwise graph; mirrors the arith/math/kapy ops
+ * Builder.create_* can emit (ir.cc:744-1000, :1106-1157).  Every op rounds to
+ * `dtype`, its tensor element type, as the reference's per-op lowering does
+ * (ElementwiseOpToLLVM.cpp:424-485; bf16 mul/add/sub are single-rounding
+ * fma.rn.bf16, :771-892). */
+typedef enum {
+  KAPYB_OP_LOAD = 0,   /* dst = inputs[flags]            (kapy.ld_global) */
+  KAPYB_OP_CONST = 1,  /* dst = imm rounded to dtype     (arith.constant + kapy.splat) */
+  KAPYB_OP_CVT = 2,    /* dst = cast(a), flags = kapyb_rounding (extf/truncf/fptofp) */
+  KAPYB_OP_ADD = 3,
+  KAPYB_OP_SUB = 4,
+  KAPYB_OP_MUL = 5,
+  KAPYB_OP_DIV = 6,
+  KAPYB_OP_FMA = 7,    /* dst = a*b + c, one rounding    (math.fma) */
+  KAPYB_OP_MAXIMUM = 8,  /* arith.maximumf: NaN if either is NaN */
+  KAPYB_OP_MINIMUM = 9,
+  KAPYB_OP_MAXNUM = 10,  /* arith.maxnumf: the non-NaN operand */
+  KAPYB_OP_MINNUM = 11,
+  KAPYB_OP_CLAMP = 12, /* clampf(a, low=b, high=c); flags = propagate_nan */
+  KAPYB_OP_ABS = 13,
+  KAPYB_OP_NEG = 14,
+  KAPYB_OP_EXP = 15,
+  KAPYB_OP_EXP2 = 16,
+  KAPYB_OP_LOG = 17,
+  KAPYB_OP_LOG2 = 18,
+  KAPYB_OP_SQRT = 19,
+  KAPYB_OP_RSQRT = 20,
+  KAPYB_OP_ERF = 21,
+  KAPYB_OP_SIN = 22,
+  KAPYB_OP_COS = 23,
+  KAPYB_OP_FLOOR = 24,
+  KAPYB_OP_CEIL = 25,
+  KAPYB_OP_TANH = 26,  /* elementwise_extern_lib "__nv_tanhf" (Ops.td:459-484) */
+  KAPYB_OP_STORE = 27, /* output = a                      (kapy.st_global) */
+  KAPYB_OP_COUNT_
+} kapyb_opcode;
+
+#define KAPYB_MAX_REGS 16
+#define KAPYB_MAX_INSTS 64
+#define KAPYB_MAX_INPUTS 4
+
+typedef struct {
+  int32_t op;    /* kapyb_opcode */
+  int32_t dtype; /* kapyb_dtype of the result */
+  int32_t dst;   /* register 0..KAPYB_MAX_REGS-1 */
+  int32_t a, b, c; /* source registers, -1 when unused */
+  float imm;     /* KAPYB_OP_CONST */
+  int32_t flags; /* see the opcode */
+} kapyb_inst;
+
+/* ------------------------------------------------------------------ handle */
+
+typedef struct kapyb_context *kapyb_handle;
+
+/* Library version (major*100 + minor). */
+KAPYB_API int kapyb_version(void);
+
+/* Creates a handle bound to CUDA device `device`.  Fails with KAPYB_CUDA_ERROR
+ * when the device is absent or is not compute capability 10.x: there is no CPU
+ * fallback.  The handle owns its workspace, its status word and its tensor-map
+ * cache; the caller owns every tensor.  Not thread-safe: one handle per thread
+ * and device.  Replaces the reference's MLIRContext + PassManager pair
+ * (ir.cc:157-170, passes.cc:69-75). */
+KAPYB_API kapyb_status kapyb_create(kapyb_handle *out, int device);
+KAPYB_API kapyb_status kapyb_destroy(kapyb_handle h);
+
+/* Text of the last non-OK status returned through `h` (also valid for
+ * h == NULL: the last failure of kapyb_create on this thread).  Stands in for
+ * the what() of the exceptions the reference throws (passes.cc:74,
+ * ir.cc:257,431,588,677,1085). */
+KAPYB_API const char *kapyb_last_error_string(kapyb_handle h);
+
+/* Synchronises `stream` and reports what the device recorded: KAPYB_TIMEOUT if
+ * a kernel gave up on a bounded wait, KAPYB_CUDA_ERROR on a sticky error. */
+KAPYB_API kapyb_status kapyb_check(kapyb_handle h, void *stream);
+
+/* Grows the handle's device workspace (split-K partials, host-call staging) to
+ * at least `bytes`.  Called implicitly when needed; call it up front to keep
+ * allocation out of a timed region. */
+KAPYB_API kapyb_status kapyb_reserve_workspace(kapyb_handle h, size_t bytes);
+
+/* ------------------------------------------------------------------ matmul */
+
+/* kapy.matmul (Ops.td:416-439) at whole-problem scope:
+ *   out[M,N] = epilogue( lhs[M,K] . rhs[K,N] (+ acc[M,N]) ).
+ * lhs/rhs: f16 or bf16, same dtype (Kapy.cpp:484-487); either may be row- or
+ * column-major (one unit stride, CoalesceAccess.cpp:32-40).  `acc` may be NULL
+ * (= zero accumulator, the arith.constant dense<0.0> of matmul.mlir:6) or an
+ * f16/f32 [M,N] tensor added in fp32.  out: f16, bf16 or f32.
+ * Returns KAPYB_INVALID_ARG for the shape/dtype violations MatmulOp::verify
+ * rejects (Kapy.cpp:459-487). */
+KAPYB_API kapyb_status kapyb_matmul(kapyb_handle h, const kapyb_tensor2d *lhs,
+                                    const kapyb_tensor2d *rhs,
+                                    const kapyb_tensor2d *acc,
+                                    const kapyb_tensor2d *out,
+                                    const kapyb_epilogue *epilogue,
+                                    int32_t impl_way, void *stream);
+
+/* `batch` independent matmuls; operand b of batch i starts batch_stride_*
+ * elements after batch i-1.  In the reference the batch is the grid's z axis
+ * (kapy.program_id axis 2, ir.cc:1091-1096). */
+KAPYB_API kapyb_status kapyb_matmul_batched(
+    kapyb_handle h, const kapyb_tensor2d *lhs, const kapyb_tensor2d *rhs,
+    const kapyb_tensor2d *out, int32_t batch, int64_t batch_stride_lhs,
+    int64_t batch_stride_rhs, int64_t batch_stride_out,
+    const kapyb_epilogue *epilogue, int32_t impl_way, void *stream);
+
+/* kapyb_matmul with HOST buffers: copies lhs/rhs (and bias) to the handle's
+ * workspace, runs the same kernels, copies `out` back and returns when it has
+ * landed.  This is the call a binding makes when the caller's arrays live in
+ * host memory (numpy), and the one the end-to-end benchmark times. */
+KAPYB_API kapyb_status kapyb_matmul_host(kapyb_handle h,
+                                         const kapyb_tensor2d *lhs,
+                                         const kapyb_tensor2d *rhs,
+                                         const kapyb_tensor2d *out,
+                                         const kapyb_epilogue *epilogue,
+                                         int32_t impl_way, void *stream);
+
+/* N-sharded matmul with the gather fused into the epilogue: this rank owns
+ * columns [col_begin, col_begin + rhs->size1) of the full [M, n_total] output
+ * and stores each finished tile of them into the full-size output of every
+ * peer (peer_out[r] = base pointer of rank r's [M, n_total] buffer with row
+ * stride out_stride0, reachable from this device; peer_out[my rank] included).
+ * No loads from remote memory are issued.  The caller synchronises ranks
+ * (stream-ordered barrier) before reading. */
+KAPYB_API kapyb_status kapyb_matmul_push(
+    kapyb_handle h, const kapyb_tensor2d *lhs, const kapyb_tensor2d *rhs,
+    void *const *peer_out, int32_t n_peers, int32_t out_dtype,
+    int32_t out_stride0, int32_t col_begin, int32_t n_total,
+    const kapyb_epilogue *epilogue, int32_t impl_way, void *stream);
+
+/* --------------------------------------------------- elementwise / reduce */
+
+/* Runs a recorded elementwise graph over out->size0 x out->size1 elements.
+ * inputs[k] is what the k-th KAPYB_OP_LOAD reads; an input whose size on an
+ * axis is 1 broadcasts along it (kapy.broadcast, Ops.td:342-356).  Canonical
+ * graphs (affine, affine + gelu_tanh, binary add/sub/mul, casts) run as fused
+ * 128-bit-vectorised kernels; any other valid program runs on the generic
+ * device interpreter.  Programs are validated (register use before def, dtype
+ * agreement, downcasts need a rounding mode) as the op verifiers would. */
+KAPYB_API kapyb_status kapyb_elementwise(kapyb_handle h, const kapyb_inst *prog,
+                                         int32_t n_inst,
+                                         const kapyb_tensor2d *inputs,
+                                         int32_t n_inputs,
+                                         const kapyb_tensor2d *out,
+                                         void *stream);
+
+/* kapy.reduce (Ops.td:441-457; lowering ReduceOpToLLVM.cpp:76-119) over a whole
+ * [size0,size1] tensor: axis 1 -> dst [size0,1], axis 0 -> dst [1,size1].
+ * src elements are widened to dst->dtype (arith.extf) before combining when
+ * the dtypes differ; dst->dtype must be f32 or equal src->dtype.  The order of
+ * combination is unspecified, as in the reference. */
+KAPYB_API kapyb_status kapyb_reduce(kapyb_handle h, const kapyb_tensor2d *src,
+                                    const kapyb_tensor2d *dst, int32_t axis,
+                                    int32_t combiner, void *stream);
+
+/* ------------------------------------------------------------- shard math */
+
+/* Range [begin, end) of `total` units owned by `rank` of `parts` when units
+ * are dealt in blocks of `align` (the last blocks may be short or empty).
+ * Pure host arithmetic; no reference counterpart (the reference has no
+ * multi-GPU code). */
+KAPYB_API kapyb_status kapyb_shard_range(int64_t total, int32_t parts,
+                                         int32_t rank, int64_t align,
+                                         int64_t *begin, int64_t *end);
+
+/* ------------------------------------------------------------ diagnostics */
+
+/* Name of the kernel family the last matmul on `h` dispatched to
+ * ("tcgen05_1cta", "tcgen05_2cta", "tcgen05_skinny", "simt"). */
+KAPYB_API const char *kapyb_last_kernel(kapyb_handle h);
+
+/* Number of kernels this handle has launched since creation. */
+KAPYB_API int64_t kapyb_launch_count(kapyb_handle h);
+
+/* Forces a kernel family for matmul ("auto", "1cta", "2cta", "skinny",
+ * "simt"); for tests and profiling. */
+KAPYB_API kapyb_status kapyb_set_matmul_path(kapyb_handle h, const char *name);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* KAPYB_H_ */

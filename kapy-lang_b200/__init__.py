@@ -1,0 +1,14 @@
+"""B200 (sm_100a) backend for kapy-lang's matmul / elementwise / reduce path.
+
+The directory name carries a hyphen, so the package is registered under the
+importable name ``kapy_lang_b200`` by ``__graft_entry__.load_package()``.
+Nothing here computes on the CPU: every op is a CUDA kernel reached through the
+C ABI in ``include/kapyb.h``.
+"""
+from . import _abi as abi  # noqa: F401
+from . import programs  # noqa: F401
+from .build import build  # noqa: F401
+from .runtime import Handle, KapybError, KapybTimeout, shard_range, tensor2d  # noqa: F401
+
+__all__ = ["abi", "programs", "build", "Handle", "KapybError", "KapybTimeout", "shard_range",
+           "tensor2d"]

@@ -1,0 +1,300 @@
+// Elementwise kernels.
+//
+//  * elt_interp_kernel: executes a recorded op list per element with a rounding
+//    to the op's element type after every op -- the semantics of the reference's
+//    per-op lowering (ElementwiseOpToLLVM.cpp:424-485; bf16/f16 mul/add/sub/fma
+//    as single-rounding fma, :771-892).  Handles any strides, broadcast inputs
+//    and out-of-bounds padding.  Correct for every valid program; not tuned.
+//  * elt_unary16_kernel / elt_binary_kernel: the same op sequences for the
+//    canonical graphs, as streaming kernels with 128-bit coalesced accesses.
+//    They execute exactly the ops the interpreter would, in the same order, so
+//    both produce identical bits.
+#pragma once
+
+#include "common.cuh"
+
+namespace kapyb {
+
+struct EltTensor {
+  const void *ptr;  // element (0,0)
+  long long s0, s1;
+  int size0, size1;
+  int dtype;
+  int padding;
+};
+
+struct EltProgram {
+  kapyb_inst inst[KAPYB_MAX_INSTS];
+  int n_inst;
+  EltTensor in[KAPYB_MAX_INPUTS];
+  int n_in;
+  EltTensor out;
+};
+
+__device__ __forceinline__ float round_to_dtype(float v, int dtype, int rn) {
+  if (dtype == KAPYB_F32) return v;
+  return cvt_16_to_f32(cvt_f32_to_16(v, dtype, rn), dtype);
+}
+
+// a*b + c with ONE rounding at `dtype`; operands are exactly representable.
+__device__ __forceinline__ float fma_at(float a, float b, float c, int dtype) {
+  if (dtype == KAPYB_F32) return __fmaf_rn(a, b, c);
+  if (dtype == KAPYB_BF16)
+    return __bfloat162float(
+        __hfma(__float2bfloat16_rn(a), __float2bfloat16_rn(b), __float2bfloat16_rn(c)));
+  return __half2float(__hfma(__float2half_rn(a), __float2half_rn(b), __float2half_rn(c)));
+}
+
+__device__ __forceinline__ float pad_value(int padding) {
+  switch (padding) {
+  case KAPYB_PAD_QNAN: return __uint_as_float(0x7fffffffu);
+  case KAPYB_PAD_PINF: return __uint_as_float(0x7f800000u);
+  case KAPYB_PAD_NINF: return __uint_as_float(0xff800000u);
+  default: return 0.0f;
+  }
+}
+
+__device__ __forceinline__ float maximum_f(float a, float b) {
+  if (a != a || b != b) return __uint_as_float(0x7fffffffu);
+  return fmaxf(a, b);  // fmaxf orders -0 < +0
+}
+__device__ __forceinline__ float minimum_f(float a, float b) {
+  if (a != a || b != b) return __uint_as_float(0x7fffffffu);
+  return fminf(a, b);
+}
+
+__device__ float interp_one(const EltProgram &P, int i, int j, bool *stored, float *store_val) {
+  float r[KAPYB_MAX_REGS];
+#pragma unroll
+  for (int t = 0; t < KAPYB_MAX_REGS; ++t) r[t] = 0.0f;
+  float last = 0.0f;
+  for (int pc = 0; pc < P.n_inst; ++pc) {
+    const kapyb_inst in = P.inst[pc];
+    const float a = in.a >= 0 ? r[in.a & (KAPYB_MAX_REGS - 1)] : 0.0f;
+    const float b = in.b >= 0 ? r[in.b & (KAPYB_MAX_REGS - 1)] : 0.0f;
+    const float c = in.c >= 0 ? r[in.c & (KAPYB_MAX_REGS - 1)] : 0.0f;
+    float v = 0.0f;
+    const int dt = in.dtype;
+    switch (in.op) {
+    case KAPYB_OP_LOAD: {
+      const EltTensor &t = P.in[in.flags & (KAPYB_MAX_INPUTS - 1)];
+      const int ii = t.size0 == 1 ? 0 : i, jj = t.size1 == 1 ? 0 : j;
+      if (ii >= t.size0 || jj >= t.size1)
+        v = pad_value(t.padding);
+      else
+        v = load_as_f32(t.ptr, t.dtype, ii * t.s0 + jj * t.s1);
+      break;
+    }
+    case KAPYB_OP_CONST: v = round_to_dtype(in.imm, dt, 1); break;
+    case KAPYB_OP_CVT: v = round_to_dtype(a, dt, in.flags); break;
+    case KAPYB_OP_ADD: v = dt == KAPYB_F32 ? __fadd_rn(a, b) : fma_at(a, 1.0f, b, dt); break;
+    case KAPYB_OP_SUB: v = dt == KAPYB_F32 ? __fsub_rn(a, b) : fma_at(b, -1.0f, a, dt); break;
+    case KAPYB_OP_MUL: v = dt == KAPYB_F32 ? __fmul_rn(a, b) : fma_at(a, b, -0.0f, dt); break;
+    case KAPYB_OP_FMA: v = fma_at(a, b, c, dt); break;
+    case KAPYB_OP_DIV:
+      v = dt == KAPYB_F32 ? div_full(a, b) : round_to_dtype(__fdiv_rn(a, b), dt, 1);
+      break;
+    case KAPYB_OP_MAXIMUM: v = maximum_f(a, b); break;
+    case KAPYB_OP_MINIMUM: v = minimum_f(a, b); break;
+    case KAPYB_OP_MAXNUM: v = fmaxf(a, b); break;
+    case KAPYB_OP_MINNUM: v = fminf(a, b); break;
+    case KAPYB_OP_CLAMP:
+      v = in.flags ? minimum_f(maximum_f(a, b), c) : fminf(fmaxf(a, b), c);
+      break;
+    case KAPYB_OP_ABS: v = fabsf(a); break;
+    case KAPYB_OP_NEG: v = -a; break;
+    case KAPYB_OP_EXP: v = dt == KAPYB_F32 ? kapy_exp(a) : round_to_dtype(expf(a), dt, 1); break;
+    case KAPYB_OP_EXP2: v = round_to_dtype(exp2f(a), dt, 1); break;
+    case KAPYB_OP_LOG: v = round_to_dtype(logf(a), dt, 1); break;
+    case KAPYB_OP_LOG2: v = round_to_dtype(log2f(a), dt, 1); break;
+    case KAPYB_OP_SQRT: v = round_to_dtype(__fsqrt_rn(a), dt, 1); break;
+    case KAPYB_OP_RSQRT: v = round_to_dtype(rsqrtf(a), dt, 1); break;
+    case KAPYB_OP_ERF: v = round_to_dtype(erff(a), dt, 1); break;
+    case KAPYB_OP_SIN: v = round_to_dtype(sinf(a), dt, 1); break;
+    case KAPYB_OP_COS: v = round_to_dtype(cosf(a), dt, 1); break;
+    case KAPYB_OP_FLOOR: v = floorf(a); break;
+    case KAPYB_OP_CEIL: v = ceilf(a); break;
+    case KAPYB_OP_TANH: v = round_to_dtype(tanhf(a), dt, 1); break;
+    case KAPYB_OP_STORE:
+      *stored = true;
+      *store_val = a;
+      break;
+    default: break;
+    }
+    if (in.op != KAPYB_OP_STORE && in.dst >= 0) r[in.dst & (KAPYB_MAX_REGS - 1)] = v;
+    last = v;
+  }
+  return last;
+}
+
+__global__ void __launch_bounds__(256) elt_interp_kernel(const EltProgram P) {
+  const long long total = static_cast<long long>(P.out.size0) * P.out.size1;
+  const long long step = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long e = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; e < total;
+       e += step) {
+    // walk along the unit-stride axis of the output for coalescing
+    int i, j;
+    if (P.out.s1 == 1 || P.out.size0 == 1) {
+      i = static_cast<int>(e / P.out.size1);
+      j = static_cast<int>(e - static_cast<long long>(i) * P.out.size1);
+    } else {
+      j = static_cast<int>(e / P.out.size0);
+      i = static_cast<int>(e - static_cast<long long>(j) * P.out.size0);
+    }
+    bool stored = false;
+    float sv = 0.0f;
+    interp_one(P, i, j, &stored, &sv);
+    if (stored) {
+      void *o = const_cast<void *>(P.out.ptr);
+      const long long idx = i * P.out.s0 + j * P.out.s1;
+      // the stored register already holds a value of the output's type
+      if (P.out.dtype == KAPYB_F32)
+        static_cast<float *>(o)[idx] = sv;
+      else
+        static_cast<uint16_t *>(o)[idx] = cvt_f32_to_16(sv, P.out.dtype, 1);
+    }
+  }
+}
+
+// ------------------------------------------------------------ fused kernels
+
+// y = cvt16( act( fma(ext(x), s, b) ) ): the "affine (+ gelu_tanh)" graph.
+// The gelu constants come from the program so the kernel reproduces whatever
+// constants the caller recorded.
+struct AffineGelu {
+  float s, b;
+  int gelu;        // 0: affine only
+  float c0, c1;    // k = c0 * fma(c1*u*u, u, u)
+  float m2, one;   // y = u / (one + exp(m2 * k))
+  __device__ __forceinline__ float operator()(float x) const {
+    const float u = __fmaf_rn(x, s, b);
+    if (!gelu) return u;
+    const float t = __fmul_rn(__fmul_rn(c1, u), u);
+    const float k = __fmul_rn(c0, __fmaf_rn(t, u, u));
+    const float e = kapy_exp(__fmul_rn(m2, k));
+    return div_full(u, __fadd_rn(one, e));
+  }
+};
+
+__device__ __forceinline__ uint4 ld_stream(const uint4 *p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+__device__ __forceinline__ void st_stream(uint4 *p, uint4 v) {
+  asm volatile("st.global.cs.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y),
+               "r"(v.z), "r"(v.w)
+               : "memory");
+}
+
+template <class F>
+__device__ __forceinline__ uint32_t apply2_16(uint32_t w, const F &f, int din, int dout, int rn) {
+  const float lo = f(cvt_16_to_f32(static_cast<uint16_t>(w & 0xffffu), din));
+  const float hi = f(cvt_16_to_f32(static_cast<uint16_t>(w >> 16), din));
+  return cvt_pack2(lo, hi, dout, rn);
+}
+
+constexpr int kEltUnroll = 4;
+
+// 16-bit in, 16-bit out, contiguous, 16-byte aligned; n_vec vectors of 8
+// elements plus a scalar tail handled by the last block.
+template <class F>
+__global__ void __launch_bounds__(256)
+elt_unary16_kernel(const uint4 *__restrict__ x, uint4 *__restrict__ y, long long n_vec,
+                   long long n_elems, F f, int din, int dout, int rn) {
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  for (; i + (kEltUnroll - 1) * stride < n_vec; i += kEltUnroll * stride) {
+    uint4 v[kEltUnroll];
+#pragma unroll
+    for (int u = 0; u < kEltUnroll; ++u) v[u] = ld_stream(x + i + u * stride);
+#pragma unroll
+    for (int u = 0; u < kEltUnroll; ++u) {
+      uint4 o;
+      o.x = apply2_16(v[u].x, f, din, dout, rn);
+      o.y = apply2_16(v[u].y, f, din, dout, rn);
+      o.z = apply2_16(v[u].z, f, din, dout, rn);
+      o.w = apply2_16(v[u].w, f, din, dout, rn);
+      st_stream(y + i + u * stride, o);
+    }
+  }
+  for (; i < n_vec; i += stride) {
+    const uint4 v = ld_stream(x + i);
+    uint4 o;
+    o.x = apply2_16(v.x, f, din, dout, rn);
+    o.y = apply2_16(v.y, f, din, dout, rn);
+    o.z = apply2_16(v.z, f, din, dout, rn);
+    o.w = apply2_16(v.w, f, din, dout, rn);
+    st_stream(y + i, o);
+  }
+  if (blockIdx.x == gridDim.x - 1) {
+    const uint16_t *xs = reinterpret_cast<const uint16_t *>(x);
+    uint16_t *ys = reinterpret_cast<uint16_t *>(y);
+    for (long long e = n_vec * 8 + threadIdx.x; e < n_elems; e += blockDim.x)
+      ys[e] = cvt_f32_to_16(f(cvt_16_to_f32(xs[e], din)), dout, rn);
+  }
+}
+
+// z = a (op) b at one element type, contiguous and 16-byte aligned.
+template <int OP>
+__device__ __forceinline__ float binop_at(float a, float b, int dt) {
+  if (OP == KAPYB_OP_ADD) return dt == KAPYB_F32 ? __fadd_rn(a, b) : fma_at(a, 1.0f, b, dt);
+  if (OP == KAPYB_OP_SUB) return dt == KAPYB_F32 ? __fsub_rn(a, b) : fma_at(b, -1.0f, a, dt);
+  return dt == KAPYB_F32 ? __fmul_rn(a, b) : fma_at(a, b, -0.0f, dt);
+}
+
+template <int OP>
+__device__ __forceinline__ uint32_t binop_word(uint32_t wa, uint32_t wb, int dt) {
+  if (dt == KAPYB_F32)
+    return __float_as_uint(binop_at<OP>(__uint_as_float(wa), __uint_as_float(wb), dt));
+  if (dt == KAPYB_BF16) {
+    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162 *>(&wa);
+    const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162 *>(&wb);
+    __nv_bfloat162 r;
+    if (OP == KAPYB_OP_ADD)
+      r = __hfma2(a, __float2bfloat162_rn(1.0f), b);
+    else if (OP == KAPYB_OP_SUB)
+      r = __hfma2(b, __float2bfloat162_rn(-1.0f), a);
+    else
+      r = __hfma2(a, b, __float2bfloat162_rn(-0.0f));
+    return *reinterpret_cast<const uint32_t *>(&r);
+  }
+  const __half2 a = *reinterpret_cast<const __half2 *>(&wa);
+  const __half2 b = *reinterpret_cast<const __half2 *>(&wb);
+  __half2 r;
+  if (OP == KAPYB_OP_ADD)
+    r = __hadd2(a, b);
+  else if (OP == KAPYB_OP_SUB)
+    r = __hsub2(a, b);
+  else
+    r = __hmul2(a, b);
+  return *reinterpret_cast<const uint32_t *>(&r);
+}
+
+template <int OP>
+__global__ void __launch_bounds__(256)
+elt_binary_kernel(const uint4 *__restrict__ a, const uint4 *__restrict__ b, uint4 *__restrict__ z,
+                  long long n_vec, long long n_elems, int dt) {
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n_vec;
+       i += stride) {
+    const uint4 va = ld_stream(a + i), vb = ld_stream(b + i);
+    uint4 o;
+    o.x = binop_word<OP>(va.x, vb.x, dt);
+    o.y = binop_word<OP>(va.y, vb.y, dt);
+    o.z = binop_word<OP>(va.z, vb.z, dt);
+    o.w = binop_word<OP>(va.w, vb.w, dt);
+    st_stream(z + i, o);
+  }
+  if (blockIdx.x == gridDim.x - 1) {
+    const int per = dt == KAPYB_F32 ? 4 : 8;
+    for (long long e = n_vec * per + threadIdx.x; e < n_elems; e += blockDim.x) {
+      const float x = load_as_f32(a, dt, e), y = load_as_f32(b, dt, e);
+      store_from_f32(z, dt, e, binop_at<OP>(x, y, dt), 1);
+    }
+  }
+}
+
+}  // namespace kapyb

@@ -1,0 +1,397 @@
+// Persistent warp-specialised GEMM for sm_100a:
+//   TMA (cp.async.bulk.tensor, per-CTA loads only) -> 128-byte-swizzled shared
+//   memory ring -> tcgen05.mma with fp32 accumulators in TMEM (two accumulator
+//   slots, so the epilogue of tile i overlaps the main loop of tile i+1) ->
+//   tcgen05.ld -> fused epilogue (alpha, bias, addend, activation, downcast)
+//   -> swizzled staging -> TMA store.
+//
+// Replaces the schedule the reference spells out by hand in
+// test/Conversion/KapyToKgpu/matmul.mlir:46-128 (2-stage cp.async ring, ldmatrix,
+// mma.sync m16n8k8 chain, MatmulOpToLLVM.cpp:58-266) at whole-problem scope.
+//
+// Warp roles (192 threads): warp 0 = TMA producer (one lane), warp 1 = TMEM
+// allocator + MMA issuer (one lane), warps 2..5 = epilogue (warp w owns TMEM
+// lanes 32*(w%4) .. +31).
+//
+// CTAS == 2 pairs two CTAs of a cluster on one 256-row tile
+// (tcgen05.mma.cta_group::2): each CTA loads its own 128 rows of A and its own
+// half of the B columns; only the leader CTA (cluster rank 0) issues MMAs.  The
+// pair shares no loads, so no multicast is involved.
+#pragma once
+
+#include <cuda.h>
+
+#include "common.cuh"
+#include "ptx_sm100.cuh"
+
+namespace kapyb {
+
+constexpr int kGemmThreads = 192;
+constexpr int kMaxOutputs = 8;  // own output + up to 7 peers for the push epilogue
+
+struct TmapArray {
+  CUtensorMap m[kMaxOutputs];
+};
+
+struct GemmParams {
+  int M, N, K, batch;
+  int tiles_m, tiles_n;  // tile grid of one batch entry
+  int num_tiles;         // tiles_m * tiles_n * batch
+  int num_kb;            // ceil(K / 64)
+  int group_m;           // rasterisation: tiles_m are walked in groups of this many
+  int a_mn_major;        // 1: lhs is column-major (M contiguous)
+  int b_mn_major;        // 1: rhs is row-major [K,N] (N contiguous)
+  int out_dtype;
+  int n_out;             // number of output tensor maps (1, or n_peers for push)
+  int out_col_offset;    // column offset of this shard inside each output
+  uint32_t idesc;
+  uint32_t *status;
+  EpilogueArgs ep;
+};
+
+template <int BN, int CTAS>
+struct GemmCfg {
+  static constexpr int BM = 128;  // rows per CTA (TMEM lanes)
+  static constexpr int BK = 64;   // 128 bytes of a 16-bit type: one swizzle span
+  static constexpr int TILE_M = BM * CTAS;
+  static constexpr int BN_CTA = BN / CTAS;  // B columns this CTA loads
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = BN_CTA * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int C_WARP_BYTES = 2 * 4096;  // two 32-row x 128-byte buffers
+  static constexpr int C_BYTES = 4 * C_WARP_BYTES;
+  static constexpr int CTRL_BYTES = 1024;
+  static constexpr int SMEM_LIMIT = 232448;  // 227 KB opt-in maximum
+  static constexpr int STAGES_RAW = (SMEM_LIMIT - 1024 - CTRL_BYTES - C_BYTES) / STAGE_BYTES;
+  static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
+  static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + C_BYTES + CTRL_BYTES;
+  static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
+  static_assert(BN % 64 == 0 && BN <= 256, "BN must be 64, 128 or 256");
+  static_assert((TMEM_COLS & (TMEM_COLS - 1)) == 0 && TMEM_COLS <= 512, "TMEM columns");
+  static_assert(STAGES >= 2, "pipeline too shallow");
+};
+
+// Linear tile index -> (batch, m block, n block); m blocks are walked in groups
+// so that concurrently running CTAs share A rows and B columns in L2.
+__device__ __forceinline__ void decode_tile(const GemmParams &p, int tile, int &b, int &mb,
+                                            int &nb) {
+  const int per_batch = p.tiles_m * p.tiles_n;
+  b = tile / per_batch;
+  const int r = tile - b * per_batch;
+  const int in_group = p.group_m * p.tiles_n;
+  const int g = r / in_group;
+  const int first_m = g * p.group_m;
+  const int gsize = min(p.group_m, p.tiles_m - first_m);
+  const int rr = r - g * in_group;
+  mb = first_m + rr % gsize;
+  nb = rr / gsize;
+}
+
+template <int BN, int CTAS>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
+                    const __grid_constant__ CUtensorMap tmB,
+                    const __grid_constant__ TmapArray tmC, const GemmParams p) {
+  using Cfg = GemmCfg<BN, CTAS>;
+  constexpr int STAGES = Cfg::STAGES;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t *smem = reinterpret_cast<uint8_t *>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint8_t *sA = smem;
+  uint8_t *sB = sA + STAGES * Cfg::A_BYTES;
+  uint8_t *sC = sB + STAGES * Cfg::B_BYTES;
+  uint64_t *bars = reinterpret_cast<uint64_t *>(sC + Cfg::C_BYTES);
+  uint64_t *full_bar = bars;                 // [STAGES]
+  uint64_t *empty_bar = bars + STAGES;       // [STAGES]
+  uint64_t *tfull_bar = bars + 2 * STAGES;   // [2]
+  uint64_t *tempty_bar = tfull_bar + 2;      // [2]
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tempty_bar + 2);
+  volatile uint32_t *abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = CTAS == 2 ? ptx::cluster_ctarank() : 0u;
+  const int unit = CTAS == 2 ? (blockIdx.x >> 1) : blockIdx.x;      // CTA (pair) index
+  const int unit_step = CTAS == 2 ? (gridDim.x >> 1) : gridDim.x;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      ptx::mbar_init(ptx::smem_u32(&full_bar[s]), CTAS);  // one expect_tx arrival per CTA
+      ptx::mbar_init(ptx::smem_u32(&empty_bar[s]), 1);    // one tcgen05.commit
+    }
+    for (int a = 0; a < 2; ++a) {
+      ptx::mbar_init(ptx::smem_u32(&tfull_bar[a]), 1);          // one tcgen05.commit
+      ptx::mbar_init(ptx::smem_u32(&tempty_bar[a]), 4 * CTAS);  // one arrival per epilogue warp
+    }
+    *abort_flag = 0u;
+    ptx::fence_barrier_init();
+  }
+  if (warp == 0 && lane == 0) {
+    ptx::prefetch_tensormap(&tmA);
+    ptx::prefetch_tensormap(&tmB);
+    ptx::prefetch_tensormap(&tmC.m[0]);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc<CTAS>(ptx::smem_u32(tmem_slot), Cfg::TMEM_COLS);
+    ptx::tmem_relinquish<CTAS>();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  if constexpr (CTAS == 2) {
+    ptx::cluster_arrive();
+    ptx::cluster_wait();
+  }
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0 && lane == 0) {
+    // ------------------------------------------------------------ producer
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int tile = unit; tile < p.num_tiles && ok; tile += unit_step) {
+      int b, mb, nb;
+      decode_tile(p, tile, b, mb, nb);
+      const int m0 = mb * Cfg::TILE_M + static_cast<int>(rank) * Cfg::BM;
+      const int nB0 = nb * BN + static_cast<int>(rank) * Cfg::BN_CTA;
+      for (int kb = 0; kb < p.num_kb; ++kb) {
+        if (!ptx::mbar_wait(ptx::smem_u32(&empty_bar[stage]), phase ^ 1u, abort_flag)) {
+          ok = false;
+          break;
+        }
+        const int k0 = kb * Cfg::BK;
+        const uint32_t a_dst = ptx::smem_u32(sA + stage * Cfg::A_BYTES);
+        const uint32_t b_dst = ptx::smem_u32(sB + stage * Cfg::B_BYTES);
+        if constexpr (CTAS == 1) {
+          const uint32_t fb = ptx::smem_u32(&full_bar[stage]);
+          ptx::mbar_arrive_expect_tx(fb, Cfg::STAGE_BYTES);
+          if (!p.a_mn_major) {
+            ptx::tma_load_3d(a_dst, &tmA, fb, k0, m0, b);
+          } else {
+#pragma unroll
+            for (int j = 0; j < Cfg::BM / 64; ++j)
+              ptx::tma_load_3d(a_dst + j * 8192, &tmA, fb, m0 + 64 * j, k0, b);
+          }
+          if (!p.b_mn_major) {
+            ptx::tma_load_3d(b_dst, &tmB, fb, k0, nB0, b);
+          } else {
+#pragma unroll
+            for (int j = 0; j < Cfg::BN_CTA / 64; ++j)
+              ptx::tma_load_3d(b_dst + j * 8192, &tmB, fb, nB0 + 64 * j, k0, b);
+          }
+        } else {
+          // Both CTAs of the pair report to the leader's barrier.
+          const uint32_t fb = ptx::mapa(ptx::smem_u32(&full_bar[stage]), 0);
+          asm volatile(
+              "mbarrier.arrive.expect_tx.release.cluster.shared::cluster.b64 _, [%0], %1;" ::"r"(
+                  fb),
+              "r"(static_cast<uint32_t>(Cfg::STAGE_BYTES))
+              : "memory");
+          if (!p.a_mn_major) {
+            ptx::tma_load_3d_pair(a_dst, &tmA, fb, k0, m0, b);
+          } else {
+#pragma unroll
+            for (int j = 0; j < Cfg::BM / 64; ++j)
+              ptx::tma_load_3d_pair(a_dst + j * 8192, &tmA, fb, m0 + 64 * j, k0, b);
+          }
+          if (!p.b_mn_major) {
+            ptx::tma_load_3d_pair(b_dst, &tmB, fb, k0, nB0, b);
+          } else {
+#pragma unroll
+            for (int j = 0; j < Cfg::BN_CTA / 64; ++j)
+              ptx::tma_load_3d_pair(b_dst + j * 8192, &tmB, fb, nB0 + 64 * j, k0, b);
+          }
+        }
+        if (++stage == STAGES) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      }
+    }
+  } else if (warp == 1 && lane == 0 && rank == 0) {
+    // ---------------------------------------------------------- MMA issuer
+    // K-major operand: rows are 128 bytes, 8-row groups 1024 bytes apart; one
+    // UMMA K step (16 elements) is 32 bytes along the row.
+    // MN-major operand: 64-element (128-byte) MN chunks 8192 bytes apart, K
+    // rows 128 bytes apart in groups of 8 (1024 bytes); one K step is 16 rows.
+    const uint32_t a_lbo = p.a_mn_major ? 8192u : 16u, a_sbo = 1024u;
+    const uint32_t b_lbo = p.b_mn_major ? 8192u : 16u, b_sbo = 1024u;
+    const uint32_t a_kadv = p.a_mn_major ? 2048u : 32u;
+    const uint32_t b_kadv = p.b_mn_major ? 2048u : 32u;
+    int stage = 0;
+    uint32_t phase = 0;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int tile = unit; tile < p.num_tiles && ok; tile += unit_step) {
+      if (!ptx::mbar_wait(ptx::smem_u32(&tempty_bar[acc]), acc_phase ^ 1u, abort_flag)) break;
+      ptx::tc_fence_after();
+      const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
+      for (int kb = 0; kb < p.num_kb; ++kb) {
+        if (!ptx::mbar_wait(ptx::smem_u32(&full_bar[stage]), phase, abort_flag)) {
+          ok = false;
+          break;
+        }
+        ptx::tc_fence_after();
+        const uint32_t a_base = ptx::smem_u32(sA + stage * Cfg::A_BYTES);
+        const uint32_t b_base = ptx::smem_u32(sB + stage * Cfg::B_BYTES);
+#pragma unroll
+        for (int k = 0; k < Cfg::BK / 16; ++k) {
+          const uint64_t adesc = ptx::make_smem_desc_sw128(a_base + k * a_kadv, a_lbo, a_sbo);
+          const uint64_t bdesc = ptx::make_smem_desc_sw128(b_base + k * b_kadv, b_lbo, b_sbo);
+          ptx::umma_f16<CTAS>(d_tmem, adesc, bdesc, p.idesc, (kb | k) != 0 ? 1u : 0u);
+        }
+        // Free the stage in every CTA that filled it.
+        ptx::umma_commit<CTAS>(ptx::smem_u32(&empty_bar[stage]));
+        if constexpr (CTAS == 2)
+          ptx::umma_commit<CTAS>(ptx::mapa(ptx::smem_u32(&empty_bar[stage]), 1));
+        if (++stage == STAGES) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      }
+      if (!ok) break;
+      ptx::umma_commit<CTAS>(ptx::smem_u32(&tfull_bar[acc]));
+      if constexpr (CTAS == 2)
+        ptx::umma_commit<CTAS>(ptx::mapa(ptx::smem_u32(&tfull_bar[acc]), 1));
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1u;
+    }
+  } else if (warp >= 2) {
+    // ------------------------------------------------------------ epilogue
+    const int q = warp & 3;  // TMEM lane quarter this warp may touch
+    uint8_t *stg = sC + (warp - 2) * Cfg::C_WARP_BYTES;
+    const bool out32 = p.out_dtype == KAPYB_F32;
+    const int CW = out32 ? 32 : 64;  // output columns per 128-byte staging row
+    const uint32_t tempty_leader = CTAS == 2 ? ptx::mapa(ptx::smem_u32(&tempty_bar[0]), 0)
+                                             : ptx::smem_u32(&tempty_bar[0]);
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    int buf = 0;
+    for (int tile = unit; tile < p.num_tiles; tile += unit_step) {
+      int b, mb, nb;
+      decode_tile(p, tile, b, mb, nb);
+      const int m0 = mb * Cfg::TILE_M + static_cast<int>(rank) * Cfg::BM + q * 32;
+      const int n0 = nb * BN;
+      if (!ptx::mbar_wait(ptx::smem_u32(&tfull_bar[acc]), acc_phase, abort_flag)) break;
+      ptx::tc_fence_after();
+      const int row = m0 + lane;
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
+                             static_cast<uint32_t>(acc * BN);
+      if (m0 < p.M) {
+        float bias_row = 0.0f;
+        if (p.ep.bias != nullptr && p.ep.bias_axis == 0 && row < p.M)
+          bias_row = load_as_f32(p.ep.bias, p.ep.bias_dtype, row);
+        const int n_chunks = BN / CW;
+        for (int c = 0; c < n_chunks; ++c) {
+          const int nc = n0 + c * CW;
+          if (nc >= p.N) break;
+          uint8_t *sbuf = stg + buf * 4096;
+          // The store issued two chunks ago read this buffer; let it finish.
+          if (lane == 0) ptx::tma_store_wait_read<1>();
+          __syncwarp();
+#pragma unroll 1
+          for (int h = 0; h < CW / 32; ++h) {
+            uint32_t v[32];
+            ptx::tmem_ld_32x32(t_row + static_cast<uint32_t>(c * CW + h * 32), v);
+            ptx::tmem_ld_wait();
+            const int col0 = nc + h * 32;
+            float bias_lane = 0.0f;
+            if (p.ep.bias != nullptr && p.ep.bias_axis == 1 && col0 + lane < p.N)
+              bias_lane = load_as_f32(p.ep.bias, p.ep.bias_dtype, col0 + lane);
+            float f[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              float x = __uint_as_float(v[i]) * p.ep.alpha;
+              const float bc = __shfl_sync(0xffffffffu, bias_lane, i);
+              x += (p.ep.bias_axis == 1) ? bc : bias_row;
+              f[i] = x;
+            }
+            if (p.ep.acc != nullptr && row < p.M) {
+              const long long base = static_cast<long long>(b) * p.ep.acc_batch_stride +
+                                     static_cast<long long>(row) * p.ep.acc_stride0;
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                if (col0 + i < p.N)
+                  f[i] += load_as_f32(p.ep.acc, p.ep.acc_dtype,
+                                      base + static_cast<long long>(col0 + i) * p.ep.acc_stride1);
+            }
+            if (p.ep.activation != KAPYB_ACT_NONE) {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) f[i] = apply_activation(p.ep.activation, f[i]);
+            }
+            // Row `lane` of the staging tile, 128-byte swizzle: 16-byte chunk j
+            // of row r lives at chunk position j ^ (r & 7).
+            uint8_t *srow = sbuf + lane * 128;
+            if (out32) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                uint4 w = make_uint4(__float_as_uint(f[4 * j]), __float_as_uint(f[4 * j + 1]),
+                                     __float_as_uint(f[4 * j + 2]), __float_as_uint(f[4 * j + 3]));
+                *reinterpret_cast<uint4 *>(srow + ((j ^ (lane & 7)) << 4)) = w;
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                uint4 w;
+                w.x = cvt_pack2(f[8 * j], f[8 * j + 1], p.out_dtype, p.ep.rounding);
+                w.y = cvt_pack2(f[8 * j + 2], f[8 * j + 3], p.out_dtype, p.ep.rounding);
+                w.z = cvt_pack2(f[8 * j + 4], f[8 * j + 5], p.out_dtype, p.ep.rounding);
+                w.w = cvt_pack2(f[8 * j + 6], f[8 * j + 7], p.out_dtype, p.ep.rounding);
+                const int jj = h * 4 + j;
+                *reinterpret_cast<uint4 *>(srow + ((jj ^ (lane & 7)) << 4)) = w;
+              }
+            }
+          }
+          ptx::fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            for (int o = 0; o < p.n_out; ++o)
+              ptx::tma_store_3d(&tmC.m[o], ptx::smem_u32(sbuf), p.out_col_offset + nc, m0, b);
+            ptx::tma_store_commit();
+          }
+          buf ^= 1;
+        }
+      }
+      // All of this warp's TMEM reads of the slot are done: hand it back.
+      ptx::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        const uint32_t bar = tempty_leader + static_cast<uint32_t>(acc * 8);
+        if constexpr (CTAS == 2)
+          ptx::mbar_arrive_cluster(bar);
+        else
+          ptx::mbar_arrive(bar);
+      }
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1u;
+    }
+    if (lane == 0) ptx::tma_store_wait_all<0>();
+    __syncwarp();
+  }
+
+  // ---------------------------------------------------------------- teardown
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (*abort_flag != 0u) {
+    if (threadIdx.x == 0) atomicExch(p.status, kStatusTimeout);
+    // Give loads that are still in flight time to land before the shared
+    // memory they target is released.
+    const uint64_t t0 = ptx::globaltimer_ns();
+    while (ptx::globaltimer_ns() - t0 < 200000ull) {
+    }
+    __syncthreads();
+  }
+  if constexpr (CTAS == 2) {
+    // The peer may still address this CTA's barriers / shared memory.
+    ptx::cluster_arrive();
+    ptx::cluster_wait();
+  }
+  if (warp == 1) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc<CTAS>(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+}  // namespace kapyb

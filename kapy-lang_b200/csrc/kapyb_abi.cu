@@ -1,0 +1,1151 @@
+// C ABI of the library (include/kapyb.h): handle management, verifier-equivalent
+// validation, kernel selection and launch.  Everything here runs on the host;
+// the arithmetic lives in the .cuh kernels.  There is no CPU compute path: a
+// call either launches CUDA kernels or returns an error status.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <string>
+
+#include "../../include/kapyb.h"
+#include "eltwise.cuh"
+#include "gemm_simt.cuh"
+#include "gemm_skinny_sm100.cuh"
+#include "gemm_sm100.cuh"
+#include "reduce.cuh"
+
+using namespace kapyb;
+
+// ------------------------------------------------------------------ context
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+                                  const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                  const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+enum MatmulPath { PATH_AUTO = 0, PATH_1CTA, PATH_2CTA, PATH_SKINNY, PATH_SIMT };
+
+struct kapyb_context {
+  int device = 0;
+  int sm_count = 0;
+  uint32_t *status = nullptr;  // device word written by kernels that give up
+  void *workspace = nullptr;
+  size_t workspace_bytes = 0;
+  EncodeTiledFn encode = nullptr;
+  std::string last_error;
+  const char *last_kernel = "none";
+  int64_t launches = 0;
+  int forced_path = PATH_AUTO;
+  int forced_bn = 0;
+};
+
+static thread_local std::string g_create_error;
+
+static kapyb_status fail(kapyb_handle h, kapyb_status st, const char *fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof(buf), fmt, ap);
+  va_end(ap);
+  if (h)
+    h->last_error = buf;
+  else
+    g_create_error = buf;
+  return st;
+}
+
+#define CUDA_TRY(h, expr)                                                                  \
+  do {                                                                                     \
+    cudaError_t e_ = (expr);                                                               \
+    if (e_ != cudaSuccess)                                                                 \
+      return fail(h, KAPYB_CUDA_ERROR, "%s failed: %s", #expr, cudaGetErrorString(e_));    \
+  } while (0)
+
+extern "C" KAPYB_API int kapyb_version(void) { return 100; }
+
+extern "C" KAPYB_API kapyb_status kapyb_create(kapyb_handle *out, int device) {
+  if (!out) return fail(nullptr, KAPYB_INVALID_ARG, "kapyb_create: out is NULL");
+  *out = nullptr;
+  int n = 0;
+  cudaError_t e = cudaGetDeviceCount(&n);
+  if (e != cudaSuccess || n == 0)
+    return fail(nullptr, KAPYB_CUDA_ERROR,
+                "kapyb_create: no CUDA device (%s); this library has no CPU path",
+                e != cudaSuccess ? cudaGetErrorString(e) : "device count is 0");
+  if (device < 0 || device >= n)
+    return fail(nullptr, KAPYB_INVALID_ARG, "kapyb_create: device %d out of range [0,%d)", device,
+                n);
+  cudaDeviceProp prop;
+  CUDA_TRY(nullptr, cudaGetDeviceProperties(&prop, device));
+  if (prop.major != 10)
+    return fail(nullptr, KAPYB_CUDA_ERROR,
+                "kapyb_create: device %d is sm_%d%d; kernels are built for sm_100a only", device,
+                prop.major, prop.minor);
+  CUDA_TRY(nullptr, cudaSetDevice(device));
+  kapyb_context *c = new kapyb_context();
+  c->device = device;
+  c->sm_count = prop.multiProcessorCount;
+  cudaDriverEntryPointQueryResult q;
+  void *fn = nullptr;
+  e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
+  if (e != cudaSuccess || fn == nullptr || q != cudaDriverEntryPointSuccess) {
+    delete c;
+    return fail(nullptr, KAPYB_CUDA_ERROR, "kapyb_create: cuTensorMapEncodeTiled not available");
+  }
+  c->encode = reinterpret_cast<EncodeTiledFn>(fn);
+  e = cudaMalloc(&c->status, sizeof(uint32_t));
+  if (e == cudaSuccess) e = cudaMemset(c->status, 0, sizeof(uint32_t));
+  if (e != cudaSuccess) {
+    delete c;
+    return fail(nullptr, KAPYB_CUDA_ERROR, "kapyb_create: status word: %s", cudaGetErrorString(e));
+  }
+  *out = c;
+  return KAPYB_OK;
+}
+
+extern "C" KAPYB_API kapyb_status kapyb_destroy(kapyb_handle h) {
+  if (!h) return KAPYB_OK;
+  cudaSetDevice(h->device);
+  if (h->workspace) cudaFree(h->workspace);
+  if (h->status) cudaFree(h->status);
+  delete h;
+  return KAPYB_OK;
+}
+
+extern "C" KAPYB_API const char *kapyb_last_error_string(kapyb_handle h) {
+  return h ? h->last_error.c_str() : g_create_error.c_str();
+}
+
+extern "C" KAPYB_API const char *kapyb_last_kernel(kapyb_handle h) {
+  return h ? h->last_kernel : "none";
+}
+
+extern "C" KAPYB_API int64_t kapyb_launch_count(kapyb_handle h) { return h ? h->launches : 0; }
+
+extern "C" KAPYB_API kapyb_status kapyb_set_matmul_path(kapyb_handle h, const char *name) {
+  if (!h || !name) return fail(h, KAPYB_INVALID_ARG, "kapyb_set_matmul_path: NULL argument");
+  std::string s(name);
+  h->forced_bn = 0;
+  size_t colon = s.find(':');
+  if (colon != std::string::npos) {
+    h->forced_bn = atoi(s.c_str() + colon + 1);
+    s = s.substr(0, colon);
+    if (h->forced_bn != 64 && h->forced_bn != 128 && h->forced_bn != 256)
+      return fail(h, KAPYB_INVALID_ARG, "kapyb_set_matmul_path: tile width must be 64/128/256");
+  }
+  if (s == "auto")
+    h->forced_path = PATH_AUTO;
+  else if (s == "1cta")
+    h->forced_path = PATH_1CTA;
+  else if (s == "2cta")
+    h->forced_path = PATH_2CTA;
+  else if (s == "skinny")
+    h->forced_path = PATH_SKINNY;
+  else if (s == "simt")
+    h->forced_path = PATH_SIMT;
+  else
+    return fail(h, KAPYB_INVALID_ARG, "kapyb_set_matmul_path: unknown path '%s'", name);
+  return KAPYB_OK;
+}
+
+extern "C" KAPYB_API kapyb_status kapyb_check(kapyb_handle h, void *stream) {
+  if (!h) return fail(h, KAPYB_INVALID_ARG, "kapyb_check: NULL handle");
+  CUDA_TRY(h, cudaSetDevice(h->device));
+  CUDA_TRY(h, cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+  uint32_t st = 0;
+  CUDA_TRY(h, cudaMemcpy(&st, h->status, sizeof(st), cudaMemcpyDeviceToHost));
+  if (st != kStatusOk) {
+    cudaMemset(h->status, 0, sizeof(uint32_t));
+    // a kernel that gave up may have left split-K partial sums behind
+    if (h->workspace)
+      cudaMemset(h->workspace, 0, std::min(h->workspace_bytes, kSkinnyCounterBytes + kSkinnyScratchBytes));
+    return fail(h, KAPYB_TIMEOUT, "a kernel gave up on a bounded wait (status %u)", st);
+  }
+  return KAPYB_OK;
+}
+
+extern "C" KAPYB_API kapyb_status kapyb_reserve_workspace(kapyb_handle h, size_t bytes) {
+  if (!h) return fail(h, KAPYB_INVALID_ARG, "kapyb_reserve_workspace: NULL handle");
+  if (bytes <= h->workspace_bytes) return KAPYB_OK;
+  CUDA_TRY(h, cudaSetDevice(h->device));
+  CUDA_TRY(h, cudaDeviceSynchronize());
+  if (h->workspace) {
+    cudaFree(h->workspace);
+    h->workspace = nullptr;
+    h->workspace_bytes = 0;
+  }
+  size_t want = (bytes + (1u << 20) - 1) & ~static_cast<size_t>((1u << 20) - 1);
+  CUDA_TRY(h, cudaMalloc(&h->workspace, want));
+  // Split-K partial sums and tile counters must start at zero; kernels that use
+  // them leave them zeroed again when they finish.
+  CUDA_TRY(h, cudaMemset(h->workspace, 0, want));
+  h->workspace_bytes = want;
+  return KAPYB_OK;
+}
+
+extern "C" KAPYB_API kapyb_status kapyb_shard_range(int64_t total, int32_t parts, int32_t rank,
+                                                    int64_t align, int64_t *begin,
+                                                    int64_t *end) {
+  if (!begin || !end || total < 0 || parts <= 0 || rank < 0 || rank >= parts || align <= 0)
+    return KAPYB_INVALID_ARG;
+  const int64_t blocks = (total + align - 1) / align;
+  const int64_t base = blocks / parts, extra = blocks % parts;
+  const int64_t b0 = rank * base + std::min<int64_t>(rank, extra);
+  const int64_t b1 = b0 + base + (rank < extra ? 1 : 0);
+  *begin = std::min(total, b0 * align);
+  *end = std::min(total, b1 * align);
+  return KAPYB_OK;
+}
+
+// --------------------------------------------------------------- validation
+
+static bool valid_dtype(int d) { return d == KAPYB_F16 || d == KAPYB_BF16 || d == KAPYB_F32; }
+
+static const char *dtype_name(int d) {
+  return d == KAPYB_F16 ? "f16" : d == KAPYB_BF16 ? "bf16" : d == KAPYB_F32 ? "f32" : "?";
+}
+
+static const void *elem_ptr(const kapyb_tensor2d *t) {
+  return static_cast<const char *>(t->ptr) + t->offset_elems * dtype_size(t->dtype);
+}
+
+// The checks of MatmulOp::verify (Kapy.cpp:459-565) that apply at whole-problem
+// scope, with the reference's diagnostics.
+static kapyb_status verify_matmul(kapyb_handle h, const kapyb_tensor2d *lhs,
+                                  const kapyb_tensor2d *rhs, const kapyb_tensor2d *acc,
+                                  const kapyb_tensor2d *out, const kapyb_epilogue *ep,
+                                  int impl_way) {
+  if (!lhs || !rhs || !out) return fail(h, KAPYB_INVALID_ARG, "matmul: NULL tensor descriptor");
+  if (!lhs->ptr || !rhs->ptr || !out->ptr) return fail(h, KAPYB_INVALID_ARG, "matmul: NULL data pointer");
+  if (!valid_dtype(lhs->dtype) || !valid_dtype(rhs->dtype) || !valid_dtype(out->dtype))
+    return fail(h, KAPYB_INVALID_ARG, "matmul: unknown element type");
+  if (lhs->size0 < 0 || lhs->size1 < 0 || rhs->size0 < 0 || rhs->size1 < 0)
+    return fail(h, KAPYB_INVALID_ARG, "matmul: negative size");
+  if (lhs->size1 != rhs->size0)
+    return fail(h, KAPYB_INVALID_ARG,
+                "matmul: number of columns of lhs must be equal to number of rows of rhs");
+  if (out->size0 != lhs->size0)
+    return fail(h, KAPYB_INVALID_ARG,
+                "matmul: number of rows of acc must be equal to number of rows of lhs");
+  if (out->size1 != rhs->size1)
+    return fail(h, KAPYB_INVALID_ARG,
+                "matmul: number of columns of acc must be equal to number of columns of rhs");
+  if (lhs->dtype == KAPYB_F32 || rhs->dtype == KAPYB_F32)
+    return fail(h, KAPYB_UNSUPPORTED, "matmul: f32 (tf32) operands are not implemented");
+  if (lhs->dtype != rhs->dtype)
+    return fail(h, KAPYB_INVALID_ARG,
+                "matmul: lhs and rhs must have same element type unless they have f8 element type");
+  if (acc) {
+    if (!acc->ptr || (acc->dtype != KAPYB_F16 && acc->dtype != KAPYB_F32))
+      return fail(h, KAPYB_INVALID_ARG, "matmul: result must have f16 or f32 element type");
+    if (lhs->dtype == KAPYB_BF16 && acc->dtype == KAPYB_F16)
+      return fail(h, KAPYB_INVALID_ARG,
+                  "matmul: result must have f32 element type when operands are bf16 element type");
+    if (acc->size0 != out->size0 || acc->size1 != out->size1)
+      return fail(h, KAPYB_INVALID_ARG, "matmul: acc shape must match the result shape");
+  }
+  switch (impl_way) {
+  case KAPYB_MMA_ANY:
+  case KAPYB_MMA_M16N8K8_F16:
+  case KAPYB_MMA_M16N8K16_F16: break;
+  case KAPYB_MMA_M16N8K8_TF32:
+    return fail(h, KAPYB_INVALID_ARG, "matmul: mma_m16n8k8_tf32 operands must have f32 element type");
+  case KAPYB_MMA_M16N8K16_F8:
+    return fail(h, KAPYB_INVALID_ARG,
+                "matmul: mma_m16n8k16_f8 operands must have f8E4M3 or f8E5M2 element type");
+  default: return fail(h, KAPYB_INVALID_ARG, "matmul: unknown MatmulImplWay %d", impl_way);
+  }
+  if (ep) {
+    if (ep->bias && !valid_dtype(ep->bias_dtype)) return fail(h, KAPYB_INVALID_ARG, "matmul: bad bias dtype");
+    if (ep->bias_axis != 0 && ep->bias_axis != 1) return fail(h, KAPYB_INVALID_ARG, "matmul: bias_axis must be 0 or 1");
+    if (ep->activation < KAPYB_ACT_NONE || ep->activation > KAPYB_ACT_SILU)
+      return fail(h, KAPYB_INVALID_ARG, "matmul: unknown activation %d", ep->activation);
+    if (ep->rounding != KAPYB_RZ && ep->rounding != KAPYB_RN)
+      return fail(h, KAPYB_INVALID_ARG, "matmul: rounding mode must be set for down cast");
+  }
+  return KAPYB_OK;
+}
+
+// ------------------------------------------------------------- tensor maps
+
+static CUtensorMapDataType tmap_dtype(int dtype) {
+  return dtype == KAPYB_F32   ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+         : dtype == KAPYB_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                              : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+}
+
+// 3-D map over a matrix whose unit-stride axis has `inner` elements and whose
+// other axis has `outer` rows `ld` elements apart, repeated `batch` times.
+static kapyb_status make_tmap(kapyb_handle h, CUtensorMap *map, const void *base, int dtype,
+                              uint64_t inner, uint64_t outer, uint64_t batch, uint64_t ld,
+                              uint64_t batch_stride, uint32_t box_inner, uint32_t box_outer) {
+  const uint64_t esz = dtype_size(dtype);
+  cuuint64_t dims[3] = {inner, outer, batch};
+  uint64_t bs = batch_stride * esz;
+  if (batch <= 1 || bs == 0) bs = ((std::max<uint64_t>(outer, 1) * ld * esz) + 15) / 16 * 16;
+  cuuint64_t strides[2] = {ld * esz, bs};
+  cuuint32_t box[3] = {box_inner, box_outer, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = h->encode(map, tmap_dtype(dtype), 3, const_cast<void *>(base), dims, strides, box,
+                         estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return fail(h, KAPYB_CUDA_ERROR,
+                "cuTensorMapEncodeTiled failed (%d): dims=%llu,%llu,%llu ld=%llu box=%u,%u", (int)r,
+                (unsigned long long)inner, (unsigned long long)outer, (unsigned long long)batch,
+                (unsigned long long)ld, box_inner, box_outer);
+  return KAPYB_OK;
+}
+
+static bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// A 2-D operand is TMA-describable when one stride is 1, its base is 16-byte
+// aligned and the other stride (and the batch stride) are multiples of 16 bytes.
+static bool tma_ok(const void *base, int dtype, int64_t unit_extent, int64_t other_extent,
+                   int64_t ld, int64_t batch, int64_t batch_stride) {
+  const int64_t esz = dtype_size(dtype);
+  if (!aligned16(base)) return false;
+  if (unit_extent <= 0 || other_extent <= 0) return false;
+  if (other_extent > 1 && ((ld * esz) % 16 != 0 || ld < unit_extent)) return false;
+  if (other_extent == 1 && (ld * esz) % 16 != 0) return false;
+  if (batch > 1 && ((batch_stride * esz) % 16 != 0 || batch_stride <= 0)) return false;
+  if (ld * esz >= (1ll << 40)) return false;
+  return true;
+}
+
+// ------------------------------------------------------------------ matmul
+
+struct MatmulProblem {
+  const void *a, *b;
+  void *c;
+  int M, N, K, batch;
+  long long a_s0, a_s1, a_bs, b_s0, b_s1, b_bs, c_s0, c_s1, c_bs;
+  int in_dtype, out_dtype;
+  EpilogueArgs ep;
+};
+
+static EpilogueArgs make_ep(const kapyb_epilogue *ep, const kapyb_tensor2d *acc) {
+  EpilogueArgs e;
+  e.alpha = ep ? ep->alpha : 1.0f;
+  e.bias = ep ? ep->bias : nullptr;
+  e.bias_dtype = ep ? ep->bias_dtype : KAPYB_F32;
+  e.bias_axis = ep ? ep->bias_axis : 1;
+  e.activation = ep ? ep->activation : KAPYB_ACT_NONE;
+  e.rounding = ep ? ep->rounding : KAPYB_RN;
+  e.acc = acc ? elem_ptr(acc) : nullptr;
+  e.acc_dtype = acc ? acc->dtype : KAPYB_F32;
+  e.acc_stride0 = acc ? acc->stride0 : 0;
+  e.acc_stride1 = acc ? acc->stride1 : 0;
+  e.acc_batch_stride = 0;
+  return e;
+}
+
+static void transpose_problem(MatmulProblem &p) {
+  // C^T = B^T . A^T
+  std::swap(p.a, p.b);
+  std::swap(p.M, p.N);
+  long long a0 = p.a_s0, a1 = p.a_s1, ab = p.a_bs;
+  p.a_s0 = p.b_s1;
+  p.a_s1 = p.b_s0;
+  p.a_bs = p.b_bs;
+  p.b_s0 = a1;
+  p.b_s1 = a0;
+  p.b_bs = ab;
+  std::swap(p.c_s0, p.c_s1);
+  std::swap(p.ep.acc_stride0, p.ep.acc_stride1);
+  p.ep.bias_axis ^= 1;
+}
+
+static kapyb_status launch_simt(kapyb_handle h, const MatmulProblem &p, cudaStream_t stream) {
+  SimtGemmParams sp;
+  sp.a = p.a;
+  sp.b = p.b;
+  sp.c = p.c;
+  sp.M = p.M;
+  sp.N = p.N;
+  sp.K = p.K;
+  sp.batch = p.batch;
+  sp.a_s0 = p.a_s0;
+  sp.a_s1 = p.a_s1;
+  sp.a_bs = p.a_bs;
+  sp.b_s0 = p.b_s0;
+  sp.b_s1 = p.b_s1;
+  sp.b_bs = p.b_bs;
+  sp.c_s0 = p.c_s0;
+  sp.c_s1 = p.c_s1;
+  sp.c_bs = p.c_bs;
+  sp.in_dtype = p.in_dtype;
+  sp.out_dtype = p.out_dtype;
+  sp.ep = p.ep;
+  dim3 grid((p.N + kSimtTile - 1) / kSimtTile, (p.M + kSimtTile - 1) / kSimtTile, p.batch);
+  if (grid.y > 65535 || grid.z > 65535)
+    return fail(h, KAPYB_UNSUPPORTED, "matmul (simt path): problem too large");
+  gemm_simt_kernel<<<grid, 256, 0, stream>>>(sp);
+  CUDA_TRY(h, cudaGetLastError());
+  h->launches++;
+  h->last_kernel = "simt";
+  return KAPYB_OK;
+}
+
+template <int BN, int CTAS>
+static kapyb_status launch_tcgen05(kapyb_handle h, const MatmulProblem &p, bool a_mn, bool b_mn,
+                                   void *const *outs, int n_out, cudaStream_t stream) {
+  using Cfg = GemmCfg<BN, CTAS>;
+  CUtensorMap tmA, tmB;
+  TmapArray tmC;
+  kapyb_status st;
+  // A: K-major -> inner K, rows M, box {64, 128}; MN-major -> inner M, rows K, box {64, 64}.
+  if (!a_mn)
+    st = make_tmap(h, &tmA, p.a, p.in_dtype, p.K, p.M, p.batch, p.a_s0, p.a_bs, 64, Cfg::BM);
+  else
+    st = make_tmap(h, &tmA, p.a, p.in_dtype, p.M, p.K, p.batch, p.a_s1, p.a_bs, 64, 64);
+  if (st != KAPYB_OK) return st;
+  // B [K,N]: MN-major (N contiguous) -> inner N, rows K, box {64, 64};
+  //          K-major (K contiguous)  -> inner K, rows N, box {64, BN_CTA}.
+  if (b_mn)
+    st = make_tmap(h, &tmB, p.b, p.in_dtype, p.N, p.K, p.batch, p.b_s0, p.b_bs, 64, 64);
+  else
+    st = make_tmap(h, &tmB, p.b, p.in_dtype, p.K, p.N, p.batch, p.b_s1, p.b_bs, 64, Cfg::BN_CTA);
+  if (st != KAPYB_OK) return st;
+  const uint32_t cw = p.out_dtype == KAPYB_F32 ? 32 : 64;
+  for (int o = 0; o < n_out; ++o) {
+    st = make_tmap(h, &tmC.m[o], outs[o], p.out_dtype, p.N, p.M, p.batch, p.c_s0, p.c_bs, cw, 32);
+    if (st != KAPYB_OK) return st;
+  }
+  for (int o = n_out; o < kMaxOutputs; ++o) tmC.m[o] = tmC.m[0];
+
+  GemmParams gp;
+  gp.M = p.M;
+  gp.N = p.N;
+  gp.K = p.K;
+  gp.batch = p.batch;
+  gp.tiles_m = (p.M + Cfg::TILE_M - 1) / Cfg::TILE_M;
+  gp.tiles_n = (p.N + BN - 1) / BN;
+  gp.num_tiles = gp.tiles_m * gp.tiles_n * p.batch;
+  gp.num_kb = (p.K + Cfg::BK - 1) / Cfg::BK;
+  gp.group_m = std::max(1, std::min(gp.tiles_m, 16 / CTAS));
+  gp.a_mn_major = a_mn ? 1 : 0;
+  gp.b_mn_major = b_mn ? 1 : 0;
+  gp.out_dtype = p.out_dtype;
+  gp.n_out = n_out;
+  gp.out_col_offset = 0;
+  gp.idesc = ptx::make_idesc_f16(p.in_dtype == KAPYB_BF16, a_mn, b_mn, Cfg::TILE_M, BN);
+  gp.status = h->status;
+  gp.ep = p.ep;
+
+  auto kern = gemm_tcgen05_kernel<BN, CTAS>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    CUDA_TRY(h, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     Cfg::SMEM_BYTES));
+    attr_set = true;
+  }
+  int units = std::min(gp.num_tiles, h->sm_count / CTAS);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(units * CTAS, 1, 1);
+  cfg.blockDim = dim3(kGemmThreads, 1, 1);
+  cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = CTAS;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  CUDA_TRY(h, cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmC, gp));
+  h->launches++;
+  h->last_kernel = CTAS == 2 ? "tcgen05_2cta" : "tcgen05_1cta";
+  return KAPYB_OK;
+}
+
+static size_t skinny_workspace_bytes() { return kSkinnyCounterBytes + kSkinnyScratchBytes; }
+
+static bool skinny_supported(int M, int N, int K) {
+  const int m_pad = (M + 15) / 16 * 16;
+  const long long n_tiles = (N + 127) / 128;
+  return M >= 1 && M <= kSkinnyMaxM && K >= 1 &&
+         n_tiles * 4 * sizeof(uint32_t) <= kSkinnyCounterBytes &&
+         static_cast<size_t>(n_tiles) * m_pad * 128 * sizeof(float) <= kSkinnyScratchBytes;
+}
+
+// Launches the weight-streaming kernel.  `scratch`/`counters` must be zero on
+// entry and are zero again when the kernel has finished.
+static kapyb_status launch_skinny_on(kapyb_handle h, const MatmulProblem &p, bool a_mn, bool b_mn,
+                                     float *scratch, uint32_t *counters, cudaStream_t stream) {
+  SkinnyParams sp;
+  sp.M = p.M;
+  sp.N = p.N;
+  sp.K = p.K;
+  sp.m_pad = (p.M + 15) / 16 * 16;
+  sp.num_kb = (p.K + 63) / 64;
+  sp.n_tiles = (p.N + 127) / 128;
+  sp.w_mn_major = b_mn ? 1 : 0;
+  sp.x_mn_major = a_mn ? 1 : 0;
+  sp.x_bytes = a_mn ? 8192 : sp.m_pad * 128;
+  int cols = 32;
+  while (cols < 2 * sp.m_pad) cols *= 2;
+  sp.tmem_cols = cols;
+  sp.out_dtype = p.out_dtype;
+  sp.c_s0 = p.c_s0;
+  sp.c_s1 = p.c_s1;
+  sp.c = p.c;
+  sp.scratch = scratch;
+  sp.counters = counters;
+  sp.idesc = ptx::make_idesc_f16(p.in_dtype == KAPYB_BF16, b_mn, a_mn, 128, sp.m_pad);
+  sp.status = h->status;
+  sp.ep = p.ep;
+  const long long total = static_cast<long long>(sp.n_tiles) * sp.num_kb;
+  const int ctas = static_cast<int>(std::min<long long>(h->sm_count, total));
+  sp.span = static_cast<int>((total + ctas - 1) / ctas);
+  const int grid = static_cast<int>((total + sp.span - 1) / sp.span);
+  const int stage_bytes = 128 * 64 * 2 + sp.x_bytes;
+  const int budget = 232448 - 1024 - 1024;
+  sp.stages = std::max(2, std::min(kSkinnyMaxStages, budget / stage_bytes));
+  const int smem = 1024 + sp.stages * stage_bytes + 1024;
+
+  CUtensorMap tmW, tmX;
+  kapyb_status st;
+  if (b_mn)
+    st = make_tmap(h, &tmW, p.b, p.in_dtype, p.N, p.K, 1, p.b_s0, 0, 64, 64);
+  else
+    st = make_tmap(h, &tmW, p.b, p.in_dtype, p.K, p.N, 1, p.b_s1, 0, 64, 128);
+  if (st != KAPYB_OK) return st;
+  if (a_mn)
+    st = make_tmap(h, &tmX, p.a, p.in_dtype, p.M, p.K, 1, p.a_s1, 0, 64, 64);
+  else
+    st = make_tmap(h, &tmX, p.a, p.in_dtype, p.K, p.M, 1, p.a_s0, 0, 64, sp.m_pad);
+  if (st != KAPYB_OK) return st;
+  static bool attr_set = false;
+  if (!attr_set) {
+    CUDA_TRY(h, cudaFuncSetAttribute(gemm_skinny_kernel,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, 232448));
+    attr_set = true;
+  }
+  gemm_skinny_kernel<<<grid, kSkinnyThreads, smem, stream>>>(tmW, tmX, sp);
+  CUDA_TRY(h, cudaGetLastError());
+  h->launches++;
+  h->last_kernel = "tcgen05_skinny";
+  return KAPYB_OK;
+}
+
+static kapyb_status launch_skinny(kapyb_handle h, const MatmulProblem &p, bool a_mn, bool b_mn,
+                                  cudaStream_t stream) {
+  if (!skinny_supported(p.M, p.N, p.K))
+    return fail(h, KAPYB_UNSUPPORTED, "matmul: shape outside the skinny kernel's range");
+  kapyb_status st = kapyb_reserve_workspace(h, skinny_workspace_bytes());
+  if (st != KAPYB_OK) return st;
+  uint32_t *counters = static_cast<uint32_t *>(h->workspace);
+  float *scratch = reinterpret_cast<float *>(static_cast<char *>(h->workspace) + kSkinnyCounterBytes);
+  return launch_skinny_on(h, p, a_mn, b_mn, scratch, counters, stream);
+}
+
+static kapyb_status run_matmul(kapyb_handle h, MatmulProblem p, void *const *peer_outs,
+                               int n_peers, cudaStream_t stream) {
+  if (p.M == 0 || p.N == 0 || p.batch == 0) return KAPYB_OK;  // empty result
+  CUDA_TRY(h, cudaSetDevice(h->device));
+  // Put the output's unit stride on axis 1 (compute the transposed problem otherwise).
+  if (p.c_s1 != 1 && p.c_s0 == 1 && n_peers == 0) transpose_problem(p);
+  const bool c_unit = p.c_s1 == 1 || p.N == 1;
+  const bool a_k = p.a_s1 == 1 || p.K == 1, a_m = p.a_s0 == 1 || p.M == 1;
+  const bool b_n = p.b_s1 == 1 || p.N == 1, b_k = p.b_s0 == 1 || p.K == 1;
+  const bool a_mn = !a_k && a_m;
+  const bool b_mn = b_n;  // prefer N-contiguous when both hold
+  bool tma = c_unit && (a_k || a_m) && (b_n || b_k) && p.K > 0;
+  if (tma) {
+    tma = tma_ok(p.a, p.in_dtype, a_mn ? p.M : p.K, a_mn ? p.K : p.M, a_mn ? p.a_s1 : p.a_s0,
+                 p.batch, p.a_bs) &&
+          tma_ok(p.b, p.in_dtype, b_mn ? p.N : p.K, b_mn ? p.K : p.N, b_mn ? p.b_s0 : p.b_s1,
+                 p.batch, p.b_bs) &&
+          tma_ok(p.c, p.out_dtype, p.N, p.M, p.c_s0, p.batch, p.c_bs);
+    for (int o = 0; tma && o < n_peers; ++o)
+      tma = tma_ok(peer_outs[o], p.out_dtype, p.N, p.M, p.c_s0, 1, 0);
+  }
+  int path = h->forced_path;
+  if (path == PATH_SIMT || !tma) {
+    if (n_peers > 0)
+      return fail(h, KAPYB_UNSUPPORTED, "matmul_push: operands must be TMA-describable "
+                                        "(16-byte aligned bases and leading dimensions)");
+    if (path != PATH_AUTO && path != PATH_SIMT && !tma)
+      return fail(h, KAPYB_UNSUPPORTED, "matmul: forced tcgen05 path but operands are not "
+                                        "TMA-describable");
+    if (p.K == 0) {
+      // empty contraction: the epilogue of a zero accumulator
+    }
+    return launch_simt(h, p, stream);
+  }
+  void *own[1] = {p.c};
+  void *const *outs = n_peers > 0 ? peer_outs : own;
+  const int n_out = n_peers > 0 ? n_peers : 1;
+
+  if (path == PATH_AUTO) {
+    if (p.M <= kSkinnyMaxM && n_peers == 0 && p.batch == 1 && skinny_supported(p.M, p.N, p.K))
+      path = PATH_SKINNY;
+    else
+      path = PATH_1CTA;
+  }
+  if (path == PATH_SKINNY) {
+    if (n_peers > 0 || p.batch != 1 || p.M > kSkinnyMaxM)
+      return fail(h, KAPYB_UNSUPPORTED, "matmul: skinny path needs M <= %d, batch 1", kSkinnyMaxM);
+    return launch_skinny(h, p, a_mn, b_mn, stream);
+  }
+  // Tile width: the widest tile that still yields about a wave of work.
+  int bn = h->forced_bn;
+  if (bn == 0) {
+    const long long tm = (p.M + 127) / 128;
+    auto tiles = [&](int w) { return tm * ((p.N + w - 1) / w) * p.batch; };
+    if (tiles(256) >= h->sm_count || p.N > 128 * 16)
+      bn = 256;
+    else if (tiles(128) >= h->sm_count / 2 || p.N > 64 * 16)
+      bn = 128;
+    else
+      bn = 64;
+    if (p.N <= 64) bn = 64;
+    else if (p.N <= 128 && bn > 128) bn = 128;
+  }
+  if (path == PATH_2CTA) {
+    if (bn == 64) bn = 128;
+    if (bn == 128) return launch_tcgen05<128, 2>(h, p, a_mn, b_mn, outs, n_out, stream);
+    return launch_tcgen05<256, 2>(h, p, a_mn, b_mn, outs, n_out, stream);
+  }
+  if (bn == 64) return launch_tcgen05<64, 1>(h, p, a_mn, b_mn, outs, n_out, stream);
+  if (bn == 128) return launch_tcgen05<128, 1>(h, p, a_mn, b_mn, outs, n_out, stream);
+  return launch_tcgen05<256, 1>(h, p, a_mn, b_mn, outs, n_out, stream);
+}
+
+static MatmulProblem make_problem(const kapyb_tensor2d *lhs, const kapyb_tensor2d *rhs,
+                                  const kapyb_tensor2d *acc, const kapyb_tensor2d *out,
+                                  const kapyb_epilogue *ep) {
+  MatmulProblem p;
+  p.a = elem_ptr(lhs);
+  p.b = elem_ptr(rhs);
+  p.c = const_cast<void *>(elem_ptr(out));
+  p.M = lhs->size0;
+  p.K = lhs->size1;
+  p.N = rhs->size1;
+  p.batch = 1;
+  p.a_s0 = lhs->stride0;
+  p.a_s1 = lhs->stride1;
+  p.b_s0 = rhs->stride0;
+  p.b_s1 = rhs->stride1;
+  p.c_s0 = out->stride0;
+  p.c_s1 = out->stride1;
+  p.a_bs = p.b_bs = p.c_bs = 0;
+  p.in_dtype = lhs->dtype;
+  p.out_dtype = out->dtype;
+  p.ep = make_ep(ep, acc);
+  return p;
+}
+
+extern "C" KAPYB_API kapyb_status kapyb_matmul(kapyb_handle h, const kapyb_tensor2d *lhs,
+                                               const kapyb_tensor2d *rhs,
+                                               const kapyb_tensor2d *acc,
+                                               const kapyb_tensor2d *out,
+                                               const kapyb_epilogue *epilogue, int32_t impl_way,
+                                               void *stream) {
+  if (!h) return fail(h, KAPYB_INVALID_ARG, "kapyb_matmul: NULL handle");
+  kapyb_status st = verify_matmul(h, lhs, rhs, acc, out, epilogue, impl_way);
+  if (st != KAPYB_OK) return st;
+  return run_matmul(h, make_problem(lhs, rhs, acc, out, epilogue), nullptr, 0,
+                    static_cast<cudaStream_t>(stream));
+}
+
+extern "C" KAPYB_API kapyb_status kapyb_matmul_batched(
+    kapyb_handle h, const kapyb_tensor2d *lhs, const kapyb_tensor2d *rhs,
+    const kapyb_tensor2d *out, int32_t batch, int64_t batch_stride_lhs, int64_t batch_stride_rhs,
+    int64_t batch_stride_out, const kapyb_epilogue *epilogue, int32_t impl_way, void *stream) {
+  if (!h) return fail(h, KAPYB_INVALID_ARG, "kapyb_matmul_batched: NULL handle");
+  kapyb_status st = verify_matmul(h, lhs, rhs, nullptr, out, epilogue, impl_way);
+  if (st != KAPYB_OK) return st;
+  if (batch < 0 || batch > 65535) return fail(h, KAPYB_INVALID_ARG, "matmul_batched: batch must be in [0, 65535]");
+  if (batch > 1 && (batch_stride_lhs < 0 || batch_stride_rhs < 0 || batch_stride_out <= 0))
+    return fail(h, KAPYB_INVALID_ARG, "matmul_batched: bad batch stride");
+  MatmulProblem p = make_problem(lhs, rhs, nullptr, out, epilogue);
+  p.batch = batch;
+  p.a_bs = batch_stride_lhs;
+  p.b_bs = batch_stride_rhs;
+  p.c_bs = batch_stride_out;
+  return run_matmul(h, p, nullptr, 0, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" KAPYB_API kapyb_status kapyb_matmul_push(
+    kapyb_handle h, const kapyb_tensor2d *lhs, const kapyb_tensor2d *rhs, void *const *peer_out,
+    int32_t n_peers, int32_t out_dtype, int32_t out_stride0, int32_t col_begin, int32_t n_total,
+    const kapyb_epilogue *epilogue, int32_t impl_way, void *stream) {
+  if (!h) return fail(h, KAPYB_INVALID_ARG, "kapyb_matmul_push: NULL handle");
+  if (!peer_out || n_peers < 1 || n_peers > kMaxOutputs)
+    return fail(h, KAPYB_INVALID_ARG, "matmul_push: n_peers must be in [1, %d]", kMaxOutputs);
+  if (!lhs || !rhs) return fail(h, KAPYB_INVALID_ARG, "matmul_push: NULL tensor descriptor");
+  if (col_begin < 0 || col_begin + rhs->size1 > n_total || out_stride0 < n_total)
+    return fail(h, KAPYB_INVALID_ARG, "matmul_push: column block [%d, %d) outside [0, %d)",
+                col_begin, col_begin + rhs->size1, n_total);
+  kapyb_tensor2d out;
+  out.ptr = peer_out[0];
+  out.offset_elems = col_begin;
+  out.size0 = lhs->size0;
+  out.size1 = rhs->size1;
+  out.stride0 = out_stride0;
+  out.stride1 = 1;
+  out.dtype = out_dtype;
+  out.padding = 0;
+  kapyb_status st = verify_matmul(h, lhs, rhs, nullptr, &out, epilogue, impl_way);
+  if (st != KAPYB_OK) return st;
+  void *outs[kMaxOutputs];
+  for (int r = 0; r < n_peers; ++r) {
+    if (!peer_out[r]) return fail(h, KAPYB_INVALID_ARG, "matmul_push: peer_out[%d] is NULL", r);
+    outs[r] = static_cast<char *>(peer_out[r]) + static_cast<int64_t>(col_begin) * dtype_size(out_dtype);
+  }
+  MatmulProblem p = make_problem(lhs, rhs, nullptr, &out, epilogue);
+  return run_matmul(h, p, outs, n_peers, static_cast<cudaStream_t>(stream));
+}
+
+// Number of bytes spanned by a host tensor starting at its element (0,0).
+static size_t span_bytes(const kapyb_tensor2d *t) {
+  if (t->size0 <= 0 || t->size1 <= 0) return 0;
+  const int64_t last = static_cast<int64_t>(t->size0 - 1) * t->stride0 +
+                       static_cast<int64_t>(t->size1 - 1) * t->stride1;
+  return static_cast<size_t>(last + 1) * dtype_size(t->dtype);
+}
+
+static size_t round256(size_t x) { return (x + 255) & ~static_cast<size_t>(255); }
+
+extern "C" KAPYB_API kapyb_status kapyb_matmul_host(kapyb_handle h, const kapyb_tensor2d *lhs,
+                                                    const kapyb_tensor2d *rhs,
+                                                    const kapyb_tensor2d *out,
+                                                    const kapyb_epilogue *epilogue,
+                                                    int32_t impl_way, void *stream_) {
+  if (!h) return fail(h, KAPYB_INVALID_ARG, "kapyb_matmul_host: NULL handle");
+  kapyb_status st = verify_matmul(h, lhs, rhs, nullptr, out, epilogue, impl_way);
+  if (st != KAPYB_OK) return st;
+  if (lhs->stride0 < 0 || lhs->stride1 < 0 || rhs->stride0 < 0 || rhs->stride1 < 0 ||
+      out->stride0 < 0 || out->stride1 < 0)
+    return fail(h, KAPYB_UNSUPPORTED, "matmul_host: negative strides are not supported");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const size_t na = span_bytes(lhs), nb = span_bytes(rhs), nc = span_bytes(out);
+  size_t nbias = 0;
+  if (epilogue && epilogue->bias)
+    nbias = static_cast<size_t>(epilogue->bias_axis == 1 ? rhs->size1 : lhs->size0) *
+            dtype_size(epilogue->bias_dtype);
+  const size_t skinny_ws = skinny_workspace_bytes();
+  const size_t need = skinny_ws + round256(na) + round256(nb) + round256(nc) + round256(nbias);
+  st = kapyb_reserve_workspace(h, need);
+  if (st != KAPYB_OK) return st;
+  CUDA_TRY(h, cudaSetDevice(h->device));
+  char *w = static_cast<char *>(h->workspace) + skinny_ws;
+  char *da = w, *db = da + round256(na), *dc = db + round256(nb), *dbias = dc + round256(nc);
+  CUDA_TRY(h, cudaMemcpyAsync(da, elem_ptr(lhs), na, cudaMemcpyHostToDevice, stream));
+  CUDA_TRY(h, cudaMemcpyAsync(db, elem_ptr(rhs), nb, cudaMemcpyHostToDevice, stream));
+  kapyb_epilogue ep;
+  if (epilogue)
+    ep = *epilogue;
+  else {
+    ep.alpha = 1.0f;
+    ep.bias = nullptr;
+    ep.bias_dtype = KAPYB_F32;
+    ep.bias_axis = 1;
+    ep.activation = KAPYB_ACT_NONE;
+    ep.rounding = KAPYB_RN;
+  }
+  if (nbias) {
+    CUDA_TRY(h, cudaMemcpyAsync(dbias, ep.bias, nbias, cudaMemcpyHostToDevice, stream));
+    ep.bias = dbias;
+  }
+  kapyb_tensor2d dl = *lhs, dr = *rhs, dout = *out;
+  dl.ptr = da;
+  dl.offset_elems = 0;
+  dr.ptr = db;
+  dr.offset_elems = 0;
+  dout.ptr = dc;
+  dout.offset_elems = 0;
+  st = run_matmul(h, make_problem(&dl, &dr, nullptr, &dout, &ep), nullptr, 0, stream);
+  if (st != KAPYB_OK) return st;
+  // Only the elements the kernel wrote are defined; the caller's buffer keeps
+  // its gaps when `out` is a strided view, so copy row by row in that case.
+  const bool dense = (out->stride1 == 1 && out->stride0 == out->size1) ||
+                     (out->stride0 == 1 && out->stride1 == out->size0);
+  void *hc = const_cast<void *>(elem_ptr(out));
+  if (dense) {
+    CUDA_TRY(h, cudaMemcpyAsync(hc, dc, nc, cudaMemcpyDeviceToHost, stream));
+  } else if (out->stride1 == 1) {
+    const size_t esz = dtype_size(out->dtype);
+    CUDA_TRY(h, cudaMemcpy2DAsync(hc, out->stride0 * esz, dc, out->stride0 * esz,
+                                  out->size1 * esz, out->size0, cudaMemcpyDeviceToHost, stream));
+  } else if (out->stride0 == 1) {
+    const size_t esz = dtype_size(out->dtype);
+    CUDA_TRY(h, cudaMemcpy2DAsync(hc, out->stride1 * esz, dc, out->stride1 * esz,
+                                  out->size0 * esz, out->size1, cudaMemcpyDeviceToHost, stream));
+  } else {
+    return fail(h, KAPYB_UNSUPPORTED, "matmul_host: out needs one unit stride");
+  }
+  return kapyb_check(h, stream);
+}
+
+// ------------------------------------------------------------- elementwise
+
+static kapyb_status verify_program(kapyb_handle h, const kapyb_inst *prog, int n_inst,
+                                   const kapyb_tensor2d *inputs, int n_inputs,
+                                   const kapyb_tensor2d *out) {
+  if (!prog || n_inst <= 0 || n_inst > KAPYB_MAX_INSTS)
+    return fail(h, KAPYB_INVALID_ARG, "elementwise: program must have 1..%d ops", KAPYB_MAX_INSTS);
+  if (n_inputs < 0 || n_inputs > KAPYB_MAX_INPUTS || (n_inputs > 0 && !inputs))
+    return fail(h, KAPYB_INVALID_ARG, "elementwise: at most %d inputs", KAPYB_MAX_INPUTS);
+  if (!out || !out->ptr || !valid_dtype(out->dtype) || out->size0 < 0 || out->size1 < 0)
+    return fail(h, KAPYB_INVALID_ARG, "elementwise: bad output descriptor");
+  for (int k = 0; k < n_inputs; ++k) {
+    const kapyb_tensor2d &t = inputs[k];
+    if (!t.ptr || !valid_dtype(t.dtype) || t.size0 < 0 || t.size1 < 0)
+      return fail(h, KAPYB_INVALID_ARG, "elementwise: bad input descriptor %d", k);
+    if (t.padding < KAPYB_PAD_ZERO || t.padding > KAPYB_PAD_NINF)
+      return fail(h, KAPYB_INVALID_ARG, "elementwise: bad padding option on input %d", k);
+  }
+  int reg_dtype[KAPYB_MAX_REGS];
+  for (int r = 0; r < KAPYB_MAX_REGS; ++r) reg_dtype[r] = -1;
+  int stores = 0;
+  for (int pc = 0; pc < n_inst; ++pc) {
+    const kapyb_inst &in = prog[pc];
+    if (in.op < 0 || in.op >= KAPYB_OP_COUNT_)
+      return fail(h, KAPYB_INVALID_ARG, "elementwise: op %d at %d is unknown", in.op, pc);
+    int nsrc = 0;
+    switch (in.op) {
+    case KAPYB_OP_LOAD:
+    case KAPYB_OP_CONST: nsrc = 0; break;
+    case KAPYB_OP_FMA:
+    case KAPYB_OP_CLAMP: nsrc = 3; break;
+    case KAPYB_OP_ADD:
+    case KAPYB_OP_SUB:
+    case KAPYB_OP_MUL:
+    case KAPYB_OP_DIV:
+    case KAPYB_OP_MAXIMUM:
+    case KAPYB_OP_MINIMUM:
+    case KAPYB_OP_MAXNUM:
+    case KAPYB_OP_MINNUM: nsrc = 2; break;
+    default: nsrc = 1; break;
+    }
+    const int srcs[3] = {in.a, in.b, in.c};
+    for (int s = 0; s < nsrc; ++s) {
+      if (srcs[s] < 0 || srcs[s] >= KAPYB_MAX_REGS || reg_dtype[srcs[s]] < 0)
+        return fail(h, KAPYB_INVALID_ARG, "elementwise: op %d reads an undefined value", pc);
+    }
+    if (in.op == KAPYB_OP_STORE) {
+      if (reg_dtype[in.a] != out->dtype)
+        return fail(h, KAPYB_INVALID_ARG,
+                    "elementwise: st_global source is %s but the target tensor is %s",
+                    dtype_name(reg_dtype[in.a]), dtype_name(out->dtype));
+      ++stores;
+      continue;
+    }
+    if (!valid_dtype(in.dtype)) return fail(h, KAPYB_INVALID_ARG, "elementwise: op %d has a bad element type", pc);
+    if (in.dst < 0 || in.dst >= KAPYB_MAX_REGS)
+      return fail(h, KAPYB_INVALID_ARG, "elementwise: op %d writes register %d", pc, in.dst);
+    if (in.op == KAPYB_OP_LOAD) {
+      if (in.flags < 0 || in.flags >= n_inputs)
+        return fail(h, KAPYB_INVALID_ARG, "elementwise: ld_global of input %d, but %d given", in.flags, n_inputs);
+      if (inputs[in.flags].dtype != in.dtype)
+        return fail(h, KAPYB_INVALID_ARG, "elementwise: ld_global result type differs from its source");
+    } else if (in.op == KAPYB_OP_CVT) {
+      // FPToFPOp::verify (Kapy.cpp:272-287): a downcast must name a rounding mode.
+      if (dtype_size(in.dtype) < dtype_size(reg_dtype[in.a]) && in.flags != KAPYB_RZ && in.flags != KAPYB_RN)
+        return fail(h, KAPYB_INVALID_ARG, "elementwise: rounding mode must be set for down cast");
+    } else {
+      for (int s = 0; s < nsrc; ++s)
+        if (reg_dtype[srcs[s]] != in.dtype)
+          return fail(h, KAPYB_INVALID_ARG,
+                      "elementwise: op %d requires the same element type for all operands and results", pc);
+    }
+    reg_dtype[in.dst] = in.dtype;
+  }
+  if (stores != 1) return fail(h, KAPYB_INVALID_ARG, "elementwise: a program stores exactly once (%d found)", stores);
+  return KAPYB_OK;
+}
+
+// Expression-tree view of a program, used to recognise the canonical graphs.
+struct ExprNode {
+  int op, dtype, a, b, c, flags;
+  float imm;
+};
+
+static int build_nodes(const kapyb_inst *prog, int n, ExprNode *nodes, int *store_src) {
+  int reg_node[KAPYB_MAX_REGS];
+  for (int r = 0; r < KAPYB_MAX_REGS; ++r) reg_node[r] = -1;
+  int cnt = 0;
+  *store_src = -1;
+  for (int pc = 0; pc < n; ++pc) {
+    const kapyb_inst &in = prog[pc];
+    if (in.op == KAPYB_OP_STORE) {
+      *store_src = reg_node[in.a];
+      continue;
+    }
+    ExprNode nd;
+    nd.op = in.op;
+    nd.dtype = in.dtype;
+    nd.a = in.a >= 0 ? reg_node[in.a] : -1;
+    nd.b = in.b >= 0 ? reg_node[in.b] : -1;
+    nd.c = in.c >= 0 ? reg_node[in.c] : -1;
+    nd.flags = in.flags;
+    nd.imm = in.imm;
+    nodes[cnt] = nd;
+    reg_node[in.dst] = cnt++;
+  }
+  return cnt;
+}
+
+struct Matcher {
+  const ExprNode *n;
+  bool is(int i, int op, int dt) const { return i >= 0 && n[i].op == op && n[i].dtype == dt; }
+  bool cst(int i, float *v) const {
+    if (!is(i, KAPYB_OP_CONST, KAPYB_F32)) return false;
+    *v = n[i].imm;
+    return true;
+  }
+  // mul(f32) with one constant operand; returns the other operand
+  bool mul_const(int i, float *cv, int *other) const {
+    if (!is(i, KAPYB_OP_MUL, KAPYB_F32)) return false;
+    if (cst(n[i].a, cv)) {
+      *other = n[i].b;
+      return true;
+    }
+    if (cst(n[i].b, cv)) {
+      *other = n[i].a;
+      return true;
+    }
+    return false;
+  }
+  // u = fma(ext(load), s, b)
+  bool affine(int i, float *s, float *b, int *load) const {
+    if (!is(i, KAPYB_OP_FMA, KAPYB_F32)) return false;
+    const int x = n[i].a;
+    if (!is(x, KAPYB_OP_CVT, KAPYB_F32)) return false;
+    const int ld = n[x].a;
+    if (ld < 0 || n[ld].op != KAPYB_OP_LOAD || n[ld].dtype == KAPYB_F32) return false;
+    if (!cst(n[i].b, s) || !cst(n[i].c, b)) return false;
+    *load = ld;
+    return true;
+  }
+};
+
+// Recognises  cvt16( fma(ext(x), s, b) )  and the gelu_tanh graph around it.
+static bool match_affine_gelu(const ExprNode *nodes, int root, AffineGelu *f, int *load_input,
+                              int *in_dtype, int *rounding) {
+  Matcher m{nodes};
+  if (root < 0 || nodes[root].op != KAPYB_OP_CVT || nodes[root].dtype == KAPYB_F32) return false;
+  *rounding = nodes[root].flags;
+  const int y = nodes[root].a;
+  int ld = -1;
+  if (m.affine(y, &f->s, &f->b, &ld)) {
+    f->gelu = 0;
+    f->c0 = f->c1 = f->m2 = f->one = 0.0f;
+  } else {
+    // y = u / (one + exp(m2 * k)), k = c0 * fma((c1*u)*u, u, u)
+    if (!m.is(y, KAPYB_OP_DIV, KAPYB_F32)) return false;
+    const int u = nodes[y].a, den = nodes[y].b;
+    if (!m.affine(u, &f->s, &f->b, &ld)) return false;
+    if (!m.is(den, KAPYB_OP_ADD, KAPYB_F32)) return false;
+    int e = -1;
+    if (m.cst(nodes[den].a, &f->one))
+      e = nodes[den].b;
+    else if (m.cst(nodes[den].b, &f->one))
+      e = nodes[den].a;
+    else
+      return false;
+    if (!m.is(e, KAPYB_OP_EXP, KAPYB_F32)) return false;
+    int k = -1;
+    if (!m.mul_const(nodes[e].a, &f->m2, &k)) return false;
+    int inner = -1;
+    if (!m.mul_const(k, &f->c0, &inner)) return false;
+    if (!m.is(inner, KAPYB_OP_FMA, KAPYB_F32)) return false;
+    if (nodes[inner].b != u || nodes[inner].c != u) return false;
+    const int t2 = nodes[inner].a;  // (c1*u)*u
+    if (!m.is(t2, KAPYB_OP_MUL, KAPYB_F32)) return false;
+    int t1 = -1;
+    if (nodes[t2].b == u)
+      t1 = nodes[t2].a;
+    else if (nodes[t2].a == u)
+      t1 = nodes[t2].b;
+    else
+      return false;
+    int uu = -1;
+    if (!m.mul_const(t1, &f->c1, &uu) || uu != u) return false;
+    f->gelu = 1;
+  }
+  *load_input = nodes[ld].flags;
+  *in_dtype = nodes[ld].dtype;
+  return true;
+}
+
+static bool contiguous_same(const kapyb_tensor2d &t, const kapyb_tensor2d &out) {
+  if (t.size0 != out.size0 || t.size1 != out.size1) return false;
+  const bool rm = (t.stride1 == 1 || t.size1 == 1) && (t.stride0 == t.size1 || t.size0 == 1);
+  const bool orm = (out.stride1 == 1 || out.size1 == 1) && (out.stride0 == out.size1 || out.size0 == 1);
+  return rm && orm;
+}
+
+static int stream_grid(kapyb_handle h, long long n_vec, int per_thread) {
+  long long blocks = (n_vec + 256ll * per_thread - 1) / (256ll * per_thread);
+  const long long cap = static_cast<long long>(h->sm_count) * 16;
+  return static_cast<int>(std::max(1ll, std::min(blocks, cap)));
+}
+
+extern "C" KAPYB_API kapyb_status kapyb_elementwise(kapyb_handle h, const kapyb_inst *prog,
+                                                    int32_t n_inst, const kapyb_tensor2d *inputs,
+                                                    int32_t n_inputs, const kapyb_tensor2d *out,
+                                                    void *stream_) {
+  if (!h) return fail(h, KAPYB_INVALID_ARG, "kapyb_elementwise: NULL handle");
+  kapyb_status st = verify_program(h, prog, n_inst, inputs, n_inputs, out);
+  if (st != KAPYB_OK) return st;
+  const long long total = static_cast<long long>(out->size0) * out->size1;
+  if (total == 0) return KAPYB_OK;
+  CUDA_TRY(h, cudaSetDevice(h->device));
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+
+  ExprNode nodes[KAPYB_MAX_INSTS];
+  int root = -1;
+  build_nodes(prog, n_inst, nodes, &root);
+
+  // Fused path 1: 16-bit -> 16-bit affine (+ gelu_tanh), contiguous.
+  {
+    AffineGelu f;
+    int li = -1, din = 0, rn = 1;
+    if (match_affine_gelu(nodes, root, &f, &li, &din, &rn) && out->dtype != KAPYB_F32 &&
+        nodes[root].dtype == out->dtype && contiguous_same(inputs[li], *out) &&
+        aligned16(elem_ptr(&inputs[li])) && aligned16(elem_ptr(out))) {
+      const long long n_vec = total / 8;
+      const int grid = stream_grid(h, n_vec, kEltUnroll);
+      elt_unary16_kernel<AffineGelu><<<grid, 256, 0, stream>>>(
+          static_cast<const uint4 *>(elem_ptr(&inputs[li])),
+          static_cast<uint4 *>(const_cast<void *>(elem_ptr(out))), n_vec, total, f, din,
+          out->dtype, rn);
+      CUDA_TRY(h, cudaGetLastError());
+      h->launches++;
+      h->last_kernel = f.gelu ? "elt_affine_gelu" : "elt_affine";
+      return KAPYB_OK;
+    }
+  }
+  // Fused path 2: z = a (add|sub|mul) b, one element type, contiguous.
+  if (root >= 0 && n_inputs >= 2) {
+    const ExprNode &r = nodes[root];
+    if ((r.op == KAPYB_OP_ADD || r.op == KAPYB_OP_SUB || r.op == KAPYB_OP_MUL) && r.a >= 0 &&
+        r.b >= 0 && nodes[r.a].op == KAPYB_OP_LOAD && nodes[r.b].op == KAPYB_OP_LOAD &&
+        r.dtype == out->dtype) {
+      const kapyb_tensor2d &ta = inputs[nodes[r.a].flags], &tb = inputs[nodes[r.b].flags];
+      if (ta.dtype == r.dtype && tb.dtype == r.dtype && contiguous_same(ta, *out) &&
+          contiguous_same(tb, *out) && aligned16(elem_ptr(&ta)) && aligned16(elem_ptr(&tb)) &&
+          aligned16(elem_ptr(out))) {
+        const int per = r.dtype == KAPYB_F32 ? 4 : 8;
+        const long long n_vec = total / per;
+        const int grid = stream_grid(h, n_vec, 2);
+        const uint4 *pa = static_cast<const uint4 *>(elem_ptr(&ta));
+        const uint4 *pb = static_cast<const uint4 *>(elem_ptr(&tb));
+        uint4 *pz = static_cast<uint4 *>(const_cast<void *>(elem_ptr(out)));
+        if (r.op == KAPYB_OP_ADD)
+          elt_binary_kernel<KAPYB_OP_ADD><<<grid, 256, 0, stream>>>(pa, pb, pz, n_vec, total, r.dtype);
+        else if (r.op == KAPYB_OP_SUB)
+          elt_binary_kernel<KAPYB_OP_SUB><<<grid, 256, 0, stream>>>(pa, pb, pz, n_vec, total, r.dtype);
+        else
+          elt_binary_kernel<KAPYB_OP_MUL><<<grid, 256, 0, stream>>>(pa, pb, pz, n_vec, total, r.dtype);
+        CUDA_TRY(h, cudaGetLastError());
+        h->launches++;
+        h->last_kernel = "elt_binary";
+        return KAPYB_OK;
+      }
+    }
+  }
+  // Generic interpreter.
+  EltProgram P;
+  memset(&P, 0, sizeof(P));
+  memcpy(P.inst, prog, sizeof(kapyb_inst) * n_inst);
+  P.n_inst = n_inst;
+  P.n_in = n_inputs;
+  for (int k = 0; k < n_inputs; ++k) {
+    P.in[k].ptr = elem_ptr(&inputs[k]);
+    P.in[k].s0 = inputs[k].stride0;
+    P.in[k].s1 = inputs[k].stride1;
+    P.in[k].size0 = inputs[k].size0;
+    P.in[k].size1 = inputs[k].size1;
+    P.in[k].dtype = inputs[k].dtype;
+    P.in[k].padding = inputs[k].padding;
+  }
+  P.out.ptr = elem_ptr(out);
+  P.out.s0 = out->stride0;
+  P.out.s1 = out->stride1;
+  P.out.size0 = out->size0;
+  P.out.size1 = out->size1;
+  P.out.dtype = out->dtype;
+  P.out.padding = 0;
+  const int grid = static_cast<int>(std::max(1ll, std::min((total + 255) / 256,
+                                                            static_cast<long long>(h->sm_count) * 32)));
+  elt_interp_kernel<<<grid, 256, 0, stream>>>(P);
+  CUDA_TRY(h, cudaGetLastError());
+  h->launches++;
+  h->last_kernel = "elt_interp";
+  return KAPYB_OK;
+}
+
+// ------------------------------------------------------------------ reduce
+
+template <int COMB>
+static void launch_reduce(const ReduceParams &p, bool unit_inner, bool vec, int sm_count,
+                          cudaStream_t stream) {
+  if (unit_inner) {
+    const long long blocks = (static_cast<long long>(p.rows) + 7) / 8;
+    const int grid = static_cast<int>(std::max(1ll, std::min(blocks, static_cast<long long>(sm_count) * 8)));
+    if (vec)
+      reduce_rows_kernel<COMB, true><<<grid, 256, 0, stream>>>(p);
+    else
+      reduce_rows_kernel<COMB, false><<<grid, 256, 0, stream>>>(p);
+  } else {
+    const long long blocks = (static_cast<long long>(p.rows) + 31) / 32;
+    const int grid = static_cast<int>(std::max(1ll, std::min(blocks, static_cast<long long>(sm_count) * 8)));
+    reduce_cols_kernel<COMB><<<grid, 256, 0, stream>>>(p);
+  }
+}
+
+extern "C" KAPYB_API kapyb_status kapyb_reduce(kapyb_handle h, const kapyb_tensor2d *src,
+                                               const kapyb_tensor2d *dst, int32_t axis,
+                                               int32_t combiner, void *stream_) {
+  if (!h) return fail(h, KAPYB_INVALID_ARG, "kapyb_reduce: NULL handle");
+  if (!src || !dst || !src->ptr || !dst->ptr) return fail(h, KAPYB_INVALID_ARG, "reduce: NULL tensor");
+  if (!valid_dtype(src->dtype) || !valid_dtype(dst->dtype)) return fail(h, KAPYB_INVALID_ARG, "reduce: unknown element type");
+  if (axis != 0 && axis != 1) return fail(h, KAPYB_INVALID_ARG, "reduce: axis must be 0 or 1");
+  if (combiner < KAPYB_RED_ADD || combiner > KAPYB_RED_MIN) return fail(h, KAPYB_INVALID_ARG, "reduce: unknown combiner %d", combiner);
+  if (dst->dtype != KAPYB_F32 && dst->dtype != src->dtype)
+    return fail(h, KAPYB_INVALID_ARG, "reduce: result element type must be f32 or the source's");
+  // ReduceOp::inferReturnTypes (Kapy.cpp:613-626): the reduced axis becomes 1.
+  const int want0 = axis == 0 ? 1 : src->size0, want1 = axis == 1 ? 1 : src->size1;
+  if (dst->size0 != want0 || dst->size1 != want1)
+    return fail(h, KAPYB_INVALID_ARG, "reduce: result shape must be [%d, %d]", want0, want1);
+  if (src->size0 < 0 || src->size1 < 0) return fail(h, KAPYB_INVALID_ARG, "reduce: negative size");
+  const int results = axis == 1 ? src->size0 : src->size1;
+  const int length = axis == 1 ? src->size1 : src->size0;
+  if (results == 0) return KAPYB_OK;
+  if (length == 0) return fail(h, KAPYB_INVALID_ARG, "reduce: cannot reduce an empty axis");
+  CUDA_TRY(h, cudaSetDevice(h->device));
+  ReduceParams p;
+  p.src = elem_ptr(src);
+  p.dst = const_cast<void *>(elem_ptr(dst));
+  p.rows = results;
+  p.cols = length;
+  p.src_row_stride = axis == 1 ? src->stride0 : src->stride1;
+  p.src_col_stride = axis == 1 ? src->stride1 : src->stride0;
+  p.dst_stride = axis == 1 ? dst->stride0 : dst->stride1;
+  p.src_dtype = src->dtype;
+  p.dst_dtype = dst->dtype;
+  p.combiner = combiner;
+  const bool unit_inner = p.src_col_stride == 1 || length == 1;
+  const int esz = dtype_size(src->dtype);
+  const bool vec = unit_inner && aligned16(p.src) && (p.src_row_stride * esz) % 16 == 0;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  switch (combiner) {
+  case KAPYB_RED_ADD: launch_reduce<KAPYB_RED_ADD>(p, unit_inner, vec, h->sm_count, stream); break;
+  case KAPYB_RED_MUL: launch_reduce<KAPYB_RED_MUL>(p, unit_inner, vec, h->sm_count, stream); break;
+  case KAPYB_RED_MAX: launch_reduce<KAPYB_RED_MAX>(p, unit_inner, vec, h->sm_count, stream); break;
+  default: launch_reduce<KAPYB_RED_MIN>(p, unit_inner, vec, h->sm_count, stream); break;
+  }
+  CUDA_TRY(h, cudaGetLastError());
+  h->launches++;
+  h->last_kernel = unit_inner ? "reduce_rows" : "reduce_cols";
+  return KAPYB_OK;
+}

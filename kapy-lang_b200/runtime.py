@@ -1,0 +1,242 @@
+"""Host-side runtime: a `Handle` per GPU that turns torch tensors (device memory
+and streams are torch's job) into the descriptors of ``include/kapyb.h`` and
+calls the C ABI.  Errors come back as the exception classes the reference's
+bindings raise: ``ValueError`` for verifier-style rejections (the reference
+raises ``std::invalid_argument`` / fails ``verify()``), ``RuntimeError`` for
+everything else (``std::runtime_error("pass manager run failed")``,
+python/src/passes.cc:72-75).
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional, Sequence
+
+from . import _abi as abi
+
+
+class KapybError(RuntimeError):
+    def __init__(self, status: int, message: str):
+        super().__init__(f"kapyb status {status}: {message}")
+        self.status = status
+
+
+class KapybTimeout(KapybError):
+    pass
+
+
+def _torch():
+    import torch
+    return torch
+
+
+def dtype_code(dt) -> int:
+    torch = _torch()
+    if dt == torch.float16:
+        return abi.F16
+    if dt == torch.bfloat16:
+        return abi.BF16
+    if dt == torch.float32:
+        return abi.F32
+    raise ValueError(f"unsupported element type {dt}")
+
+
+def torch_dtype(code: int):
+    torch = _torch()
+    return {abi.F16: torch.float16, abi.BF16: torch.bfloat16, abi.F32: torch.float32}[code]
+
+
+def tensor2d(t, padding: int = abi.PAD_ZERO) -> abi.Tensor2d:
+    """kapy.mk_global over a 2-D torch tensor (any strides that fit i32)."""
+    if t.dim() != 2:
+        raise ValueError("kapy tensors are rank 2")
+    s0, s1 = t.stride()
+    for v in (t.shape[0], t.shape[1], s0, s1):
+        if v >= 2 ** 31:
+            raise ValueError("sizes and strides must fit i32")
+    return abi.Tensor2d(t.data_ptr(), 0, t.shape[0], t.shape[1], s0, s1, dtype_code(t.dtype),
+                        padding)
+
+
+class Handle:
+    """One per (thread, GPU).  Owns the library context; tensors stay the caller's."""
+
+    def __init__(self, device: int = 0):
+        self._lib = abi.load()
+        self._h = C.c_void_p()
+        st = self._lib.kapyb_create(C.byref(self._h), int(device))
+        if st != abi.OK:
+            msg = self._lib.kapyb_last_error_string(None).decode()
+            raise KapybError(st, msg)
+        self.device = int(device)
+
+    def close(self):
+        if getattr(self, "_h", None) is not None and self._h:
+            self._lib.kapyb_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # ------------------------------------------------------------ utilities
+    def _raise(self, st: int):
+        msg = self._lib.kapyb_last_error_string(self._h).decode()
+        if st == abi.INVALID_ARG:
+            raise ValueError(msg)
+        if st == abi.TIMEOUT:
+            raise KapybTimeout(st, msg)
+        raise KapybError(st, msg)
+
+    def _stream(self, stream=None) -> C.c_void_p:
+        if stream is None:
+            stream = _torch().cuda.current_stream(self.device)
+        return C.c_void_p(getattr(stream, "cuda_stream", stream))
+
+    def check(self, stream=None):
+        """Synchronises the stream and raises if a kernel reported a timeout."""
+        st = self._lib.kapyb_check(self._h, self._stream(stream))
+        if st != abi.OK:
+            self._raise(st)
+
+    def reserve_workspace(self, nbytes: int):
+        st = self._lib.kapyb_reserve_workspace(self._h, int(nbytes))
+        if st != abi.OK:
+            self._raise(st)
+
+    @property
+    def last_kernel(self) -> str:
+        return self._lib.kapyb_last_kernel(self._h).decode()
+
+    @property
+    def launch_count(self) -> int:
+        return int(self._lib.kapyb_launch_count(self._h))
+
+    def set_matmul_path(self, name: str):
+        st = self._lib.kapyb_set_matmul_path(self._h, name.encode())
+        if st != abi.OK:
+            self._raise(st)
+
+    def _epilogue(self, alpha, bias, bias_axis, activation, rounding):
+        ep = abi.Epilogue(float(alpha), None, abi.F32, int(bias_axis), int(activation),
+                          int(rounding))
+        if bias is not None:
+            if not bias.is_contiguous():
+                raise ValueError("bias must be contiguous")
+            ep.bias = bias.data_ptr()
+            ep.bias_dtype = dtype_code(bias.dtype)
+        return ep
+
+    # --------------------------------------------------------------- matmul
+    def matmul(self, lhs, rhs, out=None, *, acc=None, alpha: float = 1.0, bias=None,
+               bias_axis: int = 1, activation: int = abi.ACT_NONE, rounding: int = abi.RN,
+               out_dtype=None, impl_way: int = abi.MMA_ANY, stream=None):
+        """kapy.matmul at whole-problem scope; 3-D operands run as a batch."""
+        torch = _torch()
+        if lhs.dim() == 3:
+            return self._matmul_batched(lhs, rhs, out, alpha=alpha, bias=bias, bias_axis=bias_axis,
+                                        activation=activation, rounding=rounding,
+                                        out_dtype=out_dtype, impl_way=impl_way, stream=stream)
+        if out is None:
+            out = torch.empty((lhs.shape[0], rhs.shape[1]), device=lhs.device,
+                              dtype=out_dtype or lhs.dtype)
+        tl, tr, to = tensor2d(lhs), tensor2d(rhs), tensor2d(out)
+        ta = tensor2d(acc) if acc is not None else None
+        ep = self._epilogue(alpha, bias, bias_axis, activation, rounding)
+        st = self._lib.kapyb_matmul(self._h, C.byref(tl), C.byref(tr),
+                                    C.byref(ta) if ta is not None else None, C.byref(to),
+                                    C.byref(ep), impl_way, self._stream(stream))
+        if st != abi.OK:
+            self._raise(st)
+        return out
+
+    def _matmul_batched(self, lhs, rhs, out, *, alpha, bias, bias_axis, activation, rounding,
+                        out_dtype, impl_way, stream):
+        torch = _torch()
+        if rhs.dim() != 3 or rhs.shape[0] != lhs.shape[0]:
+            raise ValueError("batched matmul needs [B,M,K] and [B,K,N]")
+        B = lhs.shape[0]
+        if out is None:
+            out = torch.empty((B, lhs.shape[1], rhs.shape[2]), device=lhs.device,
+                              dtype=out_dtype or lhs.dtype)
+        tl, tr, to = tensor2d(lhs[0]), tensor2d(rhs[0]), tensor2d(out[0])
+        ep = self._epilogue(alpha, bias, bias_axis, activation, rounding)
+        st = self._lib.kapyb_matmul_batched(self._h, C.byref(tl), C.byref(tr), C.byref(to), B,
+                                            lhs.stride(0), rhs.stride(0), out.stride(0),
+                                            C.byref(ep), impl_way, self._stream(stream))
+        if st != abi.OK:
+            self._raise(st)
+        return out
+
+    def matmul_host(self, lhs, rhs, out, *, alpha: float = 1.0, bias=None, bias_axis: int = 1,
+                    activation: int = abi.ACT_NONE, rounding: int = abi.RN,
+                    impl_way: int = abi.MMA_ANY, stream=None):
+        """Same call on CPU tensors (pinned or pageable): copies in, computes on
+        the GPU, copies `out` back, returns when it has landed."""
+        for t in (lhs, rhs, out):
+            if t.is_cuda:
+                raise ValueError("matmul_host takes host tensors")
+        tl, tr, to = tensor2d(lhs), tensor2d(rhs), tensor2d(out)
+        ep = self._epilogue(alpha, bias, bias_axis, activation, rounding)
+        st = self._lib.kapyb_matmul_host(self._h, C.byref(tl), C.byref(tr), C.byref(to),
+                                         C.byref(ep), impl_way, self._stream(stream))
+        if st != abi.OK:
+            self._raise(st)
+        return out
+
+    def matmul_push(self, lhs, rhs_shard, peer_ptrs: Sequence[int], *, out_dtype, out_stride0: int,
+                    col_begin: int, n_total: int, alpha: float = 1.0, bias=None,
+                    activation: int = abi.ACT_NONE, rounding: int = abi.RN,
+                    impl_way: int = abi.MMA_ANY, stream=None):
+        """N-sharded matmul whose epilogue stores this rank's column block into
+        every peer's full-size output (device pointers in `peer_ptrs`)."""
+        tl, tr = tensor2d(lhs), tensor2d(rhs_shard)
+        ep = self._epilogue(alpha, bias, 1, activation, rounding)
+        arr = (C.c_void_p * len(peer_ptrs))(*[C.c_void_p(p) for p in peer_ptrs])
+        st = self._lib.kapyb_matmul_push(self._h, C.byref(tl), C.byref(tr), arr, len(peer_ptrs),
+                                         dtype_code(out_dtype), out_stride0, col_begin, n_total,
+                                         C.byref(ep), impl_way, self._stream(stream))
+        if st != abi.OK:
+            self._raise(st)
+
+    # ---------------------------------------------------- elementwise/reduce
+    def elementwise(self, insts, inputs, out, paddings: Optional[Sequence[int]] = None,
+                    stream=None):
+        """Runs a recorded op list [(op,dtype,dst,a,b,c,imm,flags), ...]."""
+        prog = (abi.Inst * max(1, len(insts)))()
+        for i, t in enumerate(insts):
+            prog[i] = abi.Inst(*t)
+        tin = (abi.Tensor2d * max(1, len(inputs)))()
+        for i, t in enumerate(inputs):
+            tin[i] = tensor2d(t, paddings[i] if paddings else abi.PAD_ZERO)
+        to = tensor2d(out)
+        st = self._lib.kapyb_elementwise(self._h, prog, len(insts), tin, len(inputs),
+                                         C.byref(to), self._stream(stream))
+        if st != abi.OK:
+            self._raise(st)
+        return out
+
+    def reduce(self, src, axis: int, combiner: int = abi.RED_ADD, out=None, out_dtype=None,
+               stream=None):
+        """kapy.reduce along `axis` of a 2-D tensor; the reduced axis becomes 1."""
+        torch = _torch()
+        if out is None:
+            shape = (1, src.shape[1]) if axis == 0 else (src.shape[0], 1)
+            out = torch.empty(shape, device=src.device, dtype=out_dtype or src.dtype)
+        ts, td = tensor2d(src), tensor2d(out)
+        st = self._lib.kapyb_reduce(self._h, C.byref(ts), C.byref(td), int(axis), int(combiner),
+                                    self._stream(stream))
+        if st != abi.OK:
+            self._raise(st)
+        return out
+
+
+def shard_range(total: int, parts: int, rank: int, align: int = 1):
+    """[begin, end) of `total` units owned by `rank` (blocks of `align`)."""
+    lib = abi.load()
+    b, e = C.c_int64(), C.c_int64()
+    st = lib.kapyb_shard_range(total, parts, rank, align, C.byref(b), C.byref(e))
+    if st != abi.OK:
+        raise ValueError("bad shard arguments")
+    return int(b.value), int(e.value)

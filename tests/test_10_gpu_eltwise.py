@@ -1,0 +1,166 @@
+"""Elementwise kernels against the CPU checker, through the C ABI.
+Bit-exact for pure arithmetic; <= 2 ulp of the output type once a
+transcendental or a division is involved."""
+import numpy as np
+import pytest
+import torch
+
+from util import bits, normal
+
+pytestmark = pytest.mark.gpu
+
+
+def run_both(handle, ko, prog, inputs, out_shape, out_dtype, paddings=None):
+    dev = [t.cuda() for t in inputs]
+    out = torch.empty(out_shape, dtype=out_dtype, device="cuda")
+    handle.elementwise(prog, dev, out, paddings=paddings)
+    handle.check()
+    code = {torch.float16: 0, torch.bfloat16: 1, torch.float32: 2}
+    want = ko.eltwise(prog, [bits(t) for t in inputs], [code[t.dtype] for t in inputs], out_shape,
+                      code[out_dtype], paddings=paddings)
+    return bits(out.cpu()), want
+
+
+@pytest.mark.parametrize("n", [1 << 16, 8 * 1000 + 3, 5, 0])
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+def test_affine_bit_exact(handle, ko, pkg, n, dt):
+    x = normal((1, n), 1003, dtype=dt)
+    prog = pkg.programs.affine(pkg.runtime.dtype_code(dt), 0.5, 0.1)
+    got, want = run_both(handle, ko, prog, [x], (1, n), dt)
+    if n:
+        assert handle.last_kernel == "elt_affine"
+    assert np.array_equal(got, want)
+
+
+@pytest.mark.parametrize("n", [1 << 18, 4099])
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+def test_affine_gelu_within_2ulp(handle, ko, pkg, n, dt):
+    x = normal((1, n), 1003, dtype=dt) * 2
+    prog = pkg.programs.affine_gelu_tanh(pkg.runtime.dtype_code(dt), 0.5, 0.1)
+    got, want = run_both(handle, ko, prog, [x], (1, n), dt)
+    assert handle.last_kernel == "elt_affine_gelu"
+    d = ko.ulp_diff(got, want)
+    assert d.max() <= 2, (d.max(), np.flatnonzero(d > 2)[:5])
+    assert (d == 0).mean() > 0.95
+
+
+def test_fused_equals_interpreter(handle, ko, pkg):
+    """A misaligned view forces the generic interpreter; it must give the same
+    bits as the fused kernel."""
+    x = normal((1, 4096 + 1), 11)
+    xd = x.cuda()
+    prog = pkg.programs.affine_gelu_tanh(pkg.abi.BF16, 0.5, 0.1)
+    y_fused = torch.empty((1, 4096), dtype=torch.bfloat16, device="cuda")
+    handle.elementwise(prog, [xd[:, :4096]], y_fused)
+    assert handle.last_kernel == "elt_affine_gelu"
+    y_interp = torch.empty((1, 4096), dtype=torch.bfloat16, device="cuda")
+    src = torch.empty((1, 4097), dtype=torch.bfloat16, device="cuda")
+    src[:, 1:] = xd[:, :4096]
+    handle.elementwise(prog, [src[:, 1:]], y_interp)
+    assert handle.last_kernel == "elt_interp"
+    handle.check()
+    assert torch.equal(y_fused, y_interp)
+
+
+@pytest.mark.parametrize("op", ["ADD", "SUB", "MUL"])
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16, torch.float32])
+def test_binary_bit_exact(handle, ko, pkg, op, dt):
+    """elementwise_add.mlir:17-23 at whole-tensor scope: [1,n] f16 add, and its
+    siblings; bf16 ops are single-rounding fma (ElementwiseOpToLLVM.cpp:771-892)."""
+    n = 512 * 37 + 5
+    a, b = normal((1, n), 21, dtype=dt), normal((1, n), 22, dtype=dt) * 3
+    prog = pkg.programs.binary(getattr(pkg.abi, "OP_" + op), pkg.runtime.dtype_code(dt))
+    got, want = run_both(handle, ko, prog, [a, b], (1, n), dt)
+    assert handle.last_kernel == "elt_binary"
+    if dt == torch.float32:
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    else:
+        assert np.array_equal(got, want)
+
+
+def test_interpreter_all_bf16_graph(handle, ko, pkg):
+    """An all-bf16 chain rounds after every op: ((x*s)+b) clamp, abs, max."""
+    A = pkg.abi
+    x = normal((48, 200), 31)
+    y = normal((48, 1), 32)      # broadcast along axis 1
+    B = A.BF16
+    prog = [
+        (A.OP_LOAD, B, 0, -1, -1, -1, 0.0, 0), (A.OP_LOAD, B, 1, -1, -1, -1, 0.0, 1),
+        (A.OP_CONST, B, 2, -1, -1, -1, 0.3, 0), (A.OP_MUL, B, 3, 0, 2, -1, 0.0, 0),
+        (A.OP_ADD, B, 4, 3, 1, -1, 0.0, 0), (A.OP_FMA, B, 5, 4, 0, 1, 0.0, 0),
+        (A.OP_CONST, B, 6, -1, -1, -1, -0.75, 0), (A.OP_CONST, B, 7, -1, -1, -1, 0.75, 0),
+        (A.OP_CLAMP, B, 8, 5, 6, 7, 0.0, 0), (A.OP_ABS, B, 9, 8, -1, -1, 0.0, 0),
+        (A.OP_SUB, B, 10, 9, 1, -1, 0.0, 0), (A.OP_MAXIMUM, B, 11, 10, 3, -1, 0.0, 0),
+        (A.OP_STORE, B, -1, 11, -1, -1, 0.0, 0),
+    ]
+    got, want = run_both(handle, ko, prog, [x, y], (48, 200), torch.bfloat16)
+    assert handle.last_kernel == "elt_interp"
+    assert np.array_equal(got, want)
+
+
+def test_interpreter_transcendentals_f32(handle, ko, pkg):
+    A = pkg.abi
+    x = normal((4, 1000), 41, dtype=torch.float32).abs() + 0.01
+    F = A.F32
+    for op in (A.OP_EXP, A.OP_EXP2, A.OP_LOG, A.OP_LOG2, A.OP_SQRT, A.OP_RSQRT, A.OP_ERF,
+               A.OP_SIN, A.OP_COS, A.OP_TANH):
+        prog = [(A.OP_LOAD, F, 0, -1, -1, -1, 0.0, 0), (op, F, 1, 0, -1, -1, 0.0, 0),
+                (A.OP_STORE, F, -1, 1, -1, -1, 0.0, 0)]
+        got, want = run_both(handle, ko, prog, [x], (4, 1000), torch.float32)
+        ulp = np.abs(got.view(np.int32).astype(np.int64) - want.view(np.int32).astype(np.int64))
+        # ex2.approx / lg2-based paths: a few f32 ulp; after a bf16 downcast
+        # these are far inside 2 ulp of the output type
+        assert ulp.max() <= 64, (op, ulp.max())
+        prog16 = prog[:2] + [(A.OP_CVT, A.BF16, 2, 1, -1, -1, 0.0, A.RN),
+                             (A.OP_STORE, A.BF16, -1, 2, -1, -1, 0.0, 0)]
+        g16, w16 = run_both(handle, ko, prog16, [x], (4, 1000), torch.bfloat16)
+        assert ko.ulp_diff(g16, w16).max() <= 2, op
+
+
+def test_padding_broadcast_and_strides(handle, ko, pkg):
+    A = pkg.abi
+    x = normal((20, 30), 51, dtype=torch.float32)
+    prog = [(A.OP_LOAD, A.F32, 0, -1, -1, -1, 0.0, 0), (A.OP_NEG, A.F32, 1, 0, -1, -1, 0.0, 0),
+            (A.OP_STORE, A.F32, -1, 1, -1, -1, 0.0, 0)]
+    for pad in (A.PAD_ZERO, A.PAD_PINF, A.PAD_NINF):
+        got, want = run_both(handle, ko, prog, [x], (24, 32), torch.float32, paddings=[pad])
+        assert np.array_equal(got, want)
+    # transposed (column-major) input view and output
+    xt = x.t()
+    out = torch.empty((20, 30), dtype=torch.float32, device="cuda").t()
+    handle.elementwise(prog, [xt.cuda()], out)
+    handle.check()
+    assert torch.equal(out.cpu(), -xt)
+
+
+def test_cvt_rounding_modes(handle, ko, pkg):
+    A = pkg.abi
+    x = normal((1, 5000), 61, dtype=torch.float32) * 100
+    for dt, tdt in ((A.BF16, torch.bfloat16), (A.F16, torch.float16)):
+        for rnd in (A.RN, A.RZ):
+            prog = [(A.OP_LOAD, A.F32, 0, -1, -1, -1, 0.0, 0),
+                    (A.OP_CVT, dt, 1, 0, -1, -1, 0.0, rnd), (A.OP_STORE, dt, -1, 1, -1, -1, 0.0, 0)]
+            got, want = run_both(handle, ko, prog, [x], (1, 5000), tdt)
+            assert np.array_equal(got, want)
+
+
+def test_verifier_rejections(handle, pkg):
+    A = pkg.abi
+    x = torch.zeros((1, 8), dtype=torch.bfloat16, device="cuda")
+    y = torch.zeros((1, 8), dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(ValueError, match="undefined value"):
+        handle.elementwise([(A.OP_ADD, A.BF16, 0, 1, 2, -1, 0.0, 0),
+                            (A.OP_STORE, A.BF16, -1, 0, -1, -1, 0.0, 0)], [x], y)
+    with pytest.raises(ValueError, match="same element type"):
+        handle.elementwise([(A.OP_LOAD, A.BF16, 0, -1, -1, -1, 0.0, 0),
+                            (A.OP_CONST, A.F32, 1, -1, -1, -1, 1.0, 0),
+                            (A.OP_ADD, A.F32, 2, 0, 1, -1, 0.0, 0),
+                            (A.OP_CVT, A.BF16, 3, 2, -1, -1, 0.0, 1),
+                            (A.OP_STORE, A.BF16, -1, 3, -1, -1, 0.0, 0)], [x], y)
+    with pytest.raises(ValueError, match="rounding mode must be set"):
+        handle.elementwise([(A.OP_LOAD, A.BF16, 0, -1, -1, -1, 0.0, 0),
+                            (A.OP_CVT, A.F32, 1, 0, -1, -1, 0.0, 1),
+                            (A.OP_CVT, A.BF16, 2, 1, -1, -1, 0.0, 7),
+                            (A.OP_STORE, A.BF16, -1, 2, -1, -1, 0.0, 0)], [x], y)
+    with pytest.raises(ValueError, match="stores exactly once"):
+        handle.elementwise([(A.OP_LOAD, A.BF16, 0, -1, -1, -1, 0.0, 0)], [x], y)

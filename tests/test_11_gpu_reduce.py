@@ -1,0 +1,93 @@
+"""kapy.reduce against the f64 checker.  The reference fixes no combination
+order (ReduceOpToLLVM.cpp:76-119), so sums are held to 4*eps_f32*sum|x| (plus
+one rounding of a 16-bit result); max/min are exact."""
+import numpy as np
+import pytest
+import torch
+
+from util import bits, code, normal
+
+pytestmark = pytest.mark.gpu
+EPS32 = 2.0 ** -24
+
+
+def check_sum(ko, got64, X, dt, axis, out_dtype):
+    ref, ab = ko.reduce_f64(bits(X), code(dt), axis)
+    tol = 4 * EPS32 * ab + 1e-30
+    if out_dtype != torch.float32:
+        tol = tol + np.abs(ref) * (2.0 ** -8 if out_dtype == torch.bfloat16 else 2.0 ** -11)
+    assert np.all(np.abs(got64 - ref) <= tol), np.abs(got64 - ref).max()
+
+
+@pytest.mark.parametrize("shape", [(64, 4096), (37, 300), (5, 8), (3, 1), (1000, 2056)])
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16, torch.float32])
+def test_row_sum_f32(handle, ko, shape, dt):
+    X = normal(shape, 1004, dtype=dt)
+    out = handle.reduce(X.cuda(), axis=1, out_dtype=torch.float32)
+    handle.check()
+    assert out.shape == (shape[0], 1)
+    assert handle.last_kernel == "reduce_rows"
+    check_sum(ko, out.cpu().numpy().ravel().astype(np.float64), X, dt, 1, torch.float32)
+
+
+def test_reduce_sum_mlir_shape(handle, ko):
+    """reduce_sum.mlir:10-25: [n, 256] f16 -> [n, 1] f16 with an addf lambda."""
+    X = normal((128, 256), 5, dtype=torch.float16)
+    out = handle.reduce(X.cuda(), axis=1)
+    handle.check()
+    assert out.dtype == torch.float16 and out.shape == (128, 1)
+    check_sum(ko, out.cpu().double().numpy().ravel(), X, torch.float16, 1, torch.float16)
+
+
+@pytest.mark.parametrize("shape", [(300, 37), (4096, 64), (7, 1)])
+def test_axis0_and_strided(handle, ko, shape):
+    X = normal(shape, 77)
+    out = handle.reduce(X.cuda(), axis=0, out_dtype=torch.float32)
+    handle.check()
+    assert out.shape == (1, shape[1]) and handle.last_kernel == "reduce_cols"
+    check_sum(ko, out.cpu().numpy().ravel().astype(np.float64), X, torch.bfloat16, 0,
+              torch.float32)
+    # a column-major view reduced along axis 1 is the same computation
+    Xt = X.t()
+    out2 = handle.reduce(Xt.cuda(), axis=1, out_dtype=torch.float32)
+    handle.check()
+    assert torch.equal(out2.cpu().ravel(), out.cpu().ravel())
+    # misaligned rows fall off the 128-bit path but give a valid sum
+    Y = normal((shape[0], shape[1] + 1), 78)[:, 1:]
+    o3 = handle.reduce(Y.cuda(), axis=1, out_dtype=torch.float32)
+    handle.check()
+    check_sum(ko, o3.cpu().numpy().ravel().astype(np.float64), Y, torch.bfloat16, 1,
+              torch.float32)
+
+
+@pytest.mark.parametrize("comb", ["MAX", "MIN", "MUL"])
+def test_other_combiners(handle, ko, pkg, comb):
+    X = normal((33, 129), 9, dtype=torch.float32)
+    if comb == "MUL":
+        X = X * 0.1 + 1.0
+    c = getattr(pkg.abi, "RED_" + comb)
+    out = handle.reduce(X.cuda(), axis=1, combiner=c)
+    handle.check()
+    ref, _ = ko.reduce_f64(bits(X), 2, 1, c)
+    got = out.cpu().numpy().ravel().astype(np.float64)
+    if comb == "MUL":
+        assert np.allclose(got, ref, rtol=129 * 2 * EPS32)
+    else:
+        assert np.array_equal(got, ref)
+    Xn = X.clone()
+    Xn[3, 5] = float("nan")
+    if comb != "MUL":
+        o = handle.reduce(Xn.cuda(), axis=1, combiner=c).cpu().ravel()
+        assert torch.isnan(o[3]) and not torch.isnan(o[2])   # maximumf propagates NaN
+
+
+def test_shape_rules(handle, pkg):
+    X = torch.zeros((4, 8), dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(ValueError, match="result shape"):
+        handle.reduce(X, axis=1, out=torch.zeros((4, 2), dtype=torch.bfloat16, device="cuda"))
+    with pytest.raises(ValueError, match="axis"):
+        handle.reduce(X, axis=2)
+    with pytest.raises(ValueError, match="element type"):
+        handle.reduce(X, axis=1, out=torch.zeros((4, 1), dtype=torch.float16, device="cuda"))
+    e = handle.reduce(torch.zeros((0, 8), dtype=torch.bfloat16, device="cuda"), axis=1)
+    assert e.shape == (0, 1)

@@ -1,0 +1,95 @@
+"""The shape-specialised matmul paths: decode-shape (skinny) weight streaming,
+batched, and the CTA-pair kernel."""
+import numpy as np
+import pytest
+import torch
+
+from util import bits, code, normal, uniform
+from test_20_gpu_matmul import check
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("shape", [(16, 512, 256), (1, 384, 8192), (16, 3584, 2048), (5, 200, 136),
+                                   (33, 1000, 520), (64, 256, 64)])
+@pytest.mark.parametrize("wl", ["n", "t"])
+def test_skinny(handle, ko, shape, wl):
+    M, N, K = shape
+    X = normal((M, K), 1005)
+    W = normal((K, N), 2005, 0.02)
+    Wd = W.cuda() if wl == "n" else W.t().contiguous().cuda().t()
+    bias = uniform((N,), 15, -0.1, 0.1, torch.bfloat16)
+    out = handle.matmul(X.cuda(), Wd, bias=bias.cuda())
+    handle.check()
+    assert handle.last_kernel == "tcgen05_skinny"
+    check(ko, out, X, W, bias=bias)
+    # a second launch reuses the (self-cleaned) scratch and must agree
+    out2 = handle.matmul(X.cuda(), Wd, bias=bias.cuda(), out_dtype=torch.float32)
+    handle.check()
+    check(ko, out2, X, W, bias=bias)
+
+
+def test_config4_decode_shape(handle, ko):
+    """M=16, N=28672, K=8192 bf16; activations N(0,1), weights N(0,0.02)."""
+    X = normal((16, 8192), 1005)
+    W = normal((8192, 28672), 2005, 0.02)
+    out = handle.matmul(X.cuda(), W.cuda())
+    handle.check()
+    assert handle.last_kernel == "tcgen05_skinny"
+    cols = np.sort(np.random.default_rng(1).choice(28672, 512, replace=False)).astype(np.int32)
+    cols[:4] = [0, 127, 128, 28671]
+    cols = np.unique(cols).astype(np.int32)
+    check(ko, out, X, W, rows=np.arange(16, dtype=np.int32), cols=cols)
+    # whole output against the big-tile kernel (different summation order)
+    handle.set_matmul_path("1cta:128")
+    try:
+        ref = handle.matmul(X.cuda(), W.cuda(), out_dtype=torch.float32)
+    finally:
+        handle.set_matmul_path("auto")
+    handle.check()
+    assert (out.float() - ref).abs().max().item() <= 2 ** -5 * ref.abs().max().item()
+
+
+@pytest.mark.parametrize("batch,M,N,K", [(3, 128, 256, 64), (4, 200, 136, 128), (64, 256, 256, 128)])
+def test_batched(handle, ko, batch, M, N, K):
+    Q = normal((batch, M, K), 1006)
+    Kt = normal((batch, K, N), 2006)
+    alpha = K ** -0.5
+    out = handle.matmul(Q.cuda(), Kt.cuda(), alpha=alpha)
+    handle.check()
+    assert out.shape == (batch, M, N) and handle.last_kernel.startswith("tcgen05")
+    for b in {0, batch // 2, batch - 1}:
+        check(ko, out[b], Q[b], Kt[b], alpha=alpha)
+
+
+def test_config5_attention_scores(handle, ko):
+    """batch 64 x (2048 x 2048 x 128) bf16 with the fused 1/sqrt(128) scale."""
+    Q = normal((64, 2048, 128), 1006)
+    Kt = normal((64, 128, 2048), 2006)
+    alpha = 128 ** -0.5
+    out = handle.matmul(Q.cuda(), Kt.cuda(), alpha=alpha)
+    handle.check()
+    rows = np.array([0, 1, 127, 128, 1000, 2047], dtype=np.int32)
+    for b in (0, 31, 63):
+        check(ko, out[b], Q[b], Kt[b], alpha=alpha, rows=rows, cols=np.arange(2048, dtype=np.int32))
+    ref = torch.bmm(Q.cuda(), Kt.cuda()).float() * alpha
+    assert (out.float() - ref).abs().max().item() <= 2 ** -4
+
+
+@pytest.mark.parametrize("shape", [(256, 256, 64), (512, 768, 320), (300, 264, 136), (1024, 1024, 1024)])
+@pytest.mark.parametrize("bn", [128, 256])
+@pytest.mark.parametrize("layout", ["nn", "nt"])
+def test_cta_pair_kernel(handle, ko, shape, bn, layout):
+    """tcgen05.mma.cta_group::2: two CTAs share one 256-row tile."""
+    M, N, K = shape
+    A, B = normal((M, K), 16, K ** -0.5), normal((K, N), 17)
+    Bd = B.cuda() if layout[1] == "n" else B.t().contiguous().cuda().t()
+    bias = uniform((N,), 18, -0.1, 0.1, torch.bfloat16)
+    handle.set_matmul_path(f"2cta:{bn}")
+    try:
+        out = handle.matmul(A.cuda(), Bd, bias=bias.cuda())
+        handle.check()
+        assert handle.last_kernel == "tcgen05_2cta"
+    finally:
+        handle.set_matmul_path("auto")
+    check(ko, out, A, B, bias=bias)

@@ -1,0 +1,28 @@
+"""Helpers shared by the tests: seeded inputs and torch <-> bit-pattern views."""
+import numpy as np
+import torch
+
+
+def bits(t: torch.Tensor) -> np.ndarray:
+    """Storage view of a CPU tensor: uint16 for f16/bf16, float32 otherwise
+    (strides preserved)."""
+    t = t.detach().cpu()
+    if t.dtype == torch.float32:
+        return t.numpy()
+    return t.view(torch.int16).numpy().view(np.uint16)
+
+
+def code(dt) -> int:
+    return {torch.float16: 0, torch.bfloat16: 1, torch.float32: 2}[dt]
+
+
+def gen(seed: int) -> torch.Generator:
+    return torch.Generator(device="cpu").manual_seed(seed)
+
+
+def normal(shape, seed, std=1.0, dtype=torch.bfloat16):
+    return (torch.randn(*shape, generator=gen(seed)) * std).to(dtype)
+
+
+def uniform(shape, seed, lo=-1.0, hi=1.0, dtype=torch.float16):
+    return (torch.rand(*shape, generator=gen(seed)) * (hi - lo) + lo).to(dtype)
