@@ -220,7 +220,9 @@ static kapyb_status verify_matmul(kapyb_handle h, const kapyb_tensor2d *lhs,
                                   const kapyb_tensor2d *out, const kapyb_epilogue *ep,
                                   int impl_way) {
   if (!lhs || !rhs || !out) return fail(h, KAPYB_INVALID_ARG, "matmul: NULL tensor descriptor");
-  if (!lhs->ptr || !rhs->ptr || !out->ptr) return fail(h, KAPYB_INVALID_ARG, "matmul: NULL data pointer");
+  auto empty = [](const kapyb_tensor2d *t) { return t->size0 == 0 || t->size1 == 0; };
+  if ((!lhs->ptr && !empty(lhs)) || (!rhs->ptr && !empty(rhs)) || (!out->ptr && !empty(out)))
+    return fail(h, KAPYB_INVALID_ARG, "matmul: NULL data pointer");
   if (!valid_dtype(lhs->dtype) || !valid_dtype(rhs->dtype) || !valid_dtype(out->dtype))
     return fail(h, KAPYB_INVALID_ARG, "matmul: unknown element type");
   if (lhs->size0 < 0 || lhs->size1 < 0 || rhs->size0 < 0 || rhs->size1 < 0)
@@ -793,11 +795,13 @@ static kapyb_status verify_program(kapyb_handle h, const kapyb_inst *prog, int n
     return fail(h, KAPYB_INVALID_ARG, "elementwise: program must have 1..%d ops", KAPYB_MAX_INSTS);
   if (n_inputs < 0 || n_inputs > KAPYB_MAX_INPUTS || (n_inputs > 0 && !inputs))
     return fail(h, KAPYB_INVALID_ARG, "elementwise: at most %d inputs", KAPYB_MAX_INPUTS);
-  if (!out || !out->ptr || !valid_dtype(out->dtype) || out->size0 < 0 || out->size1 < 0)
+  if (!out || !valid_dtype(out->dtype) || out->size0 < 0 || out->size1 < 0 ||
+      (!out->ptr && out->size0 != 0 && out->size1 != 0))
     return fail(h, KAPYB_INVALID_ARG, "elementwise: bad output descriptor");
   for (int k = 0; k < n_inputs; ++k) {
     const kapyb_tensor2d &t = inputs[k];
-    if (!t.ptr || !valid_dtype(t.dtype) || t.size0 < 0 || t.size1 < 0)
+    if (!valid_dtype(t.dtype) || t.size0 < 0 || t.size1 < 0 ||
+        (!t.ptr && t.size0 != 0 && t.size1 != 0))
       return fail(h, KAPYB_INVALID_ARG, "elementwise: bad input descriptor %d", k);
     if (t.padding < KAPYB_PAD_ZERO || t.padding > KAPYB_PAD_NINF)
       return fail(h, KAPYB_INVALID_ARG, "elementwise: bad padding option on input %d", k);
@@ -1107,7 +1111,9 @@ extern "C" KAPYB_API kapyb_status kapyb_reduce(kapyb_handle h, const kapyb_tenso
                                                const kapyb_tensor2d *dst, int32_t axis,
                                                int32_t combiner, void *stream_) {
   if (!h) return fail(h, KAPYB_INVALID_ARG, "kapyb_reduce: NULL handle");
-  if (!src || !dst || !src->ptr || !dst->ptr) return fail(h, KAPYB_INVALID_ARG, "reduce: NULL tensor");
+  if (!src || !dst) return fail(h, KAPYB_INVALID_ARG, "reduce: NULL tensor");
+  if ((!src->ptr && src->size0 != 0 && src->size1 != 0) || (!dst->ptr && dst->size0 != 0 && dst->size1 != 0))
+    return fail(h, KAPYB_INVALID_ARG, "reduce: NULL data pointer");
   if (!valid_dtype(src->dtype) || !valid_dtype(dst->dtype)) return fail(h, KAPYB_INVALID_ARG, "reduce: unknown element type");
   if (axis != 0 && axis != 1) return fail(h, KAPYB_INVALID_ARG, "reduce: axis must be 0 or 1");
   if (combiner < KAPYB_RED_ADD || combiner > KAPYB_RED_MIN) return fail(h, KAPYB_INVALID_ARG, "reduce: unknown combiner %d", combiner);
