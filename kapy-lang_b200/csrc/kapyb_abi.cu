@@ -28,6 +28,7 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 enum MatmulPath { PATH_AUTO = 0, PATH_1CTA, PATH_2CTA, PATH_SKINNY, PATH_SIMT };
+constexpr int kMaxDevices = 64;
 
 struct kapyb_context {
   int device = 0;
@@ -76,9 +77,9 @@ extern "C" KAPYB_API kapyb_status kapyb_create(kapyb_handle *out, int device) {
     return fail(nullptr, KAPYB_CUDA_ERROR,
                 "kapyb_create: no CUDA device (%s); this library has no CPU path",
                 e != cudaSuccess ? cudaGetErrorString(e) : "device count is 0");
-  if (device < 0 || device >= n)
+  if (device < 0 || device >= n || device >= kMaxDevices)
     return fail(nullptr, KAPYB_INVALID_ARG, "kapyb_create: device %d out of range [0,%d)", device,
-                n);
+                std::min(n, kMaxDevices));
   cudaDeviceProp prop;
   CUDA_TRY(nullptr, cudaGetDeviceProperties(&prop, device));
   if (prop.major != 10)
@@ -440,11 +441,11 @@ static kapyb_status launch_tcgen05(kapyb_handle h, const MatmulProblem &p, bool 
   gp.ep = p.ep;
 
   auto kern = gemm_tcgen05_kernel<BN, CTAS>;
-  static bool attr_set = false;
-  if (!attr_set) {
+  static bool attr_set[kMaxDevices] = {};
+  if (!attr_set[h->device]) {
     CUDA_TRY(h, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      Cfg::SMEM_BYTES));
-    attr_set = true;
+    attr_set[h->device] = true;
   }
   int units = std::min(gp.num_tiles, h->sm_count / CTAS);
   cudaLaunchConfig_t cfg = {};
@@ -522,11 +523,11 @@ static kapyb_status launch_skinny_on(kapyb_handle h, const MatmulProblem &p, boo
   else
     st = make_tmap(h, &tmX, p.a, p.in_dtype, p.K, p.M, 1, p.a_s0, 0, 64, sp.m_pad);
   if (st != KAPYB_OK) return st;
-  static bool attr_set = false;
-  if (!attr_set) {
+  static bool attr_set[kMaxDevices] = {};
+  if (!attr_set[h->device]) {
     CUDA_TRY(h, cudaFuncSetAttribute(gemm_skinny_kernel,
                                      cudaFuncAttributeMaxDynamicSharedMemorySize, 232448));
-    attr_set = true;
+    attr_set[h->device] = true;
   }
   gemm_skinny_kernel<<<grid, kSkinnyThreads, smem, stream>>>(tmW, tmX, sp);
   CUDA_TRY(h, cudaGetLastError());
