@@ -265,6 +265,46 @@ KAPYB_API kapyb_status kapyb_matmul_push(
     int32_t out_stride0, int32_t col_begin, int32_t n_total,
     const kapyb_epilogue *epilogue, int32_t impl_way, void *stream);
 
+/* The decode-shape (few-row) matmul for callers that must not allocate device
+ * memory.  No counterpart in the reference.
+ *
+ * Who needs it: a host whose memory pool already owns the whole GPU (a serving
+ * engine that reserved all of HBM up front, so a plugin's cudaMalloc fails or
+ * steals from the pool), a latency-critical loop that cannot afford the
+ * device-wide synchronisation cudaMalloc/cudaFree imply, or an embedding that
+ * forbids allocation after start-up.  kapyb_matmul on this shape splits weight
+ * tiles between SMs and sums the pieces in scratch memory taken from the
+ * handle's workspace (a cudaMalloc); this variant takes no handle and keeps that
+ * scratch in a fixed array inside the library image instead.
+ *
+ *   out[M,N] = epilogue(lhs[M,K] . rhs[K,N]),  1 <= M <= 64, f16/bf16 operands.
+ *
+ * Limits and rules:
+ *  - the fixed scratch is 4 MiB of partial sums + 16 KiB of counters per GPU
+ *    (held by every GPU that loads the library, until exit); a call needs
+ *    ceil(N/128) * roundup16(M) * 512 bytes of it, i.e. N * roundup16(M) must not
+ *    exceed 1,048,576 (N <= 65536 at M <= 16).  Larger problems are refused with
+ *    KAPYB_UNSUPPORTED and a message saying so; nothing is launched;
+ *  - operands must be TMA-describable (one unit stride, 16-byte aligned base,
+ *    leading dimension a multiple of 16 bytes); there is no fallback kernel;
+ *  - the call runs on the CURRENT device.  Its first call on each device looks
+ *    up the array's device address (cudaGetSymbolAddress) and the device's
+ *    properties; make that first call outside any stream capture;
+ *  - it calls no cudaMalloc/cudaFree and no allocating library routine.  It
+ *    clears the part of the scratch it will use (cudaMemsetAsync on `stream`),
+ *    then launches the kernel on `stream`;
+ *  - all calls on one GPU share the one array: two calls whose kernels can
+ *    overlap on the GPU (different streams, no dependency) race and give wrong
+ *    results.  Keep them on one stream or order them yourself;
+ *  - sync_and_check != 0 waits for `stream` and returns KAPYB_TIMEOUT if the
+ *    kernel gave up on a bounded wait; with 0 the call returns after launching.
+ * Error text: kapyb_last_error_string(NULL) on the calling thread. */
+KAPYB_API kapyb_status kapyb_matmul_decode_static(const kapyb_tensor2d *lhs,
+                                                  const kapyb_tensor2d *rhs,
+                                                  const kapyb_tensor2d *out,
+                                                  const kapyb_epilogue *epilogue,
+                                                  int32_t sync_and_check, void *stream);
+
 /* --------------------------------------------------- elementwise / reduce */
 
 /* Runs a recorded elementwise graph over out->size0 x out->size1 elements.

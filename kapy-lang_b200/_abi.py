@@ -74,6 +74,9 @@ PROTOTYPES = {
                                     C.POINTER(C.c_void_p), C.c_int32, C.c_int32, C.c_int32,
                                     C.c_int32, C.c_int32, C.POINTER(Epilogue), C.c_int32,
                                     C.c_void_p]),
+    "kapyb_matmul_decode_static": (C.c_int, [C.POINTER(Tensor2d), C.POINTER(Tensor2d),
+                                             C.POINTER(Tensor2d), C.POINTER(Epilogue), C.c_int32,
+                                             C.c_void_p]),
     "kapyb_elementwise": (C.c_int, [C.c_void_p, C.POINTER(Inst), C.c_int32, C.POINTER(Tensor2d),
                                     C.c_int32, C.POINTER(Tensor2d), C.c_void_p]),
     "kapyb_reduce": (C.c_int, [C.c_void_p, C.POINTER(Tensor2d), C.POINTER(Tensor2d), C.c_int32,

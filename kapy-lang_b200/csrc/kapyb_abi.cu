@@ -1156,3 +1156,121 @@ extern "C" KAPYB_API kapyb_status kapyb_reduce(kapyb_handle h, const kapyb_tenso
   h->last_kernel = unit_inner ? "reduce_rows" : "reduce_cols";
   return KAPYB_OK;
 }
+
+// ------------------------------------------- decode matmul without allocation
+
+// Fixed scratch for kapyb_matmul_decode_static: tile counters followed by the
+// fp32 partial sums of split weight tiles.  It lives in the library image, so
+// every GPU that loads the library carries these bytes until the process exits.
+constexpr size_t kStaticCounterBytes = 16 * 1024;
+constexpr size_t kStaticPartialBytes = 4u << 20;
+static __device__ __align__(256) unsigned char g_decode_scratch[kStaticCounterBytes + kStaticPartialBytes];
+static __device__ uint32_t g_decode_status;
+
+struct StaticDeviceState {
+  bool ready = false;
+  unsigned char *scratch = nullptr;  // device address of g_decode_scratch on this device
+  uint32_t *status = nullptr;        // device address of g_decode_status on this device
+  int sm_count = 0;
+  EncodeTiledFn encode = nullptr;
+};
+static StaticDeviceState g_static_state[kMaxDevices];
+
+extern "C" KAPYB_API kapyb_status kapyb_matmul_decode_static(const kapyb_tensor2d *lhs,
+                                                             const kapyb_tensor2d *rhs,
+                                                             const kapyb_tensor2d *out,
+                                                             const kapyb_epilogue *epilogue,
+                                                             int32_t sync_and_check,
+                                                             void *stream_) {
+  // A stack context lets this call share the launcher of the ordinary path
+  // without creating a handle (which would allocate).
+  kapyb_context ctx;
+  auto bail = [&](kapyb_status st) {
+    g_create_error = ctx.last_error;
+    return st;
+  };
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail(nullptr, KAPYB_CUDA_ERROR, "matmul_decode_static: cudaGetDevice: %s", cudaGetErrorString(e));
+  if (dev < 0 || dev >= kMaxDevices)
+    return fail(nullptr, KAPYB_UNSUPPORTED, "matmul_decode_static: device index %d not supported", dev);
+  StaticDeviceState &sd = g_static_state[dev];
+  if (!sd.ready) {
+    // First call on this device: resolve where the static arrays live there.
+    // The symbol name is only a host-side stand-in, so ask the runtime for the
+    // device address while this device is current.
+    cudaDeviceProp prop;
+    e = cudaGetDeviceProperties(&prop, dev);
+    if (e != cudaSuccess) return fail(nullptr, KAPYB_CUDA_ERROR, "matmul_decode_static: device properties: %s", cudaGetErrorString(e));
+    if (prop.major != 10)
+      return fail(nullptr, KAPYB_CUDA_ERROR, "matmul_decode_static: device %d is sm_%d%d; kernels are built for sm_100a only", dev, prop.major, prop.minor);
+    void *p_scratch = nullptr, *p_status = nullptr;
+    e = cudaGetSymbolAddress(&p_scratch, g_decode_scratch);
+    if (e != cudaSuccess) return fail(nullptr, KAPYB_CUDA_ERROR, "matmul_decode_static: cudaGetSymbolAddress(scratch): %s", cudaGetErrorString(e));
+    e = cudaGetSymbolAddress(&p_status, g_decode_status);
+    if (e != cudaSuccess) return fail(nullptr, KAPYB_CUDA_ERROR, "matmul_decode_static: cudaGetSymbolAddress(status): %s", cudaGetErrorString(e));
+    cudaDriverEntryPointQueryResult q;
+    void *fn = nullptr;
+    e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
+    if (e != cudaSuccess || fn == nullptr || q != cudaDriverEntryPointSuccess)
+      return fail(nullptr, KAPYB_CUDA_ERROR, "matmul_decode_static: cuTensorMapEncodeTiled not available");
+    sd.scratch = static_cast<unsigned char *>(p_scratch);
+    sd.status = static_cast<uint32_t *>(p_status);
+    sd.sm_count = prop.multiProcessorCount;
+    sd.encode = reinterpret_cast<EncodeTiledFn>(fn);
+    sd.ready = true;
+  }
+  ctx.device = dev;
+  ctx.sm_count = sd.sm_count;
+  ctx.status = sd.status;
+  ctx.encode = sd.encode;
+
+  kapyb_status st = verify_matmul(&ctx, lhs, rhs, nullptr, out, epilogue, KAPYB_MMA_ANY);
+  if (st != KAPYB_OK) return bail(st);
+  MatmulProblem p = make_problem(lhs, rhs, nullptr, out, epilogue);
+  if (p.M == 0 || p.N == 0) return KAPYB_OK;
+  const int m_pad = (p.M + 15) / 16 * 16;
+  const long long n_tiles = (p.N + 127) / 128;
+  if (p.M > kSkinnyMaxM || p.K < 1)
+    return bail(fail(&ctx, KAPYB_UNSUPPORTED, "matmul_decode_static: needs 1 <= M <= %d and K >= 1 (got M=%d, K=%d)", kSkinnyMaxM, p.M, p.K));
+  const size_t need_counters = static_cast<size_t>(n_tiles) * 4 * sizeof(uint32_t);
+  const size_t need_partial = static_cast<size_t>(n_tiles) * m_pad * 128 * sizeof(float);
+  if (need_counters > kStaticCounterBytes || need_partial > kStaticPartialBytes)
+    return bail(fail(&ctx, KAPYB_UNSUPPORTED,
+                     "matmul_decode_static: problem needs %zu bytes of partial sums and %zu of counters; "
+                     "the fixed scratch holds %zu and %zu (N * roundup16(M) <= %zu)",
+                     need_partial, need_counters, kStaticPartialBytes, kStaticCounterBytes,
+                     kStaticPartialBytes / 4));
+  if (p.c_s1 != 1 && p.N != 1)
+    return bail(fail(&ctx, KAPYB_UNSUPPORTED, "matmul_decode_static: out must be row-major (unit stride on axis 1)"));
+  const bool a_k = p.a_s1 == 1 || p.K == 1, a_m = p.a_s0 == 1 || p.M == 1;
+  const bool b_n = p.b_s1 == 1 || p.N == 1, b_k = p.b_s0 == 1 || p.K == 1;
+  const bool a_mn = !a_k && a_m, b_mn = b_n;
+  if ( !(a_k || a_m) || !(b_n || b_k) ||
+      !tma_ok(p.a, p.in_dtype, a_mn ? p.M : p.K, a_mn ? p.K : p.M, a_mn ? p.a_s1 : p.a_s0, 1, 0) ||
+      !tma_ok(p.b, p.in_dtype, b_mn ? p.N : p.K, b_mn ? p.K : p.N, b_mn ? p.b_s0 : p.b_s1, 1, 0))
+    return bail(fail(&ctx, KAPYB_UNSUPPORTED,
+                     "matmul_decode_static: operands need a unit stride, 16-byte aligned bases and "
+                     "leading dimensions that are multiples of 16 bytes"));
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  // The array keeps whatever the previous call left (zeros after a clean run,
+  // anything after one that was cut short): clear the part this call reads.
+  e = cudaMemsetAsync(sd.scratch, 0, need_counters, stream);
+  if (e == cudaSuccess) e = cudaMemsetAsync(sd.scratch + kStaticCounterBytes, 0, need_partial, stream);
+  if (e != cudaSuccess) return fail(nullptr, KAPYB_CUDA_ERROR, "matmul_decode_static: clearing scratch: %s", cudaGetErrorString(e));
+  st = launch_skinny_on(&ctx, p, a_mn, b_mn,
+                        reinterpret_cast<float *>(sd.scratch + kStaticCounterBytes),
+                        reinterpret_cast<uint32_t *>(sd.scratch), stream);
+  if (st != KAPYB_OK) return bail(st);
+  if (sync_and_check) {
+    e = cudaStreamSynchronize(stream);
+    uint32_t word = 0;
+    if (e == cudaSuccess) e = cudaMemcpy(&word, sd.status, sizeof(word), cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return fail(nullptr, KAPYB_CUDA_ERROR, "matmul_decode_static: %s", cudaGetErrorString(e));
+    if (word != kStatusOk) {
+      cudaMemset(sd.status, 0, sizeof(uint32_t));
+      return fail(nullptr, KAPYB_TIMEOUT, "matmul_decode_static: the kernel gave up on a bounded wait");
+    }
+  }
+  return KAPYB_OK;
+}
