@@ -158,21 +158,61 @@ __global__ void __launch_bounds__(256) elt_interp_kernel(const EltProgram P) {
 
 // ------------------------------------------------------------ fused kernels
 
+// Packed f32x2 arithmetic (sm_100): each half is an independent IEEE
+// round-to-nearest op, so the bits equal those of the scalar instruction; one
+// issue slot does the work of two.
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float &lo, float &hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+
 // y = cvt16( act( fma(ext(x), s, b) ) ): the "affine (+ gelu_tanh)" graph.
 // The gelu constants come from the program so the kernel reproduces whatever
-// constants the caller recorded.
+// constants the caller recorded.  Two elements are processed per call, with the
+// same op sequence per element as the op-by-op interpreter:
+//   u = fma(x,s,b); t = (c1*u)*u; k = c0*fma(t,u,u); e = ex2(( m2*k )*log2e);
+//   y = u / (one + e)
 struct AffineGelu {
   float s, b;
   int gelu;        // 0: affine only
   float c0, c1;    // k = c0 * fma(c1*u*u, u, u)
   float m2, one;   // y = u / (one + exp(m2 * k))
-  __device__ __forceinline__ float operator()(float x) const {
-    const float u = __fmaf_rn(x, s, b);
-    if (!gelu) return u;
-    const float t = __fmul_rn(__fmul_rn(c1, u), u);
-    const float k = __fmul_rn(c0, __fmaf_rn(t, u, u));
-    const float e = kapy_exp(__fmul_rn(m2, k));
-    return div_full(u, __fadd_rn(one, e));
+  __device__ __forceinline__ void operator()(float &x0, float &x1) const {
+    const uint64_t u = fma2(pack2(x0, x1), pack2(s, s), pack2(b, b));
+    if (!gelu) {
+      unpack2(u, x0, x1);
+      return;
+    }
+    const uint64_t t = mul2(mul2(pack2(c1, c1), u), u);
+    const uint64_t k = mul2(pack2(c0, c0), fma2(t, u, u));
+    const uint64_t z = mul2(mul2(pack2(m2, m2), k),
+                            pack2(1.4426950408889634f, 1.4426950408889634f));
+    float z0, z1, u0, u1, d0, d1;
+    unpack2(z, z0, z1);
+    const uint64_t d = add2(pack2(one, one), pack2(ex2_approx(z0), ex2_approx(z1)));
+    unpack2(u, u0, u1);
+    unpack2(d, d0, d1);
+    x0 = div_full(u0, d0);
+    x1 = div_full(u1, d1);
   }
 };
 
@@ -191,49 +231,85 @@ __device__ __forceinline__ void st_stream(uint4 *p, uint4 v) {
 
 template <class F>
 __device__ __forceinline__ uint32_t apply2_16(uint32_t w, const F &f, int din, int dout, int rn) {
-  const float lo = f(cvt_16_to_f32(static_cast<uint16_t>(w & 0xffffu), din));
-  const float hi = f(cvt_16_to_f32(static_cast<uint16_t>(w >> 16), din));
+  float lo, hi;
+  if (din == KAPYB_BF16) {
+    lo = __uint_as_float(w << 16);
+    hi = __uint_as_float(w & 0xffff0000u);
+  } else {
+    lo = cvt_16_to_f32(static_cast<uint16_t>(w & 0xffffu), din);
+    hi = cvt_16_to_f32(static_cast<uint16_t>(w >> 16), din);
+  }
+  f(lo, hi);
   return cvt_pack2(lo, hi, dout, rn);
 }
 
 constexpr int kEltUnroll = 4;
 
-// 16-bit in, 16-bit out, contiguous, 16-byte aligned; n_vec vectors of 8
-// elements plus a scalar tail handled by the last block.
-template <class F>
+// One streaming access of W x 16 bytes (W = 2 uses the 256-bit ld/st forms).
+template <int W>
+struct StreamVec {
+  uint4 q[W];
+};
+template <int W>
+__device__ __forceinline__ StreamVec<W> ld_stream_vec(const uint4 *p) {
+  StreamVec<W> v;
+  if constexpr (W == 1) {
+    v.q[0] = ld_stream(p);
+  } else {
+    asm volatile("ld.global.nc.L1::no_allocate.v8.u32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(v.q[0].x), "=r"(v.q[0].y), "=r"(v.q[0].z), "=r"(v.q[0].w),
+                   "=r"(v.q[1].x), "=r"(v.q[1].y), "=r"(v.q[1].z), "=r"(v.q[1].w)
+                 : "l"(p));
+  }
+  return v;
+}
+template <int W>
+__device__ __forceinline__ void st_stream_vec(uint4 *p, const StreamVec<W> &v) {
+  if constexpr (W == 1) {
+    st_stream(p, v.q[0]);
+  } else {
+    asm volatile("st.global.cs.v8.u32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p),
+                 "r"(v.q[0].x), "r"(v.q[0].y), "r"(v.q[0].z), "r"(v.q[0].w), "r"(v.q[1].x),
+                 "r"(v.q[1].y), "r"(v.q[1].z), "r"(v.q[1].w)
+                 : "memory");
+  }
+}
+
+// 16-bit in, 16-bit out, contiguous; both pointers aligned to W x 16 bytes.
+// n_acc accesses of W*8 elements plus a scalar tail handled by the last block.
+template <class F, int W>
 __global__ void __launch_bounds__(256)
-elt_unary16_kernel(const uint4 *__restrict__ x, uint4 *__restrict__ y, long long n_vec,
+elt_unary16_kernel(const uint4 *__restrict__ x, uint4 *__restrict__ y, long long n_acc,
                    long long n_elems, F f, int din, int dout, int rn) {
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
   long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
-  for (; i + (kEltUnroll - 1) * stride < n_vec; i += kEltUnroll * stride) {
-    uint4 v[kEltUnroll];
+  auto apply = [&](const StreamVec<W> &v) {
+    StreamVec<W> o;
 #pragma unroll
-    for (int u = 0; u < kEltUnroll; ++u) v[u] = ld_stream(x + i + u * stride);
-#pragma unroll
-    for (int u = 0; u < kEltUnroll; ++u) {
-      uint4 o;
-      o.x = apply2_16(v[u].x, f, din, dout, rn);
-      o.y = apply2_16(v[u].y, f, din, dout, rn);
-      o.z = apply2_16(v[u].z, f, din, dout, rn);
-      o.w = apply2_16(v[u].w, f, din, dout, rn);
-      st_stream(y + i + u * stride, o);
+    for (int w = 0; w < W; ++w) {
+      o.q[w].x = apply2_16(v.q[w].x, f, din, dout, rn);
+      o.q[w].y = apply2_16(v.q[w].y, f, din, dout, rn);
+      o.q[w].z = apply2_16(v.q[w].z, f, din, dout, rn);
+      o.q[w].w = apply2_16(v.q[w].w, f, din, dout, rn);
     }
+    return o;
+  };
+  for (; i + (kEltUnroll - 1) * stride < n_acc; i += kEltUnroll * stride) {
+    StreamVec<W> v[kEltUnroll];
+#pragma unroll
+    for (int u = 0; u < kEltUnroll; ++u) v[u] = ld_stream_vec<W>(x + (i + u * stride) * W);
+#pragma unroll
+    for (int u = 0; u < kEltUnroll; ++u) st_stream_vec<W>(y + (i + u * stride) * W, apply(v[u]));
   }
-  for (; i < n_vec; i += stride) {
-    const uint4 v = ld_stream(x + i);
-    uint4 o;
-    o.x = apply2_16(v.x, f, din, dout, rn);
-    o.y = apply2_16(v.y, f, din, dout, rn);
-    o.z = apply2_16(v.z, f, din, dout, rn);
-    o.w = apply2_16(v.w, f, din, dout, rn);
-    st_stream(y + i, o);
-  }
+  for (; i < n_acc; i += stride) st_stream_vec<W>(y + i * W, apply(ld_stream_vec<W>(x + i * W)));
   if (blockIdx.x == gridDim.x - 1) {
     const uint16_t *xs = reinterpret_cast<const uint16_t *>(x);
     uint16_t *ys = reinterpret_cast<uint16_t *>(y);
-    for (long long e = n_vec * 8 + threadIdx.x; e < n_elems; e += blockDim.x)
-      ys[e] = cvt_f32_to_16(f(cvt_16_to_f32(xs[e], din)), dout, rn);
+    for (long long e = n_acc * (8 * W) + threadIdx.x; e < n_elems; e += blockDim.x) {
+      float a = cvt_16_to_f32(xs[e], din), unused = 0.0f;
+      f(a, unused);
+      ys[e] = cvt_f32_to_16(a, dout, rn);
+    }
   }
 }
 

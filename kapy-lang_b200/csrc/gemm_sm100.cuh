@@ -9,9 +9,10 @@
 // test/Conversion/KapyToKgpu/matmul.mlir:46-128 (2-stage cp.async ring, ldmatrix,
 // mma.sync m16n8k8 chain, MatmulOpToLLVM.cpp:58-266) at whole-problem scope.
 //
-// Warp roles (192 threads): warp 0 = TMA producer (one lane), warp 1 = TMEM
-// allocator + MMA issuer (one lane), warps 2..5 = epilogue (warp w owns TMEM
-// lanes 32*(w%4) .. +31).
+// Warp roles: warp 0 = TMA producer (one lane), warp 1 = TMEM allocator + MMA
+// issuer (one lane), warps 2 .. 2+EPI-1 = epilogue (warp w may touch TMEM lanes
+// 32*(w%4) .. +31; with EPI = 8 two warps share a lane quarter and alternate
+// column chunks, for problems whose K loop is too short to hide the epilogue).
 //
 // CTAS == 2 pairs two CTAs of a cluster on one 256-row tile
 // (tcgen05.mma.cta_group::2): each CTA loads its own 128 rows of A and its own
@@ -26,7 +27,6 @@
 
 namespace kapyb {
 
-constexpr int kGemmThreads = 192;
 constexpr int kMaxOutputs = 8;  // own output + up to 7 peers for the push epilogue
 
 struct TmapArray {
@@ -46,10 +46,11 @@ struct GemmParams {
   int out_col_offset;    // column offset of this shard inside each output
   uint32_t idesc;
   uint32_t *status;
+  int debug;  // profiling aid: bit0 skip loads, bit1 skip MMAs, bit2 skip stores (results are garbage)
   EpilogueArgs ep;
 };
 
-template <int BN, int CTAS>
+template <int BN, int CTAS, int EPI = 4>
 struct GemmCfg {
   static constexpr int BM = 128;  // rows per CTA (TMEM lanes)
   static constexpr int BK = 64;   // 128 bytes of a 16-bit type: one swizzle span
@@ -59,7 +60,8 @@ struct GemmCfg {
   static constexpr int B_BYTES = BN_CTA * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int C_WARP_BYTES = 2 * 4096;  // two 32-row x 128-byte buffers
-  static constexpr int C_BYTES = 4 * C_WARP_BYTES;
+  static constexpr int C_BYTES = EPI * C_WARP_BYTES;
+  static constexpr int THREADS = 64 + 32 * EPI;  // producer warp, MMA warp, EPI epilogue warps
   static constexpr int CTRL_BYTES = 1024;
   static constexpr int SMEM_LIMIT = 232448;  // 227 KB opt-in maximum
   static constexpr int STAGES_RAW = (SMEM_LIMIT - 1024 - CTRL_BYTES - C_BYTES) / STAGE_BYTES;
@@ -69,6 +71,7 @@ struct GemmCfg {
   static_assert(BN % 64 == 0 && BN <= 256, "BN must be 64, 128 or 256");
   static_assert((TMEM_COLS & (TMEM_COLS - 1)) == 0 && TMEM_COLS <= 512, "TMEM columns");
   static_assert(STAGES >= 2, "pipeline too shallow");
+  static_assert(EPI == 4 || EPI == 8, "4 or 8 epilogue warps");
 };
 
 // Linear tile index -> (batch, m block, n block); m blocks are walked in groups
@@ -87,12 +90,12 @@ __device__ __forceinline__ void decode_tile(const GemmParams &p, int tile, int &
   nb = rr / gsize;
 }
 
-template <int BN, int CTAS>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+template <int BN, int CTAS, int EPI>
+__global__ void __launch_bounds__(64 + 32 * EPI, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
                     const __grid_constant__ CUtensorMap tmB,
                     const __grid_constant__ TmapArray tmC, const GemmParams p) {
-  using Cfg = GemmCfg<BN, CTAS>;
+  using Cfg = GemmCfg<BN, CTAS, EPI>;
   constexpr int STAGES = Cfg::STAGES;
 
   extern __shared__ uint8_t smem_raw[];
@@ -117,12 +120,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
-      ptx::mbar_init(ptx::smem_u32(&full_bar[s]), CTAS);  // one expect_tx arrival per CTA
+      ptx::mbar_init(ptx::smem_u32(&full_bar[s]), 1);     // the (leader's) expect_tx arrival
       ptx::mbar_init(ptx::smem_u32(&empty_bar[s]), 1);    // one tcgen05.commit
     }
     for (int a = 0; a < 2; ++a) {
       ptx::mbar_init(ptx::smem_u32(&tfull_bar[a]), 1);          // one tcgen05.commit
-      ptx::mbar_init(ptx::smem_u32(&tempty_bar[a]), 4 * CTAS);  // one arrival per epilogue warp
+      ptx::mbar_init(ptx::smem_u32(&tempty_bar[a]), EPI * CTAS);  // one arrival per epilogue warp
     }
     *abort_flag = 0u;
     ptx::fence_barrier_init();
@@ -163,7 +166,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
         const int k0 = kb * Cfg::BK;
         const uint32_t a_dst = ptx::smem_u32(sA + stage * Cfg::A_BYTES);
         const uint32_t b_dst = ptx::smem_u32(sB + stage * Cfg::B_BYTES);
-        if constexpr (CTAS == 1) {
+        if (p.debug & 1) {
+          if (rank == 0) ptx::mbar_arrive(ptx::smem_u32(&full_bar[stage]));
+        } else if constexpr (CTAS == 1) {
           const uint32_t fb = ptx::smem_u32(&full_bar[stage]);
           ptx::mbar_arrive_expect_tx(fb, Cfg::STAGE_BYTES);
           if (!p.a_mn_major) {
@@ -181,13 +186,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
               ptx::tma_load_3d(b_dst + j * 8192, &tmB, fb, nB0 + 64 * j, k0, b);
           }
         } else {
-          // Both CTAs of the pair report to the leader's barrier.
+          // Both CTAs' loads report their bytes to the leader's barrier; the
+          // leader alone posts the arrival, expecting the bytes of both.  (A
+          // remote arrive.expect_tx from the peer instead halves the throughput.)
           const uint32_t fb = ptx::mapa(ptx::smem_u32(&full_bar[stage]), 0);
-          asm volatile(
-              "mbarrier.arrive.expect_tx.release.cluster.shared::cluster.b64 _, [%0], %1;" ::"r"(
-                  fb),
-              "r"(static_cast<uint32_t>(Cfg::STAGE_BYTES))
-              : "memory");
+          if (rank == 0)
+            ptx::mbar_arrive_expect_tx(ptx::smem_u32(&full_bar[stage]), 2 * Cfg::STAGE_BYTES);
           if (!p.a_mn_major) {
             ptx::tma_load_3d_pair(a_dst, &tmA, fb, k0, m0, b);
           } else {
@@ -236,11 +240,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
         ptx::tc_fence_after();
         const uint32_t a_base = ptx::smem_u32(sA + stage * Cfg::A_BYTES);
         const uint32_t b_base = ptx::smem_u32(sB + stage * Cfg::B_BYTES);
+        if (!(p.debug & 2)) {
 #pragma unroll
-        for (int k = 0; k < Cfg::BK / 16; ++k) {
-          const uint64_t adesc = ptx::make_smem_desc_sw128(a_base + k * a_kadv, a_lbo, a_sbo);
-          const uint64_t bdesc = ptx::make_smem_desc_sw128(b_base + k * b_kadv, b_lbo, b_sbo);
-          ptx::umma_f16<CTAS>(d_tmem, adesc, bdesc, p.idesc, (kb | k) != 0 ? 1u : 0u);
+          for (int k = 0; k < Cfg::BK / 16; ++k) {
+            const uint64_t adesc = ptx::make_smem_desc_sw128(a_base + k * a_kadv, a_lbo, a_sbo);
+            const uint64_t bdesc = ptx::make_smem_desc_sw128(b_base + k * b_kadv, b_lbo, b_sbo);
+            ptx::umma_f16<CTAS>(d_tmem, adesc, bdesc, p.idesc, (kb | k) != 0 ? 1u : 0u);
+          }
         }
         // Free the stage in every CTA that filled it.
         ptx::umma_commit<CTAS>(ptx::smem_u32(&empty_bar[stage]));
@@ -260,12 +266,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
     }
   } else if (warp >= 2) {
     // ------------------------------------------------------------ epilogue
-    const int q = warp & 3;  // TMEM lane quarter this warp may touch
-    uint8_t *stg = sC + (warp - 2) * Cfg::C_WARP_BYTES;
+    const int e = warp - 2;          // epilogue warp index, 0 .. EPI-1
+    const int q = warp & 3;          // TMEM lane quarter this warp may touch
+    const int cpart = e >> 2;        // with 8 epilogue warps two warps share a quarter
+    constexpr int CSTEP = EPI / 4;   //   and take alternate column chunks
+    uint8_t *stg = sC + e * Cfg::C_WARP_BYTES;
     const bool out32 = p.out_dtype == KAPYB_F32;
     const int CW = out32 ? 32 : 64;  // output columns per 128-byte staging row
     const uint32_t tempty_leader = CTAS == 2 ? ptx::mapa(ptx::smem_u32(&tempty_bar[0]), 0)
                                              : ptx::smem_u32(&tempty_bar[0]);
+    const bool bias_col = p.ep.bias != nullptr && p.ep.bias_axis == 1;
+    // 16-bit bias vectors that start on a 16-byte boundary are read with uniform
+    // 128-bit loads; anything else goes through one load per lane and shuffles.
+    const bool bias_fast = bias_col && p.ep.bias_dtype != KAPYB_F32 &&
+                           (reinterpret_cast<uintptr_t>(p.ep.bias) & 15u) == 0;
     int acc = 0;
     uint32_t acc_phase = 0;
     int buf = 0;
@@ -279,34 +293,60 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       const int row = m0 + lane;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
                              static_cast<uint32_t>(acc * BN);
-      if (m0 < p.M) {
+      if (m0 < p.M && !(p.debug & 4)) {
         float bias_row = 0.0f;
         if (p.ep.bias != nullptr && p.ep.bias_axis == 0 && row < p.M)
           bias_row = load_as_f32(p.ep.bias, p.ep.bias_dtype, row);
         const int n_chunks = BN / CW;
-        for (int c = 0; c < n_chunks; ++c) {
+        for (int c = cpart; c < n_chunks; c += CSTEP) {
           const int nc = n0 + c * CW;
           if (nc >= p.N) break;
           uint8_t *sbuf = stg + buf * 4096;
+          // Both 32-column loads of the chunk are in flight before the one wait.
+          uint32_t v[2][32];
+          ptx::tmem_ld_32x32(t_row + static_cast<uint32_t>(c * CW), v[0]);
+          if (!out32) ptx::tmem_ld_32x32(t_row + static_cast<uint32_t>(c * CW + 32), v[1]);
           // The store issued two chunks ago read this buffer; let it finish.
           if (lane == 0) ptx::tma_store_wait_read<1>();
           __syncwarp();
-#pragma unroll 1
-          for (int h = 0; h < CW / 32; ++h) {
-            uint32_t v[32];
-            ptx::tmem_ld_32x32(t_row + static_cast<uint32_t>(c * CW + h * 32), v);
-            ptx::tmem_ld_wait();
+          ptx::tmem_ld_wait();
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            if (h == 1 && out32) break;
             const int col0 = nc + h * 32;
-            float bias_lane = 0.0f;
-            if (p.ep.bias != nullptr && p.ep.bias_axis == 1 && col0 + lane < p.N)
-              bias_lane = load_as_f32(p.ep.bias, p.ep.bias_dtype, col0 + lane);
             float f[32];
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              float x = __uint_as_float(v[i]) * p.ep.alpha;
-              const float bc = __shfl_sync(0xffffffffu, bias_lane, i);
-              x += (p.ep.bias_axis == 1) ? bc : bias_row;
-              f[i] = x;
+            for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(v[h][i]);
+            if (p.ep.alpha != 1.0f) {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) f[i] *= p.ep.alpha;
+            }
+            if (bias_col) {
+              if (bias_fast && col0 + 32 <= p.N) {
+                const uint4 *bp = reinterpret_cast<const uint4 *>(
+                    static_cast<const uint16_t *>(p.ep.bias) + col0);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const uint4 w = __ldg(bp + j);
+                  const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+                  for (int t = 0; t < 4; ++t) {
+                    f[8 * j + 2 * t] += cvt_16_to_f32(static_cast<uint16_t>(ws[t] & 0xffffu),
+                                                      p.ep.bias_dtype);
+                    f[8 * j + 2 * t + 1] += cvt_16_to_f32(static_cast<uint16_t>(ws[t] >> 16),
+                                                          p.ep.bias_dtype);
+                  }
+                }
+              } else {
+                float bias_lane = 0.0f;
+                if (col0 + lane < p.N)
+                  bias_lane = load_as_f32(p.ep.bias, p.ep.bias_dtype, col0 + lane);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) f[i] += __shfl_sync(0xffffffffu, bias_lane, i);
+              }
+            } else if (p.ep.bias != nullptr) {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) f[i] += bias_row;
             }
             if (p.ep.acc != nullptr && row < p.M) {
               const long long base = static_cast<long long>(b) * p.ep.acc_batch_stride +

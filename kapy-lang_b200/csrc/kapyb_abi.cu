@@ -42,6 +42,8 @@ struct kapyb_context {
   int64_t launches = 0;
   int forced_path = PATH_AUTO;
   int forced_bn = 0;
+  int debug = 0;
+  int forced_epi = 0;  // 0: by K; 4 or 8: that many epilogue warps (single-CTA kernels)
 };
 
 static thread_local std::string g_create_error;
@@ -131,9 +133,15 @@ extern "C" KAPYB_API kapyb_status kapyb_set_matmul_path(kapyb_handle h, const ch
   if (!h || !name) return fail(h, KAPYB_INVALID_ARG, "kapyb_set_matmul_path: NULL argument");
   std::string s(name);
   h->forced_bn = 0;
+  h->debug = 0;
+  h->forced_epi = 0;
   size_t colon = s.find(':');
   if (colon != std::string::npos) {
     h->forced_bn = atoi(s.c_str() + colon + 1);
+    size_t colon2 = s.find(":d", colon + 1);
+    if (colon2 != std::string::npos) h->debug = atoi(s.c_str() + colon2 + 2);
+    size_t colon3 = s.find(":e", colon + 1);
+    if (colon3 != std::string::npos) h->forced_epi = atoi(s.c_str() + colon3 + 2);
     s = s.substr(0, colon);
     if (h->forced_bn != 64 && h->forced_bn != 128 && h->forced_bn != 256)
       return fail(h, KAPYB_INVALID_ARG, "kapyb_set_matmul_path: tile width must be 64/128/256");
@@ -394,10 +402,10 @@ static kapyb_status launch_simt(kapyb_handle h, const MatmulProblem &p, cudaStre
   return KAPYB_OK;
 }
 
-template <int BN, int CTAS>
+template <int BN, int CTAS, int EPI>
 static kapyb_status launch_tcgen05(kapyb_handle h, const MatmulProblem &p, bool a_mn, bool b_mn,
                                    void *const *outs, int n_out, cudaStream_t stream) {
-  using Cfg = GemmCfg<BN, CTAS>;
+  using Cfg = GemmCfg<BN, CTAS, EPI>;
   CUtensorMap tmA, tmB;
   TmapArray tmC;
   kapyb_status st;
@@ -438,19 +446,19 @@ static kapyb_status launch_tcgen05(kapyb_handle h, const MatmulProblem &p, bool 
   gp.out_col_offset = 0;
   gp.idesc = ptx::make_idesc_f16(p.in_dtype == KAPYB_BF16, a_mn, b_mn, Cfg::TILE_M, BN);
   gp.status = h->status;
+  gp.debug = h->debug;
   gp.ep = p.ep;
 
-  auto kern = gemm_tcgen05_kernel<BN, CTAS>;
+  auto kern = gemm_tcgen05_kernel<BN, CTAS, EPI>;
   static bool attr_set[kMaxDevices] = {};
   if (!attr_set[h->device]) {
     CUDA_TRY(h, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      Cfg::SMEM_BYTES));
     attr_set[h->device] = true;
   }
-  int units = std::min(gp.num_tiles, h->sm_count / CTAS);
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(units * CTAS, 1, 1);
-  cfg.blockDim = dim3(kGemmThreads, 1, 1);
+  cfg.gridDim = dim3(h->sm_count / CTAS * CTAS, 1, 1);
+  cfg.blockDim = dim3(Cfg::THREADS, 1, 1);
   cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
@@ -460,6 +468,22 @@ static kapyb_status launch_tcgen05(kapyb_handle h, const MatmulProblem &p, bool 
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
+  // The tile loop is statically strided, so every CTA (pair) of the grid must be
+  // resident at once: a pair that only starts when another retires would run its
+  // whole share afterwards.  Pairs need two free SMs in one GPC, which can be
+  // fewer than sm_count / 2.
+  int resident = h->sm_count / CTAS;
+  if (CTAS == 2) {
+    static int max_clusters[kMaxDevices] = {};
+    if (max_clusters[h->device] == 0) {
+      int n = 0;
+      CUDA_TRY(h, cudaOccupancyMaxActiveClusters(&n, kern, &cfg));
+      max_clusters[h->device] = std::max(1, n);
+    }
+    resident = std::min(resident, max_clusters[h->device]);
+  }
+  const int units = std::min(gp.num_tiles, resident);
+  cfg.gridDim = dim3(units * CTAS, 1, 1);
   CUDA_TRY(h, cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmC, gp));
   h->launches++;
   h->last_kernel = CTAS == 2 ? "tcgen05_2cta" : "tcgen05_1cta";
@@ -586,8 +610,15 @@ static kapyb_status run_matmul(kapyb_handle h, MatmulProblem p, void *const *pee
   const int n_out = n_peers > 0 ? n_peers : 1;
 
   if (path == PATH_AUTO) {
+    // CTA pairs (256 x 256 tiles) halve the B traffic per SM and win once there
+    // is at least about half a wave of such tiles and a K loop long enough to
+    // amortise the pair's start-up; everything else runs on single CTAs.
+    const long long pair_tiles =
+        static_cast<long long>((p.M + 255) / 256) * ((p.N + 255) / 256) * p.batch;
     if (p.M <= kSkinnyMaxM && n_peers == 0 && p.batch == 1 && skinny_supported(p.M, p.N, p.K))
       path = PATH_SKINNY;
+    else if (p.M >= 256 && p.N >= 256 && p.K >= 512 && pair_tiles * 4 >= h->sm_count && h->forced_bn == 0)
+      path = PATH_2CTA;
     else
       path = PATH_1CTA;
   }
@@ -610,14 +641,23 @@ static kapyb_status run_matmul(kapyb_handle h, MatmulProblem p, void *const *pee
     if (p.N <= 64) bn = 64;
     else if (p.N <= 128 && bn > 128) bn = 128;
   }
+  // Short K loops cannot hide the epilogue behind the next tile's main loop:
+  // give those problems eight epilogue warps instead of four.
+  const bool epi8 = (p.K + 63) / 64 <= 8 || h->forced_epi == 8;
   if (path == PATH_2CTA) {
+    if (h->forced_bn == 0) bn = 256;
     if (bn == 64) bn = 128;
-    if (bn == 128) return launch_tcgen05<128, 2>(h, p, a_mn, b_mn, outs, n_out, stream);
-    return launch_tcgen05<256, 2>(h, p, a_mn, b_mn, outs, n_out, stream);
+    if (bn == 128) return launch_tcgen05<128, 2, 4>(h, p, a_mn, b_mn, outs, n_out, stream);
+    return launch_tcgen05<256, 2, 4>(h, p, a_mn, b_mn, outs, n_out, stream);
   }
-  if (bn == 64) return launch_tcgen05<64, 1>(h, p, a_mn, b_mn, outs, n_out, stream);
-  if (bn == 128) return launch_tcgen05<128, 1>(h, p, a_mn, b_mn, outs, n_out, stream);
-  return launch_tcgen05<256, 1>(h, p, a_mn, b_mn, outs, n_out, stream);
+  if (epi8 && h->forced_epi != 4) {
+    if (bn == 64) return launch_tcgen05<64, 1, 8>(h, p, a_mn, b_mn, outs, n_out, stream);
+    if (bn == 128) return launch_tcgen05<128, 1, 8>(h, p, a_mn, b_mn, outs, n_out, stream);
+    return launch_tcgen05<256, 1, 8>(h, p, a_mn, b_mn, outs, n_out, stream);
+  }
+  if (bn == 64) return launch_tcgen05<64, 1, 4>(h, p, a_mn, b_mn, outs, n_out, stream);
+  if (bn == 128) return launch_tcgen05<128, 1, 4>(h, p, a_mn, b_mn, outs, n_out, stream);
+  return launch_tcgen05<256, 1, 4>(h, p, a_mn, b_mn, outs, n_out, stream);
 }
 
 static MatmulProblem make_problem(const kapyb_tensor2d *lhs, const kapyb_tensor2d *rhs,
@@ -990,7 +1030,7 @@ static bool contiguous_same(const kapyb_tensor2d &t, const kapyb_tensor2d &out) 
 
 static int stream_grid(kapyb_handle h, long long n_vec, int per_thread) {
   long long blocks = (n_vec + 256ll * per_thread - 1) / (256ll * per_thread);
-  const long long cap = static_cast<long long>(h->sm_count) * 16;
+  const long long cap = static_cast<long long>(h->sm_count) * 8;  // 8 x 256 threads fill an SM
   return static_cast<int>(std::max(1ll, std::min(blocks, cap)));
 }
 
@@ -1017,12 +1057,18 @@ extern "C" KAPYB_API kapyb_status kapyb_elementwise(kapyb_handle h, const kapyb_
     if (match_affine_gelu(nodes, root, &f, &li, &din, &rn) && out->dtype != KAPYB_F32 &&
         nodes[root].dtype == out->dtype && contiguous_same(inputs[li], *out) &&
         aligned16(elem_ptr(&inputs[li])) && aligned16(elem_ptr(out))) {
-      const long long n_vec = total / 8;
-      const int grid = stream_grid(h, n_vec, kEltUnroll);
-      elt_unary16_kernel<AffineGelu><<<grid, 256, 0, stream>>>(
-          static_cast<const uint4 *>(elem_ptr(&inputs[li])),
-          static_cast<uint4 *>(const_cast<void *>(elem_ptr(out))), n_vec, total, f, din,
-          out->dtype, rn);
+      const uint4 *px = static_cast<const uint4 *>(elem_ptr(&inputs[li]));
+      uint4 *py = static_cast<uint4 *>(const_cast<void *>(elem_ptr(out)));
+      const bool wide = ((reinterpret_cast<uintptr_t>(px) | reinterpret_cast<uintptr_t>(py)) & 31u) == 0;
+      if (wide) {
+        const long long n_acc = total / 16;
+        elt_unary16_kernel<AffineGelu, 2><<<stream_grid(h, n_acc, kEltUnroll), 256, 0, stream>>>(
+            px, py, n_acc, total, f, din, out->dtype, rn);
+      } else {
+        const long long n_acc = total / 8;
+        elt_unary16_kernel<AffineGelu, 1><<<stream_grid(h, n_acc, kEltUnroll), 256, 0, stream>>>(
+            px, py, n_acc, total, f, din, out->dtype, rn);
+      }
       CUDA_TRY(h, cudaGetLastError());
       h->launches++;
       h->last_kernel = f.gelu ? "elt_affine_gelu" : "elt_affine";
