@@ -90,6 +90,38 @@ __device__ __forceinline__ uint32_t cvt_pack2(float lo, float hi, int dtype, int
   return r;
 }
 
+// Compile-time variants for hot loops (a run-time dtype inside an unrolled loop
+// turns into four predicated conversions per value).
+template <int DT, int RN>
+__device__ __forceinline__ uint32_t cvt_pack2_t(float lo, float hi) {
+  uint32_t r;
+  if constexpr (DT == KAPYB_BF16) {
+    if constexpr (RN)
+      asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    else
+      asm("cvt.rz.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  } else {
+    if constexpr (RN)
+      asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    else
+      asm("cvt.rz.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  }
+  return r;
+}
+
+// Both halves of a packed 16-bit pair, widened exactly.
+template <int DT>
+__device__ __forceinline__ void unpack2_16(uint32_t w, float &lo, float &hi) {
+  if constexpr (DT == KAPYB_BF16) {
+    lo = __uint_as_float(w << 16);
+    hi = __uint_as_float(w & 0xffff0000u);
+  } else {
+    const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&w));
+    lo = f.x;
+    hi = f.y;
+  }
+}
+
 __device__ __forceinline__ float cvt_16_to_f32(uint16_t h, int dtype) {
   if (dtype == KAPYB_BF16) return __uint_as_float(static_cast<uint32_t>(h) << 16);
   return __half2float(__ushort_as_half(h));

@@ -196,6 +196,18 @@ struct AffineGelu {
   int gelu;        // 0: affine only
   float c0, c1;    // k = c0 * fma(c1*u*u, u, u)
   float m2, one;   // y = u / (one + exp(m2 * k))
+  int ftz_ok;      // |one| is large enough that a subnormal exp() cannot change one + exp()
+  __device__ __forceinline__ float ex2(float z) const {
+    // ex2.approx.f32 handles subnormals with extra scaling instructions.  When the
+    // sum that follows absorbs any subnormal (one + e == one), the flush-to-zero
+    // form gives the same bits for one instruction.
+    if (ftz_ok) {
+      float r;
+      asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(z));
+      return r;
+    }
+    return ex2_approx(z);
+  }
   __device__ __forceinline__ void operator()(float &x0, float &x1) const {
     const uint64_t u = fma2(pack2(x0, x1), pack2(s, s), pack2(b, b));
     if (!gelu) {
@@ -208,7 +220,7 @@ struct AffineGelu {
                             pack2(1.4426950408889634f, 1.4426950408889634f));
     float z0, z1, u0, u1, d0, d1;
     unpack2(z, z0, z1);
-    const uint64_t d = add2(pack2(one, one), pack2(ex2_approx(z0), ex2_approx(z1)));
+    const uint64_t d = add2(pack2(one, one), pack2(ex2(z0), ex2(z1)));
     unpack2(u, u0, u1);
     unpack2(d, d0, d1);
     x0 = div_full(u0, d0);
@@ -229,18 +241,12 @@ __device__ __forceinline__ void st_stream(uint4 *p, uint4 v) {
                : "memory");
 }
 
-template <class F>
-__device__ __forceinline__ uint32_t apply2_16(uint32_t w, const F &f, int din, int dout, int rn) {
+template <class F, int DT, int RN>
+__device__ __forceinline__ uint32_t apply2_16(uint32_t w, const F &f) {
   float lo, hi;
-  if (din == KAPYB_BF16) {
-    lo = __uint_as_float(w << 16);
-    hi = __uint_as_float(w & 0xffff0000u);
-  } else {
-    lo = cvt_16_to_f32(static_cast<uint16_t>(w & 0xffffu), din);
-    hi = cvt_16_to_f32(static_cast<uint16_t>(w >> 16), din);
-  }
+  unpack2_16<DT>(w, lo, hi);
   f(lo, hi);
-  return cvt_pack2(lo, hi, dout, rn);
+  return cvt_pack2_t<DT, RN>(lo, hi);
 }
 
 constexpr int kEltUnroll = 4;
@@ -275,22 +281,23 @@ __device__ __forceinline__ void st_stream_vec(uint4 *p, const StreamVec<W> &v) {
   }
 }
 
-// 16-bit in, 16-bit out, contiguous; both pointers aligned to W x 16 bytes.
-// n_acc accesses of W*8 elements plus a scalar tail handled by the last block.
-template <class F, int W>
+// One 16-bit element type in and out (DT), downcast rounding RN, contiguous;
+// both pointers aligned to W x 16 bytes.  n_acc accesses of W*8 elements plus a
+// scalar tail handled by the last block.
+template <class F, int W, int DT, int RN>
 __global__ void __launch_bounds__(256)
 elt_unary16_kernel(const uint4 *__restrict__ x, uint4 *__restrict__ y, long long n_acc,
-                   long long n_elems, F f, int din, int dout, int rn) {
+                   long long n_elems, F f) {
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
   long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   auto apply = [&](const StreamVec<W> &v) {
     StreamVec<W> o;
 #pragma unroll
     for (int w = 0; w < W; ++w) {
-      o.q[w].x = apply2_16(v.q[w].x, f, din, dout, rn);
-      o.q[w].y = apply2_16(v.q[w].y, f, din, dout, rn);
-      o.q[w].z = apply2_16(v.q[w].z, f, din, dout, rn);
-      o.q[w].w = apply2_16(v.q[w].w, f, din, dout, rn);
+      o.q[w].x = apply2_16<F, DT, RN>(v.q[w].x, f);
+      o.q[w].y = apply2_16<F, DT, RN>(v.q[w].y, f);
+      o.q[w].z = apply2_16<F, DT, RN>(v.q[w].z, f);
+      o.q[w].w = apply2_16<F, DT, RN>(v.q[w].w, f);
     }
     return o;
   };
@@ -306,9 +313,9 @@ elt_unary16_kernel(const uint4 *__restrict__ x, uint4 *__restrict__ y, long long
     const uint16_t *xs = reinterpret_cast<const uint16_t *>(x);
     uint16_t *ys = reinterpret_cast<uint16_t *>(y);
     for (long long e = n_acc * (8 * W) + threadIdx.x; e < n_elems; e += blockDim.x) {
-      float a = cvt_16_to_f32(xs[e], din), unused = 0.0f;
+      float a = cvt_16_to_f32(xs[e], DT), unused = 0.0f;
       f(a, unused);
-      ys[e] = cvt_f32_to_16(a, dout, rn);
+      ys[e] = cvt_f32_to_16(a, DT, RN);
     }
   }
 }

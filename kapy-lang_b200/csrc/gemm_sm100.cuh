@@ -90,6 +90,48 @@ __device__ __forceinline__ void decode_tile(const GemmParams &p, int tile, int &
   nb = rr / gsize;
 }
 
+// 32 finished columns of one row -> the row's slot in the swizzled staging tile.
+__device__ __forceinline__ void stage_half_f32(uint8_t *srow, const float (&f)[32], int lane) {
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const uint4 w = make_uint4(__float_as_uint(f[4 * j]), __float_as_uint(f[4 * j + 1]),
+                               __float_as_uint(f[4 * j + 2]), __float_as_uint(f[4 * j + 3]));
+    *reinterpret_cast<uint4 *>(srow + ((j ^ (lane & 7)) << 4)) = w;
+  }
+}
+
+template <int DT, int RN>
+__device__ __forceinline__ void stage_half_16(uint8_t *srow, const float (&f)[32], int lane,
+                                              int h) {
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    uint4 w;
+    w.x = cvt_pack2_t<DT, RN>(f[8 * j], f[8 * j + 1]);
+    w.y = cvt_pack2_t<DT, RN>(f[8 * j + 2], f[8 * j + 3]);
+    w.z = cvt_pack2_t<DT, RN>(f[8 * j + 4], f[8 * j + 5]);
+    w.w = cvt_pack2_t<DT, RN>(f[8 * j + 6], f[8 * j + 7]);
+    const int jj = h * 4 + j;
+    *reinterpret_cast<uint4 *>(srow + ((jj ^ (lane & 7)) << 4)) = w;
+  }
+}
+
+// f[0..32) += 32 consecutive 16-bit bias values read with uniform 128-bit loads.
+template <int DT>
+__device__ __forceinline__ void add_bias32(float (&f)[32], const uint4 *bp) {
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const uint4 w = __ldg(bp + j);
+    const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      float lo, hi;
+      unpack2_16<DT>(ws[t], lo, hi);
+      f[8 * j + 2 * t] += lo;
+      f[8 * j + 2 * t + 1] += hi;
+    }
+  }
+}
+
 template <int BN, int CTAS, int EPI>
 __global__ void __launch_bounds__(64 + 32 * EPI, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
@@ -273,6 +315,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
     uint8_t *stg = sC + e * Cfg::C_WARP_BYTES;
     const bool out32 = p.out_dtype == KAPYB_F32;
     const int CW = out32 ? 32 : 64;  // output columns per 128-byte staging row
+    // 0: f32; 1/2: bf16 rn/rz; 3/4: f16 rn/rz -- picked once, outside the loops
+    const int out_kind = out32 ? 0
+                         : (p.out_dtype == KAPYB_BF16 ? (p.ep.rounding ? 1 : 2)
+                                                      : (p.ep.rounding ? 3 : 4));
     const uint32_t tempty_leader = CTAS == 2 ? ptx::mapa(ptx::smem_u32(&tempty_bar[0]), 0)
                                              : ptx::smem_u32(&tempty_bar[0]);
     const bool bias_col = p.ep.bias != nullptr && p.ep.bias_axis == 1;
@@ -325,18 +371,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
               if (bias_fast && col0 + 32 <= p.N) {
                 const uint4 *bp = reinterpret_cast<const uint4 *>(
                     static_cast<const uint16_t *>(p.ep.bias) + col0);
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                  const uint4 w = __ldg(bp + j);
-                  const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
-#pragma unroll
-                  for (int t = 0; t < 4; ++t) {
-                    f[8 * j + 2 * t] += cvt_16_to_f32(static_cast<uint16_t>(ws[t] & 0xffffu),
-                                                      p.ep.bias_dtype);
-                    f[8 * j + 2 * t + 1] += cvt_16_to_f32(static_cast<uint16_t>(ws[t] >> 16),
-                                                          p.ep.bias_dtype);
-                  }
-                }
+                if (p.ep.bias_dtype == KAPYB_BF16)
+                  add_bias32<KAPYB_BF16>(f, bp);
+                else
+                  add_bias32<KAPYB_F16>(f, bp);
               } else {
                 float bias_lane = 0.0f;
                 if (col0 + lane < p.N)
@@ -364,24 +402,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
             // Row `lane` of the staging tile, 128-byte swizzle: 16-byte chunk j
             // of row r lives at chunk position j ^ (r & 7).
             uint8_t *srow = sbuf + lane * 128;
-            if (out32) {
-#pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                uint4 w = make_uint4(__float_as_uint(f[4 * j]), __float_as_uint(f[4 * j + 1]),
-                                     __float_as_uint(f[4 * j + 2]), __float_as_uint(f[4 * j + 3]));
-                *reinterpret_cast<uint4 *>(srow + ((j ^ (lane & 7)) << 4)) = w;
-              }
-            } else {
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                uint4 w;
-                w.x = cvt_pack2(f[8 * j], f[8 * j + 1], p.out_dtype, p.ep.rounding);
-                w.y = cvt_pack2(f[8 * j + 2], f[8 * j + 3], p.out_dtype, p.ep.rounding);
-                w.z = cvt_pack2(f[8 * j + 4], f[8 * j + 5], p.out_dtype, p.ep.rounding);
-                w.w = cvt_pack2(f[8 * j + 6], f[8 * j + 7], p.out_dtype, p.ep.rounding);
-                const int jj = h * 4 + j;
-                *reinterpret_cast<uint4 *>(srow + ((jj ^ (lane & 7)) << 4)) = w;
-              }
+            switch (out_kind) {
+            case 0: stage_half_f32(srow, f, lane); break;
+            case 1: stage_half_16<KAPYB_BF16, 1>(srow, f, lane, h); break;
+            case 2: stage_half_16<KAPYB_BF16, 0>(srow, f, lane, h); break;
+            case 3: stage_half_16<KAPYB_F16, 1>(srow, f, lane, h); break;
+            default: stage_half_16<KAPYB_F16, 0>(srow, f, lane, h); break;
             }
           }
           ptx::fence_proxy_async_smem();

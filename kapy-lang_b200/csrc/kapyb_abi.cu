@@ -1028,9 +1028,11 @@ static bool contiguous_same(const kapyb_tensor2d &t, const kapyb_tensor2d &out) 
   return rm && orm;
 }
 
-static int stream_grid(kapyb_handle h, long long n_vec, int per_thread) {
+// Grid for a grid-stride streaming kernel: enough blocks for the work, at most
+// one resident wave (`blocks_per_sm` x 256 threads per SM).
+static int stream_grid(kapyb_handle h, long long n_vec, int per_thread, int blocks_per_sm = 8) {
   long long blocks = (n_vec + 256ll * per_thread - 1) / (256ll * per_thread);
-  const long long cap = static_cast<long long>(h->sm_count) * 8;  // 8 x 256 threads fill an SM
+  const long long cap = static_cast<long long>(h->sm_count) * blocks_per_sm;
   return static_cast<int>(std::max(1ll, std::min(blocks, cap)));
 }
 
@@ -1055,20 +1057,25 @@ extern "C" KAPYB_API kapyb_status kapyb_elementwise(kapyb_handle h, const kapyb_
     AffineGelu f;
     int li = -1, din = 0, rn = 1;
     if (match_affine_gelu(nodes, root, &f, &li, &din, &rn) && out->dtype != KAPYB_F32 &&
-        nodes[root].dtype == out->dtype && contiguous_same(inputs[li], *out) &&
+        nodes[root].dtype == out->dtype && din == out->dtype && (rn == 0 || rn == 1) &&
+        contiguous_same(inputs[li], *out) &&
         aligned16(elem_ptr(&inputs[li])) && aligned16(elem_ptr(out))) {
       const uint4 *px = static_cast<const uint4 *>(elem_ptr(&inputs[li]));
       uint4 *py = static_cast<uint4 *>(const_cast<void *>(elem_ptr(out)));
       const bool wide = ((reinterpret_cast<uintptr_t>(px) | reinterpret_cast<uintptr_t>(py)) & 31u) == 0;
-      if (wide) {
-        const long long n_acc = total / 16;
-        elt_unary16_kernel<AffineGelu, 2><<<stream_grid(h, n_acc, kEltUnroll), 256, 0, stream>>>(
-            px, py, n_acc, total, f, din, out->dtype, rn);
+      f.ftz_ok = (f.one >= 1e-30f || f.one <= -1e-30f) ? 1 : 0;
+      const long long n_acc = total / (wide ? 16 : 8);
+      const int grid = stream_grid(h, n_acc, kEltUnroll, wide ? 4 : 7);  // 60 / 34 registers
+#define KAPYB_LAUNCH_UNARY(W, DT, RN) \
+  elt_unary16_kernel<AffineGelu, W, DT, RN><<<grid, 256, 0, stream>>>(px, py, n_acc, total, f)
+      if (din == KAPYB_BF16) {
+        if (wide) { if (rn) KAPYB_LAUNCH_UNARY(2, KAPYB_BF16, 1); else KAPYB_LAUNCH_UNARY(2, KAPYB_BF16, 0); }
+        else      { if (rn) KAPYB_LAUNCH_UNARY(1, KAPYB_BF16, 1); else KAPYB_LAUNCH_UNARY(1, KAPYB_BF16, 0); }
       } else {
-        const long long n_acc = total / 8;
-        elt_unary16_kernel<AffineGelu, 1><<<stream_grid(h, n_acc, kEltUnroll), 256, 0, stream>>>(
-            px, py, n_acc, total, f, din, out->dtype, rn);
+        if (wide) { if (rn) KAPYB_LAUNCH_UNARY(2, KAPYB_F16, 1); else KAPYB_LAUNCH_UNARY(2, KAPYB_F16, 0); }
+        else      { if (rn) KAPYB_LAUNCH_UNARY(1, KAPYB_F16, 1); else KAPYB_LAUNCH_UNARY(1, KAPYB_F16, 0); }
       }
+#undef KAPYB_LAUNCH_UNARY
       CUDA_TRY(h, cudaGetLastError());
       h->launches++;
       h->last_kernel = f.gelu ? "elt_affine_gelu" : "elt_affine";
@@ -1137,16 +1144,26 @@ extern "C" KAPYB_API kapyb_status kapyb_elementwise(kapyb_handle h, const kapyb_
 
 // ------------------------------------------------------------------ reduce
 
+template <int COMB, int DT>
+static void launch_reduce_rows(const ReduceParams &p, bool vec, int grid, cudaStream_t stream) {
+  if (vec)
+    reduce_rows_kernel<COMB, true, DT><<<grid, 256, 0, stream>>>(p);
+  else
+    reduce_rows_kernel<COMB, false, DT><<<grid, 256, 0, stream>>>(p);
+}
+
 template <int COMB>
 static void launch_reduce(const ReduceParams &p, bool unit_inner, bool vec, int sm_count,
                           cudaStream_t stream) {
   if (unit_inner) {
     const long long blocks = (static_cast<long long>(p.rows) + 7) / 8;
     const int grid = static_cast<int>(std::max(1ll, std::min(blocks, static_cast<long long>(sm_count) * 8)));
-    if (vec)
-      reduce_rows_kernel<COMB, true><<<grid, 256, 0, stream>>>(p);
+    if (p.src_dtype == KAPYB_F32)
+      launch_reduce_rows<COMB, KAPYB_F32>(p, vec, grid, stream);
+    else if (p.src_dtype == KAPYB_BF16)
+      launch_reduce_rows<COMB, KAPYB_BF16>(p, vec, grid, stream);
     else
-      reduce_rows_kernel<COMB, false><<<grid, 256, 0, stream>>>(p);
+      launch_reduce_rows<COMB, KAPYB_F16>(p, vec, grid, stream);
   } else {
     const long long blocks = (static_cast<long long>(p.rows) + 31) / 32;
     const int grid = static_cast<int>(std::max(1ll, std::min(blocks, static_cast<long long>(sm_count) * 8)));
@@ -1189,7 +1206,8 @@ extern "C" KAPYB_API kapyb_status kapyb_reduce(kapyb_handle h, const kapyb_tenso
   p.combiner = combiner;
   const bool unit_inner = p.src_col_stride == 1 || length == 1;
   const int esz = dtype_size(src->dtype);
-  const bool vec = unit_inner && aligned16(p.src) && (p.src_row_stride * esz) % 16 == 0;
+  const bool vec = unit_inner && (reinterpret_cast<uintptr_t>(p.src) & 31u) == 0 &&
+                   (p.src_row_stride * esz) % 32 == 0;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   switch (combiner) {
   case KAPYB_RED_ADD: launch_reduce<KAPYB_RED_ADD>(p, unit_inner, vec, h->sm_count, stream); break;

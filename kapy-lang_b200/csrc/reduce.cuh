@@ -41,77 +41,71 @@ __device__ __forceinline__ float warp_reduce(float v) {
   return v;
 }
 
-__device__ __forceinline__ uint4 ld_nc_v4(const void *p) {
-  uint4 v;
-  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+struct Vec32B {
+  uint32_t w[8];
+};
+
+// 256-bit streaming load (sm_100): 32 bytes per lane, 1 KB per warp instruction.
+__device__ __forceinline__ Vec32B ld_nc_v8(const void *p) {
+  Vec32B v;
+  asm volatile("ld.global.nc.L1::no_allocate.v8.u32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=r"(v.w[0]), "=r"(v.w[1]), "=r"(v.w[2]), "=r"(v.w[3]), "=r"(v.w[4]),
+                 "=r"(v.w[5]), "=r"(v.w[6]), "=r"(v.w[7])
                : "l"(p));
   return v;
 }
 
-template <int COMB>
-__device__ __forceinline__ float fold_word16(float acc, uint32_t w, int dt) {
-  acc = combine<COMB>(acc, cvt_16_to_f32(static_cast<uint16_t>(w & 0xffffu), dt));
-  return combine<COMB>(acc, cvt_16_to_f32(static_cast<uint16_t>(w >> 16), dt));
+template <int COMB, int DT>
+__device__ __forceinline__ float fold_vec(float acc, const Vec32B &v) {
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    if constexpr (DT == KAPYB_F32) {
+      acc = combine<COMB>(acc, __uint_as_float(v.w[k]));
+    } else {
+      float lo, hi;
+      unpack2_16<DT>(v.w[k], lo, hi);
+      acc = combine<COMB>(combine<COMB>(acc, lo), hi);
+    }
+  }
+  return acc;
 }
 
-// One warp per row; rows are contiguous along the reduced axis and every row
-// starts on a 16-byte boundary (VEC) or anything else (!VEC).
-template <int COMB, bool VEC>
+constexpr int kReduceUnroll = 8;
+
+// One warp per row; the reduced axis is contiguous.  VEC: every row starts on a
+// 32-byte boundary, so the row is read with 256-bit loads, eight in flight per
+// lane (8 KB per warp: one whole row of 4096 16-bit values).  !VEC: scalar loads
+// with any strides.
+template <int COMB, bool VEC, int DT>
 __global__ void __launch_bounds__(256) reduce_rows_kernel(const ReduceParams p) {
   const int lane = threadIdx.x & 31;
   const int warps_per_block = blockDim.x >> 5;
-  const long long warp_global = static_cast<long long>(blockIdx.x) * warps_per_block + (threadIdx.x >> 5);
+  const long long warp_global =
+      static_cast<long long>(blockIdx.x) * warps_per_block + (threadIdx.x >> 5);
   const long long warp_step = static_cast<long long>(gridDim.x) * warps_per_block;
-  const int esz = dtype_size(p.src_dtype);
+  constexpr int esz = DT == KAPYB_F32 ? 4 : 2;
   for (long long row = warp_global; row < p.rows; row += warp_step) {
     const char *base = static_cast<const char *>(p.src) + row * p.src_row_stride * esz;
     float acc[4];
 #pragma unroll
     for (int u = 0; u < 4; ++u) acc[u] = identity<COMB>();
-    if (VEC) {
-      const int per = 16 / esz;
+    if constexpr (VEC) {
+      constexpr int per = 32 / esz;
       const int n_vec = p.cols / per;
-      const uint4 *v = reinterpret_cast<const uint4 *>(base);
       int i = lane;
-      for (; i + 96 < n_vec; i += 128) {
-        uint4 w[4];
+      for (; i + 32 * (kReduceUnroll - 1) < n_vec; i += 32 * kReduceUnroll) {
+        Vec32B v[kReduceUnroll];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) w[u] = ld_nc_v4(v + i + 32 * u);
+        for (int u = 0; u < kReduceUnroll; ++u) v[u] = ld_nc_v8(base + (i + 32 * u) * 32ll);
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          if (p.src_dtype == KAPYB_F32) {
-            acc[u] = combine<COMB>(acc[u], __uint_as_float(w[u].x));
-            acc[u] = combine<COMB>(acc[u], __uint_as_float(w[u].y));
-            acc[u] = combine<COMB>(acc[u], __uint_as_float(w[u].z));
-            acc[u] = combine<COMB>(acc[u], __uint_as_float(w[u].w));
-          } else {
-            acc[u] = fold_word16<COMB>(acc[u], w[u].x, p.src_dtype);
-            acc[u] = fold_word16<COMB>(acc[u], w[u].y, p.src_dtype);
-            acc[u] = fold_word16<COMB>(acc[u], w[u].z, p.src_dtype);
-            acc[u] = fold_word16<COMB>(acc[u], w[u].w, p.src_dtype);
-          }
-        }
+        for (int u = 0; u < kReduceUnroll; ++u) acc[u & 3] = fold_vec<COMB, DT>(acc[u & 3], v[u]);
       }
-      for (; i < n_vec; i += 32) {
-        const uint4 w = ld_nc_v4(v + i);
-        if (p.src_dtype == KAPYB_F32) {
-          acc[0] = combine<COMB>(acc[0], __uint_as_float(w.x));
-          acc[0] = combine<COMB>(acc[0], __uint_as_float(w.y));
-          acc[0] = combine<COMB>(acc[0], __uint_as_float(w.z));
-          acc[0] = combine<COMB>(acc[0], __uint_as_float(w.w));
-        } else {
-          acc[0] = fold_word16<COMB>(acc[0], w.x, p.src_dtype);
-          acc[0] = fold_word16<COMB>(acc[0], w.y, p.src_dtype);
-          acc[0] = fold_word16<COMB>(acc[0], w.z, p.src_dtype);
-          acc[0] = fold_word16<COMB>(acc[0], w.w, p.src_dtype);
-        }
-      }
+      for (; i < n_vec; i += 32) acc[0] = fold_vec<COMB, DT>(acc[0], ld_nc_v8(base + i * 32ll));
       for (int e = n_vec * per + lane; e < p.cols; e += 32)
-        acc[1] = combine<COMB>(acc[1], load_as_f32(base, p.src_dtype, e));
+        acc[1] = combine<COMB>(acc[1], load_as_f32(base, DT, e));
     } else {
       for (int e = lane; e < p.cols; e += 32)
-        acc[0] = combine<COMB>(acc[0], load_as_f32(base, p.src_dtype, e * p.src_col_stride));
+        acc[0] = combine<COMB>(acc[0], load_as_f32(base, DT, e * p.src_col_stride));
     }
     float r = combine<COMB>(combine<COMB>(acc[0], acc[1]), combine<COMB>(acc[2], acc[3]));
     r = warp_reduce<COMB>(r);
