@@ -1,0 +1,138 @@
+"""The textual kapy IR reader and the lifting of parsed kernels.
+
+The fixtures under tests/golden/kernels/ are kernels written for this test in
+the reference's assembly syntax.  When the reference checkout is present (it is
+not on the GPU box) its own three test inputs are parsed and lifted too."""
+import glob
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from fake_handle import FakeHandle
+from util import bits, normal
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+KERNELS = os.path.join(HERE, "golden", "kernels")
+REF = "/root/reference/test/Conversion/KapyToKgpu"
+
+
+def load(pkg, name):
+    mod = pkg.ir.parse_mlir_module(os.path.join(KERNELS, name), pkg.ir.MLIRContext())
+    return mod, next(iter(mod.functions.values()))
+
+
+def test_parse_fixtures(pkg):
+    for f in sorted(glob.glob(os.path.join(KERNELS, "*.mlir"))):
+        mod = pkg.mlir_text.parse_file(f)
+        assert len(mod.functions) == 1 and mod.get_int_attr("kapy.num_warps") >= 1
+    with pytest.raises(RuntimeError, match="parse mlir module file failed"):
+        pkg.ir.parse_mlir_module(os.path.join(KERNELS, "missing.mlir"), None)
+    with pytest.raises(SyntaxError, match="outside the recognised subset"):
+        pkg.mlir_text.parse_text("module {\n kapy.func public @f() {\n  gpu.barrier\n }\n}\n")
+
+
+def test_lift_scale_shift(pkg):
+    mod, fn = load(pkg, "scale_shift_bf16.mlir")
+    n = 4096
+    x, y = torch.zeros(n, dtype=torch.bfloat16), torch.zeros(n, dtype=torch.bfloat16)
+    h = FakeHandle()
+    pkg.executor.launch(fn, (4, 1, 1), [x, y, n], h, module=mod)
+    kind, insts, tin, tout = h.log[0]
+    A = pkg.abi
+    assert kind == "elementwise" and (tout.size0, tout.size1) == (1, 4096)
+    assert [t[0] for t in insts] == [A.OP_LOAD, A.OP_CVT, A.OP_CONST, A.OP_CONST, A.OP_FMA,
+                                     A.OP_CVT, A.OP_STORE]
+
+
+def test_lift_row_max(pkg):
+    mod, fn = load(pkg, "row_max_f32.mlir")
+    m = 64
+    src, dst = torch.zeros((m, 128)), torch.zeros((m, 1))
+    h = FakeHandle()
+    pkg.executor.launch(fn, (m // 8, 1, 1), [src, dst, m], h, module=mod)
+    kind, tsrc, tdst, axis, comb = h.log[0]
+    assert kind == "reduce" and axis == 1 and comb == pkg.abi.RED_MAX
+    assert (tsrc.size0, tsrc.size1, tsrc.stride0) == (64, 128, 128)
+    assert (tdst.size0, tdst.size1) == (64, 1)
+
+
+def test_lift_gemm_ring(pkg):
+    mod, fn = load(pkg, "gemm_ring_bf16.mlir")
+    M, K, N = 128, 64, 96
+    a, b, c = (torch.zeros(s, dtype=torch.bfloat16) for s in ((M, K), (K, N), (M, N)))
+    h = FakeHandle()
+    pkg.executor.launch(fn, (M // 32, N // 32, 1), [a, b, c, M, K, N], h, module=mod)
+    kind, tl, tr, to, ep, way = h.log[0]
+    assert kind == "matmul" and way == int(pkg.ir.MatmulImplWay.MMA_M16N8K16_F16)
+    assert (tl.size0, tl.size1, tl.stride0, tl.ptr) == (M, K, K, a.data_ptr())
+    assert (tr.size0, tr.size1, tr.stride0, tr.ptr) == (K, N, N, b.data_ptr())
+    assert (to.size0, to.size1, to.ptr) == (M, N, c.data_ptr())
+    assert ep.alpha == 1.0 and ep.rounding == pkg.abi.RN and not ep.bias
+
+
+@pytest.mark.skipif(not os.path.isdir(REF), reason="reference checkout not present")
+def test_reference_inputs_parse_and_lift(pkg):
+    """elementwise_add.mlir, reduce_sum.mlir and matmul.mlir run unchanged: each
+    becomes one library call over the region its grid covers."""
+    mod = pkg.mlir_text.parse_file(os.path.join(REF, "elementwise_add.mlir"))
+    n = 2048
+    t = [torch.zeros(n, dtype=torch.float16) for _ in range(3)]
+    h = FakeHandle()
+    pkg.executor.launch(mod, (n // 512, 1, 1), [*t, n], h)
+    kind, insts, tin, tout = h.log[0]
+    A = pkg.abi
+    assert kind == "elementwise" and [i[0] for i in insts] == [A.OP_LOAD, A.OP_LOAD, A.OP_ADD, A.OP_STORE]
+    assert tout.size1 == n and tout.ptr == t[2].data_ptr() and len(tin) == 2
+
+    mod = pkg.mlir_text.parse_file(os.path.join(REF, "reduce_sum.mlir"))
+    rows = 64
+    src, dst = torch.zeros((rows, 256), dtype=torch.float16), torch.zeros(rows, dtype=torch.float16)
+    h = FakeHandle()
+    pkg.executor.launch(mod, (rows // 4, 1, 1), [src, dst, rows], h)
+    kind, tsrc, tdst, axis, comb = h.log[0]
+    assert kind == "reduce" and axis == 1 and comb == A.RED_ADD and tsrc.size0 == rows
+
+    mod = pkg.mlir_text.parse_file(os.path.join(REF, "matmul.mlir"))
+    M, K, N = 256, 192, 384
+    a, b, c = (torch.zeros(s, dtype=torch.float16) for s in ((M, K), (K, N), (M, N)))
+    h = FakeHandle()
+    pkg.executor.launch(mod, (M // 128, N // 128, 1), [a, b, c, M, K, N], h)
+    kind, tl, tr, to, ep, way = h.log[0]
+    assert kind == "matmul" and (tl.size0, tl.size1, tr.size1) == (M, K, N)
+    assert (to.size0, to.size1) == (M, N) and way == 1
+
+
+@pytest.mark.gpu
+def test_fixtures_run_on_gpu(handle, ko, pkg):
+    # scale + shift, bit-exact
+    mod, fn = load(pkg, "scale_shift_bf16.mlir")
+    n = 1024 * 33
+    x = normal((n,), 5)
+    xd, yd = x.cuda(), torch.zeros(n, dtype=torch.bfloat16, device="cuda")
+    assert pkg.executor.launch(fn, (33, 1, 1), [xd, yd, n], handle, module=mod) == ["elt_affine"]
+    handle.check()
+    want = ko.eltwise(pkg.programs.affine(pkg.abi.BF16, 0.5, 0.1), [bits(x).reshape(1, -1)], [1],
+                      (1, n), 1)
+    assert np.array_equal(bits(yd.cpu()).reshape(1, -1), want)
+    # row max, exact
+    mod, fn = load(pkg, "row_max_f32.mlir")
+    m = 8 * 25
+    src = normal((m, 128), 6, dtype=torch.float32)
+    dst = torch.zeros((m, 1), dtype=torch.float32, device="cuda")
+    pkg.executor.launch(fn, (25, 1, 1), [src.cuda(), dst, m], handle, module=mod)
+    handle.check()
+    assert torch.equal(dst.cpu().ravel(), src.max(dim=1).values)
+    # pipelined gemm -> tcgen05 kernel
+    mod, fn = load(pkg, "gemm_ring_bf16.mlir")
+    M, K, N = 256, 512, 384
+    A, B = normal((M, K), 7, K ** -0.5), normal((K, N), 8)
+    Cd = torch.zeros((M, N), dtype=torch.bfloat16, device="cuda")
+    ran = pkg.executor.launch(fn, (M // 32, N // 32, 1), [A.cuda(), B.cuda(), Cd, M, K, N], handle,
+                              module=mod)
+    handle.check()
+    assert ran[0].startswith("tcgen05")
+    ref = ko.matmul_f64(bits(A), 1, bits(B), 1)
+    err, _ = ko.max_rel_err(Cd.cpu().double().numpy(), ref)
+    assert err <= 1e-2
