@@ -336,6 +336,53 @@ def run_ours(args):
            "d2h_bytes_per_step": d2h, "ms_per_step": e2e_t * 1e3}
     assert torch.equal(C_pin, Cd.cpu()), "host-buffer call and device call disagree"
 
+    # ---- N > 1: the same step with the full output assembled on every rank
+    gather = None
+    if world > 1:
+        gather = {"bytes_received_per_gpu": int(M * (N - (c1 - c0)) * 2)}
+        spans = pkg.dist.column_shards(N, world, 256)
+
+        def timed(fn, iters):
+            for _ in range(2):
+                fn()
+            barrier()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(iters):
+                fn()
+            b.record()
+            b.synchronize()
+            barrier()
+            t = torch.tensor([a.elapsed_time(b) * 1e-3 / iters], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return float(t.item())
+
+        iters = max(2, min(args.steps, 10))
+        try:
+            full = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
+
+            def nccl_step():
+                h.matmul(Ad, Bd, out=Cd, bias=bd)
+                pkg.dist.all_gather_columns(Cd, spans, out=full)
+            tn = timed(nccl_step, iters)
+            gather["nccl_all_gather"] = {"value": FLOPS / tn / 1e12, "unit": UNIT, "ms_per_step": tn * 1e3}
+            del full
+        except Exception as ex:  # report, keep the main number
+            gather["nccl_all_gather"] = {"error": repr(ex)[:200]}
+        try:
+            pg = pkg.dist.PushGather(M, N, torch.bfloat16, torch.device("cuda", local))
+
+            def push_step():
+                pg.matmul(h, Ad, Bd, c0, bias_shard=bd)
+                pg.wait()
+            tp = timed(push_step, iters)
+            h.check()
+            ok = bool(torch.equal(pg.full[:, c0:c1], Cd))
+            gather["fused_push"] = {"value": FLOPS / tp / 1e12, "unit": UNIT, "ms_per_step": tp * 1e3,
+                                    "matches_local_shard": ok}
+        except Exception as ex:
+            gather["fused_push"] = {"error": repr(ex)[:200]}
+
     line = None
     if rank == 0:
         long_run = elapsed > 1.0
@@ -359,6 +406,8 @@ def run_ours(args):
                        "l2": "A+B+C = 384 MiB per step, larger than the 126 MB L2"},
             "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks, "roofline": roofline,
         }
+        if gather is not None:
+            line["gather"] = gather
 
     # ---- CPU baseline: the checker's fp32-accumulate port on a bounded row sample
     if rank == 0 and world == 1:

@@ -6,6 +6,7 @@ Nothing here computes on the CPU: every op is a CUDA kernel reached through the
 C ABI in ``include/kapyb.h``.
 """
 from . import _abi as abi  # noqa: F401
+from . import dist  # noqa: F401
 from . import executor  # noqa: F401
 from . import ir  # noqa: F401
 from . import mlir_text  # noqa: F401
@@ -14,5 +15,5 @@ from . import runtime  # noqa: F401
 from .build import build  # noqa: F401
 from .runtime import Handle, KapybError, KapybTimeout, shard_range, tensor2d  # noqa: F401
 
-__all__ = ["abi", "executor", "ir", "mlir_text", "programs", "runtime", "build", "Handle", "KapybError", "KapybTimeout", "shard_range",
+__all__ = ["abi", "dist", "executor", "ir", "mlir_text", "programs", "runtime", "build", "Handle", "KapybError", "KapybTimeout", "shard_range",
            "tensor2d"]

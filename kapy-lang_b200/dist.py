@@ -1,0 +1,95 @@
+"""Multi-GPU plumbing for the sharded matmul paths (one process per GPU,
+``torch.distributed`` for rendezvous and collectives).
+
+The reference has no multi-GPU code; the partitioning follows the shapes it is
+asked to run: large GEMMs shard by columns of B and of the output, batched
+GEMMs by batch.  Outputs stay sharded unless the caller asks for the full
+matrix, in which case there are two ways to assemble it:
+
+  * ``all_gather_columns``: NCCL all-gather of the column blocks into a staging
+    buffer followed by a strided copy (column blocks of a row-major matrix are
+    not contiguous, so the gather cannot land in place);
+  * ``PushGather``: every rank's GEMM epilogue stores its finished tiles
+    straight into all peers' full-size outputs through peer-mapped pointers
+    (``kapyb_matmul_push``), so the transfer overlaps the main loop tile by
+    tile and no staging copy exists.  Only stores cross NVLink.
+"""
+from __future__ import annotations
+
+from typing import Callable, List, Optional, Sequence, Tuple
+
+from . import runtime
+
+
+def column_shards(n_total: int, world: int, align: int = 256) -> List[Tuple[int, int]]:
+    """[begin, end) of output columns per rank, in blocks of `align` columns."""
+    return [runtime.shard_range(n_total, world, r, align) for r in range(world)]
+
+
+def batch_shards(batch: int, world: int) -> List[Tuple[int, int]]:
+    return [runtime.shard_range(batch, world, r, 1) for r in range(world)]
+
+
+def all_gather_columns(shard, spans: Sequence[Tuple[int, int]], group=None, out=None):
+    """Assembles [M, N] from per-rank column blocks [M, end-begin] (ragged or
+    empty blocks allowed).  Works on any backend (NCCL on GPUs, gloo on CPU)."""
+    import torch
+    import torch.distributed as dist
+    world = dist.get_world_size(group)
+    assert len(spans) == world
+    M = shard.shape[0]
+    width = max(e - b for b, e in spans)
+    n_total = spans[-1][1]
+    rank = dist.get_rank(group)
+    if shard.shape[1] != spans[rank][1] - spans[rank][0]:
+        raise ValueError("shard width does not match this rank's span")
+    staging = torch.empty((world, M, width), dtype=shard.dtype, device=shard.device)
+    mine = shard
+    if shard.shape[1] != width:
+        mine = torch.zeros((M, width), dtype=shard.dtype, device=shard.device)
+        mine[:, : shard.shape[1]] = shard
+    dist.all_gather_into_tensor(staging.view(world * M, width), mine.contiguous(), group=group)
+    if out is None:
+        out = torch.empty((M, n_total), dtype=shard.dtype, device=shard.device)
+    for r, (b, e) in enumerate(spans):
+        if e > b:
+            out[:, b:e] = staging[r, :, : e - b]
+    return out
+
+
+def sharded_matmul(handle, lhs, rhs_shard, spans, *, bias_shard=None, gather: str = "none",
+                   group=None, compute: Optional[Callable] = None, **epilogue):
+    """N-sharded matmul: this rank multiplies by its column block of B.  `gather`
+    is "none" (return the local [M, n_local] block) or "nccl" (return [M, N])."""
+    compute = compute or (lambda a, b, bias: handle.matmul(a, b, bias=bias, **epilogue))
+    local = compute(lhs, rhs_shard, bias_shard)
+    if gather == "none":
+        return local
+    if gather == "nccl":
+        return all_gather_columns(local, spans, group=group)
+    raise ValueError("gather must be 'none' or 'nccl' (use PushGather for the fused variant)")
+
+
+class PushGather:
+    """Full-size outputs in symmetric memory plus the fused push epilogue."""
+
+    def __init__(self, M: int, n_total: int, dtype, device, group=None):
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+        self.group = group or dist.group.WORLD
+        self.full = symm.empty((M, n_total), dtype=dtype, device=device)
+        self.hdl = symm.rendezvous(self.full, group=self.group)
+        self.peer_ptrs = [int(p) for p in self.hdl.buffer_ptrs]
+        self.M, self.n_total, self.dtype = M, n_total, dtype
+
+    def matmul(self, handle, lhs, rhs_shard, col_begin: int, *, bias_shard=None, **epilogue):
+        """Runs this rank's shard and stores it into every rank's `full`."""
+        handle.matmul_push(lhs, rhs_shard, self.peer_ptrs, out_dtype=self.dtype,
+                           out_stride0=self.n_total, col_begin=col_begin, n_total=self.n_total,
+                           bias=bias_shard, **epilogue)
+
+    def wait(self):
+        """Stream-ordered barrier: after it, every peer's stores into `full` have
+        been issued and completed on their streams."""
+        self.hdl.barrier(channel=0)
+        return self.full
