@@ -184,19 +184,23 @@ def secondary(torch, pkg, h, peaks):
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
 
     def timeit(fn, iters=10, flush_l2=False):
+        """Median over 5 samples of `iters` back-to-back launches (one event pair
+        per sample), or of single launches with an L2 flush before each when the
+        working set would otherwise stay in L2."""
         for _ in range(3):
             fn()
         torch.cuda.synchronize()
         ts = []
-        for _ in range(iters):
+        for _ in range(5 if not flush_l2 else iters):
             if flush_l2:
                 flush.zero_()
             s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             s.record()
-            fn()
+            for _ in range(1 if flush_l2 else iters):
+                fn()
             e.record()
             e.synchronize()
-            ts.append(s.elapsed_time(e) * 1e-3)
+            ts.append(s.elapsed_time(e) * 1e-3 / (1 if flush_l2 else iters))
         return statistics.median(ts)
 
     g = torch.Generator(device="cpu").manual_seed(1003)

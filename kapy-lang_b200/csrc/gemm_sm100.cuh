@@ -46,7 +46,8 @@ struct GemmParams {
   int out_col_offset;    // column offset of this shard inside each output
   uint32_t idesc;
   uint32_t *status;
-  int debug;  // profiling aid: bit0 skip loads, bit1 skip MMAs, bit2 skip stores (results are garbage)
+  int debug;  // profiling aid (results are garbage): bit0 skip loads, bit1 skip MMAs,
+              // bit2 skip the epilogue body, bit3 skip only the TMA stores
   EpilogueArgs ep;
 };
 
@@ -412,7 +413,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
           }
           ptx::fence_proxy_async_smem();
           __syncwarp();
-          if (lane == 0) {
+          if (lane == 0 && !(p.debug & 8)) {
             for (int o = 0; o < p.n_out; ++o)
               ptx::tma_store_3d(&tmC.m[o], ptx::smem_u32(sbuf), p.out_col_offset + nc, m0, b);
             ptx::tma_store_commit();
