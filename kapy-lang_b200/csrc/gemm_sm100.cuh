@@ -133,6 +133,101 @@ __device__ __forceinline__ void add_bias32(float (&f)[32], const uint4 *bp) {
   }
 }
 
+// What one epilogue warp needs to drain its share of one accumulator tile.
+struct EpiTile {
+  int b, m0, n0, row, lane, cpart;
+  uint32_t t_row;   // TMEM address of this warp's lanes, column 0 of the slot
+  uint8_t *stg;     // this warp's two 4 KB staging buffers
+  bool bias_col, bias_fast;
+  float bias_row;
+};
+
+// OUTK: 0 f32, 1/2 bf16 rn/rz, 3/4 f16 rn/rz.  PLAIN: the epilogue is only the
+// scale (no bias, addend or activation), so none of those are even tested.
+template <int BN, int EPI, int OUTK, bool PLAIN>
+__device__ __forceinline__ void epilogue_tile(const GemmParams &p, const TmapArray &tmC,
+                                              const EpiTile &t, int &buf) {
+  constexpr bool OUT32 = OUTK == 0;
+  constexpr int CW = OUT32 ? 32 : 64;  // output columns per 128-byte staging row
+  constexpr int NH = CW / 32;
+  constexpr int CSTEP = EPI / 4;
+  const int lane = t.lane;
+  for (int c = t.cpart; c < BN / CW; c += CSTEP) {
+    const int nc = t.n0 + c * CW;
+    if (nc >= p.N) break;
+    uint8_t *sbuf = t.stg + buf * 4096;
+    // All loads of the chunk are in flight before the one wait.
+    uint32_t v[NH][32];
+#pragma unroll
+    for (int h = 0; h < NH; ++h)
+      ptx::tmem_ld_32x32(t.t_row + static_cast<uint32_t>(c * CW + h * 32), v[h]);
+    // The store issued two chunks ago read this buffer; let it finish.
+    if (lane == 0) ptx::tma_store_wait_read<1>();
+    __syncwarp();
+    ptx::tmem_ld_wait();
+    uint8_t *srow = sbuf + lane * 128;
+#pragma unroll
+    for (int h = 0; h < NH; ++h) {
+      const int col0 = nc + h * 32;
+      float f[32];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(v[h][i]);
+      if (p.ep.alpha != 1.0f) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) f[i] *= p.ep.alpha;
+      }
+      if constexpr (!PLAIN) {
+        if (t.bias_col) {
+          if (t.bias_fast && col0 + 32 <= p.N) {
+            const uint4 *bp =
+                reinterpret_cast<const uint4 *>(static_cast<const uint16_t *>(p.ep.bias) + col0);
+            if (p.ep.bias_dtype == KAPYB_BF16)
+              add_bias32<KAPYB_BF16>(f, bp);
+            else
+              add_bias32<KAPYB_F16>(f, bp);
+          } else {
+            float bias_lane = 0.0f;
+            if (col0 + lane < p.N) bias_lane = load_as_f32(p.ep.bias, p.ep.bias_dtype, col0 + lane);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) f[i] += __shfl_sync(0xffffffffu, bias_lane, i);
+          }
+        } else if (p.ep.bias != nullptr) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) f[i] += t.bias_row;
+        }
+        if (p.ep.acc != nullptr && t.row < p.M) {
+          const long long base = static_cast<long long>(t.b) * p.ep.acc_batch_stride +
+                                 static_cast<long long>(t.row) * p.ep.acc_stride0;
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (col0 + i < p.N)
+              f[i] += load_as_f32(p.ep.acc, p.ep.acc_dtype,
+                                  base + static_cast<long long>(col0 + i) * p.ep.acc_stride1);
+        }
+        if (p.ep.activation != KAPYB_ACT_NONE) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) f[i] = apply_activation(p.ep.activation, f[i]);
+        }
+      }
+      // Row `lane` of the staging tile, 128-byte swizzle: 16-byte chunk j of row
+      // r lives at chunk position j ^ (r & 7).
+      if constexpr (OUTK == 0) stage_half_f32(srow, f, lane);
+      if constexpr (OUTK == 1) stage_half_16<KAPYB_BF16, 1>(srow, f, lane, h);
+      if constexpr (OUTK == 2) stage_half_16<KAPYB_BF16, 0>(srow, f, lane, h);
+      if constexpr (OUTK == 3) stage_half_16<KAPYB_F16, 1>(srow, f, lane, h);
+      if constexpr (OUTK == 4) stage_half_16<KAPYB_F16, 0>(srow, f, lane, h);
+    }
+    ptx::fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0 && !(p.debug & 8)) {
+      for (int o = 0; o < p.n_out; ++o)
+        ptx::tma_store_3d(&tmC.m[o], ptx::smem_u32(sbuf), p.out_col_offset + nc, t.m0, t.b);
+      ptx::tma_store_commit();
+    }
+    buf ^= 1;
+  }
+}
+
 template <int BN, int CTAS, int EPI>
 __global__ void __launch_bounds__(64 + 32 * EPI, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
@@ -312,10 +407,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
     const int e = warp - 2;          // epilogue warp index, 0 .. EPI-1
     const int q = warp & 3;          // TMEM lane quarter this warp may touch
     const int cpart = e >> 2;        // with 8 epilogue warps two warps share a quarter
-    constexpr int CSTEP = EPI / 4;   //   and take alternate column chunks
+                                     //   and take alternate column chunks
     uint8_t *stg = sC + e * Cfg::C_WARP_BYTES;
     const bool out32 = p.out_dtype == KAPYB_F32;
-    const int CW = out32 ? 32 : 64;  // output columns per 128-byte staging row
     // 0: f32; 1/2: bf16 rn/rz; 3/4: f16 rn/rz -- picked once, outside the loops
     const int out_kind = out32 ? 0
                          : (p.out_dtype == KAPYB_BF16 ? (p.ep.rounding ? 1 : 2)
@@ -327,6 +421,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
     // 128-bit loads; anything else goes through one load per lane and shuffles.
     const bool bias_fast = bias_col && p.ep.bias_dtype != KAPYB_F32 &&
                            (reinterpret_cast<uintptr_t>(p.ep.bias) & 15u) == 0;
+    // "plain": nothing but the scale between the accumulator and the downcast
+    const bool plain = p.ep.bias == nullptr && p.ep.acc == nullptr &&
+                       p.ep.activation == KAPYB_ACT_NONE;
     int acc = 0;
     uint32_t acc_phase = 0;
     int buf = 0;
@@ -341,84 +438,33 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
                              static_cast<uint32_t>(acc * BN);
       if (m0 < p.M && !(p.debug & 4)) {
-        float bias_row = 0.0f;
+        EpiTile et;
+        et.b = b;
+        et.m0 = m0;
+        et.n0 = n0;
+        et.row = row;
+        et.lane = lane;
+        et.t_row = t_row;
+        et.cpart = cpart;
+        et.stg = stg;
+        et.bias_col = bias_col;
+        et.bias_fast = bias_fast;
+        et.bias_row = 0.0f;
         if (p.ep.bias != nullptr && p.ep.bias_axis == 0 && row < p.M)
-          bias_row = load_as_f32(p.ep.bias, p.ep.bias_dtype, row);
-        const int n_chunks = BN / CW;
-        for (int c = cpart; c < n_chunks; c += CSTEP) {
-          const int nc = n0 + c * CW;
-          if (nc >= p.N) break;
-          uint8_t *sbuf = stg + buf * 4096;
-          // Both 32-column loads of the chunk are in flight before the one wait.
-          uint32_t v[2][32];
-          ptx::tmem_ld_32x32(t_row + static_cast<uint32_t>(c * CW), v[0]);
-          if (!out32) ptx::tmem_ld_32x32(t_row + static_cast<uint32_t>(c * CW + 32), v[1]);
-          // The store issued two chunks ago read this buffer; let it finish.
-          if (lane == 0) ptx::tma_store_wait_read<1>();
-          __syncwarp();
-          ptx::tmem_ld_wait();
-#pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            if (h == 1 && out32) break;
-            const int col0 = nc + h * 32;
-            float f[32];
-#pragma unroll
-            for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(v[h][i]);
-            if (p.ep.alpha != 1.0f) {
-#pragma unroll
-              for (int i = 0; i < 32; ++i) f[i] *= p.ep.alpha;
-            }
-            if (bias_col) {
-              if (bias_fast && col0 + 32 <= p.N) {
-                const uint4 *bp = reinterpret_cast<const uint4 *>(
-                    static_cast<const uint16_t *>(p.ep.bias) + col0);
-                if (p.ep.bias_dtype == KAPYB_BF16)
-                  add_bias32<KAPYB_BF16>(f, bp);
-                else
-                  add_bias32<KAPYB_F16>(f, bp);
-              } else {
-                float bias_lane = 0.0f;
-                if (col0 + lane < p.N)
-                  bias_lane = load_as_f32(p.ep.bias, p.ep.bias_dtype, col0 + lane);
-#pragma unroll
-                for (int i = 0; i < 32; ++i) f[i] += __shfl_sync(0xffffffffu, bias_lane, i);
-              }
-            } else if (p.ep.bias != nullptr) {
-#pragma unroll
-              for (int i = 0; i < 32; ++i) f[i] += bias_row;
-            }
-            if (p.ep.acc != nullptr && row < p.M) {
-              const long long base = static_cast<long long>(b) * p.ep.acc_batch_stride +
-                                     static_cast<long long>(row) * p.ep.acc_stride0;
-#pragma unroll
-              for (int i = 0; i < 32; ++i)
-                if (col0 + i < p.N)
-                  f[i] += load_as_f32(p.ep.acc, p.ep.acc_dtype,
-                                      base + static_cast<long long>(col0 + i) * p.ep.acc_stride1);
-            }
-            if (p.ep.activation != KAPYB_ACT_NONE) {
-#pragma unroll
-              for (int i = 0; i < 32; ++i) f[i] = apply_activation(p.ep.activation, f[i]);
-            }
-            // Row `lane` of the staging tile, 128-byte swizzle: 16-byte chunk j
-            // of row r lives at chunk position j ^ (r & 7).
-            uint8_t *srow = sbuf + lane * 128;
-            switch (out_kind) {
-            case 0: stage_half_f32(srow, f, lane); break;
-            case 1: stage_half_16<KAPYB_BF16, 1>(srow, f, lane, h); break;
-            case 2: stage_half_16<KAPYB_BF16, 0>(srow, f, lane, h); break;
-            case 3: stage_half_16<KAPYB_F16, 1>(srow, f, lane, h); break;
-            default: stage_half_16<KAPYB_F16, 0>(srow, f, lane, h); break;
-            }
-          }
-          ptx::fence_proxy_async_smem();
-          __syncwarp();
-          if (lane == 0 && !(p.debug & 8)) {
-            for (int o = 0; o < p.n_out; ++o)
-              ptx::tma_store_3d(&tmC.m[o], ptx::smem_u32(sbuf), p.out_col_offset + nc, m0, b);
-            ptx::tma_store_commit();
-          }
-          buf ^= 1;
+          et.bias_row = load_as_f32(p.ep.bias, p.ep.bias_dtype, row);
+        // One specialised copy of the chunk loop per (output kind, plain/full
+        // epilogue): the switch runs once per tile, the loops inside are tight.
+        switch (out_kind * 2 + (plain ? 1 : 0)) {
+        case 0: epilogue_tile<BN, EPI, 0, false>(p, tmC, et, buf); break;
+        case 1: epilogue_tile<BN, EPI, 0, true>(p, tmC, et, buf); break;
+        case 2: epilogue_tile<BN, EPI, 1, false>(p, tmC, et, buf); break;
+        case 3: epilogue_tile<BN, EPI, 1, true>(p, tmC, et, buf); break;
+        case 4: epilogue_tile<BN, EPI, 2, false>(p, tmC, et, buf); break;
+        case 5: epilogue_tile<BN, EPI, 2, true>(p, tmC, et, buf); break;
+        case 6: epilogue_tile<BN, EPI, 3, false>(p, tmC, et, buf); break;
+        case 7: epilogue_tile<BN, EPI, 3, true>(p, tmC, et, buf); break;
+        case 8: epilogue_tile<BN, EPI, 4, false>(p, tmC, et, buf); break;
+        default: epilogue_tile<BN, EPI, 4, true>(p, tmC, et, buf); break;
         }
       }
       // All of this warp's TMEM reads of the slot are done: hand it back.
