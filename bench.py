@@ -37,8 +37,10 @@ FLOPS = 2.0 * M * N * K                       # algorithmic FLOPs of one step
 ALG_BYTES = 3 * M * N * 2 + N * 2             # A + B + C (bf16) + bias
 CPU_SAMPLE_ROWS = 512                         # rows of the output the CPU arm computes per step
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant
-# kernel, from the ncu capture summarised under profiles/ (None until captured).
-NCU_TRAFFIC_BYTES = None
+# kernel.  Captured with ncu on the M=4096, N=8192, K=4096 case of the same kernel
+# (222.1 MB, profiles/gemm_tcgen05_2cta_bf16_4096x8192x4096.txt) and scaled by the
+# units processed (tile x k-block count: 4x) to the 8192^3 launch.
+NCU_TRAFFIC_BYTES = 4 * (173_657_600 + 48_438_016)
 
 
 def load_peaks():

@@ -77,6 +77,23 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
+// try_wait with a suspend-time hint: the thread may sleep in hardware for up to
+// `ns` and is woken as soon as the phase completes, instead of re-issuing the
+// probe every few hundred nanoseconds (waiting roles then cost no issue slots).
+__device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(ns)
+      : "memory");
+  return ok != 0;
+}
+
 // Wall-clock budget of one wait.  A healthy pipeline waits microseconds; two
 // seconds means something upstream will never arrive.
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
@@ -89,7 +106,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
   if (mbar_try_wait(bar, parity)) return true;
   uint64_t t0 = 0;
   for (uint32_t it = 1;; ++it) {
-    if (mbar_try_wait(bar, parity)) return true;
+    if (mbar_try_wait_hint(bar, parity, 200000u)) return true;
     if ((it & 63u) == 0u) {
       if (*abort_flag != 0u) return false;
       uint64_t now = globaltimer_ns();

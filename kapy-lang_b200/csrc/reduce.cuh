@@ -1,7 +1,7 @@
 // kapy.reduce over a whole 2-D tensor (Ops.td:441-457).  The reference folds
 // within a lane, then butterflies across the warp with shfl.sync.bfly
 // (ReduceOpToLLVM.cpp:76-119); here one warp owns one row (axis 1), reads it
-// with 128-bit coalesced loads, folds in registers and finishes with the same
+// with 256-bit coalesced loads, folds in registers and finishes with the same
 // xor-shuffle tree.  Values are widened to f32 before combining; a 16-bit
 // destination is rounded once at the end.
 #pragma once
