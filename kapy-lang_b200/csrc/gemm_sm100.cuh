@@ -60,7 +60,10 @@ struct GemmCfg {
   static constexpr int A_BYTES = BM * BK * 2;
   static constexpr int B_BYTES = BN_CTA * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int C_WARP_BYTES = 2 * 4096;  // two 32-row x 128-byte buffers
+  // 32-row x 128-byte staging buffers per epilogue warp: two, except where eight
+  // warps and 48 KB stages leave room for one only
+  static constexpr int C_BUFS = (BN == 512 && EPI == 8) ? 1 : 2;
+  static constexpr int C_WARP_BYTES = C_BUFS * 4096;
   static constexpr int C_BYTES = EPI * C_WARP_BYTES;
   static constexpr int THREADS = 64 + 32 * EPI;  // producer warp, MMA warp, EPI epilogue warps
   static constexpr int CTRL_BYTES = 1024;
@@ -68,8 +71,15 @@ struct GemmCfg {
   static constexpr int STAGES_RAW = (SMEM_LIMIT - 1024 - CTRL_BYTES - C_BYTES) / STAGE_BYTES;
   static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
   static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + C_BYTES + CTRL_BYTES;
-  static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
-  static_assert(BN % 64 == 0 && BN <= 256, "BN must be 64, 128 or 256");
+  // BN = 512 (CTA pairs only): the tile is two 256-column halves that share the A
+  // stage, each with its own accumulator; together they fill TMEM, so the two
+  // slots hold the halves of ONE tile instead of two tiles in flight.  That cuts
+  // the operand bytes pulled from L2 per flop by a quarter.
+  static constexpr int HALVES = BN == 512 ? 2 : 1;
+  static constexpr int MMA_N = BN / HALVES;
+  static constexpr int TMEM_COLS = HALVES == 2 ? 512 : (2 * BN < 32 ? 32 : 2 * BN);
+  static_assert(BN % 64 == 0 && (BN <= 256 || (BN == 512 && CTAS == 2)),
+                "BN must be 64, 128, 256, or 512 for CTA pairs");
   static_assert((TMEM_COLS & (TMEM_COLS - 1)) == 0 && TMEM_COLS <= 512, "TMEM columns");
   static_assert(STAGES >= 2, "pipeline too shallow");
   static_assert(EPI == 4 || EPI == 8, "4 or 8 epilogue warps");
@@ -136,7 +146,8 @@ __device__ __forceinline__ void add_bias32(float (&f)[32], const uint4 *bp) {
 // What one epilogue warp needs to drain its share of one accumulator tile.
 struct EpiTile {
   int b, m0, n0, row, lane, cpart;
-  uint32_t t_row;   // TMEM address of this warp's lanes, column 0 of the slot
+  int col_begin, col_end;  // tile columns to drain in this call (one accumulator slot)
+  uint32_t t_row;   // TMEM address of this warp's lanes at tile column 0
   uint8_t *stg;     // this warp's two 4 KB staging buffers
   bool bias_col, bias_fast;
   float bias_row;
@@ -151,18 +162,20 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams &p, const TmapArr
   constexpr int CW = OUT32 ? 32 : 64;  // output columns per 128-byte staging row
   constexpr int NH = CW / 32;
   constexpr int CSTEP = EPI / 4;
+  constexpr int C_BUFS = (BN == 512 && EPI == 8) ? 1 : 2;
   const int lane = t.lane;
-  for (int c = t.cpart; c < BN / CW; c += CSTEP) {
+  for (int c = t.col_begin / CW + t.cpart; c < t.col_end / CW; c += CSTEP) {
     const int nc = t.n0 + c * CW;
     if (nc >= p.N) break;
-    uint8_t *sbuf = t.stg + buf * 4096;
+    uint8_t *sbuf = t.stg + (C_BUFS == 2 ? buf : 0) * 4096;
     // All loads of the chunk are in flight before the one wait.
     uint32_t v[NH][32];
 #pragma unroll
     for (int h = 0; h < NH; ++h)
       ptx::tmem_ld_32x32(t.t_row + static_cast<uint32_t>(c * CW + h * 32), v[h]);
-    // The store issued two chunks ago read this buffer; let it finish.
-    if (lane == 0) ptx::tma_store_wait_read<1>();
+    // The store that last read this buffer (two chunks ago, or the previous one
+    // with a single buffer) must have finished reading it.
+    if (lane == 0) ptx::tma_store_wait_read<C_BUFS - 1>();
     __syncwarp();
     ptx::tmem_ld_wait();
     uint8_t *srow = sbuf + lane * 128;
@@ -295,7 +308,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       int b, mb, nb;
       decode_tile(p, tile, b, mb, nb);
       const int m0 = mb * Cfg::TILE_M + static_cast<int>(rank) * Cfg::BM;
-      const int nB0 = nb * BN + static_cast<int>(rank) * Cfg::BN_CTA;
+      // first B column this CTA loads; with two halves its columns are two groups
+      // of MMA_N / CTAS, one per half
+      const int nB0 = nb * BN + static_cast<int>(rank) * (Cfg::MMA_N / CTAS);
+      constexpr int kGroupCols = Cfg::MMA_N / CTAS;   // columns per half this CTA owns
       for (int kb = 0; kb < p.num_kb; ++kb) {
         if (!ptx::mbar_wait(ptx::smem_u32(&empty_bar[stage]), phase ^ 1u, abort_flag)) {
           ok = false;
@@ -323,6 +339,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
             for (int j = 0; j < Cfg::BN_CTA / 64; ++j)
               ptx::tma_load_3d(b_dst + j * 8192, &tmB, fb, nB0 + 64 * j, k0, b);
           }
+          (void)kGroupCols;
         } else {
           // Both CTAs' loads report their bytes to the leader's barrier; the
           // leader alone posts the arrival, expecting the bytes of both.  (A
@@ -338,11 +355,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
               ptx::tma_load_3d_pair(a_dst + j * 8192, &tmA, fb, m0 + 64 * j, k0, b);
           }
           if (!p.b_mn_major) {
-            ptx::tma_load_3d_pair(b_dst, &tmB, fb, k0, nB0, b);
+            // one box of kGroupCols rows per half
+#pragma unroll
+            for (int hh = 0; hh < Cfg::HALVES; ++hh)
+              ptx::tma_load_3d_pair(b_dst + hh * (kGroupCols * 128), &tmB, fb, k0,
+                                    nB0 + hh * Cfg::MMA_N, b);
           } else {
 #pragma unroll
-            for (int j = 0; j < Cfg::BN_CTA / 64; ++j)
-              ptx::tma_load_3d_pair(b_dst + j * 8192, &tmB, fb, nB0 + 64 * j, k0, b);
+            for (int j = 0; j < Cfg::BN_CTA / 64; ++j) {
+              const int hh = (j * 64) / kGroupCols, within = (j * 64) % kGroupCols;
+              ptx::tma_load_3d_pair(b_dst + j * 8192, &tmB, fb, nB0 + hh * Cfg::MMA_N + within,
+                                    k0, b);
+            }
           }
         }
         if (++stage == STAGES) {
@@ -367,9 +391,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
     uint32_t acc_phase = 0;
     bool ok = true;
     for (int tile = unit; tile < p.num_tiles && ok; tile += unit_step) {
-      if (!ptx::mbar_wait(ptx::smem_u32(&tempty_bar[acc]), acc_phase ^ 1u, abort_flag)) break;
+      if constexpr (Cfg::HALVES == 2) {
+        // both halves of the previous tile must have been drained
+        if (!ptx::mbar_wait(ptx::smem_u32(&tempty_bar[0]), acc_phase ^ 1u, abort_flag)) break;
+        if (!ptx::mbar_wait(ptx::smem_u32(&tempty_bar[1]), acc_phase ^ 1u, abort_flag)) break;
+      } else {
+        if (!ptx::mbar_wait(ptx::smem_u32(&tempty_bar[acc]), acc_phase ^ 1u, abort_flag)) break;
+      }
       ptx::tc_fence_after();
-      const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
+      const uint32_t d_tmem =
+          tmem_base + (Cfg::HALVES == 2 ? 0u : static_cast<uint32_t>(acc * BN));
       for (int kb = 0; kb < p.num_kb; ++kb) {
         if (!ptx::mbar_wait(ptx::smem_u32(&full_bar[stage]), phase, abort_flag)) {
           ok = false;
@@ -382,8 +413,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
 #pragma unroll
           for (int k = 0; k < Cfg::BK / 16; ++k) {
             const uint64_t adesc = ptx::make_smem_desc_sw128(a_base + k * a_kadv, a_lbo, a_sbo);
-            const uint64_t bdesc = ptx::make_smem_desc_sw128(b_base + k * b_kadv, b_lbo, b_sbo);
-            ptx::umma_f16<CTAS>(d_tmem, adesc, bdesc, p.idesc, (kb | k) != 0 ? 1u : 0u);
+#pragma unroll
+            for (int hh = 0; hh < Cfg::HALVES; ++hh) {
+              // this CTA's B bytes of half hh start (MMA_N / CTAS) rows of 128 bytes
+              // after those of half hh-1, in either layout
+              const uint32_t b_half = b_base + hh * (Cfg::MMA_N / CTAS) * 128;
+              const uint64_t bdesc = ptx::make_smem_desc_sw128(b_half + k * b_kadv, b_lbo, b_sbo);
+              ptx::umma_f16<CTAS>(d_tmem + hh * Cfg::MMA_N, adesc, bdesc, p.idesc,
+                                  (kb | k) != 0 ? 1u : 0u);
+            }
           }
         }
         // Free the stage in every CTA that filled it.
@@ -396,11 +434,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
         }
       }
       if (!ok) break;
-      ptx::umma_commit<CTAS>(ptx::smem_u32(&tfull_bar[acc]));
-      if constexpr (CTAS == 2)
-        ptx::umma_commit<CTAS>(ptx::mapa(ptx::smem_u32(&tfull_bar[acc]), 1));
-      acc ^= 1;
-      if (acc == 0) acc_phase ^= 1u;
+      if constexpr (Cfg::HALVES == 2) {
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+          ptx::umma_commit<CTAS>(ptx::smem_u32(&tfull_bar[hh]));
+          ptx::umma_commit<CTAS>(ptx::mapa(ptx::smem_u32(&tfull_bar[hh]), 1));
+        }
+        acc_phase ^= 1u;
+      } else {
+        ptx::umma_commit<CTAS>(ptx::smem_u32(&tfull_bar[acc]));
+        if constexpr (CTAS == 2)
+          ptx::umma_commit<CTAS>(ptx::mapa(ptx::smem_u32(&tfull_bar[acc]), 1));
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1u;
+      }
     }
   } else if (warp >= 2) {
     // ------------------------------------------------------------ epilogue
@@ -432,53 +479,69 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       decode_tile(p, tile, b, mb, nb);
       const int m0 = mb * Cfg::TILE_M + static_cast<int>(rank) * Cfg::BM + q * 32;
       const int n0 = nb * BN;
-      if (!ptx::mbar_wait(ptx::smem_u32(&tfull_bar[acc]), acc_phase, abort_flag)) break;
-      ptx::tc_fence_after();
       const int row = m0 + lane;
-      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
-                             static_cast<uint32_t>(acc * BN);
-      if (m0 < p.M && !(p.debug & 4)) {
-        EpiTile et;
-        et.b = b;
-        et.m0 = m0;
-        et.n0 = n0;
-        et.row = row;
-        et.lane = lane;
-        et.t_row = t_row;
-        et.cpart = cpart;
-        et.stg = stg;
-        et.bias_col = bias_col;
-        et.bias_fast = bias_fast;
-        et.bias_row = 0.0f;
-        if (p.ep.bias != nullptr && p.ep.bias_axis == 0 && row < p.M)
-          et.bias_row = load_as_f32(p.ep.bias, p.ep.bias_dtype, row);
-        // One specialised copy of the chunk loop per (output kind, plain/full
-        // epilogue): the switch runs once per tile, the loops inside are tight.
-        switch (out_kind * 2 + (plain ? 1 : 0)) {
-        case 0: epilogue_tile<BN, EPI, 0, false>(p, tmC, et, buf); break;
-        case 1: epilogue_tile<BN, EPI, 0, true>(p, tmC, et, buf); break;
-        case 2: epilogue_tile<BN, EPI, 1, false>(p, tmC, et, buf); break;
-        case 3: epilogue_tile<BN, EPI, 1, true>(p, tmC, et, buf); break;
-        case 4: epilogue_tile<BN, EPI, 2, false>(p, tmC, et, buf); break;
-        case 5: epilogue_tile<BN, EPI, 2, true>(p, tmC, et, buf); break;
-        case 6: epilogue_tile<BN, EPI, 3, false>(p, tmC, et, buf); break;
-        case 7: epilogue_tile<BN, EPI, 3, true>(p, tmC, et, buf); break;
-        case 8: epilogue_tile<BN, EPI, 4, false>(p, tmC, et, buf); break;
-        default: epilogue_tile<BN, EPI, 4, true>(p, tmC, et, buf); break;
+      bool alive = true;
+#pragma unroll 1
+      for (int hh = 0; hh < Cfg::HALVES; ++hh) {
+        // slot: with two halves, half hh of this tile; otherwise the tile's slot
+        const int slot = Cfg::HALVES == 2 ? hh : acc;
+        if (!ptx::mbar_wait(ptx::smem_u32(&tfull_bar[slot]), acc_phase, abort_flag)) {
+          alive = false;
+          break;
+        }
+        ptx::tc_fence_after();
+        const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
+                               (Cfg::HALVES == 2 ? 0u : static_cast<uint32_t>(acc * BN));
+        if (m0 < p.M && !(p.debug & 4)) {
+          EpiTile et;
+          et.b = b;
+          et.m0 = m0;
+          et.n0 = n0;
+          et.row = row;
+          et.lane = lane;
+          et.t_row = t_row;
+          et.cpart = cpart;
+          et.col_begin = hh * Cfg::MMA_N;
+          et.col_end = (hh + 1) * Cfg::MMA_N;
+          et.stg = stg;
+          et.bias_col = bias_col;
+          et.bias_fast = bias_fast;
+          et.bias_row = 0.0f;
+          if (p.ep.bias != nullptr && p.ep.bias_axis == 0 && row < p.M)
+            et.bias_row = load_as_f32(p.ep.bias, p.ep.bias_dtype, row);
+          // One specialised copy of the chunk loop per (output kind, plain/full
+          // epilogue): the switch runs once per slot, the loops inside are tight.
+          switch (out_kind * 2 + (plain ? 1 : 0)) {
+          case 0: epilogue_tile<BN, EPI, 0, false>(p, tmC, et, buf); break;
+          case 1: epilogue_tile<BN, EPI, 0, true>(p, tmC, et, buf); break;
+          case 2: epilogue_tile<BN, EPI, 1, false>(p, tmC, et, buf); break;
+          case 3: epilogue_tile<BN, EPI, 1, true>(p, tmC, et, buf); break;
+          case 4: epilogue_tile<BN, EPI, 2, false>(p, tmC, et, buf); break;
+          case 5: epilogue_tile<BN, EPI, 2, true>(p, tmC, et, buf); break;
+          case 6: epilogue_tile<BN, EPI, 3, false>(p, tmC, et, buf); break;
+          case 7: epilogue_tile<BN, EPI, 3, true>(p, tmC, et, buf); break;
+          case 8: epilogue_tile<BN, EPI, 4, false>(p, tmC, et, buf); break;
+          default: epilogue_tile<BN, EPI, 4, true>(p, tmC, et, buf); break;
+          }
+        }
+        // All of this warp's TMEM reads of the slot are done: hand it back.
+        ptx::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          const uint32_t bar = tempty_leader + static_cast<uint32_t>(slot * 8);
+          if constexpr (CTAS == 2)
+            ptx::mbar_arrive_cluster(bar);
+          else
+            ptx::mbar_arrive(bar);
         }
       }
-      // All of this warp's TMEM reads of the slot are done: hand it back.
-      ptx::tc_fence_before();
-      __syncwarp();
-      if (lane == 0) {
-        const uint32_t bar = tempty_leader + static_cast<uint32_t>(acc * 8);
-        if constexpr (CTAS == 2)
-          ptx::mbar_arrive_cluster(bar);
-        else
-          ptx::mbar_arrive(bar);
+      if (!alive) break;
+      if constexpr (Cfg::HALVES == 2) {
+        acc_phase ^= 1u;
+      } else {
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1u;
       }
-      acc ^= 1;
-      if (acc == 0) acc_phase ^= 1u;
     }
     if (lane == 0) ptx::tma_store_wait_all<0>();
     __syncwarp();

@@ -143,8 +143,8 @@ extern "C" KAPYB_API kapyb_status kapyb_set_matmul_path(kapyb_handle h, const ch
     size_t colon3 = s.find(":e", colon + 1);
     if (colon3 != std::string::npos) h->forced_epi = atoi(s.c_str() + colon3 + 2);
     s = s.substr(0, colon);
-    if (h->forced_bn != 64 && h->forced_bn != 128 && h->forced_bn != 256)
-      return fail(h, KAPYB_INVALID_ARG, "kapyb_set_matmul_path: tile width must be 64/128/256");
+    if (h->forced_bn != 64 && h->forced_bn != 128 && h->forced_bn != 256 && h->forced_bn != 512)
+      return fail(h, KAPYB_INVALID_ARG, "kapyb_set_matmul_path: tile width must be 64/128/256/512");
   }
   if (s == "auto")
     h->forced_path = PATH_AUTO;
@@ -420,7 +420,8 @@ static kapyb_status launch_tcgen05(kapyb_handle h, const MatmulProblem &p, bool 
   if (b_mn)
     st = make_tmap(h, &tmB, p.b, p.in_dtype, p.N, p.K, p.batch, p.b_s0, p.b_bs, 64, 64);
   else
-    st = make_tmap(h, &tmB, p.b, p.in_dtype, p.K, p.N, p.batch, p.b_s1, p.b_bs, 64, Cfg::BN_CTA);
+    st = make_tmap(h, &tmB, p.b, p.in_dtype, p.K, p.N, p.batch, p.b_s1, p.b_bs, 64,
+                   Cfg::MMA_N / CTAS);
   if (st != KAPYB_OK) return st;
   const uint32_t cw = p.out_dtype == KAPYB_F32 ? 32 : 64;
   for (int o = 0; o < n_out; ++o) {
@@ -444,7 +445,8 @@ static kapyb_status launch_tcgen05(kapyb_handle h, const MatmulProblem &p, bool 
   gp.out_dtype = p.out_dtype;
   gp.n_out = n_out;
   gp.out_col_offset = 0;
-  gp.idesc = ptx::make_idesc_f16(p.in_dtype == KAPYB_BF16, a_mn, b_mn, Cfg::TILE_M, BN);
+  gp.idesc = ptx::make_idesc_f16(p.in_dtype == KAPYB_BF16, a_mn, b_mn, Cfg::TILE_M, Cfg::MMA_N);
+  if (BN == 512) gp.group_m = std::max(1, std::min(gp.tiles_m, 12));
   gp.status = h->status;
   gp.debug = h->debug;
   gp.ep = p.ep;
@@ -645,9 +647,22 @@ static kapyb_status run_matmul(kapyb_handle h, MatmulProblem p, void *const *pee
   // give those problems eight epilogue warps instead of four.
   const bool epi8 = (p.K + 63) / 64 <= 8 || h->forced_epi == 8;
   if (path == PATH_2CTA) {
-    if (h->forced_bn == 0) bn = 256;
+    if (h->forced_bn == 0) {
+      // 256 x 512 pair tiles move a quarter fewer operand bytes per flop than
+      // 256 x 256; take them unless they fill the last wave much worse.
+      const int pairs = std::max(1, h->sm_count / 2);
+      auto wave_eff = [&](int w) {
+        const long long t = static_cast<long long>((p.M + 255) / 256) * ((p.N + w - 1) / w) * p.batch;
+        return static_cast<double>(t) / static_cast<double>((t + pairs - 1) / pairs * pairs);
+      };
+      bn = (p.N >= 512 && wave_eff(512) >= wave_eff(256) - 0.05) ? 512 : 256;
+    }
     if (bn == 64) bn = 128;
     if (bn == 128) return launch_tcgen05<128, 2, 4>(h, p, a_mn, b_mn, outs, n_out, stream);
+    if (bn == 512) {
+      if (h->forced_epi == 4) return launch_tcgen05<512, 2, 4>(h, p, a_mn, b_mn, outs, n_out, stream);
+      return launch_tcgen05<512, 2, 8>(h, p, a_mn, b_mn, outs, n_out, stream);
+    }
     return launch_tcgen05<256, 2, 4>(h, p, a_mn, b_mn, outs, n_out, stream);
   }
   if (epi8 && h->forced_epi != 4) {

@@ -77,7 +77,7 @@ def test_config5_attention_scores(handle, ko):
 
 
 @pytest.mark.parametrize("shape", [(256, 256, 64), (512, 768, 320), (300, 264, 136), (1024, 1024, 1024)])
-@pytest.mark.parametrize("bn", [128, 256])
+@pytest.mark.parametrize("bn", [128, 256, 512])
 @pytest.mark.parametrize("layout", ["nn", "nt"])
 def test_cta_pair_kernel(handle, ko, shape, bn, layout):
     """tcgen05.mma.cta_group::2: two CTAs share one 256-row tile."""
