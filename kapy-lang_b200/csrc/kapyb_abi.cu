@@ -44,6 +44,10 @@ struct kapyb_context {
   int forced_bn = 0;
   int debug = 0;
   int forced_epi = 0;  // 0: by K; 4 or 8: that many epilogue warps (single-CTA kernels)
+  // host-buffer calls: copy streams and events for the chunked pipeline
+  cudaStream_t copy_in = nullptr, copy_out = nullptr;
+  cudaEvent_t ev[2 * 16 + 2] = {};
+  bool pipe_ready = false;
 };
 
 static thread_local std::string g_create_error;
@@ -115,6 +119,12 @@ extern "C" KAPYB_API kapyb_status kapyb_destroy(kapyb_handle h) {
   cudaSetDevice(h->device);
   if (h->workspace) cudaFree(h->workspace);
   if (h->status) cudaFree(h->status);
+  if (h->pipe_ready) {
+    cudaStreamDestroy(h->copy_in);
+    cudaStreamDestroy(h->copy_out);
+    for (cudaEvent_t e : h->ev)
+      if (e) cudaEventDestroy(e);
+  }
   delete h;
   return KAPYB_OK;
 }
@@ -795,7 +805,11 @@ extern "C" KAPYB_API kapyb_status kapyb_matmul_host(kapyb_handle h, const kapyb_
   CUDA_TRY(h, cudaSetDevice(h->device));
   char *w = static_cast<char *>(h->workspace) + skinny_ws;
   char *da = w, *db = da + round256(na), *dc = db + round256(nb), *dbias = dc + round256(nc);
-  CUDA_TRY(h, cudaMemcpyAsync(da, elem_ptr(lhs), na, cudaMemcpyHostToDevice, stream));
+  const bool pipelined = lhs->stride1 == 1 && out->stride1 == 1 && out->stride0 == out->size1 &&
+                         lhs->stride0 == lhs->size1 && lhs->size0 >= 2048 &&
+                         (static_cast<size_t>(lhs->size0) * lhs->size1 >= (1u << 22));
+  if (!pipelined)
+    CUDA_TRY(h, cudaMemcpyAsync(da, elem_ptr(lhs), na, cudaMemcpyHostToDevice, stream));
   CUDA_TRY(h, cudaMemcpyAsync(db, elem_ptr(rhs), nb, cudaMemcpyHostToDevice, stream));
   kapyb_epilogue ep;
   if (epilogue)
@@ -819,6 +833,61 @@ extern "C" KAPYB_API kapyb_status kapyb_matmul_host(kapyb_handle h, const kapyb_
   dr.offset_elems = 0;
   dout.ptr = dc;
   dout.offset_elems = 0;
+  // Large row-major problems: cut the rows into chunks and overlap the upload of
+  // chunk i+1, the GEMM of chunk i and the download of chunk i-1 (PCIe is full
+  // duplex; a single stream would serialise the three).
+  constexpr int kMaxChunks = 16;
+  const bool can_pipe = lhs->stride1 == 1 && out->stride1 == 1 && out->stride0 == out->size1 &&
+                        lhs->stride0 == lhs->size1 && lhs->size0 >= 2048 &&
+                        (static_cast<size_t>(lhs->size0) * lhs->size1 >= (1u << 22));
+  if (can_pipe) {
+    if (!h->pipe_ready) {
+      CUDA_TRY(h, cudaStreamCreateWithFlags(&h->copy_in, cudaStreamNonBlocking));
+      CUDA_TRY(h, cudaStreamCreateWithFlags(&h->copy_out, cudaStreamNonBlocking));
+      for (cudaEvent_t &e : h->ev) CUDA_TRY(h, cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+      h->pipe_ready = true;
+    }
+    const int M = lhs->size0;
+    const int chunks = std::min(kMaxChunks, std::max(2, M / 1024));
+    const int rows_per = ((M + chunks - 1) / chunks + 255) / 256 * 256;
+    cudaEvent_t ev_start = h->ev[2 * kMaxChunks], ev_done = h->ev[2 * kMaxChunks + 1];
+    // B and the bias are already on their way on `stream`; A goes up chunk by chunk
+    CUDA_TRY(h, cudaEventRecord(ev_start, stream));
+    CUDA_TRY(h, cudaStreamWaitEvent(h->copy_in, ev_start, 0));
+    CUDA_TRY(h, cudaStreamWaitEvent(h->copy_out, ev_start, 0));
+    const size_t esz_a = dtype_size(lhs->dtype), esz_c = dtype_size(out->dtype);
+    const char *ha = static_cast<const char *>(elem_ptr(lhs));
+    char *hc = static_cast<char *>(const_cast<void *>(elem_ptr(out)));
+    int n_chunks = 0;
+    for (int r0 = 0; r0 < M; r0 += rows_per, ++n_chunks) {
+      const int rows = std::min(rows_per, M - r0);
+      const size_t a_off = static_cast<size_t>(r0) * lhs->stride0 * esz_a;
+      const size_t c_off = static_cast<size_t>(r0) * out->stride0 * esz_c;
+      CUDA_TRY(h, cudaMemcpyAsync(da + a_off, ha + a_off,
+                                  static_cast<size_t>(rows) * lhs->stride0 * esz_a,
+                                  cudaMemcpyHostToDevice, h->copy_in));
+      CUDA_TRY(h, cudaEventRecord(h->ev[2 * n_chunks], h->copy_in));
+      CUDA_TRY(h, cudaStreamWaitEvent(stream, h->ev[2 * n_chunks], 0));
+      kapyb_tensor2d cl = dl, co = dout;
+      cl.offset_elems = static_cast<int64_t>(r0) * lhs->stride0;
+      cl.size0 = rows;
+      co.offset_elems = static_cast<int64_t>(r0) * out->stride0;
+      co.size0 = rows;
+      kapyb_epilogue cep = ep;
+      if (cep.bias && cep.bias_axis == 0)
+        cep.bias = static_cast<const char *>(cep.bias) + static_cast<size_t>(r0) * dtype_size(cep.bias_dtype);
+      st = run_matmul(h, make_problem(&cl, &dr, nullptr, &co, &cep), nullptr, 0, stream);
+      if (st != KAPYB_OK) return st;
+      CUDA_TRY(h, cudaEventRecord(h->ev[2 * n_chunks + 1], stream));
+      CUDA_TRY(h, cudaStreamWaitEvent(h->copy_out, h->ev[2 * n_chunks + 1], 0));
+      CUDA_TRY(h, cudaMemcpyAsync(hc + c_off, dc + c_off,
+                                  static_cast<size_t>(rows) * out->stride0 * esz_c,
+                                  cudaMemcpyDeviceToHost, h->copy_out));
+    }
+    CUDA_TRY(h, cudaEventRecord(ev_done, h->copy_out));
+    CUDA_TRY(h, cudaStreamWaitEvent(stream, ev_done, 0));
+    return kapyb_check(h, stream);
+  }
   st = run_matmul(h, make_problem(&dl, &dr, nullptr, &dout, &ep), nullptr, 0, stream);
   if (st != KAPYB_OK) return st;
   // Only the elements the kernel wrote are defined; the caller's buffer keeps

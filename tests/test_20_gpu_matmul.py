@@ -176,6 +176,19 @@ def test_host_buffers(handle, ko):
     dev = handle.matmul(A.cuda(), B.cuda(), bias=bias.cuda())
     handle.check()
     assert torch.equal(dev.cpu(), out)
+    # large row-major problems go through the chunked upload / compute / download
+    # pipeline (ragged last chunk, per-row bias offset per chunk)
+    M, N, K = 2304 + 40, 512, 2048
+    A, B = normal((M, K), 15, K ** -0.5), normal((K, N), 16)
+    bias_r = uniform((M,), 17, -0.1, 0.1, torch.float32)
+    out = torch.empty((M, N), dtype=torch.bfloat16).pin_memory()
+    for _ in range(2):
+        out.zero_()
+        handle.matmul_host(A.pin_memory(), B.pin_memory(), out, bias=bias_r, bias_axis=0)
+        dev = handle.matmul(A.cuda(), B.cuda(), bias=bias_r.cuda(), bias_axis=0)
+        handle.check()
+        assert torch.equal(dev.cpu(), out)
+    check(ko, out, A, B, bias=bias_r, bias_axis=0)
 
 
 @pytest.mark.parametrize("n", [8192])
