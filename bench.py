@@ -36,11 +36,10 @@ UNIT = "TFLOP/s"
 FLOPS = 2.0 * M * N * K                       # algorithmic FLOPs of one step
 ALG_BYTES = 3 * M * N * 2 + N * 2             # A + B + C (bf16) + bias
 CPU_SAMPLE_ROWS = 512                         # rows of the output the CPU arm computes per step
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant
-# kernel.  Captured with ncu on the M=4096, N=8192, K=4096 case of the same kernel
-# (222.1 MB, profiles/gemm_tcgen05_2cta_bf16_4096x8192x4096.txt) and scaled by the
-# units processed (tile x k-block count: 4x) to the 8192^3 launch.
-NCU_TRAFFIC_BYTES = 4 * (173_657_600 + 48_438_016)
+# dram__bytes_read.sum + dram__bytes_write.sum of one full-size launch of the
+# dominant kernel, from a one-pass ncu capture of this benchmark (command and
+# figures in profiles/gemm_tcgen05_2cta_256x512_bf16_8192x8192x4096.txt).
+NCU_TRAFFIC_BYTES = 868_958_720 + 119_379_200
 
 
 def load_peaks():
@@ -467,7 +466,7 @@ def run_profile_case(args):
     g = torch.Generator(device="cpu").manual_seed(1)
     case = args.profile_case
     if case == "gemm":
-        m, n, k = 4096, 8192, 4096
+        m, n, k = 8192, 8192, 4096   # same tile grid as the benchmark, half of its K loop
         A = (torch.randn(m, k, generator=g) * k ** -0.5).to(torch.bfloat16).cuda()
         B = (torch.randn(k, n, generator=g) * k ** -0.5).to(torch.bfloat16).cuda()
         bias = torch.zeros(n, dtype=torch.bfloat16, device="cuda")

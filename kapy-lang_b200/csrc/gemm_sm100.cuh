@@ -147,6 +147,8 @@ __device__ __forceinline__ void add_bias32(float (&f)[32], const uint4 *bp) {
 struct EpiTile {
   int b, m0, n0, row, lane, cpart;
   int col_begin, col_end;  // tile columns to drain in this call (one accumulator slot)
+  uint32_t tempty_addr;    // barrier that returns the slot to the MMA thread
+  bool remote_arrive;      // the barrier lives in the pair's leader CTA
   uint32_t t_row;   // TMEM address of this warp's lanes at tile column 0
   uint8_t *stg;     // this warp's two 4 KB staging buffers
   bool bias_col, bias_fast;
@@ -155,8 +157,9 @@ struct EpiTile {
 
 // OUTK: 0 f32, 1/2 bf16 rn/rz, 3/4 f16 rn/rz.  PLAIN: the epilogue is only the
 // scale (no bias, addend or activation), so none of those are even tested.
+// Returns whether the slot was handed back (false when this warp had no chunk).
 template <int BN, int EPI, int OUTK, bool PLAIN>
-__device__ __forceinline__ void epilogue_tile(const GemmParams &p, const TmapArray &tmC,
+__device__ __forceinline__ bool epilogue_tile(const GemmParams &p, const TmapArray &tmC,
                                               const EpiTile &t, int &buf) {
   constexpr bool OUT32 = OUTK == 0;
   constexpr int CW = OUT32 ? 32 : 64;  // output columns per 128-byte staging row
@@ -164,6 +167,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams &p, const TmapArr
   constexpr int CSTEP = EPI / 4;
   constexpr int C_BUFS = (BN == 512 && EPI == 8) ? 1 : 2;
   const int lane = t.lane;
+  bool handed_back = false;
   for (int c = t.col_begin / CW + t.cpart; c < t.col_end / CW; c += CSTEP) {
     const int nc = t.n0 + c * CW;
     if (nc >= p.N) break;
@@ -178,6 +182,19 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams &p, const TmapArr
     if (lane == 0) ptx::tma_store_wait_read<C_BUFS - 1>();
     __syncwarp();
     ptx::tmem_ld_wait();
+    if (c + CSTEP >= t.col_end / CW || t.n0 + (c + CSTEP) * CW >= p.N) {
+      // That was this warp's last read of the slot: hand it back now, so the next
+      // tile's MMAs do not wait for the arithmetic and the stores below.
+      handed_back = true;
+      ptx::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        if (t.remote_arrive)
+          ptx::mbar_arrive_cluster(t.tempty_addr);
+        else
+          ptx::mbar_arrive(t.tempty_addr);
+      }
+    }
     uint8_t *srow = sbuf + lane * 128;
 #pragma unroll
     for (int h = 0; h < NH; ++h) {
@@ -239,6 +256,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams &p, const TmapArr
     }
     buf ^= 1;
   }
+  return handed_back;
 }
 
 template <int BN, int CTAS, int EPI>
@@ -492,8 +510,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
         ptx::tc_fence_after();
         const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
                                (Cfg::HALVES == 2 ? 0u : static_cast<uint32_t>(acc * BN));
+        bool handed_back = false;
+        const uint32_t slot_bar = tempty_leader + static_cast<uint32_t>(slot * 8);
         if (m0 < p.M && !(p.debug & 4)) {
           EpiTile et;
+          et.tempty_addr = slot_bar;
+          et.remote_arrive = CTAS == 2;
           et.b = b;
           et.m0 = m0;
           et.n0 = n0;
@@ -512,27 +534,28 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
           // One specialised copy of the chunk loop per (output kind, plain/full
           // epilogue): the switch runs once per slot, the loops inside are tight.
           switch (out_kind * 2 + (plain ? 1 : 0)) {
-          case 0: epilogue_tile<BN, EPI, 0, false>(p, tmC, et, buf); break;
-          case 1: epilogue_tile<BN, EPI, 0, true>(p, tmC, et, buf); break;
-          case 2: epilogue_tile<BN, EPI, 1, false>(p, tmC, et, buf); break;
-          case 3: epilogue_tile<BN, EPI, 1, true>(p, tmC, et, buf); break;
-          case 4: epilogue_tile<BN, EPI, 2, false>(p, tmC, et, buf); break;
-          case 5: epilogue_tile<BN, EPI, 2, true>(p, tmC, et, buf); break;
-          case 6: epilogue_tile<BN, EPI, 3, false>(p, tmC, et, buf); break;
-          case 7: epilogue_tile<BN, EPI, 3, true>(p, tmC, et, buf); break;
-          case 8: epilogue_tile<BN, EPI, 4, false>(p, tmC, et, buf); break;
-          default: epilogue_tile<BN, EPI, 4, true>(p, tmC, et, buf); break;
+          case 0: handed_back = epilogue_tile<BN, EPI, 0, false>(p, tmC, et, buf); break;
+          case 1: handed_back = epilogue_tile<BN, EPI, 0, true>(p, tmC, et, buf); break;
+          case 2: handed_back = epilogue_tile<BN, EPI, 1, false>(p, tmC, et, buf); break;
+          case 3: handed_back = epilogue_tile<BN, EPI, 1, true>(p, tmC, et, buf); break;
+          case 4: handed_back = epilogue_tile<BN, EPI, 2, false>(p, tmC, et, buf); break;
+          case 5: handed_back = epilogue_tile<BN, EPI, 2, true>(p, tmC, et, buf); break;
+          case 6: handed_back = epilogue_tile<BN, EPI, 3, false>(p, tmC, et, buf); break;
+          case 7: handed_back = epilogue_tile<BN, EPI, 3, true>(p, tmC, et, buf); break;
+          case 8: handed_back = epilogue_tile<BN, EPI, 4, false>(p, tmC, et, buf); break;
+          default: handed_back = epilogue_tile<BN, EPI, 4, true>(p, tmC, et, buf); break;
           }
         }
-        // All of this warp's TMEM reads of the slot are done: hand it back.
-        ptx::tc_fence_before();
-        __syncwarp();
-        if (lane == 0) {
-          const uint32_t bar = tempty_leader + static_cast<uint32_t>(slot * 8);
-          if constexpr (CTAS == 2)
-            ptx::mbar_arrive_cluster(bar);
-          else
-            ptx::mbar_arrive(bar);
+        if (!handed_back) {
+          // nothing was read (rows or columns outside the problem): return the slot
+          ptx::tc_fence_before();
+          __syncwarp();
+          if (lane == 0) {
+            if constexpr (CTAS == 2)
+              ptx::mbar_arrive_cluster(slot_bar);
+            else
+              ptx::mbar_arrive(slot_bar);
+          }
         }
       }
       if (!alive) break;

@@ -665,7 +665,9 @@ static kapyb_status run_matmul(kapyb_handle h, MatmulProblem p, void *const *pee
         const long long t = static_cast<long long>((p.M + 255) / 256) * ((p.N + w - 1) / w) * p.batch;
         return static_cast<double>(t) / static_cast<double>((t + pairs - 1) / pairs * pairs);
       };
-      bn = (p.N >= 512 && wave_eff(512) >= wave_eff(256) - 0.05) ? 512 : 256;
+      // ... and only for long K loops: the halves share TMEM, so the epilogue of a
+      // tile is not hidden behind the next tile's main loop.
+      bn = (p.N >= 512 && p.K >= 4096 && wave_eff(512) >= wave_eff(256) - 0.05) ? 512 : 256;
     }
     if (bn == 64) bn = 128;
     if (bn == 128) return launch_tcgen05<128, 2, 4>(h, p, a_mn, b_mn, outs, n_out, stream);
