@@ -53,7 +53,10 @@ typedef enum {
 typedef enum {
   KAPYB_F16 = 0,
   KAPYB_BF16 = 1,
-  KAPYB_F32 = 2
+  KAPYB_F32 = 2,
+  /* matmul operands only (MatmulImplWay MMA_M16N8K16_F8, Kapy.cpp:547-564) */
+  KAPYB_F8E4M3 = 3,
+  KAPYB_F8E5M2 = 4
 } kapyb_dtype;
 
 /* Enums.td:52-61 -- value returned for out-of-bounds lanes of ld_global. */
@@ -219,7 +222,9 @@ KAPYB_API kapyb_status kapyb_reserve_workspace(kapyb_handle h, size_t bytes);
 
 /* kapy.matmul (Ops.td:416-439) at whole-problem scope:
  *   out[M,N] = epilogue( lhs[M,K] . rhs[K,N] (+ acc[M,N]) ).
- * lhs/rhs: f16 or bf16, same dtype (Kapy.cpp:484-487); either may be row- or
+ * lhs/rhs: both f16, both bf16, both f32 (multiplied as tf32: the tensor core
+ * reads the upper 19 bits of each operand, as mma_m16n8k8_tf32 does), or each
+ * one of the two fp8 types (Kapy.cpp:484-487, :530-564); either may be row- or
  * column-major (one unit stride, CoalesceAccess.cpp:32-40).  `acc` may be NULL
  * (= zero accumulator, the arith.constant dense<0.0> of matmul.mlir:6) or an
  * f16/f32 [M,N] tensor added in fp32.  out: f16, bf16 or f32.
@@ -348,6 +353,13 @@ KAPYB_API const char *kapyb_last_kernel(kapyb_handle h);
 
 /* Number of kernels this handle has launched since creation. */
 KAPYB_API int64_t kapyb_launch_count(kapyb_handle h);
+
+/* SM cycles and wall nanoseconds the MMA-issuing thread of the first CTA spent
+ * in its tile loop during the last tcgen05 matmul launched with debug bit 7
+ * (":d128" in kapyb_set_matmul_path); cycles / nanoseconds is the SM clock in
+ * GHz while the kernel ran.  Synchronises `stream`.  For profiling. */
+KAPYB_API kapyb_status kapyb_probe_clock(kapyb_handle h, void *stream, uint32_t *cycles,
+                                         uint32_t *nanoseconds);
 
 /* Forces a kernel family for matmul ("auto", "1cta", "2cta", "skinny",
  * "simt"); for tests and profiling. */

@@ -14,7 +14,7 @@ SO_PATH = os.path.join(_HERE, "libkapyb.so")
 # kapyb_status
 OK, INVALID_ARG, UNSUPPORTED, CUDA_ERROR, NCCL_ERROR, TIMEOUT = range(6)
 # kapyb_dtype
-F16, BF16, F32 = 0, 1, 2
+F16, BF16, F32, F8E4M3, F8E5M2 = 0, 1, 2, 3, 4
 # kapyb_padding (Enums.td:52-61)
 PAD_ZERO, PAD_QNAN, PAD_PINF, PAD_NINF = 0, 1, 2, 3
 # kapyb_rounding (Enums.td:102-109)
@@ -85,6 +85,8 @@ PROTOTYPES = {
                                     C.POINTER(C.c_int64), C.POINTER(C.c_int64)]),
     "kapyb_last_kernel": (C.c_char_p, [C.c_void_p]),
     "kapyb_launch_count": (C.c_int64, [C.c_void_p]),
+    "kapyb_probe_clock": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(C.c_uint32),
+                                    C.POINTER(C.c_uint32)]),
     "kapyb_set_matmul_path": (C.c_int, [C.c_void_p, C.c_char_p]),
 }
 

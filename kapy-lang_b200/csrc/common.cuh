@@ -5,6 +5,7 @@
 
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
+#include <cuda_fp8.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -15,7 +16,9 @@ namespace kapyb {
 // Status word layout (one uint32 in device memory per handle).
 enum : uint32_t { kStatusOk = 0, kStatusTimeout = 1 };
 
-__host__ __device__ inline int dtype_size(int dtype) { return dtype == KAPYB_F32 ? 4 : 2; }
+__host__ __device__ inline int dtype_size(int dtype) {
+  return dtype == KAPYB_F32 ? 4 : (dtype == KAPYB_F8E4M3 || dtype == KAPYB_F8E5M2) ? 1 : 2;
+}
 
 // ---- primitives with the reference's instruction choice --------------------
 
@@ -127,8 +130,17 @@ __device__ __forceinline__ float cvt_16_to_f32(uint16_t h, int dtype) {
   return __half2float(__ushort_as_half(h));
 }
 
+// fp8 -> f32, exact (E4M3 has no infinities; its all-ones pattern is NaN).
+__device__ __forceinline__ float cvt_fp8_to_f32(uint8_t v, int dtype) {
+  const __half_raw h = __nv_cvt_fp8_to_halfraw(
+      static_cast<__nv_fp8_storage_t>(v), dtype == KAPYB_F8E4M3 ? __NV_E4M3 : __NV_E5M2);
+  return __half2float(__half(h));
+}
+
 __device__ __forceinline__ float load_as_f32(const void *base, int dtype, int64_t idx) {
   if (dtype == KAPYB_F32) return static_cast<const float *>(base)[idx];
+  if (dtype == KAPYB_F8E4M3 || dtype == KAPYB_F8E5M2)
+    return cvt_fp8_to_f32(static_cast<const uint8_t *>(base)[idx], dtype);
   return cvt_16_to_f32(static_cast<const uint16_t *>(base)[idx], dtype);
 }
 

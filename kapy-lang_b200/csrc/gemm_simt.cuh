@@ -17,7 +17,8 @@ struct SimtGemmParams {
   long long a_s0, a_s1, a_bs;  // element strides (row, column, batch)
   long long b_s0, b_s1, b_bs;
   long long c_s0, c_s1, c_bs;
-  int in_dtype, out_dtype;
+  int in_dtype, in_dtype_b, out_dtype;
+  int tf32;  // f32 operands multiplied as tf32: the low 13 mantissa bits are dropped
   EpilogueArgs ep;
 };
 
@@ -30,8 +31,6 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const SimtGemmParams p) 
   const int bz = blockIdx.z;
   const int m0 = blockIdx.y * kSimtTile, n0 = blockIdx.x * kSimtTile;
   const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
-  const uint16_t *a16 = static_cast<const uint16_t *>(p.a);
-  const uint16_t *b16 = static_cast<const uint16_t *>(p.b);
   float acc[4][4];
 #pragma unroll
   for (int i = 0; i < 4; ++i)
@@ -44,12 +43,14 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const SimtGemmParams p) 
       const int gm = m0 + mm, gk = k0 + kk;
       float va = 0.0f;
       if (gm < p.M && gk < p.K)
-        va = cvt_16_to_f32(a16[bz * p.a_bs + gm * p.a_s0 + gk * p.a_s1], p.in_dtype);
+        va = load_as_f32(p.a, p.in_dtype, bz * p.a_bs + gm * p.a_s0 + gk * p.a_s1);
+      if (p.tf32) va = __uint_as_float(__float_as_uint(va) & 0xffffe000u);
       sa[kk][mm] = va;
       const int gn = n0 + mm;
       float vb = 0.0f;
       if (gn < p.N && gk < p.K)
-        vb = cvt_16_to_f32(b16[bz * p.b_bs + gk * p.b_s0 + gn * p.b_s1], p.in_dtype);
+        vb = load_as_f32(p.b, p.in_dtype_b, bz * p.b_bs + gk * p.b_s0 + gn * p.b_s1);
+      if (p.tf32) vb = __uint_as_float(__float_as_uint(vb) & 0xffffe000u);
       sb[kk][mm] = vb;
     }
     __syncthreads();

@@ -43,6 +43,7 @@ struct SkinnyParams {
   uint32_t *counters;  // [n_tiles][4], zero between launches
   uint32_t idesc;
   uint32_t *status;
+  uint32_t wait_limit_us;  // 0: the default limit of a bounded wait
   EpilogueArgs ep;
 };
 
@@ -82,7 +83,8 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       ptx::mbar_init(ptx::smem_u32(&tfull_bar[a]), 1);
       ptx::mbar_init(ptx::smem_u32(&tempty_bar[a]), 4);
     }
-    *abort_flag = 0u;
+    abort_flag[0] = 0u;
+    abort_flag[1] = p.wait_limit_us;
     ptx::fence_barrier_init();
   }
   if (warp == 0 && lane == 0) {

@@ -45,9 +45,25 @@ struct GemmParams {
   int n_out;             // number of output tensor maps (1, or n_peers for push)
   int out_col_offset;    // column offset of this shard inside each output
   uint32_t idesc;
+  // Operand element width: a shared-memory row is always 128 bytes, so the K
+  // extent of a stage and of a 128-byte MN chunk is 128 / size elements.
+  int kind;            // tcgen05.mma kind: 0 f16/bf16, 1 tf32, 2 fp8
+  int bk_elems;        // K elements per stage: 64 (16-bit), 32 (f32), 128 (fp8)
+  uint32_t mn_lbo;     // bytes of one MN-major chunk: bk_elems rows x 128 bytes
+  uint32_t mn_kadv;    // bytes one MMA K step (32 bytes of K) advances in an MN-major tile
+  uint32_t mn_sbo;     // bytes between K-row groups of an MN-major tile: 8 rows (1024), or
+                       // 4 rows (512) in the 32-byte-unit swizzle 32-bit operands need
+  uint32_t mn_layout;  // descriptor layout type of an MN-major tile: 2, or 1 for 32-bit operands
   uint32_t *status;
+  uint32_t wait_limit_us;  // 0: the default limit of a bounded wait
   int debug;  // profiling aid (results are garbage): bit0 skip loads, bit1 skip MMAs,
-              // bit2 skip the epilogue body, bit3 skip only the TMA stores
+              // bit2 skip the epilogue body, bit3 skip only the TMA stores,
+              // bit4 the producer never loads nor signals (every other role's wait
+              // then runs out: the test of the time-out path),
+              // bit5 free-running MMAs over whatever shared memory holds (no producer,
+              // no stage barriers): an issue-rate probe,
+              // bit7 the first CTA's MMA thread records cycles and nanoseconds of its
+              // tile loop in status[2], status[3]
   EpilogueArgs ep;
 };
 
@@ -155,6 +171,74 @@ struct EpiTile {
   float bias_row;
 };
 
+// The fused arithmetic on 32 consecutive accumulator columns of one row
+// (columns col0 .. col0+31 of row t.row): scale, bias, addend, activation.
+// LEVEL 0: scale only; 1: scale and bias; 2: scale, bias, addend, activation.
+template <int LEVEL>
+__device__ __forceinline__ void finish32(const GemmParams &p, const EpiTile &t, float (&f)[32],
+                                         int col0) {
+  const int lane = t.lane;
+  if (p.ep.alpha != 1.0f) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) f[i] *= p.ep.alpha;
+  }
+  if constexpr (LEVEL >= 1) {
+    if (t.bias_col) {
+      if (t.bias_fast && col0 + 32 <= p.N) {
+        const uint4 *bp =
+            reinterpret_cast<const uint4 *>(static_cast<const uint16_t *>(p.ep.bias) + col0);
+        if (p.ep.bias_dtype == KAPYB_BF16)
+          add_bias32<KAPYB_BF16>(f, bp);
+        else
+          add_bias32<KAPYB_F16>(f, bp);
+      } else {
+        float bias_lane = 0.0f;
+        if (col0 + lane < p.N) bias_lane = load_as_f32(p.ep.bias, p.ep.bias_dtype, col0 + lane);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) f[i] += __shfl_sync(0xffffffffu, bias_lane, i);
+      }
+    } else if (p.ep.bias != nullptr) {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) f[i] += t.bias_row;
+    }
+  }
+  if constexpr (LEVEL >= 2) {
+    if (p.ep.acc != nullptr && t.row < p.M) {
+      const long long base = static_cast<long long>(t.b) * p.ep.acc_batch_stride +
+                             static_cast<long long>(t.row) * p.ep.acc_stride0;
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (col0 + i < p.N)
+          f[i] += load_as_f32(p.ep.acc, p.ep.acc_dtype,
+                              base + static_cast<long long>(col0 + i) * p.ep.acc_stride1);
+    }
+    if (p.ep.activation != KAPYB_ACT_NONE) {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) f[i] = apply_activation(p.ep.activation, f[i]);
+    }
+  }
+}
+
+// 32 finished columns -> 16 packed bf16 or f16 pairs, rounded to nearest.
+__device__ __forceinline__ void pack32_rn(const float (&f)[32], uint32_t (&w)[16], bool bf16) {
+#pragma unroll
+  for (int i = 0; i < 16; ++i)
+    w[i] = bf16 ? cvt_pack2_t<KAPYB_BF16, 1>(f[2 * i], f[2 * i + 1])
+                : cvt_pack2_t<KAPYB_F16, 1>(f[2 * i], f[2 * i + 1]);
+}
+
+// 16 packed pairs (32 columns, half h of a 64-column chunk) -> the row's slot in
+// the swizzled staging tile.
+__device__ __forceinline__ void stage_packed16(uint8_t *srow, const uint32_t (&w)[16], int lane,
+                                               int h) {
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const uint4 q = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+    const int jj = h * 4 + j;
+    *reinterpret_cast<uint4 *>(srow + ((jj ^ (lane & 7)) << 4)) = q;
+  }
+}
+
 // OUTK: 0 f32, 1/2 bf16 rn/rz, 3/4 f16 rn/rz.  PLAIN: the epilogue is only the
 // scale (no bias, addend or activation), so none of those are even tested.
 // Returns whether the slot was handed back (false when this warp had no chunk).
@@ -202,43 +286,7 @@ __device__ __forceinline__ bool epilogue_tile(const GemmParams &p, const TmapArr
       float f[32];
 #pragma unroll
       for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(v[h][i]);
-      if (p.ep.alpha != 1.0f) {
-#pragma unroll
-        for (int i = 0; i < 32; ++i) f[i] *= p.ep.alpha;
-      }
-      if constexpr (!PLAIN) {
-        if (t.bias_col) {
-          if (t.bias_fast && col0 + 32 <= p.N) {
-            const uint4 *bp =
-                reinterpret_cast<const uint4 *>(static_cast<const uint16_t *>(p.ep.bias) + col0);
-            if (p.ep.bias_dtype == KAPYB_BF16)
-              add_bias32<KAPYB_BF16>(f, bp);
-            else
-              add_bias32<KAPYB_F16>(f, bp);
-          } else {
-            float bias_lane = 0.0f;
-            if (col0 + lane < p.N) bias_lane = load_as_f32(p.ep.bias, p.ep.bias_dtype, col0 + lane);
-#pragma unroll
-            for (int i = 0; i < 32; ++i) f[i] += __shfl_sync(0xffffffffu, bias_lane, i);
-          }
-        } else if (p.ep.bias != nullptr) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) f[i] += t.bias_row;
-        }
-        if (p.ep.acc != nullptr && t.row < p.M) {
-          const long long base = static_cast<long long>(t.b) * p.ep.acc_batch_stride +
-                                 static_cast<long long>(t.row) * p.ep.acc_stride0;
-#pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (col0 + i < p.N)
-              f[i] += load_as_f32(p.ep.acc, p.ep.acc_dtype,
-                                  base + static_cast<long long>(col0 + i) * p.ep.acc_stride1);
-        }
-        if (p.ep.activation != KAPYB_ACT_NONE) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) f[i] = apply_activation(p.ep.activation, f[i]);
-        }
-      }
+      finish32<PLAIN ? 0 : 2>(p, t, f, col0);
       // Row `lane` of the staging tile, 128-byte swizzle: 16-byte chunk j of row
       // r lives at chunk position j ^ (r & 7).
       if constexpr (OUTK == 0) stage_half_f32(srow, f, lane);
@@ -257,6 +305,170 @@ __device__ __forceinline__ bool epilogue_tile(const GemmParams &p, const TmapArr
     buf ^= 1;
   }
   return handed_back;
+}
+
+// Two-half tiles (BN = 512) with a 16-bit output: the accumulator fills TMEM, so
+// the next tile's MMAs wait for the drain.  Staging chunk by chunk through the
+// one 4 KB buffer would keep TMEM busy for the whole store sequence; instead the
+// warp pulls its four 64-column chunks (two per half) into packed registers,
+// hands each half back as soon as its last load has landed, and stores from the
+// registers afterwards, under the next tile's main loop.  Covers the epilogues
+// that are a scale and an optional bias, rounded to nearest; anything more goes
+// chunk by chunk.  Returns false when a wait ran out.
+// One copy serves bf16 and f16 outputs, with or without a bias: separate copies
+// inlined into one kernel made the register allocator spill.
+template <int EPI>
+__device__ __forceinline__ bool epilogue_two_halves(const GemmParams &p, const TmapArray &tmC,
+                                                    EpiTile &t, uint32_t tfull0, uint32_t parity,
+                                                    volatile uint32_t *abort_flag, bool active,
+                                                    bool bf16) {
+  static_assert(EPI == 8, "register drain: eight epilogue warps");
+  const int lane = t.lane;
+  uint8_t *srow = t.stg + lane * 128;
+  // Chunk i = hh*2 + j covers tile columns (hh*4 + cpart + 2*j) * 64 ..  Chunk 0
+  // goes straight through the (idle) staging buffer; 1..3 wait in registers.
+  uint32_t pk[3][2][16];
+  auto store_chunk = [&](int nc) {
+    ptx::fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0 && !(p.debug & 8)) {
+      for (int o = 0; o < p.n_out; ++o)
+        ptx::tma_store_3d(&tmC.m[o], ptx::smem_u32(t.stg), p.out_col_offset + nc, t.m0, t.b);
+      ptx::tma_store_commit();
+    }
+  };
+  // A 16-bit column bias is fetched before the accumulator is awaited, so its
+  // latency hides behind the main loop: lane l keeps the eight values of columns
+  // (l & 7) * 8 .. +7 of chunk l >> 3; the pieces below pick them up by shuffle.
+  const bool bias_regs = t.bias_col && t.bias_fast;
+  const bool bias_bf16 = p.ep.bias_dtype == KAPYB_BF16;
+  uint4 bv = make_uint4(0u, 0u, 0u, 0u);
+  if (bias_regs) {
+    const int ci = lane >> 3;
+    const int col = t.n0 + ((ci >> 1) * 4 + t.cpart + 2 * (ci & 1)) * 64 + (lane & 7) * 8;
+    const uint16_t *bp = static_cast<const uint16_t *>(p.ep.bias);
+    if (col + 8 <= p.N) {
+      bv = __ldg(reinterpret_cast<const uint4 *>(bp + col));
+    } else {
+      uint32_t w[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+      for (int e = 0; e < 8; ++e)
+        if (col + e < p.N) w[e >> 1] |= static_cast<uint32_t>(__ldg(bp + col + e)) << (16 * (e & 1));
+      bv = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+  }
+  bool alive = true;  // false once a wait has run out: nothing more is read or stored
+  auto hand_back = [&](int hh) {
+    ptx::tc_fence_before();
+    __syncwarp();
+    if (lane == 0) {
+      if (t.remote_arrive)
+        ptx::mbar_arrive_cluster(t.tempty_addr + hh * 8);
+      else
+        ptx::mbar_arrive(t.tempty_addr + hh * 8);
+    }
+  };
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int hh = i >> 1, j = i & 1;
+    if (j == 0) {
+      if (!ptx::mbar_wait(tfull0 + hh * 8, parity, abort_flag)) alive = false;
+      ptx::tc_fence_after();
+    }
+    const int c = hh * 4 + t.cpart + 2 * j;
+    const int nc = t.n0 + c * 64;
+    const bool valid = alive && active && nc < p.N;
+    // 32 columns at a time: the registers hold three packed chunks already
+    uint32_t v[32];
+    if (valid) {
+      if (i == 0) {
+        // the previous tile's last store has long finished reading the buffer
+        if (lane == 0) ptx::tma_store_wait_read<0>();
+        __syncwarp();
+      }
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        ptx::tmem_ld_32x32(t.t_row + static_cast<uint32_t>(c * 64 + h * 32), v);
+        ptx::tmem_ld_wait();
+        if (j == 1 && h == 1) hand_back(hh);  // this warp's last read of half hh
+        float f[32];
+#pragma unroll
+        for (int k = 0; k < 32; ++k) f[k] = __uint_as_float(v[k]);
+        if (bias_regs) {
+          // the piece's 32 bias values sit in lanes i*8 + h*4 .. +3, eight per lane
+          if (p.ep.alpha != 1.0f) {
+#pragma unroll
+            for (int k = 0; k < 32; ++k) f[k] *= p.ep.alpha;
+          }
+#pragma unroll
+          for (int jj = 0; jj < 4; ++jj) {
+            const int src = i * 8 + h * 4 + jj;
+            const uint32_t ws[4] = {__shfl_sync(0xffffffffu, bv.x, src),
+                                    __shfl_sync(0xffffffffu, bv.y, src),
+                                    __shfl_sync(0xffffffffu, bv.z, src),
+                                    __shfl_sync(0xffffffffu, bv.w, src)};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              float lo, hi;
+              if (bias_bf16)
+                unpack2_16<KAPYB_BF16>(ws[e], lo, hi);
+              else
+                unpack2_16<KAPYB_F16>(ws[e], lo, hi);
+              f[8 * jj + 2 * e] += lo;
+              f[8 * jj + 2 * e + 1] += hi;
+            }
+          }
+        } else {
+          finish32<1>(p, t, f, nc + h * 32);
+        }
+        if (i == 0) {
+          uint32_t w[16];
+          pack32_rn(f, w, bf16);
+          stage_packed16(srow, w, lane, h);
+        } else {
+          pack32_rn(f, pk[i == 0 ? 0 : i - 1][h], bf16);
+        }
+      }
+      if (i == 0) store_chunk(nc);
+    } else if (j == 1) {
+      hand_back(hh);
+    }
+  }
+#pragma unroll
+  for (int i = 1; i < 4; ++i) {
+    const int c = (i >> 1) * 4 + t.cpart + 2 * (i & 1);
+    const int nc = t.n0 + c * 64;
+    if (alive && active && nc < p.N) {
+      if (lane == 0) ptx::tma_store_wait_read<0>();
+      __syncwarp();
+      stage_packed16(srow, pk[i - 1][0], lane, 0);
+      stage_packed16(srow, pk[i - 1][1], lane, 1);
+      store_chunk(nc);
+    }
+  }
+  return alive;
+}
+
+// The MMAs of one K block (four K steps of 32 bytes; with two halves, both
+// accumulators per step, sharing the A descriptor).  Descriptors arrive as
+// (low word of K step 0, constant high word, low-word increment per K step);
+// this CTA's B bytes of half hh start (MMA_N / CTAS) rows of 128 bytes after
+// those of half hh-1, in either layout and for any element width.
+template <int CTAS, int HALVES, int MMA_N, int KIND>
+__device__ __forceinline__ void issue_kblock(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi,
+                                             uint32_t a_kstep, uint32_t b_lo, uint32_t b_hi,
+                                             uint32_t b_kstep, uint32_t idesc, uint32_t first) {
+  constexpr uint32_t kHalfStep = (MMA_N / CTAS) * 128 / 16;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const uint64_t adesc = (static_cast<uint64_t>(a_hi) << 32) | (a_lo + k * a_kstep);
+#pragma unroll
+    for (int hh = 0; hh < HALVES; ++hh) {
+      const uint64_t bdesc =
+          (static_cast<uint64_t>(b_hi) << 32) | (b_lo + k * b_kstep + hh * kHalfStep);
+      ptx::umma_k<CTAS, KIND>(d_tmem + hh * MMA_N, adesc, bdesc, idesc, k == 0 ? first : 1u);
+    }
+  }
 }
 
 template <int BN, int CTAS, int EPI>
@@ -296,7 +508,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       ptx::mbar_init(ptx::smem_u32(&tfull_bar[a]), 1);          // one tcgen05.commit
       ptx::mbar_init(ptx::smem_u32(&tempty_bar[a]), EPI * CTAS);  // one arrival per epilogue warp
     }
-    *abort_flag = 0u;
+    abort_flag[0] = 0u;
+    abort_flag[1] = p.wait_limit_us;
     ptx::fence_barrier_init();
   }
   if (warp == 0 && lane == 0) {
@@ -322,7 +535,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
-    for (int tile = unit; tile < p.num_tiles && ok; tile += unit_step) {
+    for (int tile = unit; tile < p.num_tiles && ok && !(p.debug & (16 | 32)); tile += unit_step) {
       int b, mb, nb;
       decode_tile(p, tile, b, mb, nb);
       const int m0 = mb * Cfg::TILE_M + static_cast<int>(rank) * Cfg::BM;
@@ -335,7 +548,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
           ok = false;
           break;
         }
-        const int k0 = kb * Cfg::BK;
+        const int k0 = kb * p.bk_elems;
+        const int ce = p.bk_elems;                       // elements per 128-byte MN chunk
+        const int a_chunks = Cfg::BM / ce;
+        const int b_chunks = Cfg::BN_CTA / ce;
         const uint32_t a_dst = ptx::smem_u32(sA + stage * Cfg::A_BYTES);
         const uint32_t b_dst = ptx::smem_u32(sB + stage * Cfg::B_BYTES);
         if (p.debug & 1) {
@@ -346,16 +562,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
           if (!p.a_mn_major) {
             ptx::tma_load_3d(a_dst, &tmA, fb, k0, m0, b);
           } else {
-#pragma unroll
-            for (int j = 0; j < Cfg::BM / 64; ++j)
-              ptx::tma_load_3d(a_dst + j * 8192, &tmA, fb, m0 + 64 * j, k0, b);
+            for (int j = 0; j < a_chunks; ++j)
+              ptx::tma_load_3d(a_dst + j * p.mn_lbo, &tmA, fb, m0 + ce * j, k0, b);
           }
           if (!p.b_mn_major) {
             ptx::tma_load_3d(b_dst, &tmB, fb, k0, nB0, b);
           } else {
-#pragma unroll
-            for (int j = 0; j < Cfg::BN_CTA / 64; ++j)
-              ptx::tma_load_3d(b_dst + j * 8192, &tmB, fb, nB0 + 64 * j, k0, b);
+            for (int j = 0; j < b_chunks; ++j)
+              ptx::tma_load_3d(b_dst + j * p.mn_lbo, &tmB, fb, nB0 + ce * j, k0, b);
           }
           (void)kGroupCols;
         } else {
@@ -368,9 +582,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
           if (!p.a_mn_major) {
             ptx::tma_load_3d_pair(a_dst, &tmA, fb, k0, m0, b);
           } else {
-#pragma unroll
-            for (int j = 0; j < Cfg::BM / 64; ++j)
-              ptx::tma_load_3d_pair(a_dst + j * 8192, &tmA, fb, m0 + 64 * j, k0, b);
+            for (int j = 0; j < a_chunks; ++j)
+              ptx::tma_load_3d_pair(a_dst + j * p.mn_lbo, &tmA, fb, m0 + ce * j, k0, b);
           }
           if (!p.b_mn_major) {
             // one box of kGroupCols rows per half
@@ -379,11 +592,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
               ptx::tma_load_3d_pair(b_dst + hh * (kGroupCols * 128), &tmB, fb, k0,
                                     nB0 + hh * Cfg::MMA_N, b);
           } else {
-#pragma unroll
-            for (int j = 0; j < Cfg::BN_CTA / 64; ++j) {
-              const int hh = (j * 64) / kGroupCols, within = (j * 64) % kGroupCols;
-              ptx::tma_load_3d_pair(b_dst + j * 8192, &tmB, fb, nB0 + hh * Cfg::MMA_N + within,
-                                    k0, b);
+            for (int j = 0; j < b_chunks; ++j) {
+              const int hh = (j * ce) / kGroupCols, within = (j * ce) % kGroupCols;
+              ptx::tma_load_3d_pair(b_dst + j * p.mn_lbo, &tmB, fb,
+                                    nB0 + hh * Cfg::MMA_N + within, k0, b);
             }
           }
         }
@@ -396,18 +608,40 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
   } else if (warp == 1 && lane == 0 && rank == 0) {
     // ---------------------------------------------------------- MMA issuer
     // K-major operand: rows are 128 bytes, 8-row groups 1024 bytes apart; one
-    // UMMA K step (16 elements) is 32 bytes along the row.
-    // MN-major operand: 64-element (128-byte) MN chunks 8192 bytes apart, K
-    // rows 128 bytes apart in groups of 8 (1024 bytes); one K step is 16 rows.
-    const uint32_t a_lbo = p.a_mn_major ? 8192u : 16u, a_sbo = 1024u;
-    const uint32_t b_lbo = p.b_mn_major ? 8192u : 16u, b_sbo = 1024u;
-    const uint32_t a_kadv = p.a_mn_major ? 2048u : 32u;
-    const uint32_t b_kadv = p.b_mn_major ? 2048u : 32u;
+    // UMMA K step is 32 bytes along the row (16 / 8 / 32 elements of 2 / 4 / 1
+    // bytes).  MN-major operand: 128-byte MN chunks mn_lbo bytes apart (8192 for
+    // 16-bit types), K rows 128 bytes apart in groups of 8 (1024 bytes); one K
+    // step is mn_kadv bytes (16 rows = 2048 for 16-bit types).
+    //
+    // This one thread has to issue an MMA every ~128 clocks, so the loop below
+    // does as little as it can per instruction: everything in a descriptor but
+    // the start address is folded into two constants per operand up front, and
+    // each K step is one 32-bit add on the descriptor's low word.
+    const uint32_t a_lbo = p.a_mn_major ? p.mn_lbo : 16u, a_sbo = p.a_mn_major ? p.mn_sbo : 1024u;
+    const uint32_t b_lbo = p.b_mn_major ? p.mn_lbo : 16u, b_sbo = p.b_mn_major ? p.mn_sbo : 1024u;
+    const uint32_t a_lay = p.a_mn_major ? p.mn_layout : 2u;
+    const uint32_t b_lay = p.b_mn_major ? p.mn_layout : 2u;
+    // low word: start address >> 4 | LBO >> 4 << 16; high word: SBO >> 4, version 1
+    // (bit 46), layout type (bits 61..63)
+    const uint32_t a_lo_c = ((a_lbo >> 4) & 0x3FFFu) << 16;
+    const uint32_t b_lo_c = ((b_lbo >> 4) & 0x3FFFu) << 16;
+    const uint32_t a_hi = ((a_sbo >> 4) & 0x3FFFu) | (1u << 14) | (a_lay << 29);
+    const uint32_t b_hi = ((b_sbo >> 4) & 0x3FFFu) | (1u << 14) | (b_lay << 29);
+    const uint32_t a_kstep = (p.a_mn_major ? p.mn_kadv : 32u) >> 4;   // descriptor units per K step
+    const uint32_t b_kstep = (p.b_mn_major ? p.mn_kadv : 32u) >> 4;
+    const uint32_t a_lo0 = a_lo_c | (ptx::smem_u32(sA) >> 4);
+    const uint32_t b_lo0 = b_lo_c | (ptx::smem_u32(sB) >> 4);
+    const uint32_t idesc = p.idesc;
+    const int kind = p.kind;
+    const bool skip_mma = (p.debug & 2) != 0, free_run = (p.debug & 32) != 0;
     int stage = 0;
     uint32_t phase = 0;
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
+    const bool probe = (p.debug & 128) && blockIdx.x == 0;
+    const long long probe_c0 = probe ? clock64() : 0;
+    const uint64_t probe_t0 = probe ? ptx::globaltimer_ns() : 0;
     for (int tile = unit; tile < p.num_tiles && ok; tile += unit_step) {
       if constexpr (Cfg::HALVES == 2) {
         // both halves of the previous tile must have been drained
@@ -420,32 +654,31 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       const uint32_t d_tmem =
           tmem_base + (Cfg::HALVES == 2 ? 0u : static_cast<uint32_t>(acc * BN));
       for (int kb = 0; kb < p.num_kb; ++kb) {
-        if (!ptx::mbar_wait(ptx::smem_u32(&full_bar[stage]), phase, abort_flag)) {
+        if (!free_run && !ptx::mbar_wait(ptx::smem_u32(&full_bar[stage]), phase, abort_flag)) {
           ok = false;
           break;
         }
         ptx::tc_fence_after();
-        const uint32_t a_base = ptx::smem_u32(sA + stage * Cfg::A_BYTES);
-        const uint32_t b_base = ptx::smem_u32(sB + stage * Cfg::B_BYTES);
-        if (!(p.debug & 2)) {
-#pragma unroll
-          for (int k = 0; k < Cfg::BK / 16; ++k) {
-            const uint64_t adesc = ptx::make_smem_desc_sw128(a_base + k * a_kadv, a_lbo, a_sbo);
-#pragma unroll
-            for (int hh = 0; hh < Cfg::HALVES; ++hh) {
-              // this CTA's B bytes of half hh start (MMA_N / CTAS) rows of 128 bytes
-              // after those of half hh-1, in either layout
-              const uint32_t b_half = b_base + hh * (Cfg::MMA_N / CTAS) * 128;
-              const uint64_t bdesc = ptx::make_smem_desc_sw128(b_half + k * b_kadv, b_lbo, b_sbo);
-              ptx::umma_f16<CTAS>(d_tmem + hh * Cfg::MMA_N, adesc, bdesc, p.idesc,
-                                  (kb | k) != 0 ? 1u : 0u);
-            }
-          }
+        if (!skip_mma) {
+          const uint32_t a_lo = a_lo0 + static_cast<uint32_t>(stage) * (Cfg::A_BYTES >> 4);
+          const uint32_t b_lo = b_lo0 + static_cast<uint32_t>(stage) * (Cfg::B_BYTES >> 4);
+          const uint32_t first = kb != 0 ? 1u : 0u;  // the tile's first MMA overwrites
+          if (kind == 0)
+            issue_kblock<CTAS, Cfg::HALVES, Cfg::MMA_N, 0>(d_tmem, a_lo, a_hi, a_kstep, b_lo, b_hi,
+                                                           b_kstep, idesc, first);
+          else if (kind == 1)
+            issue_kblock<CTAS, Cfg::HALVES, Cfg::MMA_N, 1>(d_tmem, a_lo, a_hi, a_kstep, b_lo, b_hi,
+                                                           b_kstep, idesc, first);
+          else
+            issue_kblock<CTAS, Cfg::HALVES, Cfg::MMA_N, 2>(d_tmem, a_lo, a_hi, a_kstep, b_lo, b_hi,
+                                                           b_kstep, idesc, first);
         }
         // Free the stage in every CTA that filled it.
-        ptx::umma_commit<CTAS>(ptx::smem_u32(&empty_bar[stage]));
-        if constexpr (CTAS == 2)
-          ptx::umma_commit<CTAS>(ptx::mapa(ptx::smem_u32(&empty_bar[stage]), 1));
+        if (!free_run) {
+          ptx::umma_commit<CTAS>(ptx::smem_u32(&empty_bar[stage]));
+          if constexpr (CTAS == 2)
+            ptx::umma_commit<CTAS>(ptx::mapa(ptx::smem_u32(&empty_bar[stage]), 1));
+        }
         if (++stage == STAGES) {
           stage = 0;
           phase ^= 1u;
@@ -466,6 +699,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1u;
       }
+    }
+    if (probe) {
+      p.status[2] = static_cast<uint32_t>(clock64() - probe_c0);
+      p.status[3] = static_cast<uint32_t>(ptx::globaltimer_ns() - probe_t0);
     }
   } else if (warp >= 2) {
     // ------------------------------------------------------------ epilogue
@@ -499,6 +736,37 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       const int n0 = nb * BN;
       const int row = m0 + lane;
       bool alive = true;
+      if constexpr (Cfg::HALVES == 2 && EPI == 8) {
+        if ((out_kind == 1 || out_kind == 3) && p.ep.acc == nullptr &&
+            p.ep.activation == KAPYB_ACT_NONE) {
+          // 16-bit output of a two-half tile: drain to registers, store afterwards
+          EpiTile et;
+          et.tempty_addr = tempty_leader;
+          et.remote_arrive = CTAS == 2;
+          et.b = b;
+          et.m0 = m0;
+          et.n0 = n0;
+          et.row = row;
+          et.lane = lane;
+          et.t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+          et.cpart = cpart;
+          et.col_begin = 0;
+          et.col_end = BN;
+          et.stg = stg;
+          et.bias_col = bias_col;
+          et.bias_fast = bias_fast;
+          et.bias_row = 0.0f;
+          if (p.ep.bias != nullptr && p.ep.bias_axis == 0 && row < p.M)
+            et.bias_row = load_as_f32(p.ep.bias, p.ep.bias_dtype, row);
+          const bool active = m0 < p.M && !(p.debug & 4);
+          const uint32_t tf0 = ptx::smem_u32(&tfull_bar[0]);
+          alive = epilogue_two_halves<EPI>(p, tmC, et, tf0, acc_phase, abort_flag, active,
+                                           out_kind == 1);
+          if (!alive) break;
+          acc_phase ^= 1u;
+          continue;
+        }
+      }
 #pragma unroll 1
       for (int hh = 0; hh < Cfg::HALVES; ++hh) {
         // slot: with two halves, half hh of this tile; otherwise the tile's slot

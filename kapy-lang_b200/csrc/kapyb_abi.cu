@@ -43,7 +43,9 @@ struct kapyb_context {
   int forced_path = PATH_AUTO;
   int forced_bn = 0;
   int debug = 0;
+  uint32_t wait_limit_us = 0;
   int forced_epi = 0;  // 0: by K; 4 or 8: that many epilogue warps (single-CTA kernels)
+  int skinny_stages = 0;  // 0: as many as fit
   // host-buffer calls: copy streams and events for the chunked pipeline
   cudaStream_t copy_in = nullptr, copy_out = nullptr;
   cudaEvent_t ev[2 * 16 + 2] = {};
@@ -104,8 +106,9 @@ extern "C" KAPYB_API kapyb_status kapyb_create(kapyb_handle *out, int device) {
     return fail(nullptr, KAPYB_CUDA_ERROR, "kapyb_create: cuTensorMapEncodeTiled not available");
   }
   c->encode = reinterpret_cast<EncodeTiledFn>(fn);
-  e = cudaMalloc(&c->status, sizeof(uint32_t));
-  if (e == cudaSuccess) e = cudaMemset(c->status, 0, sizeof(uint32_t));
+  // word 0: status; words 2, 3: the cycle / nanosecond probe of kapyb_probe_clock
+  e = cudaMalloc(&c->status, 16 * sizeof(uint32_t));
+  if (e == cudaSuccess) e = cudaMemset(c->status, 0, 16 * sizeof(uint32_t));
   if (e != cudaSuccess) {
     delete c;
     return fail(nullptr, KAPYB_CUDA_ERROR, "kapyb_create: status word: %s", cudaGetErrorString(e));
@@ -139,17 +142,40 @@ extern "C" KAPYB_API const char *kapyb_last_kernel(kapyb_handle h) {
 
 extern "C" KAPYB_API int64_t kapyb_launch_count(kapyb_handle h) { return h ? h->launches : 0; }
 
+extern "C" KAPYB_API kapyb_status kapyb_probe_clock(kapyb_handle h, void *stream,
+                                                    uint32_t *cycles, uint32_t *nanoseconds) {
+  if (!h || !cycles || !nanoseconds)
+    return fail(h, KAPYB_INVALID_ARG, "kapyb_probe_clock: NULL argument");
+  CUDA_TRY(h, cudaSetDevice(h->device));
+  CUDA_TRY(h, cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+  uint32_t w[4] = {0, 0, 0, 0};
+  CUDA_TRY(h, cudaMemcpy(w, h->status, sizeof(w), cudaMemcpyDeviceToHost));
+  *cycles = w[2];
+  *nanoseconds = w[3];
+  return KAPYB_OK;
+}
+
 extern "C" KAPYB_API kapyb_status kapyb_set_matmul_path(kapyb_handle h, const char *name) {
   if (!h || !name) return fail(h, KAPYB_INVALID_ARG, "kapyb_set_matmul_path: NULL argument");
   std::string s(name);
   h->forced_bn = 0;
   h->debug = 0;
+  h->wait_limit_us = 0;
   h->forced_epi = 0;
+  h->skinny_stages = 0;
+  if (s.rfind("skinny", 0) == 0) {
+    size_t cs = s.find(":s");
+    if (cs != std::string::npos) h->skinny_stages = atoi(s.c_str() + cs + 2);
+    h->forced_path = PATH_SKINNY;
+    return KAPYB_OK;
+  }
   size_t colon = s.find(':');
   if (colon != std::string::npos) {
     h->forced_bn = atoi(s.c_str() + colon + 1);
     size_t colon2 = s.find(":d", colon + 1);
     if (colon2 != std::string::npos) h->debug = atoi(s.c_str() + colon2 + 2);
+    size_t colonw = s.find(":w", colon + 1);
+    if (colonw != std::string::npos) h->wait_limit_us = 1000u * atoi(s.c_str() + colonw + 2);
     size_t colon3 = s.find(":e", colon + 1);
     if (colon3 != std::string::npos) h->forced_epi = atoi(s.c_str() + colon3 + 2);
     s = s.substr(0, colon);
@@ -223,9 +249,16 @@ extern "C" KAPYB_API kapyb_status kapyb_shard_range(int64_t total, int32_t parts
 // --------------------------------------------------------------- validation
 
 static bool valid_dtype(int d) { return d == KAPYB_F16 || d == KAPYB_BF16 || d == KAPYB_F32; }
+static bool is_fp8(int d) { return d == KAPYB_F8E4M3 || d == KAPYB_F8E5M2; }
+static bool valid_operand_dtype(int d) { return valid_dtype(d) || is_fp8(d); }
 
 static const char *dtype_name(int d) {
-  return d == KAPYB_F16 ? "f16" : d == KAPYB_BF16 ? "bf16" : d == KAPYB_F32 ? "f32" : "?";
+  return d == KAPYB_F16     ? "f16"
+         : d == KAPYB_BF16  ? "bf16"
+         : d == KAPYB_F32   ? "f32"
+         : d == KAPYB_F8E4M3 ? "f8E4M3"
+         : d == KAPYB_F8E5M2 ? "f8E5M2"
+                             : "?";
 }
 
 static const void *elem_ptr(const kapyb_tensor2d *t) {
@@ -242,7 +275,7 @@ static kapyb_status verify_matmul(kapyb_handle h, const kapyb_tensor2d *lhs,
   auto empty = [](const kapyb_tensor2d *t) { return t->size0 == 0 || t->size1 == 0; };
   if ((!lhs->ptr && !empty(lhs)) || (!rhs->ptr && !empty(rhs)) || (!out->ptr && !empty(out)))
     return fail(h, KAPYB_INVALID_ARG, "matmul: NULL data pointer");
-  if (!valid_dtype(lhs->dtype) || !valid_dtype(rhs->dtype) || !valid_dtype(out->dtype))
+  if (!valid_operand_dtype(lhs->dtype) || !valid_operand_dtype(rhs->dtype) || !valid_dtype(out->dtype))
     return fail(h, KAPYB_INVALID_ARG, "matmul: unknown element type");
   if (lhs->size0 < 0 || lhs->size1 < 0 || rhs->size0 < 0 || rhs->size1 < 0)
     return fail(h, KAPYB_INVALID_ARG, "matmul: negative size");
@@ -255,9 +288,9 @@ static kapyb_status verify_matmul(kapyb_handle h, const kapyb_tensor2d *lhs,
   if (out->size1 != rhs->size1)
     return fail(h, KAPYB_INVALID_ARG,
                 "matmul: number of columns of acc must be equal to number of columns of rhs");
-  if (lhs->dtype == KAPYB_F32 || rhs->dtype == KAPYB_F32)
-    return fail(h, KAPYB_UNSUPPORTED, "matmul: f32 (tf32) operands are not implemented");
-  if (lhs->dtype != rhs->dtype)
+  if (dtype_size(lhs->dtype) != dtype_size(rhs->dtype))
+    return fail(h, KAPYB_INVALID_ARG, "matmul: lhs and rhs must have same element bit width");
+  if (!is_fp8(lhs->dtype) && lhs->dtype != rhs->dtype)
     return fail(h, KAPYB_INVALID_ARG,
                 "matmul: lhs and rhs must have same element type unless they have f8 element type");
   if (acc) {
@@ -269,15 +302,26 @@ static kapyb_status verify_matmul(kapyb_handle h, const kapyb_tensor2d *lhs,
     if (acc->size0 != out->size0 || acc->size1 != out->size1)
       return fail(h, KAPYB_INVALID_ARG, "matmul: acc shape must match the result shape");
   }
+  const bool half_ops = lhs->dtype == KAPYB_F16 || lhs->dtype == KAPYB_BF16;
   switch (impl_way) {
-  case KAPYB_MMA_ANY:
+  case KAPYB_MMA_ANY: break;
   case KAPYB_MMA_M16N8K8_F16:
-  case KAPYB_MMA_M16N8K16_F16: break;
+    if (!half_ops)
+      return fail(h, KAPYB_INVALID_ARG, "matmul: mma_m16n8k8_f16 operands must have f16 or bf16 element type");
+    break;
+  case KAPYB_MMA_M16N8K16_F16:
+    if (!half_ops)
+      return fail(h, KAPYB_INVALID_ARG, "matmul: mma_m16n8k16_f16 operands must have f16 or bf16 element type");
+    break;
   case KAPYB_MMA_M16N8K8_TF32:
-    return fail(h, KAPYB_INVALID_ARG, "matmul: mma_m16n8k8_tf32 operands must have f32 element type");
+    if (lhs->dtype != KAPYB_F32)
+      return fail(h, KAPYB_INVALID_ARG, "matmul: mma_m16n8k8_tf32 operands must have f32 element type");
+    break;
   case KAPYB_MMA_M16N8K16_F8:
-    return fail(h, KAPYB_INVALID_ARG,
-                "matmul: mma_m16n8k16_f8 operands must have f8E4M3 or f8E5M2 element type");
+    if (!is_fp8(lhs->dtype) || !is_fp8(rhs->dtype))
+      return fail(h, KAPYB_INVALID_ARG,
+                  "matmul: mma_m16n8k16_f8 operands must have f8E4M3 or f8E5M2 element type");
+    break;
   default: return fail(h, KAPYB_INVALID_ARG, "matmul: unknown MatmulImplWay %d", impl_way);
   }
   if (ep) {
@@ -294,16 +338,18 @@ static kapyb_status verify_matmul(kapyb_handle h, const kapyb_tensor2d *lhs,
 // ------------------------------------------------------------- tensor maps
 
 static CUtensorMapDataType tmap_dtype(int dtype) {
-  return dtype == KAPYB_F32   ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
-         : dtype == KAPYB_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
-                              : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  return dtype == KAPYB_F32    ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+         : dtype == KAPYB_F16  ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+         : dtype == KAPYB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                               : CU_TENSOR_MAP_DATA_TYPE_UINT8;
 }
 
 // 3-D map over a matrix whose unit-stride axis has `inner` elements and whose
 // other axis has `outer` rows `ld` elements apart, repeated `batch` times.
 static kapyb_status make_tmap(kapyb_handle h, CUtensorMap *map, const void *base, int dtype,
                               uint64_t inner, uint64_t outer, uint64_t batch, uint64_t ld,
-                              uint64_t batch_stride, uint32_t box_inner, uint32_t box_outer) {
+                              uint64_t batch_stride, uint32_t box_inner, uint32_t box_outer,
+                              bool swizzle_32b_units = false) {
   const uint64_t esz = dtype_size(dtype);
   cuuint64_t dims[3] = {inner, outer, batch};
   uint64_t bs = batch_stride * esz;
@@ -312,7 +358,9 @@ static kapyb_status make_tmap(kapyb_handle h, CUtensorMap *map, const void *base
   cuuint32_t box[3] = {box_inner, box_outer, 1};
   cuuint32_t estr[3] = {1, 1, 1};
   CUresult r = h->encode(map, tmap_dtype(dtype), 3, const_cast<void *>(base), dims, strides, box,
-                         estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                         estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         swizzle_32b_units ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B
+                                           : CU_TENSOR_MAP_SWIZZLE_128B,
                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS)
     return fail(h, KAPYB_CUDA_ERROR,
@@ -345,7 +393,7 @@ struct MatmulProblem {
   void *c;
   int M, N, K, batch;
   long long a_s0, a_s1, a_bs, b_s0, b_s1, b_bs, c_s0, c_s1, c_bs;
-  int in_dtype, out_dtype;
+  int in_dtype, in_dtype_b, out_dtype;
   EpilogueArgs ep;
 };
 
@@ -368,6 +416,7 @@ static EpilogueArgs make_ep(const kapyb_epilogue *ep, const kapyb_tensor2d *acc)
 static void transpose_problem(MatmulProblem &p) {
   // C^T = B^T . A^T
   std::swap(p.a, p.b);
+  std::swap(p.in_dtype, p.in_dtype_b);
   std::swap(p.M, p.N);
   long long a0 = p.a_s0, a1 = p.a_s1, ab = p.a_bs;
   p.a_s0 = p.b_s1;
@@ -400,6 +449,8 @@ static kapyb_status launch_simt(kapyb_handle h, const MatmulProblem &p, cudaStre
   sp.c_s1 = p.c_s1;
   sp.c_bs = p.c_bs;
   sp.in_dtype = p.in_dtype;
+  sp.in_dtype_b = p.in_dtype_b;
+  sp.tf32 = p.in_dtype == KAPYB_F32 ? 1 : 0;
   sp.out_dtype = p.out_dtype;
   sp.ep = p.ep;
   dim3 grid((p.N + kSimtTile - 1) / kSimtTile, (p.M + kSimtTile - 1) / kSimtTile, p.batch);
@@ -419,18 +470,23 @@ static kapyb_status launch_tcgen05(kapyb_handle h, const MatmulProblem &p, bool 
   CUtensorMap tmA, tmB;
   TmapArray tmC;
   kapyb_status st;
-  // A: K-major -> inner K, rows M, box {64, 128}; MN-major -> inner M, rows K, box {64, 64}.
+  // A shared-memory row is 128 bytes: `ce` elements of the operand type.
+  // A: K-major -> inner K, rows M, box {ce, 128}; MN-major -> inner M, rows K, box {ce, ce}.
+  const uint32_t ce = 128 / dtype_size(p.in_dtype);
+  // A 32-bit operand whose unit stride is on M / N has to sit in shared memory
+  // swizzled in 32-byte units (4-row pattern); everything else uses 16-byte units.
+  const bool mn32 = dtype_size(p.in_dtype) == 4;
   if (!a_mn)
-    st = make_tmap(h, &tmA, p.a, p.in_dtype, p.K, p.M, p.batch, p.a_s0, p.a_bs, 64, Cfg::BM);
+    st = make_tmap(h, &tmA, p.a, p.in_dtype, p.K, p.M, p.batch, p.a_s0, p.a_bs, ce, Cfg::BM);
   else
-    st = make_tmap(h, &tmA, p.a, p.in_dtype, p.M, p.K, p.batch, p.a_s1, p.a_bs, 64, 64);
+    st = make_tmap(h, &tmA, p.a, p.in_dtype, p.M, p.K, p.batch, p.a_s1, p.a_bs, ce, ce, mn32);
   if (st != KAPYB_OK) return st;
-  // B [K,N]: MN-major (N contiguous) -> inner N, rows K, box {64, 64};
-  //          K-major (K contiguous)  -> inner K, rows N, box {64, BN_CTA}.
+  // B [K,N]: MN-major (N contiguous) -> inner N, rows K, box {ce, ce};
+  //          K-major (K contiguous)  -> inner K, rows N, box {ce, columns per CTA and half}.
   if (b_mn)
-    st = make_tmap(h, &tmB, p.b, p.in_dtype, p.N, p.K, p.batch, p.b_s0, p.b_bs, 64, 64);
+    st = make_tmap(h, &tmB, p.b, p.in_dtype_b, p.N, p.K, p.batch, p.b_s0, p.b_bs, ce, ce, mn32);
   else
-    st = make_tmap(h, &tmB, p.b, p.in_dtype, p.K, p.N, p.batch, p.b_s1, p.b_bs, 64,
+    st = make_tmap(h, &tmB, p.b, p.in_dtype_b, p.K, p.N, p.batch, p.b_s1, p.b_bs, ce,
                    Cfg::MMA_N / CTAS);
   if (st != KAPYB_OK) return st;
   const uint32_t cw = p.out_dtype == KAPYB_F32 ? 32 : 64;
@@ -448,17 +504,27 @@ static kapyb_status launch_tcgen05(kapyb_handle h, const MatmulProblem &p, bool 
   gp.tiles_m = (p.M + Cfg::TILE_M - 1) / Cfg::TILE_M;
   gp.tiles_n = (p.N + BN - 1) / BN;
   gp.num_tiles = gp.tiles_m * gp.tiles_n * p.batch;
-  gp.num_kb = (p.K + Cfg::BK - 1) / Cfg::BK;
+  gp.bk_elems = static_cast<int>(ce);
+  gp.num_kb = (p.K + gp.bk_elems - 1) / gp.bk_elems;
+  gp.kind = p.in_dtype == KAPYB_F32 ? 1 : is_fp8(p.in_dtype) ? 2 : 0;
+  gp.mn_lbo = ce * 128u;                                 // ce K rows of 128 bytes per chunk
+  gp.mn_kadv = (32u / dtype_size(p.in_dtype)) * 128u;    // K rows per MMA step x 128 bytes
+  gp.mn_sbo = mn32 ? 512u : 1024u;
+  gp.mn_layout = mn32 ? 1u : 2u;
   gp.group_m = std::max(1, std::min(gp.tiles_m, 16 / CTAS));
   gp.a_mn_major = a_mn ? 1 : 0;
   gp.b_mn_major = b_mn ? 1 : 0;
   gp.out_dtype = p.out_dtype;
   gp.n_out = n_out;
   gp.out_col_offset = 0;
-  gp.idesc = ptx::make_idesc_f16(p.in_dtype == KAPYB_BF16, a_mn, b_mn, Cfg::TILE_M, Cfg::MMA_N);
+  auto fmt = [](int dt) {
+    return dt == KAPYB_BF16 ? 1 : dt == KAPYB_F32 ? 2 : dt == KAPYB_F8E5M2 ? 1 : 0;
+  };
+  gp.idesc = ptx::make_idesc(fmt(p.in_dtype), fmt(p.in_dtype_b), a_mn, b_mn, Cfg::TILE_M, Cfg::MMA_N);
   if (BN == 512) gp.group_m = std::max(1, std::min(gp.tiles_m, 12));
   gp.status = h->status;
   gp.debug = h->debug;
+  gp.wait_limit_us = h->wait_limit_us;
   gp.ep = p.ep;
 
   auto kern = gemm_tcgen05_kernel<BN, CTAS, EPI>;
@@ -537,6 +603,7 @@ static kapyb_status launch_skinny_on(kapyb_handle h, const MatmulProblem &p, boo
   sp.counters = counters;
   sp.idesc = ptx::make_idesc_f16(p.in_dtype == KAPYB_BF16, b_mn, a_mn, 128, sp.m_pad);
   sp.status = h->status;
+  sp.wait_limit_us = h->wait_limit_us;
   sp.ep = p.ep;
   const long long total = static_cast<long long>(sp.n_tiles) * sp.num_kb;
   const int ctas = static_cast<int>(std::min<long long>(h->sm_count, total));
@@ -545,6 +612,7 @@ static kapyb_status launch_skinny_on(kapyb_handle h, const MatmulProblem &p, boo
   const int stage_bytes = 128 * 64 * 2 + sp.x_bytes;
   const int budget = 232448 - 1024 - 1024;
   sp.stages = std::max(2, std::min(kSkinnyMaxStages, budget / stage_bytes));
+  if (h->skinny_stages >= 2) sp.stages = std::min(sp.stages, h->skinny_stages);
   const int smem = 1024 + sp.stages * stage_bytes + 1024;
 
   CUtensorMap tmW, tmX;
@@ -598,7 +666,7 @@ static kapyb_status run_matmul(kapyb_handle h, MatmulProblem p, void *const *pee
   if (tma) {
     tma = tma_ok(p.a, p.in_dtype, a_mn ? p.M : p.K, a_mn ? p.K : p.M, a_mn ? p.a_s1 : p.a_s0,
                  p.batch, p.a_bs) &&
-          tma_ok(p.b, p.in_dtype, b_mn ? p.N : p.K, b_mn ? p.K : p.N, b_mn ? p.b_s0 : p.b_s1,
+          tma_ok(p.b, p.in_dtype_b, b_mn ? p.N : p.K, b_mn ? p.K : p.N, b_mn ? p.b_s0 : p.b_s1,
                  p.batch, p.b_bs) &&
           tma_ok(p.c, p.out_dtype, p.N, p.M, p.c_s0, p.batch, p.c_bs);
     for (int o = 0; tma && o < n_peers; ++o)
@@ -627,7 +695,8 @@ static kapyb_status run_matmul(kapyb_handle h, MatmulProblem p, void *const *pee
     // amortise the pair's start-up; everything else runs on single CTAs.
     const long long pair_tiles =
         static_cast<long long>((p.M + 255) / 256) * ((p.N + 255) / 256) * p.batch;
-    if (p.M <= kSkinnyMaxM && n_peers == 0 && p.batch == 1 && skinny_supported(p.M, p.N, p.K))
+    if (p.M <= kSkinnyMaxM && n_peers == 0 && p.batch == 1 && dtype_size(p.in_dtype) == 2 &&
+        skinny_supported(p.M, p.N, p.K))
       path = PATH_SKINNY;
     else if (p.M >= 256 && p.N >= 256 && p.K >= 512 && pair_tiles * 4 >= h->sm_count && h->forced_bn == 0)
       path = PATH_2CTA;
@@ -635,8 +704,9 @@ static kapyb_status run_matmul(kapyb_handle h, MatmulProblem p, void *const *pee
       path = PATH_1CTA;
   }
   if (path == PATH_SKINNY) {
-    if (n_peers > 0 || p.batch != 1 || p.M > kSkinnyMaxM)
-      return fail(h, KAPYB_UNSUPPORTED, "matmul: skinny path needs M <= %d, batch 1", kSkinnyMaxM);
+    if (n_peers > 0 || p.batch != 1 || p.M > kSkinnyMaxM || dtype_size(p.in_dtype) != 2)
+      return fail(h, KAPYB_UNSUPPORTED, "matmul: skinny path needs M <= %d, batch 1, 16-bit operands",
+                  kSkinnyMaxM);
     return launch_skinny(h, p, a_mn, b_mn, stream);
   }
   // Tile width: the widest tile that still yields about a wave of work.
@@ -653,6 +723,10 @@ static kapyb_status run_matmul(kapyb_handle h, MatmulProblem p, void *const *pee
     if (p.N <= 64) bn = 64;
     else if (p.N <= 128 && bn > 128) bn = 128;
   }
+  // An N-contiguous B arrives in chunks of 128 bytes of N: a CTA's share of the
+  // tile has to hold at least one chunk (128 columns of an 8-bit type).
+  const int min_cols = b_mn ? 128 / static_cast<int>(dtype_size(p.in_dtype_b)) : 0;
+  if (bn < min_cols) bn = min_cols;
   // Short K loops cannot hide the epilogue behind the next tile's main loop:
   // give those problems eight epilogue warps instead of four.
   const bool epi8 = (p.K + 63) / 64 <= 8 || h->forced_epi == 8;
@@ -665,11 +739,13 @@ static kapyb_status run_matmul(kapyb_handle h, MatmulProblem p, void *const *pee
         const long long t = static_cast<long long>((p.M + 255) / 256) * ((p.N + w - 1) / w) * p.batch;
         return static_cast<double>(t) / static_cast<double>((t + pairs - 1) / pairs * pairs);
       };
-      // ... and only for long K loops: the halves share TMEM, so the epilogue of a
-      // tile is not hidden behind the next tile's main loop.
-      bn = (p.N >= 512 && p.K >= 4096 && wave_eff(512) >= wave_eff(256) - 0.05) ? 512 : 256;
+      // The halves share TMEM, so a tile's drain is not hidden behind the next
+      // tile's main loop; the register drain keeps it short enough that this pays
+      // from a few K blocks on.
+      bn = (p.N >= 512 && p.K >= 512 && wave_eff(512) >= wave_eff(256) - 0.05) ? 512 : 256;
     }
     if (bn == 64) bn = 128;
+    if (bn / 2 < min_cols) bn = 2 * min_cols;
     if (bn == 128) return launch_tcgen05<128, 2, 4>(h, p, a_mn, b_mn, outs, n_out, stream);
     if (bn == 512) {
       if (h->forced_epi == 4) return launch_tcgen05<512, 2, 4>(h, p, a_mn, b_mn, outs, n_out, stream);
@@ -706,6 +782,7 @@ static MatmulProblem make_problem(const kapyb_tensor2d *lhs, const kapyb_tensor2
   p.c_s1 = out->stride1;
   p.a_bs = p.b_bs = p.c_bs = 0;
   p.in_dtype = lhs->dtype;
+  p.in_dtype_b = rhs->dtype;
   p.out_dtype = out->dtype;
   p.ep = make_ep(ep, acc);
   return p;
@@ -1381,6 +1458,8 @@ extern "C" KAPYB_API kapyb_status kapyb_matmul_decode_static(const kapyb_tensor2
   if (p.M == 0 || p.N == 0) return KAPYB_OK;
   const int m_pad = (p.M + 15) / 16 * 16;
   const long long n_tiles = (p.N + 127) / 128;
+  if (dtype_size(p.in_dtype) != 2)
+    return bail(fail(&ctx, KAPYB_UNSUPPORTED, "matmul_decode_static: operands must be f16 or bf16"));
   if (p.M > kSkinnyMaxM || p.K < 1)
     return bail(fail(&ctx, KAPYB_UNSUPPORTED, "matmul_decode_static: needs 1 <= M <= %d and K >= 1 (got M=%d, K=%d)", kSkinnyMaxM, p.M, p.K));
   const size_t need_counters = static_cast<size_t>(n_tiles) * 4 * sizeof(uint32_t);

@@ -100,18 +100,20 @@ constexpr uint64_t kWaitLimitNs = 2000000000ull;
 
 // Bounded wait.  Returns false when the limit ran out or another role already
 // raised *abort_flag (a word in shared memory); the caller then leaves its
-// loop and the kernel tears down in an orderly way.
+// loop and the kernel tears down in an orderly way.  abort_flag[1], when not
+// zero, is the limit in microseconds (tests shorten it).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
                                           volatile uint32_t *abort_flag) {
   if (mbar_try_wait(bar, parity)) return true;
   uint64_t t0 = 0;
   for (uint32_t it = 1;; ++it) {
-    if (mbar_try_wait_hint(bar, parity, 200000u)) return true;
+    if (mbar_try_wait_hint(bar, parity, 100000u)) return true;
     if ((it & 63u) == 0u) {
       if (*abort_flag != 0u) return false;
       uint64_t now = globaltimer_ns();
       if (t0 == 0) t0 = now;
-      if (now - t0 > kWaitLimitNs) {
+      const uint32_t lim_us = abort_flag[1];
+      if (now - t0 > (lim_us ? static_cast<uint64_t>(lim_us) * 1000ull : kWaitLimitNs)) {
         *abort_flag = 1u;
         return false;
       }
@@ -238,32 +240,65 @@ __device__ __forceinline__ void tc_fence_after() {
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 }
 
-// D[tmem] (+)= A[smem desc] . B[smem desc]; kind::f16 covers f16 and bf16
-// operands with an f32 accumulator.  Issued by ONE thread.
+// D[tmem] (+)= A[smem desc] . B[smem desc] with an f32 accumulator.  KIND 0:
+// kind::f16 (f16 / bf16 operands), 1: kind::tf32 (f32 operands, upper 19 bits),
+// 2: kind::f8f6f4 (fp8 operands).  Issued by ONE thread.
+#define KAPYB_UMMA_ASM(GROUP, KINDSTR)                                                     \
+  asm volatile(                                                                            \
+      "{\n\t"                                                                              \
+      ".reg .pred p;\n\t"                                                                  \
+      "setp.ne.b32 p, %4, 0;\n\t"                                                          \
+      "tcgen05.mma.cta_group::" GROUP ".kind::" KINDSTR " [%0], %1, %2, %3, p;\n\t"        \
+      "}\n"                                                                                 \
+      :                                                                                    \
+      : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)                 \
+      : "memory")
+
+template <int CTAS>
+__device__ __forceinline__ void umma(int kind, uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                     uint32_t idesc, uint32_t accumulate) {
+  if constexpr (CTAS == 1) {
+    if (kind == 0)
+      KAPYB_UMMA_ASM("1", "f16");
+    else if (kind == 1)
+      KAPYB_UMMA_ASM("1", "tf32");
+    else
+      KAPYB_UMMA_ASM("1", "f8f6f4");
+  } else {
+    if (kind == 0)
+      KAPYB_UMMA_ASM("2", "f16");
+    else if (kind == 1)
+      KAPYB_UMMA_ASM("2", "tf32");
+    else
+      KAPYB_UMMA_ASM("2", "f8f6f4");
+  }
+}
+
+// Same with the kind fixed at compile time (the main loop's form).
+template <int CTAS, int KIND>
+__device__ __forceinline__ void umma_k(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                       uint32_t idesc, uint32_t accumulate) {
+  if constexpr (CTAS == 1) {
+    if constexpr (KIND == 0)
+      KAPYB_UMMA_ASM("1", "f16");
+    else if constexpr (KIND == 1)
+      KAPYB_UMMA_ASM("1", "tf32");
+    else
+      KAPYB_UMMA_ASM("1", "f8f6f4");
+  } else {
+    if constexpr (KIND == 0)
+      KAPYB_UMMA_ASM("2", "f16");
+    else if constexpr (KIND == 1)
+      KAPYB_UMMA_ASM("2", "tf32");
+    else
+      KAPYB_UMMA_ASM("2", "f8f6f4");
+  }
+}
+
 template <int CTAS>
 __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
                                          uint32_t idesc, uint32_t accumulate) {
-  if constexpr (CTAS == 1) {
-    asm volatile(
-        "{\n\t"
-        ".reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
-        "}\n"
-        :
-        : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-        : "memory");
-  } else {
-    asm volatile(
-        "{\n\t"
-        ".reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t"
-        "}\n"
-        :
-        : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-        : "memory");
-  }
+  umma<CTAS>(0, d_tmem, a_desc, b_desc, idesc, accumulate);
 }
 
 // Makes `bar` (a shared::cluster address; a plain shared::cta address names
@@ -317,28 +352,36 @@ __device__ __forceinline__ void tmem_ld_wait() {
 // Shared-memory matrix descriptor (tcgen05), SWIZZLE_128B:
 //   bits [0,14)  start address >> 4      bits [16,30) leading byte offset >> 4
 //   bits [32,46) stride byte offset >> 4 bits [46,48) version = 1
-//   bits [61,64) layout type = 2 (128-byte swizzle)
+//   bits [61,64) layout type: 2 = 128-byte swizzle in 16-byte units, 1 = 128-byte
+//   swizzle in 32-byte units (the only layout an MN-major 32-bit operand may use)
 __device__ __forceinline__ uint64_t make_smem_desc_sw128(uint32_t smem_addr, uint32_t lbo_bytes,
-                                                         uint32_t sbo_bytes) {
+                                                         uint32_t sbo_bytes,
+                                                         uint32_t layout_type = 2) {
   uint64_t d = 0;
   d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
   d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16;
   d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFFu) << 32;
   d |= 1ull << 46;
-  d |= 2ull << 61;
+  d |= static_cast<uint64_t>(layout_type) << 61;
   return d;
 }
 
-// Instruction descriptor for kind::f16 with an f32 accumulator:
-//   [4,6) D format (1 = f32)  [7,10) A format (0 = f16, 1 = bf16)  [10,13) B format
+// Instruction descriptor with an f32 accumulator:
+//   [4,6) D format (1 = f32)  [7,10) A format  [10,13) B format
 //   [15] A major (0 = K, 1 = MN)  [16] B major  [17,23) N >> 3  [24,29) M >> 4
-__host__ __device__ constexpr uint32_t make_idesc_f16(int bf16, int a_mn_major, int b_mn_major,
-                                                      int m, int n) {
-  return (1u << 4) | (static_cast<uint32_t>(bf16 ? 1 : 0) << 7) |
-         (static_cast<uint32_t>(bf16 ? 1 : 0) << 10) |
+// Operand format codes: kind::f16 0 = f16, 1 = bf16; kind::tf32 2 = tf32;
+// kind::f8f6f4 0 = e4m3, 1 = e5m2.
+__host__ __device__ constexpr uint32_t make_idesc(int a_fmt, int b_fmt, int a_mn_major,
+                                                  int b_mn_major, int m, int n) {
+  return (1u << 4) | (static_cast<uint32_t>(a_fmt) << 7) | (static_cast<uint32_t>(b_fmt) << 10) |
          (static_cast<uint32_t>(a_mn_major ? 1 : 0) << 15) |
          (static_cast<uint32_t>(b_mn_major ? 1 : 0) << 16) |
          (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
+}
+
+__host__ __device__ constexpr uint32_t make_idesc_f16(int bf16, int a_mn_major, int b_mn_major,
+                                                      int m, int n) {
+  return make_idesc(bf16 ? 1 : 0, bf16 ? 1 : 0, a_mn_major, b_mn_major, m, n);
 }
 
 }  // namespace ptx

@@ -37,12 +37,17 @@ def dtype_code(dt) -> int:
         return abi.BF16
     if dt == torch.float32:
         return abi.F32
+    if dt == torch.float8_e4m3fn:
+        return abi.F8E4M3
+    if dt == torch.float8_e5m2:
+        return abi.F8E5M2
     raise ValueError(f"unsupported element type {dt}")
 
 
 def torch_dtype(code: int):
     torch = _torch()
-    return {abi.F16: torch.float16, abi.BF16: torch.bfloat16, abi.F32: torch.float32}[code]
+    return {abi.F16: torch.float16, abi.BF16: torch.bfloat16, abi.F32: torch.float32,
+            abi.F8E4M3: torch.float8_e4m3fn, abi.F8E5M2: torch.float8_e5m2}[code]
 
 
 def tensor2d(t, padding: int = abi.PAD_ZERO) -> abi.Tensor2d:
@@ -112,6 +117,14 @@ class Handle:
     @property
     def launch_count(self) -> int:
         return int(self._lib.kapyb_launch_count(self._h))
+
+    def probe_clock(self, stream=None):
+        """(cycles, nanoseconds) of the last matmul run with debug bit 7 (":d128")."""
+        cyc, ns = C.c_uint32(0), C.c_uint32(0)
+        st = self._lib.kapyb_probe_clock(self._h, self._stream(stream), C.byref(cyc), C.byref(ns))
+        if st != abi.OK:
+            self._raise(st)
+        return cyc.value, ns.value
 
     def set_matmul_path(self, name: str):
         st = self._lib.kapyb_set_matmul_path(self._h, name.encode())

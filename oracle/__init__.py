@@ -22,7 +22,7 @@ import numpy as np
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _SO = os.path.join(_HERE, "_build", "libkapy_oracle.so")
 
-F16, BF16, F32 = 0, 1, 2
+F16, BF16, F32, F8E4M3, F8E5M2 = 0, 1, 2, 3, 4
 RZ, RN = 0, 1
 PAD_ZERO, PAD_QNAN, PAD_PINF, PAD_NINF = 0, 1, 2, 3
 ACT_NONE, ACT_RELU, ACT_GELU_TANH, ACT_SILU = 0, 1, 2, 3
@@ -107,7 +107,18 @@ def lib():
 # --------------------------------------------------------------- numpy helpers
 
 def np_dtype(dtype: int):
+    if dtype in (F8E4M3, F8E5M2):
+        return np.uint8
     return np.float32 if dtype == F32 else np.uint16
+
+
+def f8_table(dtype: int) -> np.ndarray:
+    """The 256 values of an 8-bit float type, indexed by bit pattern (f64;
+    decoded by the C oracle, one descriptor element at a time)."""
+    bits = np.arange(256, dtype=np.uint8).reshape(1, 256)
+    ident = np.ones((1, 1), dtype=np.float32)
+    # 1x1 . 1x256 product: exact, one term per output.
+    return matmul_f64(ident, F32, bits, dtype)[0]
 
 
 def to_bits(x: np.ndarray, dtype: int, rounding: int = RN) -> np.ndarray:
@@ -136,6 +147,8 @@ def from_bits(a: np.ndarray, dtype: int) -> np.ndarray:
         return a.astype(np.float64)
     if dtype == F16:
         return a.view(np.float16).astype(np.float64)
+    if dtype in (F8E4M3, F8E5M2):
+        return f8_table(dtype)[a]
     return (a.astype(np.uint32) << 16).view(np.float32).astype(np.float64)
 
 

@@ -131,10 +131,31 @@ KO_API uint16_t ko_f32_to_f16(float x, int rn) {
   return ko_enc_f16(ko_round_to((double)x, KAPYB_F16, rn));
 }
 
+/* The two 8-bit operand types of the matmul verifier (Kapy.cpp:484-487,
+ * 548-564).  f8E4M3 is the finite-only "FN" variant: bias 7, no infinities,
+ * S.1111.111 is NaN.  f8E5M2 is a truncated f16: bias 15, IEEE specials. */
+static double ko_f8e4m3_to_f64(uint8_t b) {
+  int e = (b >> 3) & 15, m = b & 7;
+  double v;
+  if (e == 15 && m == 7) return NAN;
+  v = e == 0 ? ldexp((double)m, -9) : ldexp((double)(8 + m), e - 10);
+  return (b & 0x80) ? -v : v;
+}
+
+static double ko_f8e5m2_to_f64(uint8_t b) {
+  int e = (b >> 2) & 31, m = b & 3;
+  double v;
+  if (e == 31) v = m ? NAN : INFINITY;
+  else v = e == 0 ? ldexp((double)m, -16) : ldexp((double)(4 + m), e - 17);
+  return (b & 0x80) ? -v : v;
+}
+
 static double ko_load(const void *base, int dtype, int64_t idx) {
   switch (dtype) {
   case KAPYB_F16: return (double)ko_f16_to_f32(((const uint16_t *)base)[idx]);
   case KAPYB_BF16: return (double)ko_bf16_to_f32(((const uint16_t *)base)[idx]);
+  case KAPYB_F8E4M3: return ko_f8e4m3_to_f64(((const uint8_t *)base)[idx]);
+  case KAPYB_F8E5M2: return ko_f8e5m2_to_f64(((const uint8_t *)base)[idx]);
   default: return (double)((const float *)base)[idx];
   }
 }

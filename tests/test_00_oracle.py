@@ -151,3 +151,13 @@ def test_reduce(ko):
     assert np.array_equal(mx, v.max(axis=1))
     fast = ko.rowsum_bf16_f32(X)
     assert np.all(np.abs(fast - s) <= 4 * 2.0 ** -24 * ab)
+
+
+def test_f8_decode_tables(ko):
+    """The checker's f8E4M3 / f8E5M2 decoders against torch's conversions, all
+    256 bit patterns each (an independent implementation of the two formats)."""
+    for code, td in ((ko.F8E4M3, torch.float8_e4m3fn), (ko.F8E5M2, torch.float8_e5m2)):
+        table = ko.f8_table(code)
+        ref = torch.arange(256, dtype=torch.uint8).view(td).to(torch.float64).numpy()
+        assert np.array_equal(np.isnan(table), np.isnan(ref))
+        assert np.array_equal(table[~np.isnan(ref)], ref[~np.isnan(ref)])
