@@ -285,19 +285,20 @@ KAPYB_API kapyb_status kapyb_matmul_push(
  *   out[M,N] = epilogue(lhs[M,K] . rhs[K,N]),  1 <= M <= 64, f16/bf16 operands.
  *
  * Limits and rules:
- *  - the fixed scratch is 4 MiB of partial sums + 16 KiB of counters per GPU
+ *  - the fixed scratch is 10 MiB of partial sums + 16 KiB of counters per GPU
  *    (held by every GPU that loads the library, until exit); a call needs
- *    ceil(N/128) * roundup16(M) * 512 bytes of it, i.e. N * roundup16(M) must not
- *    exceed 1,048,576 (N <= 65536 at M <= 16).  Larger problems are refused with
- *    KAPYB_UNSUPPORTED and a message saying so; nothing is launched;
+ *    ceil(N/128) * 16 bytes of counters (N <= 131072) and 2 * SMs *
+ *    roundup16(M) * 512 bytes of partial sums (M = 64 fits on up to 160 SMs).
+ *    Larger problems are refused with KAPYB_UNSUPPORTED and a message saying
+ *    so; nothing is launched;
  *  - operands must be TMA-describable (one unit stride, 16-byte aligned base,
  *    leading dimension a multiple of 16 bytes); there is no fallback kernel;
  *  - the call runs on the CURRENT device.  Its first call on each device looks
  *    up the array's device address (cudaGetSymbolAddress) and the device's
  *    properties; make that first call outside any stream capture;
  *  - it calls no cudaMalloc/cudaFree and no allocating library routine.  It
- *    clears the part of the scratch it will use (cudaMemsetAsync on `stream`),
- *    then launches the kernel on `stream`;
+ *    clears the counters it will use (cudaMemsetAsync on `stream`), then
+ *    launches the kernel on `stream`;
  *  - all calls on one GPU share the one array: two calls whose kernels can
  *    overlap on the GPU (different streams, no dependency) race and give wrong
  *    results.  Keep them on one stream or order them yourself;
@@ -354,12 +355,15 @@ KAPYB_API const char *kapyb_last_kernel(kapyb_handle h);
 /* Number of kernels this handle has launched since creation. */
 KAPYB_API int64_t kapyb_launch_count(kapyb_handle h);
 
-/* SM cycles and wall nanoseconds the MMA-issuing thread of the first CTA spent
- * in its tile loop during the last tcgen05 matmul launched with debug bit 7
- * (":d128" in kapyb_set_matmul_path); cycles / nanoseconds is the SM clock in
- * GHz while the kernel ran.  Synchronises `stream`.  For profiling. */
-KAPYB_API kapyb_status kapyb_probe_clock(kapyb_handle h, void *stream, uint32_t *cycles,
-                                         uint32_t *nanoseconds);
+/* Profiling probes of the last matmul launched with debug bit 7 (":d128" in
+ * kapyb_set_matmul_path), then cleared.  Copies n <= 12 words after
+ * synchronising `stream`.  tcgen05 GEMM: word 0 = SM cycles, word 1 = wall
+ * nanoseconds the first CTA's MMA-issuing thread spent in its tile loop (their
+ * ratio is the SM clock in GHz while the kernel ran).  Decode kernel: words 0, 1
+ * as above; words 2..6 are readings of the nanosecond timer's low 32 bits: the
+ * complement of the earliest CTA start, then the latest, over all CTAs, of: CTA
+ * start, first operand stage landed, last MMA issued, epilogue done. */
+KAPYB_API kapyb_status kapyb_probe_read(kapyb_handle h, void *stream, uint32_t *words, int32_t n);
 
 /* Forces a kernel family for matmul ("auto", "1cta", "2cta", "skinny",
  * "simt"); for tests and profiling. */

@@ -30,7 +30,9 @@ struct SkinnyParams {
   int m_pad;      // M rounded up to 16: the MMA's N extent
   int num_kb;     // ceil(K / 64)
   int n_tiles;    // ceil(N / 128)
-  int span;       // k-block units per CTA
+  int span;       // k-block units of the split region per CTA
+  int sk_tiles;   // the first sk_tiles weight tiles are split between CTAs ...
+  int dp_per_cta; // ... the rest are whole tiles, this many per CTA (tile = sk_tiles + cta + i * grid)
   int stages;
   int w_mn_major;  // weights N-contiguous ([K,N] row-major)
   int x_mn_major;  // activations M-contiguous
@@ -39,17 +41,76 @@ struct SkinnyParams {
   int out_dtype;
   long long c_s0, c_s1;
   void *c;
-  float *scratch;      // [n_tiles][m_pad][128] fp32, zero between launches
+  float *scratch;      // [grid][2][m_pad][128] fp32 partial sums, two slots per CTA
   uint32_t *counters;  // [n_tiles][4], zero between launches
   uint32_t idesc;
   uint32_t *status;
   uint32_t wait_limit_us;  // 0: the default limit of a bounded wait
+  int debug;               // profiling only (results are wrong): bit2 skip the epilogue body,
+                           // bit3 skip the publish/count/owner pass, bit4 skip whole-tile
+                           // stores, bit5 skip the partial-sum stores; bit7 record the
+                           // timeline probes in status[2..8] (results stay right)
   EpilogueArgs ep;
 };
 
-__device__ __forceinline__ void skinny_finish(const SkinnyParams &p, int n, int m, float v) {
-  v *= p.ep.alpha;
-  if (p.ep.bias != nullptr) v += load_as_f32(p.ep.bias, p.ep.bias_dtype, p.ep.bias_axis == 1 ? n : m);
+// The work of one CTA, as a list of per-tile segments.  The first `sk_tiles`
+// weight tiles form the split region: their (tile, k-block) units are dealt out
+// as equal contiguous spans, so a CTA's share is up to two partial tiles (and
+// whole ones between them when spans are long).  The remaining tiles are whole
+// and go round-robin, `dp_per_cta` to each CTA.  The split region comes FIRST:
+// its publish / count / owner round trips then hide under the whole tiles' main
+// loops instead of forming the kernel's tail.
+struct SkinnyWork {
+  int first_tile, n_split_segs, head_kb, tail_kb, num_kb;
+  int dp_first, dp_stride, dp_count;
+  __device__ SkinnyWork(long long g_begin, long long g_end, int num_kb_, int sk_tiles, int dp_per_cta)
+      : num_kb(num_kb_) {
+    first_tile = static_cast<int>(g_begin / num_kb);
+    const int last_tile = g_end > g_begin ? static_cast<int>((g_end - 1) / num_kb) : first_tile;
+    n_split_segs = g_end > g_begin ? last_tile - first_tile + 1 : 0;
+    head_kb = static_cast<int>(g_begin - static_cast<long long>(first_tile) * num_kb);
+    tail_kb = static_cast<int>(g_end - static_cast<long long>(last_tile) * num_kb);
+    dp_first = sk_tiles + static_cast<int>(blockIdx.x);
+    dp_stride = static_cast<int>(gridDim.x);
+    dp_count = dp_per_cta;
+  }
+  __device__ int count() const { return n_split_segs + dp_count; }
+  // j-th segment in processing order
+  __device__ void get(int j, int &tile, int &kb_begin, int &kb_end) const {
+    if (j < n_split_segs) {
+      tile = first_tile + j;
+      kb_begin = j == 0 ? head_kb : 0;
+      kb_end = j == n_split_segs - 1 ? tail_kb : num_kb;
+    } else {
+      tile = dp_first + (j - n_split_segs) * dp_stride;
+      kb_begin = 0;
+      kb_end = num_kb;
+    }
+  }
+};
+
+// Sixteen finished rows of one output column, the common epilogue (scale and an
+// optional per-column bias, 16-bit output rounded to nearest): a multiply-add, a
+// conversion and a store per element.  One warp per scheduler runs this, so every
+// instruction saved comes off the kernel's tail.
+template <int DT>
+__device__ __forceinline__ void skinny_store16(uint16_t *col, long long row_stride, int rows,
+                                               const float (&v)[16], float alpha, float bias_n) {
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    if (i < rows) {
+      const float r = fmaf(v[i], alpha, bias_n);
+      col[i * row_stride] = static_cast<uint16_t>(cvt_pack2_t<DT, 1>(r, 0.0f) & 0xffffu);
+    }
+  }
+}
+
+// Epilogue of one output element.  `bias_n` is the per-column bias of column n,
+// fetched once per tile by the caller (0 when the bias runs along rows or is absent).
+__device__ __forceinline__ void skinny_finish(const SkinnyParams &p, int n, int m, float v,
+                                              float bias_n) {
+  v = v * p.ep.alpha + bias_n;
+  if (p.ep.bias != nullptr && p.ep.bias_axis != 1) v += load_as_f32(p.ep.bias, p.ep.bias_dtype, m);
   if (p.ep.acc != nullptr)
     v += load_as_f32(p.ep.acc, p.ep.acc_dtype, m * p.ep.acc_stride0 + n * p.ep.acc_stride1);
   v = apply_activation(p.ep.activation, v);
@@ -74,6 +135,12 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   volatile uint32_t *abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const bool probe = (p.debug & 128) != 0;
+  if (probe && threadIdx.x == 0) {
+    const uint32_t t = static_cast<uint32_t>(ptx::globaltimer_ns());
+    atomicMax(p.status + 4, ~t);  // earliest start, kept as the largest complement
+    atomicMax(p.status + 5, t);   // latest start
+  }
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.stages; ++s) {
       ptx::mbar_init(ptx::smem_u32(&full_bar[s]), 1);
@@ -100,53 +167,69 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  const long long total = static_cast<long long>(p.n_tiles) * p.num_kb;
-  const long long g_begin = static_cast<long long>(blockIdx.x) * p.span;
+  const long long total = static_cast<long long>(p.sk_tiles) * p.num_kb;  // units of the split region
+  const long long g_begin = min(total, static_cast<long long>(blockIdx.x) * p.span);
   const long long g_end = min(total, g_begin + p.span);
+  const SkinnyWork work(g_begin, g_end, p.num_kb, p.sk_tiles, p.dp_per_cta);
 
   if (warp == 0 && lane == 0) {
     // ------------------------------------------------------------ producer
     int stage = 0;
     uint32_t phase = 0;
     const uint32_t stage_bytes = W_BYTES + p.x_bytes;
-    for (long long g = g_begin; g < g_end; ++g) {
-      const int tile = static_cast<int>(g / p.num_kb);
-      const int kb = static_cast<int>(g - static_cast<long long>(tile) * p.num_kb);
-      if (!ptx::mbar_wait(ptx::smem_u32(&empty_bar[stage]), phase ^ 1u, abort_flag)) break;
-      const uint32_t fb = ptx::smem_u32(&full_bar[stage]);
-      ptx::mbar_arrive_expect_tx(fb, stage_bytes);
-      const int k0 = kb * 64, n0 = tile * 128;
-      const uint32_t w_dst = ptx::smem_u32(sW + stage * W_BYTES);
-      const uint32_t x_dst = ptx::smem_u32(sX + stage * p.x_bytes);
-      if (p.w_mn_major) {
-        ptx::tma_load_3d(w_dst, &tmW, fb, n0, k0, 0);
-        ptx::tma_load_3d(w_dst + 8192, &tmW, fb, n0 + 64, k0, 0);
-      } else {
-        ptx::tma_load_3d(w_dst, &tmW, fb, k0, n0, 0);
-      }
-      if (p.x_mn_major)
-        ptx::tma_load_3d(x_dst, &tmX, fb, 0, k0, 0);
-      else
-        ptx::tma_load_3d(x_dst, &tmX, fb, k0, 0, 0);
-      if (++stage == p.stages) {
-        stage = 0;
-        phase ^= 1u;
+    bool ok = true;
+    for (int j = 0; j < work.count() && ok; ++j) {
+      int tile, kb_begin, kb_end;
+      work.get(j, tile, kb_begin, kb_end);
+      for (int kb = kb_begin; kb < kb_end; ++kb) {
+        if (!ptx::mbar_wait(ptx::smem_u32(&empty_bar[stage]), phase ^ 1u, abort_flag)) {
+          ok = false;
+          break;
+        }
+        const uint32_t fb = ptx::smem_u32(&full_bar[stage]);
+        ptx::mbar_arrive_expect_tx(fb, stage_bytes);
+        const int k0 = kb * 64, n0 = tile * 128;
+        const uint32_t w_dst = ptx::smem_u32(sW + stage * W_BYTES);
+        const uint32_t x_dst = ptx::smem_u32(sX + stage * p.x_bytes);
+        if (p.w_mn_major) {
+          ptx::tma_load_3d(w_dst, &tmW, fb, n0, k0, 0);
+          ptx::tma_load_3d(w_dst + 8192, &tmW, fb, n0 + 64, k0, 0);
+        } else {
+          ptx::tma_load_3d(w_dst, &tmW, fb, k0, n0, 0);
+        }
+        if (p.x_mn_major)
+          ptx::tma_load_3d(x_dst, &tmX, fb, 0, k0, 0);
+        else
+          ptx::tma_load_3d(x_dst, &tmX, fb, k0, 0, 0);
+        if (++stage == p.stages) {
+          stage = 0;
+          phase ^= 1u;
+        }
       }
     }
   } else if (warp == 1 && lane == 0) {
     // ---------------------------------------------------------- MMA issuer
-    const uint32_t w_lbo = p.w_mn_major ? 8192u : 16u, w_kadv = p.w_mn_major ? 2048u : 32u;
-    const uint32_t x_lbo = p.x_mn_major ? 8192u : 16u, x_kadv = p.x_mn_major ? 2048u : 32u;
+    // Descriptor constants folded up front; a K step is one add on the low word
+    // (the issuing thread must keep pace with a 16 KB stage every few hundred ns).
+    const uint32_t w_lbo = p.w_mn_major ? 8192u : 16u, w_kstep = (p.w_mn_major ? 2048u : 32u) >> 4;
+    const uint32_t x_lbo = p.x_mn_major ? 8192u : 16u, x_kstep = (p.x_mn_major ? 2048u : 32u) >> 4;
+    const uint32_t desc_hi = (1024u >> 4) | (1u << 14) | (2u << 29);  // SBO, version 1, 128B swizzle
+    const uint32_t w_lo0 = ((w_lbo >> 4) << 16) | (ptx::smem_u32(sW) >> 4);
+    const uint32_t x_lo0 = ((x_lbo >> 4) << 16) | (ptx::smem_u32(sX) >> 4);
+    const uint32_t x_stage_step = static_cast<uint32_t>(p.x_bytes) >> 4;
+    const uint32_t idesc = p.idesc;
+    bool seen_first = false;
+    const long long probe_c0 = clock64();
+    const uint64_t probe_t0 = ptx::globaltimer_ns();
     int stage = 0;
     uint32_t phase = 0;
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
-    long long g = g_begin;
-    while (g < g_end && ok) {
-      const int tile = static_cast<int>(g / p.num_kb);
-      const int kb_begin = static_cast<int>(g - static_cast<long long>(tile) * p.num_kb);
-      const int kb_end = static_cast<int>(min(static_cast<long long>(p.num_kb), kb_begin + (g_end - g)));
+    for (int j = 0; j < work.count() && ok; ++j) {
+      int tile, kb_begin, kb_end;
+      work.get(j, tile, kb_begin, kb_end);
+      (void)tile;
       if (!ptx::mbar_wait(ptx::smem_u32(&tempty_bar[acc]), acc_phase ^ 1u, abort_flag)) break;
       ptx::tc_fence_after();
       const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * p.m_pad);
@@ -156,13 +239,18 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
           break;
         }
         ptx::tc_fence_after();
-        const uint32_t w_base = ptx::smem_u32(sW + stage * W_BYTES);
-        const uint32_t x_base = ptx::smem_u32(sX + stage * p.x_bytes);
+        if (probe && !seen_first) {
+          seen_first = true;
+          atomicMax(p.status + 6, static_cast<uint32_t>(ptx::globaltimer_ns()));
+        }
+        const uint32_t w_lo = w_lo0 + static_cast<uint32_t>(stage) * (W_BYTES >> 4);
+        const uint32_t x_lo = x_lo0 + static_cast<uint32_t>(stage) * x_stage_step;
+        const uint32_t first = kb > kb_begin ? 1u : 0u;
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-          const uint64_t wdesc = ptx::make_smem_desc_sw128(w_base + k * w_kadv, w_lbo, 1024u);
-          const uint64_t xdesc = ptx::make_smem_desc_sw128(x_base + k * x_kadv, x_lbo, 1024u);
-          ptx::umma_f16<1>(d_tmem, wdesc, xdesc, p.idesc, (kb > kb_begin || k > 0) ? 1u : 0u);
+          const uint64_t wdesc = (static_cast<uint64_t>(desc_hi) << 32) | (w_lo + k * w_kstep);
+          const uint64_t xdesc = (static_cast<uint64_t>(desc_hi) << 32) | (x_lo + k * x_kstep);
+          ptx::umma_k<1, 0>(d_tmem, wdesc, xdesc, idesc, k == 0 ? first : 1u);
         }
         ptx::umma_commit<1>(ptx::smem_u32(&empty_bar[stage]));
         if (++stage == p.stages) {
@@ -174,49 +262,76 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       ptx::umma_commit<1>(ptx::smem_u32(&tfull_bar[acc]));
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1u;
-      g += kb_end - kb_begin;
+    }
+    if (probe) {
+      atomicMax(p.status + 7, static_cast<uint32_t>(ptx::globaltimer_ns()));
+      if (blockIdx.x == 0) {
+        p.status[2] = static_cast<uint32_t>(clock64() - probe_c0);
+        p.status[3] = static_cast<uint32_t>(ptx::globaltimer_ns() - probe_t0);
+      }
     }
   } else if (warp >= 2) {
     // ------------------------------------------------------------ epilogue
     const int q = warp & 3;
+    // scale + optional per-column bias into a 16-bit output, rounded to nearest
+    const bool fast16 = p.ep.acc == nullptr && p.ep.activation == KAPYB_ACT_NONE &&
+                        (p.ep.bias == nullptr || p.ep.bias_axis == 1) &&
+                        p.out_dtype != KAPYB_F32 && p.ep.rounding == KAPYB_RN;
     int acc = 0;
     uint32_t acc_phase = 0;
-    long long g = g_begin;
-    while (g < g_end) {
-      const int tile = static_cast<int>(g / p.num_kb);
-      const int kb_begin = static_cast<int>(g - static_cast<long long>(tile) * p.num_kb);
-      const int kb_end = static_cast<int>(min(static_cast<long long>(p.num_kb), kb_begin + (g_end - g)));
+    for (int j = 0; j < work.count(); ++j) {
+      int tile, kb_begin, kb_end;
+      work.get(j, tile, kb_begin, kb_end);
       if (!ptx::mbar_wait(ptx::smem_u32(&tfull_bar[acc]), acc_phase, abort_flag)) break;
       ptx::tc_fence_after();
       const bool whole = kb_begin == 0 && kb_end == p.num_kb;
       const int n = tile * 128 + q * 32 + lane;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
                              static_cast<uint32_t>(acc * p.m_pad);
-      float *scr = p.scratch + (static_cast<long long>(tile) * p.m_pad) * 128 + q * 32 + lane;
-      for (int mc = 0; mc < p.m_pad; mc += 16) {
+      // A CTA's span holds at most two partial segments: one that starts inside a
+      // tile (slot 0) and one that starts a tile but does not finish it (slot 1).
+      const long long t0 = static_cast<long long>(tile) * p.num_kb;
+      const int my_slot = kb_begin > 0 ? 0 : 1;
+      float *scr = p.scratch + (static_cast<long long>(blockIdx.x * 2 + my_slot) * p.m_pad) * 128 +
+                   q * 32 + lane;
+      float bias_n = 0.0f;
+      if (p.ep.bias != nullptr && p.ep.bias_axis == 1 && n < p.N)
+        bias_n = load_as_f32(p.ep.bias, p.ep.bias_dtype, n);
+      uint16_t *col16 = static_cast<uint16_t *>(p.c) + n * p.c_s1;
+      for (int mc = 0; mc < p.m_pad && !(p.debug & 4); mc += 16) {
         uint32_t v[16];
         ptx::tmem_ld_32x16(t_row + static_cast<uint32_t>(mc), v);
         ptx::tmem_ld_wait();
         if (whole) {
-          if (n < p.N) {
+          if (n < p.N && !(p.debug & 16)) {
+            if (fast16) {
+              float f[16];
 #pragma unroll
-            for (int i = 0; i < 16; ++i)
-              if (mc + i < p.M) skinny_finish(p, n, mc + i, __uint_as_float(v[i]));
+              for (int i = 0; i < 16; ++i) f[i] = __uint_as_float(v[i]);
+              if (p.out_dtype == KAPYB_BF16)
+                skinny_store16<KAPYB_BF16>(col16 + mc * p.c_s0, p.c_s0, p.M - mc, f, p.ep.alpha, bias_n);
+              else
+                skinny_store16<KAPYB_F16>(col16 + mc * p.c_s0, p.c_s0, p.M - mc, f, p.ep.alpha, bias_n);
+            } else {
+#pragma unroll
+              for (int i = 0; i < 16; ++i)
+                if (mc + i < p.M) skinny_finish(p, n, mc + i, __uint_as_float(v[i]), bias_n);
+            }
           }
-        } else {
+        } else if (!(p.debug & 32)) {
 #pragma unroll
           for (int i = 0; i < 16; ++i)
-            if (mc + i < p.M) atomicAdd(scr + (mc + i) * 128, __uint_as_float(v[i]));
+            if (mc + i < p.M) __stcg(scr + (mc + i) * 128, __uint_as_float(v[i]));
         }
       }
       ptx::tc_fence_before();
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&tempty_bar[acc]));
-      if (!whole) {
-        // Publish this span's partial sums, then count it.  The contributor that
-        // completes the count owns the tile quarter: it reads the total, applies
-        // the epilogue and restores the zeros.
-        const long long t0 = static_cast<long long>(tile) * p.num_kb;
+      if (!whole && !(p.debug & (4 | 8))) {
+        // Publish this segment's partial sums (plain stores into this CTA's own
+        // slot), then count it.  The contributor that completes the count owns
+        // the tile quarter: it adds the slots of all contributors in CTA order
+        // (so the sum does not depend on who came last) and applies the epilogue.
         const int first = static_cast<int>(t0 / p.span);
         const int last = static_cast<int>((t0 + p.num_kb - 1) / p.span);
         const uint32_t expected = static_cast<uint32_t>(last - first + 1);
@@ -227,10 +342,34 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         seen = __shfl_sync(0xffffffffu, seen, 0);
         if (seen == expected - 1) {
           __threadfence();
-          for (int m = 0; m < p.M; ++m) {
-            const float s = __ldcg(scr + m * 128);
-            __stcg(scr + m * 128, 0.0f);
-            if (n < p.N) skinny_finish(p, n, m, s);
+          // Sixteen rows at a time, all loads of a slot issued before anything
+          // depends on them: one L2 round trip per slot and batch.
+          for (int mc = 0; mc < p.M; mc += 16) {
+            float sums[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) sums[i] = 0.0f;
+            for (int c = first; c <= last; ++c) {
+              const int slot = static_cast<long long>(c) * p.span > t0 ? 0 : 1;
+              const float *src = p.scratch + (static_cast<long long>(c * 2 + slot) * p.m_pad) * 128 +
+                                 q * 32 + lane;
+              float part[16];
+#pragma unroll
+              for (int i = 0; i < 16; ++i) part[i] = mc + i < p.M ? __ldcg(src + (mc + i) * 128) : 0.0f;
+#pragma unroll
+              for (int i = 0; i < 16; ++i) sums[i] += part[i];
+            }
+            if (n < p.N) {
+              if (fast16) {
+                if (p.out_dtype == KAPYB_BF16)
+                  skinny_store16<KAPYB_BF16>(col16 + mc * p.c_s0, p.c_s0, p.M - mc, sums, p.ep.alpha, bias_n);
+                else
+                  skinny_store16<KAPYB_F16>(col16 + mc * p.c_s0, p.c_s0, p.M - mc, sums, p.ep.alpha, bias_n);
+              } else {
+#pragma unroll
+                for (int i = 0; i < 16; ++i)
+                  if (mc + i < p.M) skinny_finish(p, n, mc + i, sums[i], bias_n);
+              }
+            }
           }
           __syncwarp();
           if (lane == 0) atomicExch(p.counters + tile * 4 + q, 0u);
@@ -238,8 +377,8 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       }
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1u;
-      g += kb_end - kb_begin;
     }
+    if (probe && lane == 0) atomicMax(p.status + 8, static_cast<uint32_t>(ptx::globaltimer_ns()));
   }
 
   ptx::tc_fence_before();

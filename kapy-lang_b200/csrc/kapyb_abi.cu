@@ -106,7 +106,7 @@ extern "C" KAPYB_API kapyb_status kapyb_create(kapyb_handle *out, int device) {
     return fail(nullptr, KAPYB_CUDA_ERROR, "kapyb_create: cuTensorMapEncodeTiled not available");
   }
   c->encode = reinterpret_cast<EncodeTiledFn>(fn);
-  // word 0: status; words 2, 3: the cycle / nanosecond probe of kapyb_probe_clock
+  // word 0: status; words 2..13: the profiling probes read by kapyb_probe_read
   e = cudaMalloc(&c->status, 16 * sizeof(uint32_t));
   if (e == cudaSuccess) e = cudaMemset(c->status, 0, 16 * sizeof(uint32_t));
   if (e != cudaSuccess) {
@@ -142,16 +142,16 @@ extern "C" KAPYB_API const char *kapyb_last_kernel(kapyb_handle h) {
 
 extern "C" KAPYB_API int64_t kapyb_launch_count(kapyb_handle h) { return h ? h->launches : 0; }
 
-extern "C" KAPYB_API kapyb_status kapyb_probe_clock(kapyb_handle h, void *stream,
-                                                    uint32_t *cycles, uint32_t *nanoseconds) {
-  if (!h || !cycles || !nanoseconds)
-    return fail(h, KAPYB_INVALID_ARG, "kapyb_probe_clock: NULL argument");
+extern "C" KAPYB_API kapyb_status kapyb_probe_read(kapyb_handle h, void *stream, uint32_t *words,
+                                                   int32_t n) {
+  if (!h || !words || n < 0 || n > 12)
+    return fail(h, KAPYB_INVALID_ARG, "kapyb_probe_read: NULL argument or n outside 0..12");
   CUDA_TRY(h, cudaSetDevice(h->device));
   CUDA_TRY(h, cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
-  uint32_t w[4] = {0, 0, 0, 0};
-  CUDA_TRY(h, cudaMemcpy(w, h->status, sizeof(w), cudaMemcpyDeviceToHost));
-  *cycles = w[2];
-  *nanoseconds = w[3];
+  if (n > 0)
+    CUDA_TRY(h, cudaMemcpy(words, h->status + 2, n * sizeof(uint32_t), cudaMemcpyDeviceToHost));
+  // probes accumulate with max/min across CTAs: start each measurement from zero
+  CUDA_TRY(h, cudaMemset(h->status + 2, 0, 12 * sizeof(uint32_t)));
   return KAPYB_OK;
 }
 
@@ -166,6 +166,8 @@ extern "C" KAPYB_API kapyb_status kapyb_set_matmul_path(kapyb_handle h, const ch
   if (s.rfind("skinny", 0) == 0) {
     size_t cs = s.find(":s");
     if (cs != std::string::npos) h->skinny_stages = atoi(s.c_str() + cs + 2);
+    size_t cd = s.find(":d");
+    if (cd != std::string::npos) h->debug = atoi(s.c_str() + cd + 2);
     h->forced_path = PATH_SKINNY;
     return KAPYB_OK;
   }
@@ -205,9 +207,9 @@ extern "C" KAPYB_API kapyb_status kapyb_check(kapyb_handle h, void *stream) {
   CUDA_TRY(h, cudaMemcpy(&st, h->status, sizeof(st), cudaMemcpyDeviceToHost));
   if (st != kStatusOk) {
     cudaMemset(h->status, 0, sizeof(uint32_t));
-    // a kernel that gave up may have left split-K partial sums behind
+    // a kernel that gave up may have left tile counters behind
     if (h->workspace)
-      cudaMemset(h->workspace, 0, std::min(h->workspace_bytes, kSkinnyCounterBytes + kSkinnyScratchBytes));
+      cudaMemset(h->workspace, 0, std::min<size_t>(h->workspace_bytes, kSkinnyCounterBytes));
     return fail(h, KAPYB_TIMEOUT, "a kernel gave up on a bounded wait (status %u)", st);
   }
   return KAPYB_OK;
@@ -570,16 +572,21 @@ static kapyb_status launch_tcgen05(kapyb_handle h, const MatmulProblem &p, bool 
 
 static size_t skinny_workspace_bytes() { return kSkinnyCounterBytes + kSkinnyScratchBytes; }
 
-static bool skinny_supported(int M, int N, int K) {
+// Partial sums of split weight tiles: two slots of [roundup16(M)][128] fp32 per CTA.
+static size_t skinny_partial_bytes(int sm_count, int M) {
   const int m_pad = (M + 15) / 16 * 16;
+  return static_cast<size_t>(sm_count) * 2 * m_pad * 128 * sizeof(float);
+}
+
+static bool skinny_supported(int sm_count, int M, int N, int K) {
   const long long n_tiles = (N + 127) / 128;
   return M >= 1 && M <= kSkinnyMaxM && K >= 1 &&
          n_tiles * 4 * sizeof(uint32_t) <= kSkinnyCounterBytes &&
-         static_cast<size_t>(n_tiles) * m_pad * 128 * sizeof(float) <= kSkinnyScratchBytes;
+         skinny_partial_bytes(sm_count, M) <= kSkinnyScratchBytes;
 }
 
-// Launches the weight-streaming kernel.  `scratch`/`counters` must be zero on
-// entry and are zero again when the kernel has finished.
+// Launches the weight-streaming kernel.  `counters` must be zero on entry and
+// are zero again when the kernel has finished; `scratch` needs no initial value.
 static kapyb_status launch_skinny_on(kapyb_handle h, const MatmulProblem &p, bool a_mn, bool b_mn,
                                      float *scratch, uint32_t *counters, cudaStream_t stream) {
   SkinnyParams sp;
@@ -604,11 +611,25 @@ static kapyb_status launch_skinny_on(kapyb_handle h, const MatmulProblem &p, boo
   sp.idesc = ptx::make_idesc_f16(p.in_dtype == KAPYB_BF16, b_mn, a_mn, 128, sp.m_pad);
   sp.status = h->status;
   sp.wait_limit_us = h->wait_limit_us;
+  sp.debug = h->debug;
   sp.ep = p.ep;
-  const long long total = static_cast<long long>(sp.n_tiles) * sp.num_kb;
-  const int ctas = static_cast<int>(std::min<long long>(h->sm_count, total));
-  sp.span = static_cast<int>((total + ctas - 1) / ctas);
-  const int grid = static_cast<int>((total + sp.span - 1) / sp.span);
+  // Whole tiles round-robin while they fill the GPU evenly; the leftover tiles
+  // (all of them when there are fewer tiles than SMs) are split into equal spans.
+  int grid;
+  if (sp.n_tiles >= h->sm_count) {
+    grid = h->sm_count;
+    sp.dp_per_cta = sp.n_tiles / grid;
+    sp.sk_tiles = sp.n_tiles % grid;
+    const long long units = static_cast<long long>(sp.sk_tiles) * sp.num_kb;
+    sp.span = static_cast<int>((units + grid - 1) / grid);
+  } else {
+    const long long units = static_cast<long long>(sp.n_tiles) * sp.num_kb;
+    const int ctas = static_cast<int>(std::min<long long>(h->sm_count, units));
+    sp.dp_per_cta = 0;
+    sp.sk_tiles = sp.n_tiles;
+    sp.span = static_cast<int>((units + ctas - 1) / ctas);
+    grid = static_cast<int>((units + sp.span - 1) / sp.span);
+  }
   const int stage_bytes = 128 * 64 * 2 + sp.x_bytes;
   const int budget = 232448 - 1024 - 1024;
   sp.stages = std::max(2, std::min(kSkinnyMaxStages, budget / stage_bytes));
@@ -642,7 +663,7 @@ static kapyb_status launch_skinny_on(kapyb_handle h, const MatmulProblem &p, boo
 
 static kapyb_status launch_skinny(kapyb_handle h, const MatmulProblem &p, bool a_mn, bool b_mn,
                                   cudaStream_t stream) {
-  if (!skinny_supported(p.M, p.N, p.K))
+  if (!skinny_supported(h->sm_count, p.M, p.N, p.K))
     return fail(h, KAPYB_UNSUPPORTED, "matmul: shape outside the skinny kernel's range");
   kapyb_status st = kapyb_reserve_workspace(h, skinny_workspace_bytes());
   if (st != KAPYB_OK) return st;
@@ -696,7 +717,7 @@ static kapyb_status run_matmul(kapyb_handle h, MatmulProblem p, void *const *pee
     const long long pair_tiles =
         static_cast<long long>((p.M + 255) / 256) * ((p.N + 255) / 256) * p.batch;
     if (p.M <= kSkinnyMaxM && n_peers == 0 && p.batch == 1 && dtype_size(p.in_dtype) == 2 &&
-        skinny_supported(p.M, p.N, p.K))
+        skinny_supported(h->sm_count, p.M, p.N, p.K))
       path = PATH_SKINNY;
     else if (p.M >= 256 && p.N >= 256 && p.K >= 512 && pair_tiles * 4 >= h->sm_count && h->forced_bn == 0)
       path = PATH_2CTA;
@@ -1387,10 +1408,11 @@ extern "C" KAPYB_API kapyb_status kapyb_reduce(kapyb_handle h, const kapyb_tenso
 // ------------------------------------------- decode matmul without allocation
 
 // Fixed scratch for kapyb_matmul_decode_static: tile counters followed by the
-// fp32 partial sums of split weight tiles.  It lives in the library image, so
+// fp32 partial sums of split weight tiles (two slots per CTA; 10 MiB hold them
+// for 64 rows on a GPU of up to 160 SMs).  It lives in the library image, so
 // every GPU that loads the library carries these bytes until the process exits.
 constexpr size_t kStaticCounterBytes = 16 * 1024;
-constexpr size_t kStaticPartialBytes = 4u << 20;
+constexpr size_t kStaticPartialBytes = 10u << 20;
 static __device__ __align__(256) unsigned char g_decode_scratch[kStaticCounterBytes + kStaticPartialBytes];
 static __device__ uint32_t g_decode_status;
 
@@ -1456,20 +1478,20 @@ extern "C" KAPYB_API kapyb_status kapyb_matmul_decode_static(const kapyb_tensor2
   if (st != KAPYB_OK) return bail(st);
   MatmulProblem p = make_problem(lhs, rhs, nullptr, out, epilogue);
   if (p.M == 0 || p.N == 0) return KAPYB_OK;
-  const int m_pad = (p.M + 15) / 16 * 16;
   const long long n_tiles = (p.N + 127) / 128;
   if (dtype_size(p.in_dtype) != 2)
     return bail(fail(&ctx, KAPYB_UNSUPPORTED, "matmul_decode_static: operands must be f16 or bf16"));
   if (p.M > kSkinnyMaxM || p.K < 1)
     return bail(fail(&ctx, KAPYB_UNSUPPORTED, "matmul_decode_static: needs 1 <= M <= %d and K >= 1 (got M=%d, K=%d)", kSkinnyMaxM, p.M, p.K));
   const size_t need_counters = static_cast<size_t>(n_tiles) * 4 * sizeof(uint32_t);
-  const size_t need_partial = static_cast<size_t>(n_tiles) * m_pad * 128 * sizeof(float);
+  const size_t need_partial = skinny_partial_bytes(ctx.sm_count, p.M);
   if (need_counters > kStaticCounterBytes || need_partial > kStaticPartialBytes)
     return bail(fail(&ctx, KAPYB_UNSUPPORTED,
-                     "matmul_decode_static: problem needs %zu bytes of partial sums and %zu of counters; "
-                     "the fixed scratch holds %zu and %zu (N * roundup16(M) <= %zu)",
-                     need_partial, need_counters, kStaticPartialBytes, kStaticCounterBytes,
-                     kStaticPartialBytes / 4));
+                     "matmul_decode_static: problem needs %zu bytes of counters and %zu of partial sums; "
+                     "the fixed scratch holds %zu and %zu (N <= %zu; 2 * SMs * roundup16(M) * 512 "
+                     "bytes of partial sums)",
+                     need_counters, need_partial, kStaticCounterBytes, kStaticPartialBytes,
+                     kStaticCounterBytes / 16 * 128));
   if (p.c_s1 != 1 && p.N != 1)
     return bail(fail(&ctx, KAPYB_UNSUPPORTED, "matmul_decode_static: out must be row-major (unit stride on axis 1)"));
   const bool a_k = p.a_s1 == 1 || p.K == 1, a_m = p.a_s0 == 1 || p.M == 1;
@@ -1482,10 +1504,10 @@ extern "C" KAPYB_API kapyb_status kapyb_matmul_decode_static(const kapyb_tensor2
                      "matmul_decode_static: operands need a unit stride, 16-byte aligned bases and "
                      "leading dimensions that are multiples of 16 bytes"));
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-  // The array keeps whatever the previous call left (zeros after a clean run,
-  // anything after one that was cut short): clear the part this call reads.
+  // The counters keep whatever the previous call left (zeros after a clean run,
+  // anything after one that was cut short): clear the ones this call uses.  The
+  // partial sums are written before they are read and need no clearing.
   e = cudaMemsetAsync(sd.scratch, 0, need_counters, stream);
-  if (e == cudaSuccess) e = cudaMemsetAsync(sd.scratch + kStaticCounterBytes, 0, need_partial, stream);
   if (e != cudaSuccess) return fail(nullptr, KAPYB_CUDA_ERROR, "matmul_decode_static: clearing scratch: %s", cudaGetErrorString(e));
   st = launch_skinny_on(&ctx, p, a_mn, b_mn,
                         reinterpret_cast<float *>(sd.scratch + kStaticCounterBytes),

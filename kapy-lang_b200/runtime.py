@@ -118,13 +118,18 @@ class Handle:
     def launch_count(self) -> int:
         return int(self._lib.kapyb_launch_count(self._h))
 
-    def probe_clock(self, stream=None):
-        """(cycles, nanoseconds) of the last matmul run with debug bit 7 (":d128")."""
-        cyc, ns = C.c_uint32(0), C.c_uint32(0)
-        st = self._lib.kapyb_probe_clock(self._h, self._stream(stream), C.byref(cyc), C.byref(ns))
+    def probe_read(self, n: int = 2, stream=None):
+        """Probe words of the last matmul run with debug bit 7 (":d128")."""
+        words = (C.c_uint32 * 12)()
+        st = self._lib.kapyb_probe_read(self._h, self._stream(stream), words, n)
         if st != abi.OK:
             self._raise(st)
-        return cyc.value, ns.value
+        return [int(w) for w in words[:n]]
+
+    def probe_clock(self, stream=None):
+        """(cycles, nanoseconds) of the last matmul run with debug bit 7 (":d128")."""
+        cyc, ns = self.probe_read(2, stream)
+        return cyc, ns
 
     def set_matmul_path(self, name: str):
         st = self._lib.kapyb_set_matmul_path(self._h, name.encode())

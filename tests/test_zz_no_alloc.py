@@ -63,8 +63,8 @@ def test_two_calls_match_the_ordinary_entry_point(handle, pkg, shape):
 def test_refuses_what_does_not_fit(pkg):
     torch.cuda.set_device(0)
     z = lambda s: torch.zeros(s, dtype=torch.bfloat16, device="cuda")
-    # 64 rows x 32768 columns needs 8 MiB of partial sums: beyond the fixed 4 MiB
-    st, msg = call_static(pkg, z((64, 64)), z((64, 32768)), z((64, 32768)))
+    # 131200 columns need 1026 tile counters of 16 bytes: beyond the fixed 16 KiB
+    st, msg = call_static(pkg, z((1, 64)), z((64, 131200)), z((1, 131200)))
     assert st == pkg.abi.UNSUPPORTED and "fixed scratch" in msg
     st, msg = call_static(pkg, z((65, 64)), z((64, 256)), z((65, 256)))
     assert st == pkg.abi.UNSUPPORTED and "M <= 64" in msg
