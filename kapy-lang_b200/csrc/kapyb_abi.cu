@@ -1212,12 +1212,13 @@ static bool contiguous_same(const kapyb_tensor2d &t, const kapyb_tensor2d &out) 
   return rm && orm;
 }
 
-// Grid for a grid-stride streaming kernel: enough blocks for the work, at most
-// one resident wave (`blocks_per_sm` x 256 threads per SM).
-static int stream_grid(kapyb_handle h, long long n_vec, int per_thread, int blocks_per_sm = 8) {
-  long long blocks = (n_vec + 256ll * per_thread - 1) / (256ll * per_thread);
-  const long long cap = static_cast<long long>(h->sm_count) * blocks_per_sm;
-  return static_cast<int>(std::max(1ll, std::min(blocks, cap)));
+// Grid of a streaming kernel whose blocks each take one contiguous chunk of
+// `per_thread` x 256 vectors (at least one block: the last one owns the scalar tail).
+static kapyb_status chunk_grid(kapyb_handle h, long long n_vec, int per_thread, int *grid) {
+  const long long blocks = std::max(1ll, (n_vec + 256ll * per_thread - 1) / (256ll * per_thread));
+  if (blocks > 0x7fffffffll) return fail(h, KAPYB_UNSUPPORTED, "elementwise: tensor too large");
+  *grid = static_cast<int>(blocks);
+  return KAPYB_OK;
 }
 
 extern "C" KAPYB_API kapyb_status kapyb_elementwise(kapyb_handle h, const kapyb_inst *prog,
@@ -1249,7 +1250,9 @@ extern "C" KAPYB_API kapyb_status kapyb_elementwise(kapyb_handle h, const kapyb_
       const bool wide = ((reinterpret_cast<uintptr_t>(px) | reinterpret_cast<uintptr_t>(py)) & 31u) == 0;
       f.ftz_ok = (f.one >= 1e-30f || f.one <= -1e-30f) ? 1 : 0;
       const long long n_acc = total / (wide ? 16 : 8);
-      const int grid = stream_grid(h, n_acc, kEltUnroll, wide ? 4 : 7);  // 60 / 34 registers
+      int grid = 1;
+      st = chunk_grid(h, n_acc, kEltUnroll, &grid);
+      if (st != KAPYB_OK) return st;
 #define KAPYB_LAUNCH_UNARY(W, DT, RN) \
   elt_unary16_kernel<AffineGelu, W, DT, RN><<<grid, 256, 0, stream>>>(px, py, n_acc, total, f)
       if (din == KAPYB_BF16) {
@@ -1278,7 +1281,9 @@ extern "C" KAPYB_API kapyb_status kapyb_elementwise(kapyb_handle h, const kapyb_
           aligned16(elem_ptr(out))) {
         const int per = r.dtype == KAPYB_F32 ? 4 : 8;
         const long long n_vec = total / per;
-        const int grid = stream_grid(h, n_vec, 2);
+        int grid = 1;
+        st = chunk_grid(h, n_vec, kBinUnroll, &grid);
+        if (st != KAPYB_OK) return st;
         const uint4 *pa = static_cast<const uint4 *>(elem_ptr(&ta));
         const uint4 *pb = static_cast<const uint4 *>(elem_ptr(&tb));
         uint4 *pz = static_cast<uint4 *>(const_cast<void *>(elem_ptr(out)));
@@ -1340,8 +1345,12 @@ template <int COMB>
 static void launch_reduce(const ReduceParams &p, bool unit_inner, bool vec, int sm_count,
                           cudaStream_t stream) {
   if (unit_inner) {
+    // One row per warp, as many blocks as that takes (capped far above a resident
+    // wave): the block scheduler then walks the SMs through neighbouring rows,
+    // which streams faster from HBM than a resident grid striding over the rows.
     const long long blocks = (static_cast<long long>(p.rows) + 7) / 8;
-    const int grid = static_cast<int>(std::max(1ll, std::min(blocks, static_cast<long long>(sm_count) * 8)));
+    const int grid = static_cast<int>(std::max(1ll, std::min(blocks, 1ll << 22)));
+    (void)sm_count;
     if (p.src_dtype == KAPYB_F32)
       launch_reduce_rows<COMB, KAPYB_F32>(p, vec, grid, stream);
     else if (p.src_dtype == KAPYB_BF16)
