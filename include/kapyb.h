@@ -359,8 +359,8 @@ KAPYB_API int64_t kapyb_launch_count(kapyb_handle h);
  * kapyb_set_matmul_path), then cleared.  Copies n <= 12 words after
  * synchronising `stream`.  tcgen05 GEMM: word 0 = SM cycles, word 1 = wall
  * nanoseconds the first CTA's MMA-issuing thread spent in its tile loop (their
- * ratio is the SM clock in GHz while the kernel ran).  Decode kernel: words 0, 1
- * as above; words 2..6 are readings of the nanosecond timer's low 32 bits: the
+ * ratio is the SM clock in GHz while the kernel ran).  Both kernels: words 2..6
+ * are readings of the nanosecond timer's low 32 bits: the
  * complement of the earliest CTA start, then the latest, over all CTAs, of: CTA
  * start, first operand stage landed, last MMA issued, epilogue done. */
 KAPYB_API kapyb_status kapyb_probe_read(kapyb_handle h, void *stream, uint32_t *words, int32_t n);

@@ -63,7 +63,9 @@ struct GemmParams {
               // bit5 free-running MMAs over whatever shared memory holds (no producer,
               // no stage barriers): an issue-rate probe,
               // bit7 the first CTA's MMA thread records cycles and nanoseconds of its
-              // tile loop in status[2], status[3]
+              // tile loop in status[2], status[3]; status[4..8] collect over all CTAs
+              // (timer low words): complement of the earliest start, latest start,
+              // latest first stage, latest last MMA issue, latest epilogue end
   EpilogueArgs ep;
 };
 
@@ -92,7 +94,12 @@ struct GemmCfg {
   // slots hold the halves of ONE tile instead of two tiles in flight.  That cuts
   // the operand bytes pulled from L2 per flop by a quarter.
   static constexpr int HALVES = BN == 512 ? 2 : 1;
-  static constexpr int MMA_N = BN / HALVES;
+  static constexpr int SLOT_COLS = BN / HALVES;  // accumulator columns behind one tfull/tempty pair
+  // Column groups a K step is issued in, one MMA each (the two halves of a 512-wide
+  // tile; splitting 256-wide tiles into 2 x 128 was measured slower: 54 % of the
+  // pipe's peak against 76 % for one 256-wide MMA per step).
+  static constexpr int SPLIT = BN == 512 ? 2 : 1;
+  static constexpr int MMA_N = BN / SPLIT;
   static constexpr int TMEM_COLS = HALVES == 2 ? 512 : (2 * BN < 32 ? 32 : 2 * BN);
   static_assert(BN % 64 == 0 && (BN <= 256 || (BN == 512 && CTAS == 2)),
                 "BN must be 64, 128, 256, or 512 for CTA pairs");
@@ -449,12 +456,12 @@ __device__ __forceinline__ bool epilogue_two_halves(const GemmParams &p, const T
   return alive;
 }
 
-// The MMAs of one K block (four K steps of 32 bytes; with two halves, both
-// accumulators per step, sharing the A descriptor).  Descriptors arrive as
+// The MMAs of one K block (four K steps of 32 bytes; with a split tile, both
+// column halves per step, sharing the A descriptor).  Descriptors arrive as
 // (low word of K step 0, constant high word, low-word increment per K step);
 // this CTA's B bytes of half hh start (MMA_N / CTAS) rows of 128 bytes after
 // those of half hh-1, in either layout and for any element width.
-template <int CTAS, int HALVES, int MMA_N, int KIND>
+template <int CTAS, int SPLIT, int MMA_N, int KIND>
 __device__ __forceinline__ void issue_kblock(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi,
                                              uint32_t a_kstep, uint32_t b_lo, uint32_t b_hi,
                                              uint32_t b_kstep, uint32_t idesc, uint32_t first) {
@@ -463,7 +470,7 @@ __device__ __forceinline__ void issue_kblock(uint32_t d_tmem, uint32_t a_lo, uin
   for (int k = 0; k < 4; ++k) {
     const uint64_t adesc = (static_cast<uint64_t>(a_hi) << 32) | (a_lo + k * a_kstep);
 #pragma unroll
-    for (int hh = 0; hh < HALVES; ++hh) {
+    for (int hh = 0; hh < SPLIT; ++hh) {
       const uint64_t bdesc =
           (static_cast<uint64_t>(b_hi) << 32) | (b_lo + k * b_kstep + hh * kHalfStep);
       ptx::umma_k<CTAS, KIND>(d_tmem + hh * MMA_N, adesc, bdesc, idesc, k == 0 ? first : 1u);
@@ -493,9 +500,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tempty_bar + 2);
   volatile uint32_t *abort_flag = tmem_slot + 1;
 
-  const int warp = threadIdx.x >> 5;
+  // the shuffle makes the warp index provably uniform for the compiler
+  const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0);
   const int lane = threadIdx.x & 31;
   const uint32_t rank = CTAS == 2 ? ptx::cluster_ctarank() : 0u;
+  const bool timeline = (p.debug & 128) != 0;  // probes: see GemmParams::debug
+  if (timeline && threadIdx.x == 0) {
+    const uint32_t t = static_cast<uint32_t>(ptx::globaltimer_ns());
+    atomicMax(p.status + 4, ~t);  // earliest CTA start, kept as the largest complement
+    atomicMax(p.status + 5, t);   // latest CTA start
+  }
   const int unit = CTAS == 2 ? (blockIdx.x >> 1) : blockIdx.x;      // CTA (pair) index
   const int unit_step = CTAS == 2 ? (gridDim.x >> 1) : gridDim.x;
 
@@ -539,8 +553,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       int b, mb, nb;
       decode_tile(p, tile, b, mb, nb);
       const int m0 = mb * Cfg::TILE_M + static_cast<int>(rank) * Cfg::BM;
-      // first B column this CTA loads; with two halves its columns are two groups
-      // of MMA_N / CTAS, one per half
+      // first B column this CTA loads; with a split tile its columns are two groups
+      // of MMA_N / CTAS, one per column half, so that accumulator column c of the
+      // pair's MMA is tile column c
       const int nB0 = nb * BN + static_cast<int>(rank) * (Cfg::MMA_N / CTAS);
       constexpr int kGroupCols = Cfg::MMA_N / CTAS;   // columns per half this CTA owns
       for (int kb = 0; kb < p.num_kb; ++kb) {
@@ -566,12 +581,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
               ptx::tma_load_3d(a_dst + j * p.mn_lbo, &tmA, fb, m0 + ce * j, k0, b);
           }
           if (!p.b_mn_major) {
-            ptx::tma_load_3d(b_dst, &tmB, fb, k0, nB0, b);
+            // one box of kGroupCols rows per column half
+#pragma unroll
+            for (int hh = 0; hh < Cfg::SPLIT; ++hh)
+              ptx::tma_load_3d(b_dst + hh * (kGroupCols * 128), &tmB, fb, k0, nB0 + hh * Cfg::MMA_N, b);
           } else {
             for (int j = 0; j < b_chunks; ++j)
               ptx::tma_load_3d(b_dst + j * p.mn_lbo, &tmB, fb, nB0 + ce * j, k0, b);
           }
-          (void)kGroupCols;
         } else {
           // Both CTAs' loads report their bytes to the leader's barrier; the
           // leader alone posts the arrival, expecting the bytes of both.  (A
@@ -588,7 +605,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
           if (!p.b_mn_major) {
             // one box of kGroupCols rows per half
 #pragma unroll
-            for (int hh = 0; hh < Cfg::HALVES; ++hh)
+            for (int hh = 0; hh < Cfg::SPLIT; ++hh)
               ptx::tma_load_3d_pair(b_dst + hh * (kGroupCols * 128), &tmB, fb, k0,
                                     nB0 + hh * Cfg::MMA_N, b);
           } else {
@@ -605,8 +622,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
         }
       }
     }
-  } else if (warp == 1 && lane == 0 && rank == 0) {
+  } else if (warp == 1 && rank == 0) {
     // ---------------------------------------------------------- MMA issuer
+    // The whole warp walks the loops in step and one elected lane issues: with
+    // warp-uniform control flow the descriptor arithmetic and the MMA operands
+    // stay in uniform registers.  Every wait ends in a vote, so the lanes can
+    // never part ways (elect.sync needs all of them), not even on a time-out.
+    auto wait_all = [&](uint32_t bar, uint32_t parity) {
+      const bool mine = ptx::mbar_wait(bar, parity, abort_flag);
+      return __all_sync(0xffffffffu, mine) != 0;
+    };
     // K-major operand: rows are 128 bytes, 8-row groups 1024 bytes apart; one
     // UMMA K step is 32 bytes along the row (16 / 8 / 32 elements of 2 / 4 / 1
     // bytes).  MN-major operand: 128-byte MN chunks mn_lbo bytes apart (8192 for
@@ -639,42 +664,48 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
-    const bool probe = (p.debug & 128) && blockIdx.x == 0;
+    bool seen_first = false;
+    const bool probe = timeline && blockIdx.x == 0;
     const long long probe_c0 = probe ? clock64() : 0;
     const uint64_t probe_t0 = probe ? ptx::globaltimer_ns() : 0;
     for (int tile = unit; tile < p.num_tiles && ok; tile += unit_step) {
       if constexpr (Cfg::HALVES == 2) {
         // both halves of the previous tile must have been drained
-        if (!ptx::mbar_wait(ptx::smem_u32(&tempty_bar[0]), acc_phase ^ 1u, abort_flag)) break;
-        if (!ptx::mbar_wait(ptx::smem_u32(&tempty_bar[1]), acc_phase ^ 1u, abort_flag)) break;
+        if (!wait_all(ptx::smem_u32(&tempty_bar[0]), acc_phase ^ 1u)) break;
+        if (!wait_all(ptx::smem_u32(&tempty_bar[1]), acc_phase ^ 1u)) break;
       } else {
-        if (!ptx::mbar_wait(ptx::smem_u32(&tempty_bar[acc]), acc_phase ^ 1u, abort_flag)) break;
+        if (!wait_all(ptx::smem_u32(&tempty_bar[acc]), acc_phase ^ 1u)) break;
       }
       ptx::tc_fence_after();
       const uint32_t d_tmem =
           tmem_base + (Cfg::HALVES == 2 ? 0u : static_cast<uint32_t>(acc * BN));
       for (int kb = 0; kb < p.num_kb; ++kb) {
-        if (!free_run && !ptx::mbar_wait(ptx::smem_u32(&full_bar[stage]), phase, abort_flag)) {
+        if (!free_run && !wait_all(ptx::smem_u32(&full_bar[stage]), phase)) {
           ok = false;
           break;
         }
         ptx::tc_fence_after();
-        if (!skip_mma) {
+        if (timeline && !seen_first) {
+          seen_first = true;
+          if (lane == 0) atomicMax(p.status + 6, static_cast<uint32_t>(ptx::globaltimer_ns()));
+        }
+        const bool elected = ptx::elect_one();
+        if (!skip_mma && elected) {
           const uint32_t a_lo = a_lo0 + static_cast<uint32_t>(stage) * (Cfg::A_BYTES >> 4);
           const uint32_t b_lo = b_lo0 + static_cast<uint32_t>(stage) * (Cfg::B_BYTES >> 4);
           const uint32_t first = kb != 0 ? 1u : 0u;  // the tile's first MMA overwrites
           if (kind == 0)
-            issue_kblock<CTAS, Cfg::HALVES, Cfg::MMA_N, 0>(d_tmem, a_lo, a_hi, a_kstep, b_lo, b_hi,
+            issue_kblock<CTAS, Cfg::SPLIT, Cfg::MMA_N, 0>(d_tmem, a_lo, a_hi, a_kstep, b_lo, b_hi,
                                                            b_kstep, idesc, first);
           else if (kind == 1)
-            issue_kblock<CTAS, Cfg::HALVES, Cfg::MMA_N, 1>(d_tmem, a_lo, a_hi, a_kstep, b_lo, b_hi,
+            issue_kblock<CTAS, Cfg::SPLIT, Cfg::MMA_N, 1>(d_tmem, a_lo, a_hi, a_kstep, b_lo, b_hi,
                                                            b_kstep, idesc, first);
           else
-            issue_kblock<CTAS, Cfg::HALVES, Cfg::MMA_N, 2>(d_tmem, a_lo, a_hi, a_kstep, b_lo, b_hi,
+            issue_kblock<CTAS, Cfg::SPLIT, Cfg::MMA_N, 2>(d_tmem, a_lo, a_hi, a_kstep, b_lo, b_hi,
                                                            b_kstep, idesc, first);
         }
         // Free the stage in every CTA that filled it.
-        if (!free_run) {
+        if (!free_run && elected) {
           ptx::umma_commit<CTAS>(ptx::smem_u32(&empty_bar[stage]));
           if constexpr (CTAS == 2)
             ptx::umma_commit<CTAS>(ptx::mapa(ptx::smem_u32(&empty_bar[stage]), 1));
@@ -685,22 +716,28 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
         }
       }
       if (!ok) break;
+      const bool elected = ptx::elect_one();
       if constexpr (Cfg::HALVES == 2) {
+        if (elected) {
 #pragma unroll
-        for (int hh = 0; hh < 2; ++hh) {
-          ptx::umma_commit<CTAS>(ptx::smem_u32(&tfull_bar[hh]));
-          ptx::umma_commit<CTAS>(ptx::mapa(ptx::smem_u32(&tfull_bar[hh]), 1));
+          for (int hh = 0; hh < 2; ++hh) {
+            ptx::umma_commit<CTAS>(ptx::smem_u32(&tfull_bar[hh]));
+            ptx::umma_commit<CTAS>(ptx::mapa(ptx::smem_u32(&tfull_bar[hh]), 1));
+          }
         }
         acc_phase ^= 1u;
       } else {
-        ptx::umma_commit<CTAS>(ptx::smem_u32(&tfull_bar[acc]));
-        if constexpr (CTAS == 2)
-          ptx::umma_commit<CTAS>(ptx::mapa(ptx::smem_u32(&tfull_bar[acc]), 1));
+        if (elected) {
+          ptx::umma_commit<CTAS>(ptx::smem_u32(&tfull_bar[acc]));
+          if constexpr (CTAS == 2)
+            ptx::umma_commit<CTAS>(ptx::mapa(ptx::smem_u32(&tfull_bar[acc]), 1));
+        }
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1u;
       }
     }
-    if (probe) {
+    if (timeline && lane == 0) atomicMax(p.status + 7, static_cast<uint32_t>(ptx::globaltimer_ns()));
+    if (probe && lane == 0) {
       p.status[2] = static_cast<uint32_t>(clock64() - probe_c0);
       p.status[3] = static_cast<uint32_t>(ptx::globaltimer_ns() - probe_t0);
     }
@@ -791,8 +828,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
           et.lane = lane;
           et.t_row = t_row;
           et.cpart = cpart;
-          et.col_begin = hh * Cfg::MMA_N;
-          et.col_end = (hh + 1) * Cfg::MMA_N;
+          et.col_begin = hh * Cfg::SLOT_COLS;
+          et.col_end = (hh + 1) * Cfg::SLOT_COLS;
           et.stg = stg;
           et.bias_col = bias_col;
           et.bias_fast = bias_fast;
@@ -836,6 +873,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
     }
     if (lane == 0) ptx::tma_store_wait_all<0>();
     __syncwarp();
+    if (timeline && lane == 0)
+      atomicMax(p.status + 8, static_cast<uint32_t>(ptx::globaltimer_ns()));
   }
 
   // ---------------------------------------------------------------- teardown

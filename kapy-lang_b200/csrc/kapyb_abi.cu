@@ -174,15 +174,19 @@ extern "C" KAPYB_API kapyb_status kapyb_set_matmul_path(kapyb_handle h, const ch
   size_t colon = s.find(':');
   if (colon != std::string::npos) {
     h->forced_bn = atoi(s.c_str() + colon + 1);
-    size_t colon2 = s.find(":d", colon + 1);
+    size_t colon2 = s.find(":d", colon);
     if (colon2 != std::string::npos) h->debug = atoi(s.c_str() + colon2 + 2);
-    size_t colonw = s.find(":w", colon + 1);
+    size_t colonw = s.find(":w", colon);
     if (colonw != std::string::npos) h->wait_limit_us = 1000u * atoi(s.c_str() + colonw + 2);
-    size_t colon3 = s.find(":e", colon + 1);
+    size_t colon3 = s.find(":e", colon);
     if (colon3 != std::string::npos) h->forced_epi = atoi(s.c_str() + colon3 + 2);
     s = s.substr(0, colon);
-    if (h->forced_bn != 64 && h->forced_bn != 128 && h->forced_bn != 256 && h->forced_bn != 512)
+    const char first_opt = s.c_str()[colon + 1];
+    const bool no_width = first_opt < '0' || first_opt > '9';  // "auto:d128": options only
+    if (!no_width && h->forced_bn != 64 && h->forced_bn != 128 && h->forced_bn != 256 &&
+        h->forced_bn != 512)
       return fail(h, KAPYB_INVALID_ARG, "kapyb_set_matmul_path: tile width must be 64/128/256/512");
+    if (no_width) h->forced_bn = 0;
   }
   if (s == "auto")
     h->forced_path = PATH_AUTO;
@@ -744,17 +748,23 @@ static kapyb_status run_matmul(kapyb_handle h, MatmulProblem p, void *const *pee
     if (p.N <= 64) bn = 64;
     else if (p.N <= 128 && bn > 128) bn = 128;
   }
-  // An N-contiguous B arrives in chunks of 128 bytes of N: a CTA's share of the
-  // tile has to hold at least one chunk (128 columns of an 8-bit type).
+  // An N-contiguous B arrives in chunks of 128 bytes of N: the columns one CTA
+  // loads for one MMA (tile width / column halves / CTAs) have to hold at least
+  // one chunk (128 columns of an 8-bit type).
   const int min_cols = b_mn ? 128 / static_cast<int>(dtype_size(p.in_dtype_b)) : 0;
-  if (bn < min_cols) bn = min_cols;
+  auto group_cols = [](int w, int ctas) { return w / (w == 512 ? 2 : 1) / ctas; };
+  if (path == PATH_2CTA && group_cols(512, 2) >= min_cols && p.N < 512 &&
+      group_cols(std::max(bn, 128), 2) < min_cols)
+    path = PATH_1CTA;  // only the 512-wide pair tile would do, and N is too narrow for it
+  while (path == PATH_1CTA && bn < 256 && group_cols(bn, 1) < min_cols) bn *= 2;
   // Short K loops cannot hide the epilogue behind the next tile's main loop:
   // give those problems eight epilogue warps instead of four.
   const bool epi8 = (p.K + 63) / 64 <= 8 || h->forced_epi == 8;
   if (path == PATH_2CTA) {
     if (h->forced_bn == 0) {
       // 256 x 512 pair tiles move a quarter fewer operand bytes per flop than
-      // 256 x 256; take them unless they fill the last wave much worse.
+      // 256 x 256 and keep the tensor pipe fuller (two accumulators in turn): measured
+      // about 1.25x per tile-wave, so take them unless they fill the waves that much worse.
       const int pairs = std::max(1, h->sm_count / 2);
       auto wave_eff = [&](int w) {
         const long long t = static_cast<long long>((p.M + 255) / 256) * ((p.N + w - 1) / w) * p.batch;
@@ -763,10 +773,10 @@ static kapyb_status run_matmul(kapyb_handle h, MatmulProblem p, void *const *pee
       // The halves share TMEM, so a tile's drain is not hidden behind the next
       // tile's main loop; the register drain keeps it short enough that this pays
       // from a few K blocks on.
-      bn = (p.N >= 512 && p.K >= 512 && wave_eff(512) >= wave_eff(256) - 0.05) ? 512 : 256;
+      bn = (p.N >= 512 && p.K >= 512 && wave_eff(512) >= 0.8 * wave_eff(256)) ? 512 : 256;
     }
     if (bn == 64) bn = 128;
-    if (bn / 2 < min_cols) bn = 2 * min_cols;
+    if (group_cols(bn, 2) < min_cols) bn = 512;
     if (bn == 128) return launch_tcgen05<128, 2, 4>(h, p, a_mn, b_mn, outs, n_out, stream);
     if (bn == 512) {
       if (h->forced_epi == 4) return launch_tcgen05<512, 2, 4>(h, p, a_mn, b_mn, outs, n_out, stream);
