@@ -134,7 +134,9 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tempty_bar + 2);
   volatile uint32_t *abort_flag = tmem_slot + 1;
 
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // the shuffle makes the warp index provably uniform for the compiler
+  const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0);
+  const int lane = threadIdx.x & 31;
   const bool probe = (p.debug & 128) != 0;
   if (probe && threadIdx.x == 0) {
     const uint32_t t = static_cast<uint32_t>(ptx::globaltimer_ns());
@@ -207,8 +209,15 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         }
       }
     }
-  } else if (warp == 1 && lane == 0) {
+  } else if (warp == 1) {
     // ---------------------------------------------------------- MMA issuer
+    // The whole warp walks the loops in step and one elected lane issues (uniform
+    // control flow keeps the descriptor arithmetic in uniform registers); every
+    // wait ends in a vote, so the lanes never part ways, not even on a time-out.
+    auto wait_all = [&](uint32_t bar, uint32_t parity) {
+      const bool mine = ptx::mbar_wait(bar, parity, abort_flag);
+      return __all_sync(0xffffffffu, mine) != 0;
+    };
     // Descriptor constants folded up front; a K step is one add on the low word
     // (the issuing thread must keep pace with a 16 KB stage every few hundred ns).
     const uint32_t w_lbo = p.w_mn_major ? 8192u : 16u, w_kstep = (p.w_mn_major ? 2048u : 32u) >> 4;
@@ -230,40 +239,42 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       int tile, kb_begin, kb_end;
       work.get(j, tile, kb_begin, kb_end);
       (void)tile;
-      if (!ptx::mbar_wait(ptx::smem_u32(&tempty_bar[acc]), acc_phase ^ 1u, abort_flag)) break;
+      if (!wait_all(ptx::smem_u32(&tempty_bar[acc]), acc_phase ^ 1u)) break;
       ptx::tc_fence_after();
       const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * p.m_pad);
       for (int kb = kb_begin; kb < kb_end; ++kb) {
-        if (!ptx::mbar_wait(ptx::smem_u32(&full_bar[stage]), phase, abort_flag)) {
+        if (!wait_all(ptx::smem_u32(&full_bar[stage]), phase)) {
           ok = false;
           break;
         }
         ptx::tc_fence_after();
         if (probe && !seen_first) {
           seen_first = true;
-          atomicMax(p.status + 6, static_cast<uint32_t>(ptx::globaltimer_ns()));
+          if (lane == 0) atomicMax(p.status + 6, static_cast<uint32_t>(ptx::globaltimer_ns()));
         }
         const uint32_t w_lo = w_lo0 + static_cast<uint32_t>(stage) * (W_BYTES >> 4);
         const uint32_t x_lo = x_lo0 + static_cast<uint32_t>(stage) * x_stage_step;
         const uint32_t first = kb > kb_begin ? 1u : 0u;
+        if (ptx::elect_one()) {
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          const uint64_t wdesc = (static_cast<uint64_t>(desc_hi) << 32) | (w_lo + k * w_kstep);
-          const uint64_t xdesc = (static_cast<uint64_t>(desc_hi) << 32) | (x_lo + k * x_kstep);
-          ptx::umma_k<1, 0>(d_tmem, wdesc, xdesc, idesc, k == 0 ? first : 1u);
+          for (int k = 0; k < 4; ++k) {
+            const uint64_t wdesc = (static_cast<uint64_t>(desc_hi) << 32) | (w_lo + k * w_kstep);
+            const uint64_t xdesc = (static_cast<uint64_t>(desc_hi) << 32) | (x_lo + k * x_kstep);
+            ptx::umma_k<1, 0>(d_tmem, wdesc, xdesc, idesc, k == 0 ? first : 1u);
+          }
+          ptx::umma_commit<1>(ptx::smem_u32(&empty_bar[stage]));
         }
-        ptx::umma_commit<1>(ptx::smem_u32(&empty_bar[stage]));
         if (++stage == p.stages) {
           stage = 0;
           phase ^= 1u;
         }
       }
       if (!ok) break;
-      ptx::umma_commit<1>(ptx::smem_u32(&tfull_bar[acc]));
+      if (ptx::elect_one()) ptx::umma_commit<1>(ptx::smem_u32(&tfull_bar[acc]));
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1u;
     }
-    if (probe) {
+    if (probe && lane == 0) {
       atomicMax(p.status + 7, static_cast<uint32_t>(ptx::globaltimer_ns()));
       if (blockIdx.x == 0) {
         p.status[2] = static_cast<uint32_t>(clock64() - probe_c0);

@@ -39,7 +39,11 @@ class Unsupported(NotImplementedError):
     pass
 
 
-_DT = {"f16": abi.F16, "bf16": abi.BF16, "f32": abi.F32}
+_DT = {"f16": abi.F16, "bf16": abi.BF16, "f32": abi.F32, "f8e4m3": abi.F8E4M3,
+       "f8e5m2": abi.F8E5M2}  # the f8 types: matmul operands only (the library checks)
+
+
+_ESZ = {abi.F16: 2, abi.BF16: 2, abi.F32: 4, abi.F8E4M3: 1, abi.F8E5M2: 1}
 
 
 def _dtype(t) -> int:
@@ -465,7 +469,7 @@ def _tensor_desc(root: GlobalRoot, tensors, lo0, hi0, lo1, hi1, padding=abi.PAD_
     t = tensors[root.arg]
     s0 = max(0, min(hi0, root.size0) - lo0)
     s1 = max(0, min(hi1, root.size1) - lo1)
-    esz = 4 if root.dtype == abi.F32 else 2
+    esz = _ESZ[root.dtype]
     if t.element_size() != esz:
         raise ValueError(f"argument {root.arg} has {t.element_size()}-byte elements but the kernel "
                          f"declares a {esz}-byte element type")
@@ -665,7 +669,7 @@ def _launch_matmul(L, handle, sp):
     if bias_root is not None:
         root, axis = bias_root
         t = L.args[root.arg]
-        esz = 4 if root.dtype == abi.F32 else 2
+        esz = _ESZ[root.dtype]
         lo = lo1 if axis == 1 else lo0
         ep.bias = t.data_ptr() + (root.offset + lo * (root.stride1 if axis == 1 else root.stride0)) * esz
         ep.bias_dtype = root.dtype

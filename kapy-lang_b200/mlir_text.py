@@ -16,6 +16,9 @@ from typing import Dict, List, Tuple
 from . import ir
 
 _ELEM = {"i1", "i8", "i16", "i32", "i64", "f16", "bf16", "f32", "f64"}
+# MLIR's spellings of the two 8-bit float types (both E4M3 spellings reach the
+# matmul as the finite-only format the MMA instruction reads)
+_F8 = {"f8E4M3": "f8e4m3", "f8E4M3FN": "f8e4m3", "f8E5M2": "f8e5m2"}
 _MEM = {"#global": ir.MemorySpace.GLOBAL_MEMORY, "#shared": ir.MemorySpace.SHARED_MEMORY,
         "#values": ir.MemorySpace.REGISTER_FILE}
 
@@ -24,13 +27,15 @@ def parse_type(text: str, aliases: Dict[str, ir.MemorySpace]):
     text = text.strip()
     if text in _ELEM:
         return ir.Type(text)
+    if text in _F8:
+        return ir.Type(_F8[text])
     if text.startswith("!kapy.ptr"):
         return ir.Type("ptr")
     m = re.fullmatch(r"tensor<([^,>]+?)(?:,\s*(#[\w.<>]+))?>", text)
     if not m:
         raise SyntaxError(f"unsupported type '{text}'")
     parts = m.group(1).split("x")
-    elem = ir.Type(parts[-1].strip())
+    elem = ir.Type(_F8.get(parts[-1].strip(), parts[-1].strip()))
     shape = tuple(-1 if p.strip() == "?" else int(p) for p in parts[:-1])
     enc = m.group(2)
     if enc is None:

@@ -72,6 +72,41 @@ def test_lift_gemm_ring(pkg):
     assert ep.alpha == 1.0 and ep.rounding == pkg.abi.RN and not ep.bias
 
 
+def test_lift_gemm_ring_f8_and_tf32(pkg):
+    """The same kernel with f8E4M3 x f8E5M2 operands (mma_m16n8k16_f8) and with
+    f32 operands (mma_m16n8k8_tf32): element types and impl way reach the call."""
+    text = open(os.path.join(KERNELS, "gemm_ring_bf16.mlir")).read()
+    body = text.replace("x16xbf16", "x16xf8E4M3").replace("16x32xbf16", "16x32xf8E5M2")
+    body = body.replace("[%k, %c1] : !kapy.ptr<1> -> tensor<?x?xbf16", "[%k, %c1] : !kapy.ptr<1> -> tensor<?x?xf8E4M3")
+    body = body.replace("%gb = kapy.mk_global %pb[%c0] [%k, %n] [%n, %c1] : !kapy.ptr<1> -> tensor<?x?xbf16",
+                        "%gb = kapy.mk_global %pb[%c0] [%k, %n] [%n, %c1] : !kapy.ptr<1> -> tensor<?x?xf8E5M2")
+    body = body.replace("%ga[%r0 : %r1, %k0 : %k1] : tensor<?x?xbf16", "%ga[%r0 : %r1, %k0 : %k1] : tensor<?x?xf8E4M3")
+    body = body.replace("%gb[%k0 : %k1, %q0 : %q1] : tensor<?x?xbf16", "%gb[%k0 : %k1, %q0 : %q1] : tensor<?x?xf8E5M2")
+    body = body.replace("mma_m16n8k16_f16", "mma_m16n8k16_f8")
+    M, K, N = 128, 64, 96
+    for src, ta, tb, way in ((body, torch.float8_e4m3fn, torch.float8_e5m2, "MMA_M16N8K16_F8"),
+                             (text.replace("x16xbf16", "x16xf32").replace("16x32xbf16", "16x32xf32")
+                                  .replace("mma_m16n8k16_f16", "mma_m16n8k8_tf32")
+                                  .replace("[%k, %c1] : !kapy.ptr<1> -> tensor<?x?xbf16", "[%k, %c1] : !kapy.ptr<1> -> tensor<?x?xf32")
+                                  .replace("%gb = kapy.mk_global %pb[%c0] [%k, %n] [%n, %c1] : !kapy.ptr<1> -> tensor<?x?xbf16",
+                                           "%gb = kapy.mk_global %pb[%c0] [%k, %n] [%n, %c1] : !kapy.ptr<1> -> tensor<?x?xf32")
+                                  .replace("%ga[%r0 : %r1, %k0 : %k1] : tensor<?x?xbf16", "%ga[%r0 : %r1, %k0 : %k1] : tensor<?x?xf32")
+                                  .replace("%gb[%k0 : %k1, %q0 : %q1] : tensor<?x?xbf16", "%gb[%k0 : %k1, %q0 : %q1] : tensor<?x?xf32"),
+                              torch.float32, torch.float32, "MMA_M16N8K8_TF32")):
+        mod = pkg.mlir_text.parse_text(src)
+        fn = next(iter(mod.functions.values()))
+        a = torch.zeros((M, K)).to(ta)
+        b = torch.zeros((K, N)).to(tb)
+        c = torch.zeros((M, N), dtype=torch.bfloat16)
+        h = FakeHandle()
+        pkg.executor.launch(fn, (M // 32, N // 32, 1), [a, b, c, M, K, N], h, module=mod)
+        kind, tl, tr, to, ep, got_way = h.log[0]
+        assert kind == "matmul" and got_way == int(getattr(pkg.ir.MatmulImplWay, way))
+        assert (tl.dtype, tr.dtype, to.dtype) == (pkg.runtime.dtype_code(ta), pkg.runtime.dtype_code(tb),
+                                                  pkg.abi.BF16)
+        assert (tl.size0, tl.size1, tl.stride0) == (M, K, K) and (tr.size0, tr.size1) == (K, N)
+
+
 @pytest.mark.skipif(not os.path.isdir(REF), reason="reference checkout not present")
 def test_reference_inputs_parse_and_lift(pkg):
     """elementwise_add.mlir, reduce_sum.mlir and matmul.mlir run unchanged: each
