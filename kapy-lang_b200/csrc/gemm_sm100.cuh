@@ -33,12 +33,34 @@ struct TmapArray {
   CUtensorMap m[kMaxOutputs];
 };
 
+// Division by a launch-time constant as a multiply-high and a shift (exact for
+// dividends below 2^31): mul = ceil(2^(31 + ceil(log2 d)) / d), shr = ceil(log2 d) - 1.
+struct FastDiv {
+  uint32_t mul, shr, d;
+  static FastDiv make(uint32_t d) {  // host side
+    FastDiv f{0u, 0u, d};
+    if (d > 1) {
+      uint32_t l = 0;
+      while ((1ull << l) < d) ++l;
+      const uint32_t p = 31 + l;
+      f.mul = static_cast<uint32_t>(((1ull << p) + d - 1) / d);
+      f.shr = p - 32;
+    }
+    return f;
+  }
+  __device__ __forceinline__ int div(int n) const {
+    return d == 1 ? n : static_cast<int>(__umulhi(static_cast<uint32_t>(n), mul) >> shr);
+  }
+};
+
 struct GemmParams {
   int M, N, K, batch;
   int tiles_m, tiles_n;  // tile grid of one batch entry
   int num_tiles;         // tiles_m * tiles_n * batch
   int num_kb;            // ceil(K / 64)
   int group_m;           // rasterisation: tiles_m are walked in groups of this many
+  FastDiv div_per_batch, div_in_group, div_group_m, div_last_group;  // decode_tile's divisors:
+                         // tiles_m * tiles_n, group_m * tiles_n, group_m, max(1, tiles_m % group_m)
   int a_mn_major;        // 1: lhs is column-major (M contiguous)
   int b_mn_major;        // 1: rhs is row-major [K,N] (N contiguous)
   int out_dtype;
@@ -65,7 +87,10 @@ struct GemmParams {
               // bit7 the first CTA's MMA thread records cycles and nanoseconds of its
               // tile loop in status[2], status[3]; status[4..8] collect over all CTAs
               // (timer low words): complement of the earliest start, latest start,
-              // latest first stage, latest last MMA issue, latest epilogue end
+              // latest first stage, latest last MMA issue, latest epilogue end; status[9..13]:
+              // clocks the first CTA's first epilogue warp spent, summed over its chunks,
+              // waiting for its staging buffer, for the accumulator loads, in arithmetic +
+              // staging, issuing the store, and (per tile) waiting for the accumulator
   EpilogueArgs ep;
 };
 
@@ -109,19 +134,19 @@ struct GemmCfg {
 };
 
 // Linear tile index -> (batch, m block, n block); m blocks are walked in groups
-// so that concurrently running CTAs share A rows and B columns in L2.
+// so that concurrently running CTAs share A rows and B columns in L2.  Every
+// role of every CTA runs this once per tile, so its divisions are FastDivs.
 __device__ __forceinline__ void decode_tile(const GemmParams &p, int tile, int &b, int &mb,
                                             int &nb) {
-  const int per_batch = p.tiles_m * p.tiles_n;
-  b = tile / per_batch;
-  const int r = tile - b * per_batch;
-  const int in_group = p.group_m * p.tiles_n;
-  const int g = r / in_group;
+  b = p.div_per_batch.div(tile);
+  const int r = tile - b * static_cast<int>(p.div_per_batch.d);
+  const int g = p.div_in_group.div(r);
   const int first_m = g * p.group_m;
-  const int gsize = min(p.group_m, p.tiles_m - first_m);
-  const int rr = r - g * in_group;
-  mb = first_m + rr % gsize;
-  nb = rr / gsize;
+  const int rr = r - g * static_cast<int>(p.div_in_group.d);
+  // every group has group_m row blocks but the last, which has the remainder
+  const bool last = first_m + p.group_m > p.tiles_m;
+  nb = last ? p.div_last_group.div(rr) : p.div_group_m.div(rr);
+  mb = first_m + rr - nb * (last ? static_cast<int>(p.div_last_group.d) : p.group_m);
 }
 
 // 32 finished columns of one row -> the row's slot in the swizzled staging tile.
@@ -176,6 +201,8 @@ struct EpiTile {
   uint8_t *stg;     // this warp's two 4 KB staging buffers
   bool bias_col, bias_fast;
   float bias_row;
+  uint32_t *prof;   // profiling (debug bit 7, one warp of the first CTA): shared words that
+                    // collect clocks spent per phase of the chunk loop; else nullptr
 };
 
 // The fused arithmetic on 32 consecutive accumulator columns of one row
@@ -265,6 +292,7 @@ __device__ __forceinline__ bool epilogue_tile(const GemmParams &p, const TmapArr
     uint8_t *sbuf = t.stg + (C_BUFS == 2 ? buf : 0) * 4096;
     // All loads of the chunk are in flight before the one wait.
     uint32_t v[NH][32];
+    const uint32_t c0 = t.prof ? static_cast<uint32_t>(clock()) : 0u;
 #pragma unroll
     for (int h = 0; h < NH; ++h)
       ptx::tmem_ld_32x32(t.t_row + static_cast<uint32_t>(c * CW + h * 32), v[h]);
@@ -272,7 +300,9 @@ __device__ __forceinline__ bool epilogue_tile(const GemmParams &p, const TmapArr
     // with a single buffer) must have finished reading it.
     if (lane == 0) ptx::tma_store_wait_read<C_BUFS - 1>();
     __syncwarp();
+    const uint32_t c1 = t.prof ? static_cast<uint32_t>(clock()) : 0u;
     ptx::tmem_ld_wait();
+    const uint32_t c2 = t.prof ? static_cast<uint32_t>(clock()) : 0u;
     if (c + CSTEP >= t.col_end / CW || t.n0 + (c + CSTEP) * CW >= p.N) {
       // That was this warp's last read of the slot: hand it back now, so the next
       // tile's MMAs do not wait for the arithmetic and the stores below.
@@ -304,10 +334,17 @@ __device__ __forceinline__ bool epilogue_tile(const GemmParams &p, const TmapArr
     }
     ptx::fence_proxy_async_smem();
     __syncwarp();
+    const uint32_t c3 = t.prof ? static_cast<uint32_t>(clock()) : 0u;
     if (lane == 0 && !(p.debug & 8)) {
       for (int o = 0; o < p.n_out; ++o)
         ptx::tma_store_3d(&tmC.m[o], ptx::smem_u32(sbuf), p.out_col_offset + nc, t.m0, t.b);
       ptx::tma_store_commit();
+    }
+    if (t.prof && lane == 0) {
+      atomicAdd(t.prof + 0, c2 - c0);  // staging buffer free again, accumulator loads landed
+      (void)c1;
+      atomicAdd(t.prof + 2, c3 - c2);  // arithmetic, staging, fence
+      atomicAdd(t.prof + 3, static_cast<uint32_t>(clock()) - c3);  // store issued
     }
     buf ^= 1;
   }
@@ -499,6 +536,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
   uint64_t *tempty_bar = tfull_bar + 2;      // [2]
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tempty_bar + 2);
   volatile uint32_t *abort_flag = tmem_slot + 1;
+  uint32_t *prof_words = tmem_slot + 8;  // [5] clocks per epilogue phase (debug bit 7)
 
   // the shuffle makes the warp index provably uniform for the compiler
   const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0);
@@ -524,6 +562,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
     }
     abort_flag[0] = 0u;
     abort_flag[1] = p.wait_limit_us;
+    for (int i = 0; i < 5; ++i) prof_words[i] = 0u;
     ptx::fence_barrier_init();
   }
   if (warp == 0 && lane == 0) {
@@ -766,9 +805,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
     int acc = 0;
     uint32_t acc_phase = 0;
     int buf = 0;
+    uint32_t *prof = (timeline && blockIdx.x == 0 && e == 0) ? prof_words : nullptr;
     for (int tile = unit; tile < p.num_tiles; tile += unit_step) {
+      const uint32_t s0 = prof ? static_cast<uint32_t>(clock()) : 0u;
       int b, mb, nb;
       decode_tile(p, tile, b, mb, nb);
+      if (prof && lane == 0) atomicAdd(prof + 1, static_cast<uint32_t>(clock()) - s0);  // tile decode
       const int m0 = mb * Cfg::TILE_M + static_cast<int>(rank) * Cfg::BM + q * 32;
       const int n0 = nb * BN;
       const int row = m0 + lane;
@@ -793,6 +835,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
           et.bias_col = bias_col;
           et.bias_fast = bias_fast;
           et.bias_row = 0.0f;
+          et.prof = nullptr;
           if (p.ep.bias != nullptr && p.ep.bias_axis == 0 && row < p.M)
             et.bias_row = load_as_f32(p.ep.bias, p.ep.bias_dtype, row);
           const bool active = m0 < p.M && !(p.debug & 4);
@@ -808,10 +851,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       for (int hh = 0; hh < Cfg::HALVES; ++hh) {
         // slot: with two halves, half hh of this tile; otherwise the tile's slot
         const int slot = Cfg::HALVES == 2 ? hh : acc;
+        const uint32_t w0 = prof ? static_cast<uint32_t>(clock()) : 0u;
         if (!ptx::mbar_wait(ptx::smem_u32(&tfull_bar[slot]), acc_phase, abort_flag)) {
           alive = false;
           break;
         }
+        if (prof && lane == 0) atomicAdd(prof + 4, static_cast<uint32_t>(clock()) - w0);
         ptx::tc_fence_after();
         const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
                                (Cfg::HALVES == 2 ? 0u : static_cast<uint32_t>(acc * BN));
@@ -834,6 +879,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
           et.bias_col = bias_col;
           et.bias_fast = bias_fast;
           et.bias_row = 0.0f;
+          et.prof = prof;
           if (p.ep.bias != nullptr && p.ep.bias_axis == 0 && row < p.M)
             et.bias_row = load_as_f32(p.ep.bias, p.ep.bias_dtype, row);
           // One specialised copy of the chunk loop per (output kind, plain/full
@@ -880,6 +926,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
   // ---------------------------------------------------------------- teardown
   ptx::tc_fence_before();
   __syncthreads();
+  if (timeline && blockIdx.x == 0 && threadIdx.x == 0) {
+    for (int i = 0; i < 5; ++i) p.status[9 + i] = prof_words[i];
+  }
   if (*abort_flag != 0u) {
     if (threadIdx.x == 0) atomicExch(p.status, kStatusTimeout);
     // Give loads that are still in flight time to land before the shared

@@ -528,6 +528,10 @@ static kapyb_status launch_tcgen05(kapyb_handle h, const MatmulProblem &p, bool 
   };
   gp.idesc = ptx::make_idesc(fmt(p.in_dtype), fmt(p.in_dtype_b), a_mn, b_mn, Cfg::TILE_M, Cfg::MMA_N);
   if (BN == 512) gp.group_m = std::max(1, std::min(gp.tiles_m, 12));
+  gp.div_per_batch = FastDiv::make(static_cast<uint32_t>(gp.tiles_m * gp.tiles_n));
+  gp.div_in_group = FastDiv::make(static_cast<uint32_t>(gp.group_m * gp.tiles_n));
+  gp.div_group_m = FastDiv::make(static_cast<uint32_t>(gp.group_m));
+  gp.div_last_group = FastDiv::make(static_cast<uint32_t>(std::max(1, gp.tiles_m % gp.group_m)));
   gp.status = h->status;
   gp.debug = h->debug;
   gp.wait_limit_us = h->wait_limit_us;
