@@ -356,13 +356,16 @@ KAPYB_API const char *kapyb_last_kernel(kapyb_handle h);
 KAPYB_API int64_t kapyb_launch_count(kapyb_handle h);
 
 /* Profiling probes of the last matmul launched with debug bit 7 (":d128" in
- * kapyb_set_matmul_path), then cleared.  Copies n <= 12 words after
+ * kapyb_set_matmul_path), then cleared.  Copies n <= 14 words after
  * synchronising `stream`.  tcgen05 GEMM: word 0 = SM cycles, word 1 = wall
  * nanoseconds the first CTA's MMA-issuing thread spent in its tile loop (their
  * ratio is the SM clock in GHz while the kernel ran).  Both kernels: words 2..6
  * are readings of the nanosecond timer's low 32 bits: the
  * complement of the earliest CTA start, then the latest, over all CTAs, of: CTA
- * start, first operand stage landed, last MMA issued, epilogue done. */
+ * start, first operand stage landed, last MMA issued, epilogue done.  GEMM only:
+ * words 7..11 = clocks one epilogue warp of the first CTA spent per phase of its
+ * chunk loop; words 12, 13 = clocks the first CTA's MMA warp waited for operand
+ * stages and for accumulator slots. */
 KAPYB_API kapyb_status kapyb_probe_read(kapyb_handle h, void *stream, uint32_t *words, int32_t n);
 
 /* Forces a kernel family for matmul ("auto", "1cta", "2cta", "skinny",

@@ -90,7 +90,9 @@ struct GemmParams {
               // latest first stage, latest last MMA issue, latest epilogue end; status[9..13]:
               // clocks the first CTA's first epilogue warp spent, summed over its chunks,
               // waiting for its staging buffer, for the accumulator loads, in arithmetic +
-              // staging, issuing the store, and (per tile) waiting for the accumulator
+              // staging, issuing the store, and (per tile) waiting for the accumulator;
+              // status[14], [15]: clocks the first CTA's MMA warp waited for operand stages
+              // and for accumulator slots
   EpilogueArgs ep;
 };
 
@@ -496,18 +498,21 @@ __device__ __forceinline__ bool epilogue_two_halves(const GemmParams &p, const T
 // The MMAs of one K block (four K steps of 32 bytes; with a split tile, both
 // column halves per step, sharing the A descriptor).  Descriptors arrive as
 // (low word of K step 0, constant high word, low-word increment per K step);
+// `half_mask` picks the column halves to issue (bit hh), all of them = 3;
 // this CTA's B bytes of half hh start (MMA_N / CTAS) rows of 128 bytes after
 // those of half hh-1, in either layout and for any element width.
 template <int CTAS, int SPLIT, int MMA_N, int KIND>
 __device__ __forceinline__ void issue_kblock(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi,
                                              uint32_t a_kstep, uint32_t b_lo, uint32_t b_hi,
-                                             uint32_t b_kstep, uint32_t idesc, uint32_t first) {
+                                             uint32_t b_kstep, uint32_t idesc, uint32_t first,
+                                             uint32_t half_mask) {
   constexpr uint32_t kHalfStep = (MMA_N / CTAS) * 128 / 16;
 #pragma unroll
   for (int k = 0; k < 4; ++k) {
     const uint64_t adesc = (static_cast<uint64_t>(a_hi) << 32) | (a_lo + k * a_kstep);
 #pragma unroll
     for (int hh = 0; hh < SPLIT; ++hh) {
+      if (SPLIT > 1 && !(half_mask & (1u << hh))) continue;
       const uint64_t bdesc =
           (static_cast<uint64_t>(b_hi) << 32) | (b_lo + k * b_kstep + hh * kHalfStep);
       ptx::umma_k<CTAS, KIND>(d_tmem + hh * MMA_N, adesc, bdesc, idesc, k == 0 ? first : 1u);
@@ -707,76 +712,132 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
     const bool probe = timeline && blockIdx.x == 0;
     const long long probe_c0 = probe ? clock64() : 0;
     const uint64_t probe_t0 = probe ? ptx::globaltimer_ns() : 0;
+    uint32_t stall_full = 0, stall_drain = 0;  // probe: clocks this thread waited for operands / for TMEM
     for (int tile = unit; tile < p.num_tiles && ok; tile += unit_step) {
-      if constexpr (Cfg::HALVES == 2) {
-        // both halves of the previous tile must have been drained
-        if (!wait_all(ptx::smem_u32(&tempty_bar[0]), acc_phase ^ 1u)) break;
-        if (!wait_all(ptx::smem_u32(&tempty_bar[1]), acc_phase ^ 1u)) break;
-      } else {
-        if (!wait_all(ptx::smem_u32(&tempty_bar[acc]), acc_phase ^ 1u)) break;
-      }
-      ptx::tc_fence_after();
-      const uint32_t d_tmem =
-          tmem_base + (Cfg::HALVES == 2 ? 0u : static_cast<uint32_t>(acc * BN));
-      for (int kb = 0; kb < p.num_kb; ++kb) {
-        if (!free_run && !wait_all(ptx::smem_u32(&full_bar[stage]), phase)) {
-          ok = false;
-          break;
-        }
+      // ---- helpers (every lane runs them; one elected lane issues)
+      // waits for the next operand stage; returns its index, or -1 when the wait ran out
+      auto wait_stage = [&]() -> int {
+        const uint32_t f0 = probe ? static_cast<uint32_t>(clock()) : 0u;
+        if (!free_run && !wait_all(ptx::smem_u32(&full_bar[stage]), phase)) return -1;
+        if (probe) stall_full += static_cast<uint32_t>(clock()) - f0;
         ptx::tc_fence_after();
         if (timeline && !seen_first) {
           seen_first = true;
           if (lane == 0) atomicMax(p.status + 6, static_cast<uint32_t>(ptx::globaltimer_ns()));
         }
-        const bool elected = ptx::elect_one();
-        if (!skip_mma && elected) {
-          const uint32_t a_lo = a_lo0 + static_cast<uint32_t>(stage) * (Cfg::A_BYTES >> 4);
-          const uint32_t b_lo = b_lo0 + static_cast<uint32_t>(stage) * (Cfg::B_BYTES >> 4);
-          const uint32_t first = kb != 0 ? 1u : 0u;  // the tile's first MMA overwrites
-          if (kind == 0)
-            issue_kblock<CTAS, Cfg::SPLIT, Cfg::MMA_N, 0>(d_tmem, a_lo, a_hi, a_kstep, b_lo, b_hi,
-                                                           b_kstep, idesc, first);
-          else if (kind == 1)
-            issue_kblock<CTAS, Cfg::SPLIT, Cfg::MMA_N, 1>(d_tmem, a_lo, a_hi, a_kstep, b_lo, b_hi,
-                                                           b_kstep, idesc, first);
-          else
-            issue_kblock<CTAS, Cfg::SPLIT, Cfg::MMA_N, 2>(d_tmem, a_lo, a_hi, a_kstep, b_lo, b_hi,
-                                                           b_kstep, idesc, first);
-        }
-        // Free the stage in every CTA that filled it.
-        if (!free_run && elected) {
-          ptx::umma_commit<CTAS>(ptx::smem_u32(&empty_bar[stage]));
-          if constexpr (CTAS == 2)
-            ptx::umma_commit<CTAS>(ptx::mapa(ptx::smem_u32(&empty_bar[stage]), 1));
-        }
+        const int st = stage;
         if (++stage == STAGES) {
           stage = 0;
           phase ^= 1u;
         }
-      }
-      if (!ok) break;
-      const bool elected = ptx::elect_one();
+        return st;
+      };
+      // the MMAs of stage `st` into the accumulator(s) at d_tmem; `first` = 0 overwrites
+      auto issue = [&](int st, uint32_t d_tmem, uint32_t first, uint32_t half_mask) {
+        if (skip_mma || !ptx::elect_one()) return;
+        const uint32_t a_lo = a_lo0 + static_cast<uint32_t>(st) * (Cfg::A_BYTES >> 4);
+        const uint32_t b_lo = b_lo0 + static_cast<uint32_t>(st) * (Cfg::B_BYTES >> 4);
+        if (kind == 0)
+          issue_kblock<CTAS, Cfg::SPLIT, Cfg::MMA_N, 0>(d_tmem, a_lo, a_hi, a_kstep, b_lo, b_hi,
+                                                         b_kstep, idesc, first, half_mask);
+        else if (kind == 1)
+          issue_kblock<CTAS, Cfg::SPLIT, Cfg::MMA_N, 1>(d_tmem, a_lo, a_hi, a_kstep, b_lo, b_hi,
+                                                         b_kstep, idesc, first, half_mask);
+        else
+          issue_kblock<CTAS, Cfg::SPLIT, Cfg::MMA_N, 2>(d_tmem, a_lo, a_hi, a_kstep, b_lo, b_hi,
+                                                         b_kstep, idesc, first, half_mask);
+      };
+      // frees stage `st` in every CTA that filled it, once the MMAs issued so far are done
+      auto release = [&](int st) {
+        if (free_run || !ptx::elect_one()) return;
+        ptx::umma_commit<CTAS>(ptx::smem_u32(&empty_bar[st]));
+        if constexpr (CTAS == 2) ptx::umma_commit<CTAS>(ptx::mapa(ptx::smem_u32(&empty_bar[st]), 1));
+      };
+      // publishes accumulator slot `slot` to the epilogue warps of every CTA
+      auto publish = [&](int slot) {
+        if (!ptx::elect_one()) return;
+        ptx::umma_commit<CTAS>(ptx::smem_u32(&tfull_bar[slot]));
+        if constexpr (CTAS == 2) ptx::umma_commit<CTAS>(ptx::mapa(ptx::smem_u32(&tfull_bar[slot]), 1));
+      };
+      auto wait_drained = [&](int slot) {
+        const uint32_t d0 = probe ? static_cast<uint32_t>(clock()) : 0u;
+        const bool got = wait_all(ptx::smem_u32(&tempty_bar[slot]), acc_phase ^ 1u);
+        if (probe) stall_drain += static_cast<uint32_t>(clock()) - d0;
+        ptx::tc_fence_after();
+        return got;
+      };
+
       if constexpr (Cfg::HALVES == 2) {
-        if (elected) {
-#pragma unroll
-          for (int hh = 0; hh < 2; ++hh) {
-            ptx::umma_commit<CTAS>(ptx::smem_u32(&tfull_bar[hh]));
-            ptx::umma_commit<CTAS>(ptx::mapa(ptx::smem_u32(&tfull_bar[hh]), 1));
-          }
+        // The two halves fill TMEM, so a tile's MMAs cannot start before the
+        // previous tile has been drained.  To keep the tensor pipe fed across
+        // that hand-over the halves are skewed by kSkew K blocks at the tile
+        // boundaries only: the tile ENDS with half 0's last blocks, then half
+        // 1's (half 0 drains under those), and STARTS with half 0's first
+        // blocks (half 1 still draining), then half 1's.  In between both halves
+        // of a K block are issued together and share its A stage.
+        constexpr int kSkew = 2;
+        static_assert(kSkew < STAGES, "the skewed blocks stay resident until both halves used them");
+        const uint32_t d_tmem = tmem_base;
+        const int n = p.num_kb;
+        const int skew = n >= 2 * kSkew ? kSkew : 0;
+        int held[kSkew];
+        if (!wait_drained(0)) break;
+        for (int i = 0; i < skew && ok; ++i) {
+          held[i] = wait_stage();
+          if (held[i] < 0) ok = false;
+          else issue(held[i], d_tmem, i != 0 ? 1u : 0u, 1u);
         }
+        if (!ok) break;
+        if (!wait_drained(1)) break;
+        for (int i = 0; i < skew; ++i) {
+          issue(held[i], d_tmem, i != 0 ? 1u : 0u, 2u);
+          release(held[i]);
+        }
+        for (int kb = skew; kb < n - skew; ++kb) {
+          const int st = wait_stage();
+          if (st < 0) {
+            ok = false;
+            break;
+          }
+          issue(st, d_tmem, kb != 0 ? 1u : 0u, 3u);
+          release(st);
+        }
+        if (!ok) break;
+        for (int i = 0; i < skew && ok; ++i) {
+          held[i] = wait_stage();
+          if (held[i] < 0) ok = false;
+          else issue(held[i], d_tmem, 1u, 1u);
+        }
+        if (!ok) break;
+        publish(0);
+        for (int i = 0; i < skew; ++i) {
+          issue(held[i], d_tmem, 1u, 2u);
+          release(held[i]);
+        }
+        publish(1);
         acc_phase ^= 1u;
       } else {
-        if (elected) {
-          ptx::umma_commit<CTAS>(ptx::smem_u32(&tfull_bar[acc]));
-          if constexpr (CTAS == 2)
-            ptx::umma_commit<CTAS>(ptx::mapa(ptx::smem_u32(&tfull_bar[acc]), 1));
+        if (!wait_drained(acc)) break;
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
+        for (int kb = 0; kb < p.num_kb; ++kb) {
+          const int st = wait_stage();
+          if (st < 0) {
+            ok = false;
+            break;
+          }
+          issue(st, d_tmem, kb != 0 ? 1u : 0u, 3u);
+          release(st);
         }
+        if (!ok) break;
+        publish(acc);
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1u;
       }
     }
     if (timeline && lane == 0) atomicMax(p.status + 7, static_cast<uint32_t>(ptx::globaltimer_ns()));
     if (probe && lane == 0) {
+      p.status[14] = stall_full;
+      p.status[15] = stall_drain;
       p.status[2] = static_cast<uint32_t>(clock64() - probe_c0);
       p.status[3] = static_cast<uint32_t>(ptx::globaltimer_ns() - probe_t0);
     }

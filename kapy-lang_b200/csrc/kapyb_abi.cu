@@ -106,7 +106,7 @@ extern "C" KAPYB_API kapyb_status kapyb_create(kapyb_handle *out, int device) {
     return fail(nullptr, KAPYB_CUDA_ERROR, "kapyb_create: cuTensorMapEncodeTiled not available");
   }
   c->encode = reinterpret_cast<EncodeTiledFn>(fn);
-  // word 0: status; words 2..13: the profiling probes read by kapyb_probe_read
+  // word 0: status; words 2..15: the profiling probes read by kapyb_probe_read
   e = cudaMalloc(&c->status, 16 * sizeof(uint32_t));
   if (e == cudaSuccess) e = cudaMemset(c->status, 0, 16 * sizeof(uint32_t));
   if (e != cudaSuccess) {
@@ -144,14 +144,14 @@ extern "C" KAPYB_API int64_t kapyb_launch_count(kapyb_handle h) { return h ? h->
 
 extern "C" KAPYB_API kapyb_status kapyb_probe_read(kapyb_handle h, void *stream, uint32_t *words,
                                                    int32_t n) {
-  if (!h || !words || n < 0 || n > 12)
-    return fail(h, KAPYB_INVALID_ARG, "kapyb_probe_read: NULL argument or n outside 0..12");
+  if (!h || !words || n < 0 || n > 14)
+    return fail(h, KAPYB_INVALID_ARG, "kapyb_probe_read: NULL argument or n outside 0..14");
   CUDA_TRY(h, cudaSetDevice(h->device));
   CUDA_TRY(h, cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
   if (n > 0)
     CUDA_TRY(h, cudaMemcpy(words, h->status + 2, n * sizeof(uint32_t), cudaMemcpyDeviceToHost));
   // probes accumulate with max/min across CTAs: start each measurement from zero
-  CUDA_TRY(h, cudaMemset(h->status + 2, 0, 12 * sizeof(uint32_t)));
+  CUDA_TRY(h, cudaMemset(h->status + 2, 0, 14 * sizeof(uint32_t)));
   return KAPYB_OK;
 }
 

@@ -120,7 +120,7 @@ class Handle:
 
     def probe_read(self, n: int = 2, stream=None):
         """Probe words of the last matmul run with debug bit 7 (":d128")."""
-        words = (C.c_uint32 * 12)()
+        words = (C.c_uint32 * 14)()
         st = self._lib.kapyb_probe_read(self._h, self._stream(stream), words, n)
         if st != abi.OK:
             self._raise(st)
