@@ -54,7 +54,10 @@ typedef enum {
   KAPYB_F16 = 0,
   KAPYB_BF16 = 1,
   KAPYB_F32 = 2,
-  /* matmul operands only (MatmulImplWay MMA_M16N8K16_F8, Kapy.cpp:547-564) */
+  /* The two 8-bit types: matmul operands (MatmulImplWay MMA_M16N8K16_F8,
+   * Kapy.cpp:547-564) and the two ends of a cast (FPToFPOp, Kapy.cpp:272-287);
+   * nothing computes in them.  f8E4M3 bytes are read the way the MMA and cvt
+   * instructions read them: finite-only, S.1111.111 is NaN, largest value 448. */
   KAPYB_F8E4M3 = 3,
   KAPYB_F8E5M2 = 4
 } kapyb_dtype;
@@ -316,9 +319,14 @@ KAPYB_API kapyb_status kapyb_matmul_decode_static(const kapyb_tensor2d *lhs,
 /* Runs a recorded elementwise graph over out->size0 x out->size1 elements.
  * inputs[k] is what the k-th KAPYB_OP_LOAD reads; an input whose size on an
  * axis is 1 broadcasts along it (kapy.broadcast, Ops.td:342-356).  Canonical
- * graphs (affine, affine + gelu_tanh, binary add/sub/mul, casts) run as fused
- * 128-bit-vectorised kernels; any other valid program runs on the generic
- * device interpreter.  Programs are validated (register use before def, dtype
+ * graphs (affine, affine + gelu_tanh, binary add/sub/mul, casts to or from an
+ * 8-bit type) run as fused vectorised kernels; any other valid program runs on
+ * the generic device interpreter.  Casts involving f8E4M3 / f8E5M2 follow
+ * ElementwiseOpToLLVM.cpp:83-289, :583-650: widening is exact; narrowing with
+ * rn is cvt.rn.satfinite (beyond the largest finite value, infinities included,
+ * gives that value); rz exists for f8E5M2 from f16 / f32 only (the high byte of
+ * the value truncated to f16); f8 to f8 and rz from bf16 are refused with the
+ * verifier's words (Kapy.cpp:272-287).  Programs are validated (register use before def, dtype
  * agreement, downcasts need a rounding mode) as the op verifiers would. */
 KAPYB_API kapyb_status kapyb_elementwise(kapyb_handle h, const kapyb_inst *prog,
                                          int32_t n_inst,

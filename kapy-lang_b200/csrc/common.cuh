@@ -137,6 +137,28 @@ __device__ __forceinline__ float cvt_fp8_to_f32(uint8_t v, int dtype) {
   return __half2float(__half(h));
 }
 
+// f32 -> fp8, the reference's down casts (ElementwiseOpToLLVM.cpp:83-289, :583-650):
+// rn = cvt.rn.satfinite (beyond the largest finite value, infinities included, gives
+// that value; NaN stays NaN); rz exists for E5M2 only and is the high byte of the
+// value truncated to f16.
+__device__ __forceinline__ uint8_t cvt_f32_to_fp8(float v, int dtype, int rn) {
+  uint16_t r;
+  if (dtype == KAPYB_F8E4M3) {
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(0.0f), "f"(v));
+    return static_cast<uint8_t>(r & 0xffu);
+  }
+  if (rn) {
+    asm("cvt.rn.satfinite.e5m2x2.f32 %0, %1, %2;" : "=h"(r) : "f"(0.0f), "f"(v));
+    return static_cast<uint8_t>(r & 0xffu);
+  }
+  asm("cvt.rz.f16.f32 %0, %1;" : "=h"(r) : "f"(v));
+  return static_cast<uint8_t>(r >> 8);
+}
+
+__device__ __forceinline__ bool is_fp8_dtype(int dtype) {
+  return dtype == KAPYB_F8E4M3 || dtype == KAPYB_F8E5M2;
+}
+
 __device__ __forceinline__ float load_as_f32(const void *base, int dtype, int64_t idx) {
   if (dtype == KAPYB_F32) return static_cast<const float *>(base)[idx];
   if (dtype == KAPYB_F8E4M3 || dtype == KAPYB_F8E5M2)
@@ -148,6 +170,8 @@ __device__ __forceinline__ void store_from_f32(void *base, int dtype, int64_t id
                                                int rn) {
   if (dtype == KAPYB_F32)
     static_cast<float *>(base)[idx] = v;
+  else if (is_fp8_dtype(dtype))
+    static_cast<uint8_t *>(base)[idx] = cvt_f32_to_fp8(v, dtype, rn);
   else
     static_cast<uint16_t *>(base)[idx] = cvt_f32_to_16(v, dtype, rn);
 }

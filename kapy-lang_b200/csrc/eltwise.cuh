@@ -33,6 +33,7 @@ struct EltProgram {
 
 __device__ __forceinline__ float round_to_dtype(float v, int dtype, int rn) {
   if (dtype == KAPYB_F32) return v;
+  if (is_fp8_dtype(dtype)) return cvt_fp8_to_f32(cvt_f32_to_fp8(v, dtype, rn), dtype);
   return cvt_16_to_f32(cvt_f32_to_16(v, dtype, rn), dtype);
 }
 
@@ -148,10 +149,9 @@ __global__ void __launch_bounds__(256) elt_interp_kernel(const EltProgram P) {
       void *o = const_cast<void *>(P.out.ptr);
       const long long idx = i * P.out.s0 + j * P.out.s1;
       // the stored register already holds a value of the output's type
-      if (P.out.dtype == KAPYB_F32)
-        static_cast<float *>(o)[idx] = sv;
-      else
-        static_cast<uint16_t *>(o)[idx] = cvt_f32_to_16(sv, P.out.dtype, 1);
+      // (f8E5M2: the truncating encoder, which keeps an infinity; the rounding
+      // one saturates it)
+      store_from_f32(o, P.out.dtype, idx, sv, P.out.dtype == KAPYB_F8E5M2 ? 0 : 1);
     }
   }
 }
@@ -321,6 +321,95 @@ elt_unary16_kernel(const uint4 *__restrict__ x, uint4 *__restrict__ y, long long
       f(a, unused);
       ys[e] = cvt_f32_to_16(a, DT, RN);
     }
+  }
+}
+
+// ------------------------------------------------------------ f8 casts
+//
+// y = cast(x) where one side is an 8-bit float type: contiguous, both pointers
+// 16-byte aligned.  A thread converts 16 consecutive elements (16 to 64 bytes
+// on either side, moved as 128-bit vectors); one block per contiguous chunk of
+// kCastUnroll x 256 such groups; the last block also does the scalar tail.
+constexpr int kCastUnroll = 2;
+
+template <int DT>
+__device__ __forceinline__ void load16_as_f32(const uint8_t *p, float (&f)[16]) {
+  if constexpr (DT == KAPYB_F32) {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const uint4 v = ld_stream(reinterpret_cast<const uint4 *>(p) + k);
+      f[4 * k] = __uint_as_float(v.x);
+      f[4 * k + 1] = __uint_as_float(v.y);
+      f[4 * k + 2] = __uint_as_float(v.z);
+      f[4 * k + 3] = __uint_as_float(v.w);
+    }
+  } else if constexpr (DT == KAPYB_F16 || DT == KAPYB_BF16) {
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const uint4 v = ld_stream(reinterpret_cast<const uint4 *>(p) + k);
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int t = 0; t < 4; ++t) unpack2_16<DT>(w[t], f[8 * k + 2 * t], f[8 * k + 2 * t + 1]);
+    }
+  } else {
+    const uint4 v = ld_stream(reinterpret_cast<const uint4 *>(p));
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int t = 0; t < 4; ++t)
+#pragma unroll
+      for (int b = 0; b < 4; ++b)
+        f[4 * t + b] = cvt_fp8_to_f32(static_cast<uint8_t>(w[t] >> (8 * b)), DT);
+  }
+}
+
+template <int DT, int RN>
+__device__ __forceinline__ void store16_from_f32(uint8_t *p, const float (&f)[16]) {
+  if constexpr (DT == KAPYB_F32) {
+#pragma unroll
+    for (int k = 0; k < 4; ++k)
+      st_stream(reinterpret_cast<uint4 *>(p) + k,
+                make_uint4(__float_as_uint(f[4 * k]), __float_as_uint(f[4 * k + 1]),
+                           __float_as_uint(f[4 * k + 2]), __float_as_uint(f[4 * k + 3])));
+  } else if constexpr (DT == KAPYB_F16 || DT == KAPYB_BF16) {
+#pragma unroll
+    for (int k = 0; k < 2; ++k)
+      st_stream(reinterpret_cast<uint4 *>(p) + k,
+                make_uint4(cvt_pack2_t<DT, RN>(f[8 * k], f[8 * k + 1]),
+                           cvt_pack2_t<DT, RN>(f[8 * k + 2], f[8 * k + 3]),
+                           cvt_pack2_t<DT, RN>(f[8 * k + 4], f[8 * k + 5]),
+                           cvt_pack2_t<DT, RN>(f[8 * k + 6], f[8 * k + 7])));
+  } else {
+    uint32_t w[4];
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      w[t] = 0;
+#pragma unroll
+      for (int b = 0; b < 4; ++b)
+        w[t] |= static_cast<uint32_t>(cvt_f32_to_fp8(f[4 * t + b], DT, RN)) << (8 * b);
+    }
+    st_stream(reinterpret_cast<uint4 *>(p), make_uint4(w[0], w[1], w[2], w[3]));
+  }
+}
+
+template <int SD, int DD, int RN>
+__global__ void __launch_bounds__(256)
+elt_cast_kernel(const uint8_t *__restrict__ x, uint8_t *__restrict__ y, long long n_groups,
+                long long n_elems) {
+  constexpr int ssz = SD == KAPYB_F32 ? 4 : (SD == KAPYB_F16 || SD == KAPYB_BF16) ? 2 : 1;
+  constexpr int dsz = DD == KAPYB_F32 ? 4 : (DD == KAPYB_F16 || DD == KAPYB_BF16) ? 2 : 1;
+  const long long base = static_cast<long long>(blockIdx.x) * (kCastUnroll * 256) + threadIdx.x;
+#pragma unroll
+  for (int u = 0; u < kCastUnroll; ++u) {
+    const long long g = base + u * 256;
+    if (g < n_groups) {
+      float f[16];
+      load16_as_f32<SD>(x + g * (16 * ssz), f);
+      store16_from_f32<DD, RN>(y + g * (16 * dsz), f);
+    }
+  }
+  if (blockIdx.x == gridDim.x - 1) {
+    for (long long e = n_groups * 16 + threadIdx.x; e < n_elems; e += blockDim.x)
+      store_from_f32(y, DD, e, load_as_f32(x, SD, e), RN);
   }
 }
 

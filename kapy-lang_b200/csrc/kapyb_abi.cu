@@ -1034,16 +1034,18 @@ static kapyb_status verify_program(kapyb_handle h, const kapyb_inst *prog, int n
     return fail(h, KAPYB_INVALID_ARG, "elementwise: program must have 1..%d ops", KAPYB_MAX_INSTS);
   if (n_inputs < 0 || n_inputs > KAPYB_MAX_INPUTS || (n_inputs > 0 && !inputs))
     return fail(h, KAPYB_INVALID_ARG, "elementwise: at most %d inputs", KAPYB_MAX_INPUTS);
-  if (!out || !valid_dtype(out->dtype) || out->size0 < 0 || out->size1 < 0 ||
+  if (!out || !valid_operand_dtype(out->dtype) || out->size0 < 0 || out->size1 < 0 ||
       (!out->ptr && out->size0 != 0 && out->size1 != 0))
     return fail(h, KAPYB_INVALID_ARG, "elementwise: bad output descriptor");
   for (int k = 0; k < n_inputs; ++k) {
     const kapyb_tensor2d &t = inputs[k];
-    if (!valid_dtype(t.dtype) || t.size0 < 0 || t.size1 < 0 ||
+    if (!valid_operand_dtype(t.dtype) || t.size0 < 0 || t.size1 < 0 ||
         (!t.ptr && t.size0 != 0 && t.size1 != 0))
       return fail(h, KAPYB_INVALID_ARG, "elementwise: bad input descriptor %d", k);
     if (t.padding < KAPYB_PAD_ZERO || t.padding > KAPYB_PAD_NINF)
       return fail(h, KAPYB_INVALID_ARG, "elementwise: bad padding option on input %d", k);
+    if (t.dtype == KAPYB_F8E4M3 && (t.padding == KAPYB_PAD_PINF || t.padding == KAPYB_PAD_NINF))
+      return fail(h, KAPYB_INVALID_ARG, "elementwise: f8E4M3 has no infinity to pad input %d with", k);
   }
   int reg_dtype[KAPYB_MAX_REGS];
   for (int r = 0; r < KAPYB_MAX_REGS; ++r) reg_dtype[r] = -1;
@@ -1081,7 +1083,11 @@ static kapyb_status verify_program(kapyb_handle h, const kapyb_inst *prog, int n
       ++stores;
       continue;
     }
-    if (!valid_dtype(in.dtype)) return fail(h, KAPYB_INVALID_ARG, "elementwise: op %d has a bad element type", pc);
+    if (!valid_operand_dtype(in.dtype))
+      return fail(h, KAPYB_INVALID_ARG, "elementwise: op %d has a bad element type", pc);
+    // the 8-bit types exist in memory and across casts only
+    if (is_fp8(in.dtype) && in.op != KAPYB_OP_LOAD && in.op != KAPYB_OP_CVT)
+      return fail(h, KAPYB_INVALID_ARG, "elementwise: op %d cannot compute in an f8 element type", pc);
     if (in.dst < 0 || in.dst >= KAPYB_MAX_REGS)
       return fail(h, KAPYB_INVALID_ARG, "elementwise: op %d writes register %d", pc, in.dst);
     if (in.op == KAPYB_OP_LOAD) {
@@ -1093,6 +1099,18 @@ static kapyb_status verify_program(kapyb_handle h, const kapyb_inst *prog, int n
       // FPToFPOp::verify (Kapy.cpp:272-287): a downcast must name a rounding mode.
       if (dtype_size(in.dtype) < dtype_size(reg_dtype[in.a]) && in.flags != KAPYB_RZ && in.flags != KAPYB_RN)
         return fail(h, KAPYB_INVALID_ARG, "elementwise: rounding mode must be set for down cast");
+      const int from = reg_dtype[in.a];
+      if (is_fp8(from) && is_fp8(in.dtype))
+        return fail(h, KAPYB_INVALID_ARG, "elementwise: convert f8 to f8 is not supported");
+      if (is_fp8(in.dtype) && in.flags == KAPYB_RZ) {
+        if (from == KAPYB_BF16)
+          return fail(h, KAPYB_INVALID_ARG,
+                      "elementwise: unsupported rounding mode when convert bf16 to f8");
+        // no rz entry for f8E4M3 in the reference's conversion table
+        // (ElementwiseOpToLLVM.cpp:628-650)
+        if (in.dtype == KAPYB_F8E4M3)
+          return fail(h, KAPYB_UNSUPPORTED, "elementwise: no toward-zero conversion to f8E4M3");
+      }
     } else {
       for (int s = 0; s < nsrc; ++s)
         if (reg_dtype[srcs[s]] != in.dtype)
@@ -1251,11 +1269,56 @@ extern "C" KAPYB_API kapyb_status kapyb_elementwise(kapyb_handle h, const kapyb_
   int root = -1;
   build_nodes(prog, n_inst, nodes, &root);
 
+  // Fused path 0: a bare cast to or from an 8-bit float type, contiguous.
+  if (n_inst == 3 && prog[0].op == KAPYB_OP_LOAD && prog[1].op == KAPYB_OP_CVT &&
+      prog[2].op == KAPYB_OP_STORE && prog[1].a == prog[0].dst && prog[2].a == prog[1].dst &&
+      (is_fp8(prog[0].dtype) != is_fp8(prog[1].dtype))) {
+    const kapyb_tensor2d &tin = inputs[prog[0].flags];
+    if (contiguous_same(tin, *out) && aligned16(elem_ptr(&tin)) && aligned16(elem_ptr(out))) {
+      const uint8_t *px = static_cast<const uint8_t *>(elem_ptr(&tin));
+      uint8_t *py = static_cast<uint8_t *>(const_cast<void *>(elem_ptr(out)));
+      const long long n_groups = total / 16;
+      int grid = 1;
+      st = chunk_grid(h, n_groups, kCastUnroll, &grid);
+      if (st != KAPYB_OK) return st;
+      const int sd = prog[0].dtype, dd = prog[1].dtype;
+      const int rn = is_fp8(dd) ? (prog[1].flags == KAPYB_RN ? 1 : 0) : 1;
+#define KAPYB_CAST(S, D, R)                                                                   \
+  if (sd == S && dd == D && rn == R) {                                                        \
+    elt_cast_kernel<S, D, R><<<grid, 256, 0, stream>>>(px, py, n_groups, total);              \
+    launched = true;                                                                          \
+  }
+      bool launched = false;
+      KAPYB_CAST(KAPYB_F8E4M3, KAPYB_F16, 1)
+      KAPYB_CAST(KAPYB_F8E4M3, KAPYB_BF16, 1)
+      KAPYB_CAST(KAPYB_F8E4M3, KAPYB_F32, 1)
+      KAPYB_CAST(KAPYB_F8E5M2, KAPYB_F16, 1)
+      KAPYB_CAST(KAPYB_F8E5M2, KAPYB_BF16, 1)
+      KAPYB_CAST(KAPYB_F8E5M2, KAPYB_F32, 1)
+      KAPYB_CAST(KAPYB_F16, KAPYB_F8E4M3, 1)
+      KAPYB_CAST(KAPYB_BF16, KAPYB_F8E4M3, 1)
+      KAPYB_CAST(KAPYB_F32, KAPYB_F8E4M3, 1)
+      KAPYB_CAST(KAPYB_F16, KAPYB_F8E5M2, 1)
+      KAPYB_CAST(KAPYB_BF16, KAPYB_F8E5M2, 1)
+      KAPYB_CAST(KAPYB_F32, KAPYB_F8E5M2, 1)
+      KAPYB_CAST(KAPYB_F16, KAPYB_F8E5M2, 0)
+      KAPYB_CAST(KAPYB_F32, KAPYB_F8E5M2, 0)
+#undef KAPYB_CAST
+      if (launched) {
+        CUDA_TRY(h, cudaGetLastError());
+        h->launches++;
+        h->last_kernel = "elt_cast_f8";
+        return KAPYB_OK;
+      }
+    }
+  }
+
   // Fused path 1: 16-bit -> 16-bit affine (+ gelu_tanh), contiguous.
   {
     AffineGelu f;
     int li = -1, din = 0, rn = 1;
-    if (match_affine_gelu(nodes, root, &f, &li, &din, &rn) && out->dtype != KAPYB_F32 &&
+    if (match_affine_gelu(nodes, root, &f, &li, &din, &rn) &&
+        (din == KAPYB_F16 || din == KAPYB_BF16) &&
         nodes[root].dtype == out->dtype && din == out->dtype && (rn == 0 || rn == 1) &&
         contiguous_same(inputs[li], *out) &&
         aligned16(elem_ptr(&inputs[li])) && aligned16(elem_ptr(out))) {

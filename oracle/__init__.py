@@ -79,6 +79,8 @@ def lib():
         L.ko_f32_to_bf16.argtypes = [C.c_float, C.c_int]
         L.ko_f32_to_f16.restype = C.c_uint16
         L.ko_f32_to_f16.argtypes = [C.c_float, C.c_int]
+        L.ko_f32_to_f8.restype = C.c_uint8
+        L.ko_f32_to_f8.argtypes = [C.c_float, C.c_int, C.c_int]
         L.ko_eltwise.restype = C.c_int
         L.ko_eltwise.argtypes = [C.POINTER(Inst), C.c_int, C.POINTER(Tensor2d), C.c_int,
                                  C.POINTER(Tensor2d)]
@@ -126,6 +128,9 @@ def to_bits(x: np.ndarray, dtype: int, rounding: int = RN) -> np.ndarray:
     x32 = np.ascontiguousarray(x, dtype=np.float32)
     if dtype == F32:
         return x32
+    if dtype in (F8E4M3, F8E5M2):
+        f = np.vectorize(lambda v: lib().ko_f32_to_f8(float(v), dtype, rounding), otypes=[np.uint8])
+        return f(x32)
     if dtype == F16:
         if rounding == RN:
             return x32.astype(np.float16).view(np.uint16)

@@ -45,7 +45,10 @@ static const ko_format KO_FMT[3] = {
  * (cvt.rn); rn == 0: toward zero (cvt.rz), which never turns a finite value
  * into an infinity.  Follows ElementwiseOpToLLVM.cpp:381-417 (cvt.{rn,rz}.
  * {f16,bf16}.f32) and :1006-1037 (truncf = cvt.rn). */
+static double ko_round_to_f8(double x, int dtype, int rn);
+
 static double ko_round_to(double x, int dtype, int rn) {
+  if (dtype == KAPYB_F8E4M3 || dtype == KAPYB_F8E5M2) return ko_round_to_f8(x, dtype, rn);
   if (x == 0.0 || isnan(x) || isinf(x)) return x;
   const ko_format f = KO_FMT[dtype];
   int e;
@@ -131,6 +134,62 @@ KO_API uint16_t ko_f32_to_f16(float x, int rn) {
   return ko_enc_f16(ko_round_to((double)x, KAPYB_F16, rn));
 }
 
+/* Down casts to the two 8-bit types (FPToFPOp lowering,
+ * ElementwiseOpToLLVM.cpp:83-289 and :583-600, conversion table :628-650):
+ *   rn: cvt.rn.satfinite.{e4m3x2,e5m2x2}.{f16x2,f32} -- nearest even, and
+ *       anything beyond the largest finite value (448 / 57344), infinities
+ *       included, becomes that value; NaN stays NaN.  bf16 sources are widened
+ *       to f32 first (exact), f16 sources convert directly: one rounding either
+ *       way, so the rule is a function of the source VALUE.
+ *   rz: exists for f8E5M2 only (:104-112): the high byte of the f16 pattern,
+ *       i.e. truncation toward zero with f16's specials kept (an f32 source is
+ *       first truncated to f16, :583-600, which cannot produce an infinity). */
+static double ko_round_to_f8(double x, int dtype, int rn) {
+  const int p = dtype == KAPYB_F8E4M3 ? 4 : 3;          /* significand bits */
+  const int emin = dtype == KAPYB_F8E4M3 ? -6 : -14;    /* smallest normal exponent */
+  const double maxv = dtype == KAPYB_F8E4M3 ? 448.0 : 57344.0;
+  if (isnan(x) || x == 0.0) return x;
+  if (!rn) {
+    /* f32 -> f16 toward zero, then drop the low 8 bits of the f16 pattern */
+    double h = isinf(x) ? x : ko_round_to(x, KAPYB_F16, 0);
+    if (isinf(h)) return h; /* only from an infinite source */
+    int e;
+    (void)frexp(fabs(h), &e);
+    int lead = e - 1;
+    int q = (lead < -14 ? -14 : lead) - 2; /* f16 exponent rules, 2 stored mantissa bits */
+    return copysign(ldexp(trunc(ldexp(fabs(h), -q)), q), x);
+  }
+  if (isinf(x)) return copysign(maxv, x);
+  int e;
+  (void)frexp(fabs(x), &e);
+  int lead = e - 1;
+  int q = (lead < emin ? emin : lead) - (p - 1);
+  double res = ldexp(nearbyint(ldexp(fabs(x), -q)), q);
+  if (res > maxv) res = maxv;
+  return copysign(res, x);
+}
+
+/* Encodes a double that is exactly representable in the 8-bit format. */
+static uint8_t ko_enc_f8(double v, int dtype) {
+  const int mbits = dtype == KAPYB_F8E4M3 ? 3 : 2;
+  const int bias = dtype == KAPYB_F8E4M3 ? 7 : 15;
+  uint8_t sign = signbit(v) ? 0x80u : 0;
+  if (isnan(v)) return 0x7fu;
+  if (isinf(v)) return (uint8_t)(sign | 0x7cu); /* f8E5M2 only */
+  double a = fabs(v);
+  if (a == 0.0) return sign;
+  int e;
+  double m = frexp(a, &e);
+  int lead = e - 1;
+  if (lead < 1 - bias) return (uint8_t)(sign | (uint8_t)ldexp(a, bias - 1 + mbits));
+  uint32_t man = (uint32_t)ldexp(m, mbits + 1) & ((1u << mbits) - 1u);
+  return (uint8_t)(sign | ((uint32_t)(lead + bias) << mbits) | man);
+}
+
+KO_API uint8_t ko_f32_to_f8(float x, int dtype, int rn) {
+  return ko_enc_f8(ko_round_to_f8((double)x, dtype, rn), dtype);
+}
+
 /* The two 8-bit operand types of the matmul verifier (Kapy.cpp:484-487,
  * 548-564).  f8E4M3 is the finite-only "FN" variant: bias 7, no infinities,
  * S.1111.111 is NaN.  f8E5M2 is a truncated f16: bias 15, IEEE specials. */
@@ -164,6 +223,8 @@ static void ko_store(void *base, int dtype, int64_t idx, double v) {
   switch (dtype) {
   case KAPYB_F16: ((uint16_t *)base)[idx] = isnan(v) ? 0x7fffu : ko_enc_f16(v); break;
   case KAPYB_BF16: ((uint16_t *)base)[idx] = isnan(v) ? 0x7fffu : ko_enc_bf16(v); break;
+  case KAPYB_F8E4M3:
+  case KAPYB_F8E5M2: ((uint8_t *)base)[idx] = ko_enc_f8(v, dtype); break;
   default: ((float *)base)[idx] = (float)v; break;
   }
 }

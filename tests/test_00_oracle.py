@@ -161,3 +161,24 @@ def test_f8_decode_tables(ko):
         ref = torch.arange(256, dtype=torch.uint8).view(td).to(torch.float64).numpy()
         assert np.array_equal(np.isnan(table), np.isnan(ref))
         assert np.array_equal(table[~np.isnan(ref)], ref[~np.isnan(ref)])
+
+
+def test_f8_downcasts(ko):
+    """cvt.rn.satfinite to f8E4M3 / f8E5M2 over every f16 value: equal to torch's
+    conversion wherever the value is within the format's finite range (an
+    independent implementation), the largest finite value beyond it (torch gives
+    NaN / Inf there, the reference saturates), NaN for NaN.  rz to f8E5M2 is the
+    high byte of the f16 pattern."""
+    h = np.arange(65536, dtype=np.uint16)
+    x = h.view(np.float16).astype(np.float32)
+    for code, td, maxv in ((ko.F8E4M3, torch.float8_e4m3fn, 448.0), (ko.F8E5M2, torch.float8_e5m2, 57344.0)):
+        got = ko.to_bits(x, code, ko.RN)
+        ref = torch.from_numpy(x).to(td).view(torch.uint8).numpy()
+        inr = np.isfinite(x) & (np.abs(x) <= maxv)
+        assert np.array_equal(got[inr], ref[inr])
+        big = ~np.isnan(x) & (np.abs(x) > maxv)
+        assert np.array_equal(ko.from_bits(got[big], code), np.sign(x[big]) * maxv)
+        assert np.isnan(ko.from_bits(got[np.isnan(x)], code)).all()
+    rz = ko.to_bits(x, ko.F8E5M2, ko.RZ)
+    ok = ~np.isnan(x)
+    assert np.array_equal(rz[ok], (h >> 8).astype(np.uint8)[ok])

@@ -5,7 +5,7 @@ import numpy as np
 import pytest
 import torch
 
-from util import bits, normal
+from util import bits, code, gen, normal
 
 pytestmark = pytest.mark.gpu
 
@@ -164,3 +164,109 @@ def test_verifier_rejections(handle, pkg):
                             (A.OP_STORE, A.BF16, -1, 2, -1, -1, 0.0, 0)], [x], y)
     with pytest.raises(ValueError, match="stores exactly once"):
         handle.elementwise([(A.OP_LOAD, A.BF16, 0, -1, -1, -1, 0.0, 0)], [x], y)
+
+
+# ------------------------------------------------------------------ f8 casts
+
+F8_TORCH = {3: torch.float8_e4m3fn, 4: torch.float8_e5m2}
+
+
+def _cast_prog(src, dst, rounding):
+    return [(0, src, 0, -1, -1, -1, 0.0, 0), (2, dst, 1, 0, -1, -1, 0.0, rounding),
+            (27, dst, -1, 1, -1, -1, 0.0, 0)]
+
+
+def _same_f8(got: np.ndarray, want: np.ndarray, code: int, ko):
+    """Equal bit patterns, NaN patterns compared as NaN (payload and sign free)."""
+    g, w = ko.from_bits(got, code), ko.from_bits(want, code)
+    nan = np.isnan(w)
+    assert np.array_equal(np.isnan(g), nan)
+    assert np.array_equal(got[~nan], want[~nan])
+
+
+@pytest.mark.parametrize("dst", [3, 4])
+@pytest.mark.parametrize("src_dt", [torch.float16, torch.bfloat16, torch.float32])
+def test_downcast_to_f8_rn_every_pattern(handle, ko, dst, src_dt):
+    """FPToFPOp to f8 with rn (cvt.rn.satfinite, ElementwiseOpToLLVM.cpp:83-289):
+    every f16 / bf16 bit pattern, and f32 values around every f8 rounding
+    boundary; bit-exact against the checker, saturation and NaN included."""
+    if src_dt == torch.float32:
+        base = ko.f8_table(dst)
+        base = base[np.isfinite(base)]
+        mids = (base[:, None] * np.array([1.0, 1.0 + 2.0 ** -4, 1.0 + 2.0 ** -3, 1.5, 1.0625])).ravel()
+        x = np.concatenate([mids, -mids, np.nextafter(mids.astype(np.float32), np.float32(np.inf)),
+                            np.array([np.inf, -np.inf, np.nan, 1e30, -1e30, 1e-30, 0.0, -0.0])])
+        src = torch.from_numpy(x.astype(np.float32)).view(1, -1)
+    else:
+        src = torch.arange(65536, dtype=torch.int32).to(torch.int16).view(src_dt).view(256, 256)
+    scode = code(src_dt)
+    want = ko.eltwise(_cast_prog(scode, dst, 1), [bits(src)], [scode], tuple(src.shape), dst)
+    # contiguous: the fused cast kernel; a column-major output: the interpreter
+    out = torch.empty(src.shape, dtype=torch.uint8, device="cuda").view(F8_TORCH[dst])
+    handle.elementwise(_cast_prog(scode, dst, 1), [src.cuda()], out)
+    handle.check()
+    assert handle.last_kernel == "elt_cast_f8"
+    _same_f8(out.view(torch.uint8).cpu().numpy(), want, dst, ko)
+    out_t = torch.empty(src.shape[::-1], dtype=torch.uint8, device="cuda").view(F8_TORCH[dst]).t()
+    handle.elementwise(_cast_prog(scode, dst, 1), [src.cuda()], out_t)
+    handle.check()
+    assert handle.last_kernel == ("elt_interp" if min(src.shape) > 1 else "elt_cast_f8")
+    _same_f8(out_t.contiguous().view(torch.uint8).cpu().numpy(), want, dst, ko)
+
+
+@pytest.mark.parametrize("src_dt", [torch.float16, torch.float32])
+def test_downcast_to_f8e5m2_rz(handle, ko, src_dt):
+    """rz to f8E5M2 is the high byte of the f16 pattern (:104-112); f32 goes
+    through f16 toward zero first (:583-600)."""
+    if src_dt == torch.float16:
+        src = torch.arange(65536, dtype=torch.int32).to(torch.int16).view(src_dt).view(256, 256)
+    else:
+        src = (torch.randn(64, 1024, generator=gen(5)) * torch.logspace(-8, 5, 1024)).float()
+    scode = code(src_dt)
+    out = torch.empty(src.shape, dtype=torch.uint8, device="cuda").view(torch.float8_e5m2)
+    handle.elementwise(_cast_prog(scode, 4, 0), [src.cuda()], out)
+    handle.check()
+    want = ko.eltwise(_cast_prog(scode, 4, 0), [bits(src)], [scode], tuple(src.shape), 4)
+    got = out.view(torch.uint8).cpu().numpy()
+    _same_f8(got, want, 4, ko)
+    if src_dt == torch.float16:
+        pat = np.arange(65536, dtype=np.uint16).reshape(256, 256)
+        finite = np.isfinite(pat.view(np.float16))
+        assert np.array_equal(got[finite], (pat >> 8).astype(np.uint8)[finite])
+
+
+@pytest.mark.parametrize("src", [3, 4])
+@pytest.mark.parametrize("dst_dt", [torch.float16, torch.bfloat16, torch.float32])
+def test_upcast_from_f8_is_exact(handle, ko, src, dst_dt):
+    pat = torch.arange(256, dtype=torch.uint8).repeat(4, 1)
+    out = torch.empty(pat.shape, dtype=dst_dt, device="cuda")
+    dcode = code(dst_dt)
+    handle.elementwise(_cast_prog(src, dcode, 1), [pat.view(F8_TORCH[src]).cuda()], out)
+    handle.check()
+    table = ko.f8_table(src)
+    got = out.cpu().double().numpy()
+    assert np.array_equal(np.isnan(got[0]), np.isnan(table))
+    ok = ~np.isnan(table)
+    assert np.array_equal(got[:, ok], np.broadcast_to(table[ok], (4, ok.sum())))
+
+
+def test_f8_cast_rules(handle):
+    """FPToFPOp::verify (Kapy.cpp:272-287) and the gaps of the conversion table."""
+    z = lambda dt: torch.zeros(4, 8, device="cuda").to(dt)
+    f8a, f8b = z(torch.float8_e4m3fn), z(torch.float8_e5m2)
+    with pytest.raises(ValueError, match="convert f8 to f8 is not supported"):
+        handle.elementwise(_cast_prog(3, 4, 1), [f8a], f8b)
+    with pytest.raises(ValueError, match="unsupported rounding mode when convert bf16 to f8"):
+        handle.elementwise(_cast_prog(1, 4, 0), [z(torch.bfloat16)], f8b)
+    with pytest.raises(ValueError, match="rounding mode must be set for down cast"):
+        handle.elementwise(_cast_prog(0, 3, -1), [z(torch.float16)], f8a)
+    with pytest.raises(pkg_error(handle), match="no toward-zero conversion to f8E4M3"):
+        handle.elementwise(_cast_prog(0, 3, 0), [z(torch.float16)], f8a)
+    with pytest.raises(ValueError, match="cannot compute in an f8 element type"):
+        handle.elementwise([(0, 3, 0, -1, -1, -1, 0.0, 0), (3, 3, 1, 0, 0, -1, 0.0, 0),
+                            (27, 3, -1, 1, -1, -1, 0.0, 0)], [f8a], f8a)
+
+
+def pkg_error(handle):
+    import sys
+    return sys.modules[type(handle).__module__].KapybError
