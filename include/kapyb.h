@@ -356,6 +356,20 @@ KAPYB_API kapyb_status kapyb_shard_range(int64_t total, int32_t parts,
 
 /* ------------------------------------------------------------ diagnostics */
 
+/* Describes, as a few lines of text, how kapyb_matmul would run this problem:
+ * kernel family, tile and pipeline depth, tile grid and waves, operand majors,
+ * and where an accumulator element sits in tensor memory.  The counterpart of
+ * the reference's layout printer (bin/kapy-layout.cpp:79-126): a debugging
+ * aid.  Pure host code: only the descriptors' shapes, strides, dtypes and the
+ * alignment of their addresses are looked at, nothing is launched.  `h` may be
+ * NULL when `sm_count` > 0 (then no GPU is needed at all); with a handle,
+ * sm_count = 0 means the handle's device and the path forced with
+ * kapyb_set_matmul_path applies.  `batch` > 1 plans densely packed batches. */
+KAPYB_API kapyb_status kapyb_matmul_plan(kapyb_handle h, int32_t sm_count,
+                                         const kapyb_tensor2d *lhs, const kapyb_tensor2d *rhs,
+                                         const kapyb_tensor2d *out, int32_t batch, char *text,
+                                         size_t capacity);
+
 /* Name of the kernel family the last matmul on `h` dispatched to
  * ("tcgen05_1cta", "tcgen05_2cta", "tcgen05_skinny", "simt"). */
 KAPYB_API const char *kapyb_last_kernel(kapyb_handle h);

@@ -680,17 +680,38 @@ static kapyb_status launch_skinny(kapyb_handle h, const MatmulProblem &p, bool a
   return launch_skinny_on(h, p, a_mn, b_mn, scratch, counters, stream);
 }
 
-static kapyb_status run_matmul(kapyb_handle h, MatmulProblem p, void *const *peer_outs,
-                               int n_peers, cudaStream_t stream) {
-  if (p.M == 0 || p.N == 0 || p.batch == 0) return KAPYB_OK;  // empty result
-  CUDA_TRY(h, cudaSetDevice(h->device));
+// What run_matmul decided for a problem: the kernel family, the tile, and the
+// facts the choice rests on.  Computed on the host without touching the GPU.
+struct MatmulPlan {
+  int path = PATH_SIMT;        // PATH_SIMT / PATH_SKINNY / PATH_1CTA / PATH_2CTA
+  bool transposed = false;     // the transposed problem is computed (out has its unit stride on axis 0)
+  bool a_mn = false, b_mn = false;  // operand majors as the kernel sees them
+  bool tma = false;            // operands and output are TMA-describable
+  int bn = 0, epi = 4;         // tile width and epilogue warps (tcgen05 paths)
+  const char *error = nullptr; // set with a non-OK status
+};
+
+struct PlanOptions {
+  int sm_count;
+  int forced_path, forced_bn, forced_epi;
+};
+
+// Decides how `p` runs.  `p` is transposed in place when the output's unit
+// stride is on axis 0.
+static kapyb_status plan_matmul(const PlanOptions &o, MatmulProblem &p, void *const *peer_outs,
+                                int n_peers, MatmulPlan &plan) {
   // Put the output's unit stride on axis 1 (compute the transposed problem otherwise).
-  if (p.c_s1 != 1 && p.c_s0 == 1 && n_peers == 0) transpose_problem(p);
+  if (p.c_s1 != 1 && p.c_s0 == 1 && n_peers == 0) {
+    transpose_problem(p);
+    plan.transposed = true;
+  }
   const bool c_unit = p.c_s1 == 1 || p.N == 1;
   const bool a_k = p.a_s1 == 1 || p.K == 1, a_m = p.a_s0 == 1 || p.M == 1;
   const bool b_n = p.b_s1 == 1 || p.N == 1, b_k = p.b_s0 == 1 || p.K == 1;
   const bool a_mn = !a_k && a_m;
   const bool b_mn = b_n;  // prefer N-contiguous when both hold
+  plan.a_mn = a_mn;
+  plan.b_mn = b_mn;
   bool tma = c_unit && (a_k || a_m) && (b_n || b_k) && p.K > 0;
   if (tma) {
     tma = tma_ok(p.a, p.in_dtype, a_mn ? p.M : p.K, a_mn ? p.K : p.M, a_mn ? p.a_s1 : p.a_s0,
@@ -698,54 +719,58 @@ static kapyb_status run_matmul(kapyb_handle h, MatmulProblem p, void *const *pee
           tma_ok(p.b, p.in_dtype_b, b_mn ? p.N : p.K, b_mn ? p.K : p.N, b_mn ? p.b_s0 : p.b_s1,
                  p.batch, p.b_bs) &&
           tma_ok(p.c, p.out_dtype, p.N, p.M, p.c_s0, p.batch, p.c_bs);
-    for (int o = 0; tma && o < n_peers; ++o)
-      tma = tma_ok(peer_outs[o], p.out_dtype, p.N, p.M, p.c_s0, 1, 0);
+    for (int i = 0; tma && i < n_peers; ++i)
+      tma = tma_ok(peer_outs[i], p.out_dtype, p.N, p.M, p.c_s0, 1, 0);
   }
-  int path = h->forced_path;
+  plan.tma = tma;
+  int path = o.forced_path;
   if (path == PATH_SIMT || !tma) {
-    if (n_peers > 0)
-      return fail(h, KAPYB_UNSUPPORTED, "matmul_push: operands must be TMA-describable "
-                                        "(16-byte aligned bases and leading dimensions)");
-    if (path != PATH_AUTO && path != PATH_SIMT && !tma)
-      return fail(h, KAPYB_UNSUPPORTED, "matmul: forced tcgen05 path but operands are not "
-                                        "TMA-describable");
-    if (p.K == 0) {
-      // empty contraction: the epilogue of a zero accumulator
+    if (n_peers > 0) {
+      plan.error = "matmul_push: operands must be TMA-describable (16-byte aligned bases and "
+                   "leading dimensions)";
+      return KAPYB_UNSUPPORTED;
     }
-    return launch_simt(h, p, stream);
+    if (path != PATH_AUTO && path != PATH_SIMT && !tma) {
+      plan.error = "matmul: forced tcgen05 path but operands are not TMA-describable";
+      return KAPYB_UNSUPPORTED;
+    }
+    plan.path = PATH_SIMT;  // also K == 0: the epilogue of a zero accumulator
+    return KAPYB_OK;
   }
-  void *own[1] = {p.c};
-  void *const *outs = n_peers > 0 ? peer_outs : own;
-  const int n_out = n_peers > 0 ? n_peers : 1;
-
   if (path == PATH_AUTO) {
-    // CTA pairs (256 x 256 tiles) halve the B traffic per SM and win once there
-    // is at least about half a wave of such tiles and a K loop long enough to
-    // amortise the pair's start-up; everything else runs on single CTAs.
+    // CTA pairs halve the B traffic per SM and win once there is at least about
+    // a quarter wave of pair tiles and a K loop long enough to amortise the
+    // pair's start-up; everything else runs on single CTAs.
     const long long pair_tiles =
         static_cast<long long>((p.M + 255) / 256) * ((p.N + 255) / 256) * p.batch;
     if (p.M <= kSkinnyMaxM && n_peers == 0 && p.batch == 1 && dtype_size(p.in_dtype) == 2 &&
-        skinny_supported(h->sm_count, p.M, p.N, p.K))
+        skinny_supported(o.sm_count, p.M, p.N, p.K))
       path = PATH_SKINNY;
-    else if (p.M >= 256 && p.N >= 256 && p.K >= 512 && pair_tiles * 4 >= h->sm_count && h->forced_bn == 0)
+    else if (p.M >= 256 && p.N >= 256 && p.K >= 512 && pair_tiles * 4 >= o.sm_count && o.forced_bn == 0)
       path = PATH_2CTA;
     else
       path = PATH_1CTA;
   }
   if (path == PATH_SKINNY) {
-    if (n_peers > 0 || p.batch != 1 || p.M > kSkinnyMaxM || dtype_size(p.in_dtype) != 2)
-      return fail(h, KAPYB_UNSUPPORTED, "matmul: skinny path needs M <= %d, batch 1, 16-bit operands",
-                  kSkinnyMaxM);
-    return launch_skinny(h, p, a_mn, b_mn, stream);
+    if (n_peers > 0 || p.batch != 1 || p.M > kSkinnyMaxM || dtype_size(p.in_dtype) != 2) {
+      plan.error = "matmul: skinny path needs M <= 64, batch 1, 16-bit operands";
+      return KAPYB_UNSUPPORTED;
+    }
+    if (!skinny_supported(o.sm_count, p.M, p.N, p.K)) {
+      plan.error = "matmul: shape outside the skinny kernel's range";
+      return KAPYB_UNSUPPORTED;
+    }
+    plan.path = PATH_SKINNY;
+    return KAPYB_OK;
   }
   // Tile width: the widest tile that still yields about a wave of work.
-  int bn = h->forced_bn;
+  int bn = o.forced_bn;
   if (bn == 0) {
     const long long tm = (p.M + 127) / 128;
     auto tiles = [&](int w) { return tm * ((p.N + w - 1) / w) * p.batch; };
-    if (tiles(256) >= h->sm_count || p.N > 128 * 16)
+    if (tiles(256) >= o.sm_count || p.N > 128 * 16)
       bn = 256;
-    else if (tiles(128) >= h->sm_count / 2 || p.N > 64 * 16)
+    else if (tiles(128) >= o.sm_count / 2 || p.N > 64 * 16)
       bn = 128;
     else
       bn = 64;
@@ -761,34 +786,72 @@ static kapyb_status run_matmul(kapyb_handle h, MatmulProblem p, void *const *pee
       group_cols(std::max(bn, 128), 2) < min_cols)
     path = PATH_1CTA;  // only the 512-wide pair tile would do, and N is too narrow for it
   while (path == PATH_1CTA && bn < 256 && group_cols(bn, 1) < min_cols) bn *= 2;
-  // Short K loops cannot hide the epilogue behind the next tile's main loop:
-  // give those problems eight epilogue warps instead of four.
-  const bool epi8 = (p.K + 63) / 64 <= 8 || h->forced_epi == 8;
   if (path == PATH_2CTA) {
-    if (h->forced_bn == 0) {
+    if (o.forced_bn == 0) {
       // 256 x 512 pair tiles move a quarter fewer operand bytes per flop than
       // 256 x 256 and keep the tensor pipe fuller (two accumulators in turn): measured
       // about 1.25x per tile-wave, so take them unless they fill the waves that much worse.
-      const int pairs = std::max(1, h->sm_count / 2);
+      const int pairs = std::max(1, o.sm_count / 2);
       auto wave_eff = [&](int w) {
         const long long t = static_cast<long long>((p.M + 255) / 256) * ((p.N + w - 1) / w) * p.batch;
         return static_cast<double>(t) / static_cast<double>((t + pairs - 1) / pairs * pairs);
       };
-      // The halves share TMEM, so a tile's drain is not hidden behind the next
-      // tile's main loop; the register drain keeps it short enough that this pays
-      // from a few K blocks on.
       bn = (p.N >= 512 && p.K >= 512 && wave_eff(512) >= 0.8 * wave_eff(256)) ? 512 : 256;
     }
     if (bn == 64) bn = 128;
     if (group_cols(bn, 2) < min_cols) bn = 512;
+    plan.path = PATH_2CTA;
+    plan.bn = bn;
+    plan.epi = bn == 512 && o.forced_epi != 4 ? 8 : 4;
+    return KAPYB_OK;
+  }
+  // Short K loops cannot hide the epilogue behind the next tile's main loop:
+  // give those problems eight epilogue warps instead of four.
+  const bool epi8 = (p.K + 63) / 64 <= 8 || o.forced_epi == 8;
+  plan.path = PATH_1CTA;
+  plan.bn = bn;
+  plan.epi = epi8 && o.forced_epi != 4 ? 8 : 4;
+  return KAPYB_OK;
+}
+
+// Pipeline depth of a tcgen05 configuration (GemmCfg::STAGES of the instantiation).
+static int stages_of(int bn, int ctas, int epi) {
+  if (ctas == 2) {
+    if (bn == 128) return GemmCfg<128, 2, 4>::STAGES;
+    if (bn == 256) return GemmCfg<256, 2, 4>::STAGES;
+    return epi == 8 ? GemmCfg<512, 2, 8>::STAGES : GemmCfg<512, 2, 4>::STAGES;
+  }
+  if (epi == 8)
+    return bn == 64 ? GemmCfg<64, 1, 8>::STAGES : bn == 128 ? GemmCfg<128, 1, 8>::STAGES
+                                                             : GemmCfg<256, 1, 8>::STAGES;
+  return bn == 64 ? GemmCfg<64, 1, 4>::STAGES : bn == 128 ? GemmCfg<128, 1, 4>::STAGES
+                                                           : GemmCfg<256, 1, 4>::STAGES;
+}
+
+static kapyb_status run_matmul(kapyb_handle h, MatmulProblem p, void *const *peer_outs,
+                               int n_peers, cudaStream_t stream) {
+  if (p.M == 0 || p.N == 0 || p.batch == 0) return KAPYB_OK;  // empty result
+  CUDA_TRY(h, cudaSetDevice(h->device));
+  MatmulPlan plan;
+  const PlanOptions opt{h->sm_count, h->forced_path, h->forced_bn, h->forced_epi};
+  kapyb_status st = plan_matmul(opt, p, peer_outs, n_peers, plan);
+  if (st != KAPYB_OK) return fail(h, st, "%s", plan.error);
+  const bool a_mn = plan.a_mn, b_mn = plan.b_mn;
+  if (plan.path == PATH_SIMT) return launch_simt(h, p, stream);
+  if (plan.path == PATH_SKINNY) return launch_skinny(h, p, a_mn, b_mn, stream);
+  void *own[1] = {p.c};
+  void *const *outs = n_peers > 0 ? peer_outs : own;
+  const int n_out = n_peers > 0 ? n_peers : 1;
+  const int bn = plan.bn;
+  if (plan.path == PATH_2CTA) {
     if (bn == 128) return launch_tcgen05<128, 2, 4>(h, p, a_mn, b_mn, outs, n_out, stream);
     if (bn == 512) {
-      if (h->forced_epi == 4) return launch_tcgen05<512, 2, 4>(h, p, a_mn, b_mn, outs, n_out, stream);
+      if (plan.epi == 4) return launch_tcgen05<512, 2, 4>(h, p, a_mn, b_mn, outs, n_out, stream);
       return launch_tcgen05<512, 2, 8>(h, p, a_mn, b_mn, outs, n_out, stream);
     }
     return launch_tcgen05<256, 2, 4>(h, p, a_mn, b_mn, outs, n_out, stream);
   }
-  if (epi8 && h->forced_epi != 4) {
+  if (plan.epi == 8) {
     if (bn == 64) return launch_tcgen05<64, 1, 8>(h, p, a_mn, b_mn, outs, n_out, stream);
     if (bn == 128) return launch_tcgen05<128, 1, 8>(h, p, a_mn, b_mn, outs, n_out, stream);
     return launch_tcgen05<256, 1, 8>(h, p, a_mn, b_mn, outs, n_out, stream);
@@ -821,6 +884,81 @@ static MatmulProblem make_problem(const kapyb_tensor2d *lhs, const kapyb_tensor2
   p.out_dtype = out->dtype;
   p.ep = make_ep(ep, acc);
   return p;
+}
+
+extern "C" KAPYB_API kapyb_status kapyb_matmul_plan(kapyb_handle h, int32_t sm_count,
+                                                    const kapyb_tensor2d *lhs,
+                                                    const kapyb_tensor2d *rhs,
+                                                    const kapyb_tensor2d *out, int32_t batch,
+                                                    char *text, size_t capacity) {
+  if (!text || capacity == 0) return fail(h, KAPYB_INVALID_ARG, "kapyb_matmul_plan: no text buffer");
+  text[0] = 0;
+  if (!h && sm_count <= 0)
+    return fail(h, KAPYB_INVALID_ARG, "kapyb_matmul_plan: give a handle or an SM count");
+  kapyb_status st = verify_matmul(h, lhs, rhs, nullptr, out, nullptr, KAPYB_MMA_ANY);
+  if (st != KAPYB_OK) return st;
+  if (batch < 1) return fail(h, KAPYB_INVALID_ARG, "kapyb_matmul_plan: batch must be >= 1");
+  MatmulProblem p = make_problem(lhs, rhs, nullptr, out, nullptr);
+  p.batch = batch;
+  if (batch > 1) {  // densely packed batch entries
+    p.a_bs = static_cast<long long>(p.M) * p.K;
+    p.b_bs = static_cast<long long>(p.K) * p.N;
+    p.c_bs = static_cast<long long>(p.M) * p.N;
+  }
+  PlanOptions opt{sm_count > 0 ? sm_count : h->sm_count, h ? h->forced_path : PATH_AUTO,
+                  h ? h->forced_bn : 0, h ? h->forced_epi : 0};
+  MatmulPlan plan;
+  if (p.M == 0 || p.N == 0) {
+    snprintf(text, capacity, "path: none (empty result)\n");
+    return KAPYB_OK;
+  }
+  st = plan_matmul(opt, p, nullptr, 0, plan);
+  if (st != KAPYB_OK) return fail(h, st, "%s", plan.error);
+  const char *amaj = plan.a_mn ? "M contiguous (MN-major)" : "K contiguous (K-major)";
+  const char *bmaj = plan.b_mn ? "N contiguous (MN-major)" : "K contiguous (K-major)";
+  int n = 0;
+  auto add = [&](const char *fmt, auto... args) {
+    if (n < static_cast<int>(capacity))
+      n += snprintf(text + n, capacity - n, fmt, args...);
+  };
+  if (plan.path == PATH_SIMT) {
+    add("path: simt (CUDA cores; %s)\n",
+        plan.tma ? "forced" : "an operand or the output has no unit stride, a base off 16 bytes or a "
+                              "leading dimension that is not a multiple of 16 bytes");
+    add("tile: 64 x 64 x 16 elements, 256 threads, grid %d x %d x %d\n", (p.N + 63) / 64,
+        (p.M + 63) / 64, p.batch);
+  } else if (plan.path == PATH_SKINNY) {
+    const int num_kb = (p.K + 63) / 64, n_tiles = (p.N + 127) / 128;
+    const int grid = std::min<long long>(opt.sm_count, static_cast<long long>(n_tiles) * num_kb);
+    const int dp = n_tiles >= opt.sm_count ? n_tiles / opt.sm_count : 0;
+    const int sk = n_tiles >= opt.sm_count ? n_tiles % opt.sm_count : n_tiles;
+    add("path: %s\n", "tcgen05_skinny (weights on the 128-row side of the MMA, activations on its N side)");
+    add("tile: 128 weight columns x %d rows x 64 k; %d weight tiles x %d k-blocks on %d CTAs\n",
+        (p.M + 15) / 16 * 16, n_tiles, num_kb, grid);
+    add("schedule: %d split tile(s) first, in spans of %lld k-block(s); then %d whole tile(s) per CTA\n",
+        sk, sk ? (static_cast<long long>(sk) * num_kb + grid - 1) / grid : 0ll, dp);
+  } else {
+    const int ctas = plan.path == PATH_2CTA ? 2 : 1;
+    const int tile_m = 128 * ctas;
+    const int tiles_m = (p.M + tile_m - 1) / tile_m, tiles_n = (p.N + plan.bn - 1) / plan.bn;
+    const long long tiles = static_cast<long long>(tiles_m) * tiles_n * p.batch;
+    const int units = std::max(1, opt.sm_count / ctas);
+    const long long waves = (tiles + units - 1) / units;
+    add("path: %s\n", ctas == 2 ? "tcgen05_2cta (CTA pairs, cta_group::2)" : "tcgen05_1cta");
+    add("tile: %d x %d x 128 bytes of K%s; stages %d, epilogue warps %d, TMEM columns %d\n", tile_m,
+        plan.bn, plan.bn == 512 ? " (two 256-column halves, one accumulator each)" : "",
+        stages_of(plan.bn, ctas, plan.epi), plan.epi,
+        plan.bn == 512 ? 512 : std::max(32, 2 * plan.bn));
+    add("grid: %d x %d x %d = %lld tile(s) on %d %s: %lld wave(s), %.0f %% of their slots used\n",
+        tiles_m, tiles_n, p.batch, tiles, units, ctas == 2 ? "CTA pairs" : "CTAs", waves,
+        100.0 * static_cast<double>(tiles) / static_cast<double>(waves * units));
+    add("lanes: accumulator row r of a tile -> CTA r / 128 of the %s, TMEM lane r %% 128; "
+        "column c -> TMEM column c%s\n",
+        ctas == 2 ? "pair" : "tile (always 0)", plan.bn == 512 ? "" : " + slot * tile width");
+  }
+  add("operands: A %s, B %s%s\n", amaj, bmaj,
+      plan.transposed ? "; the transposed problem is computed (out has its unit stride on axis 0)" : "");
+  return KAPYB_OK;
 }
 
 extern "C" KAPYB_API kapyb_status kapyb_matmul(kapyb_handle h, const kapyb_tensor2d *lhs,

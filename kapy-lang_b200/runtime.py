@@ -62,6 +62,34 @@ def tensor2d(t, padding: int = abi.PAD_ZERO) -> abi.Tensor2d:
                         padding)
 
 
+def matmul_plan(m: int, n: int, k: int, *, dtype=abi.BF16, rhs_dtype=None, out_dtype=None,
+                lhs_strides=None, rhs_strides=None, out_strides=None, batch: int = 1,
+                sm_count: int = 148, align: int = 256, handle=None) -> str:
+    """Text of kapyb_matmul_plan for an [m,k] x [k,n] problem described by shape,
+    strides (elements; row-major by default) and the byte alignment of its base
+    addresses.  Needs no GPU unless a handle is given."""
+    lib = abi.load()
+    rhs_dtype = dtype if rhs_dtype is None else rhs_dtype
+    out_dtype = dtype if out_dtype is None else out_dtype
+
+    def desc(rows, cols, strides, dt):
+        s0, s1 = strides if strides is not None else (cols, 1)
+        return abi.Tensor2d(align, 0, rows, cols, s0, s1, dt, abi.PAD_ZERO)
+
+    tl, tr, to = desc(m, k, lhs_strides, dtype), desc(k, n, rhs_strides, rhs_dtype), \
+        desc(m, n, out_strides, out_dtype)
+    buf = C.create_string_buffer(2048)
+    st = lib.kapyb_matmul_plan(handle._h if handle is not None else None,
+                               0 if handle is not None else int(sm_count), C.byref(tl),
+                               C.byref(tr), C.byref(to), int(batch), buf, len(buf))
+    if st != abi.OK:
+        msg = lib.kapyb_last_error_string(handle._h if handle is not None else None).decode()
+        if st == abi.INVALID_ARG:
+            raise ValueError(msg)
+        raise KapybError(st, msg)
+    return buf.value.decode()
+
+
 class Handle:
     """One per (thread, GPU).  Owns the library context; tensors stay the caller's."""
 

@@ -1,0 +1,63 @@
+"""kapyb_matmul_plan: the dispatch decisions of the matmul, checked on the host
+(no GPU: only shapes, strides, dtypes and address alignment are looked at).
+The benchmark configurations must land on the kernels the design names."""
+import pytest
+
+
+def plan(pkg, *a, **k):
+    return pkg.matmul_plan(*a, **k)
+
+
+def test_config2_takes_the_512_wide_pair_tile(pkg):
+    text = plan(pkg, 8192, 8192, 8192)
+    assert "tcgen05_2cta" in text and "tile: 256 x 512" in text and "epilogue warps 8" in text
+    assert "32 x 16 x 1 = 512 tile(s) on 74 CTA pairs: 7 wave(s)" in text
+    assert "A K contiguous" in text and "B N contiguous" in text
+
+
+@pytest.mark.parametrize("n_gpus,n_local", [(2, 4096), (4, 2048), (8, 1024)])
+def test_config2_shards_keep_the_pair_tile(pkg, n_gpus, n_local):
+    text = plan(pkg, 8192, n_local, 8192, rhs_strides=(n_local, 1), out_strides=(n_local, 1))
+    assert "tile: 256 x 512" in text
+
+
+def test_config1_small_fp16_colmajor_b(pkg):
+    text = plan(pkg, 1024, 1024, 1024, dtype=pkg.abi.F16, rhs_strides=(1, 1024))
+    assert "tcgen05_1cta" in text and "B K contiguous" in text
+
+
+def test_config4_decode_streams_weights(pkg):
+    text = plan(pkg, 16, 28672, 8192)
+    assert "tcgen05_skinny" in text
+    assert "224 weight tiles x 128 k-blocks on 148 CTAs" in text
+    assert "76 split tile(s) first, in spans of 66 k-block(s); then 1 whole tile(s) per CTA" in text
+
+
+def test_config5_short_k_gets_eight_epilogue_warps(pkg):
+    text = plan(pkg, 2048, 2048, 128, batch=64)
+    assert "tcgen05_1cta" in text and "tile: 128 x 256" in text and "epilogue warps 8" in text
+    assert "x 64 = 8192 tile(s)" in text
+
+
+def test_one_wave_problem_avoids_the_wide_tile(pkg):
+    # 2048^3: 8 x 4 tiles of 256 x 512 would fill 32 of 74 pairs; 256-wide tiles fill 64
+    assert "tile: 256 x 256" in plan(pkg, 2048, 2048, 2048)
+
+
+def test_fallbacks_and_transposition(pkg):
+    # leading dimension of 1001 bf16 elements: not a multiple of 16 bytes -> CUDA cores
+    assert "path: simt" in plan(pkg, 512, 512, 1001)
+    # base address off 16 bytes
+    assert "path: simt" in plan(pkg, 512, 512, 512, align=8)
+    # column-major output: the transposed problem runs
+    text = plan(pkg, 512, 1024, 512, out_strides=(1, 512))
+    assert "the transposed problem is computed" in text
+    # f8 with an N-contiguous B needs 128 columns per CTA and half: narrow N leaves the pair path
+    text = plan(pkg, 512, 384, 1024, dtype=pkg.abi.F8E4M3, out_dtype=pkg.abi.BF16)
+    assert "tcgen05_1cta" in text
+
+
+def test_verifier_applies(pkg):
+    with pytest.raises(ValueError, match="same element bit width"):
+        plan(pkg, 64, 64, 64, dtype=pkg.abi.F32, rhs_dtype=pkg.abi.F16, out_dtype=pkg.abi.F32)
+    assert "path: none" in plan(pkg, 0, 64, 64)
