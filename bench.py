@@ -322,6 +322,22 @@ def run_ours(args):
     sec_per_step = elapsed / args.steps
     value = FLOPS / sec_per_step / 1e12
 
+    # The SM clock INSIDE the kernel under the same load (NVML's samples are too
+    # slow for a 15 ms region): the same burst again, untimed, with the kernel's own
+    # probe on (cycles and nanoseconds of the first CTA's MMA warp, last launch).
+    if rank == 0 and clocks is not None:
+        try:
+            h.set_matmul_path("auto:d128")
+            for _ in range(args.steps):
+                step()
+            cyc, ns = h.probe_clock()
+            if ns:
+                mhz = cyc / ns * 1e3
+                clocks["sm_mhz_in_kernel"] = round(mhz, 1)
+                clocks["tensor_peak_at_that_clock_tflops"] = round(2250.0 * mhz / 1965.0, 1)
+        finally:
+            h.set_matmul_path("auto")
+
     # ---- end to end through the host-buffer C-ABI call (pinned host memory in,
     # pinned host memory out, copies inside the timed region)
     C_pin = torch.empty((M, c1 - c0), dtype=torch.bfloat16).pin_memory()
