@@ -15,7 +15,11 @@ from util import bits, normal
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 KERNELS = os.path.join(HERE, "golden", "kernels")
-REF = "/root/reference/test/Conversion/KapyToKgpu"
+# the reference checkout, when it sits beside this repository (or where
+# KAPY_REFERENCE_DIR points)
+REF = os.path.join(os.environ.get("KAPY_REFERENCE_DIR",
+                                  os.path.join(HERE, "..", "..", "reference")),
+                   "test", "Conversion", "KapyToKgpu")
 
 
 def load(pkg, name):
