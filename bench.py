@@ -99,7 +99,10 @@ class ClockSampler:
     def start(self):
         self.thread = threading.Thread(target=self._run, daemon=True)
         self.thread.start()
-        time.sleep(0.05)
+        # NVML's first call can take a while: wait for the first sample
+        t0 = time.perf_counter()
+        while not self.samples and self.err is None and time.perf_counter() - t0 < 3.0:
+            time.sleep(0.01)
 
     def stop(self, t_begin=None, t_end=None):
         self._stop.set()

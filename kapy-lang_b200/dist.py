@@ -79,7 +79,12 @@ class PushGather:
         self.group = group or dist.group.WORLD
         self.full = symm.empty((M, n_total), dtype=dtype, device=device)
         self.hdl = symm.rendezvous(self.full, group=self.group)
-        self.peer_ptrs = [int(p) for p in self.hdl.buffer_ptrs]
+        ptrs = [int(p) for p in self.hdl.buffer_ptrs]
+        # Each rank walks the destinations starting after itself (its own copy
+        # last), so that at any moment the ranks push to different peers instead
+        # of all converging on rank 0's NVLink port, then rank 1's, ...
+        r = dist.get_rank(self.group)
+        self.peer_ptrs = [ptrs[(r + 1 + i) % len(ptrs)] for i in range(len(ptrs))]
         self.M, self.n_total, self.dtype = M, n_total, dtype
 
     def matmul(self, handle, lhs, rhs_shard, col_begin: int, *, bias_shard=None, **epilogue):
