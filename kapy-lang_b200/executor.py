@@ -633,13 +633,26 @@ def _launch_matmul(L, handle, sp):
     A, B = roots[next(iter(lhs_ids))], roots[next(iter(rhs_ids))]
     Cr = tgt.root
     # epilogue between the accumulator chain and the store
+    # The fused epilogue computes downcast(act(alpha * acc + bias)): walking back
+    # from the store, an activation may only appear before any add / multiply.
     alpha, bias_root, out_dtype, rounding = 1.0, None, expr.dtype, abi.RN
+    activation, seen_affine, seen_mul = abi.ACT_NONE, False, False
     e = expr
     while e.kind == "op":
         if e.name in ("arith.truncf", "kapy.fptofp", "arith.extf"):
             rounding = e.attrs.get("rounding", abi.RN)
             e = e.args[0]
+        elif e.name in ("arith.maximumf", "arith.maxnumf") and \
+                any(_is_splat_const(a) and _splat_value(a) == 0.0 for a in e.args):
+            # max(x, 0): relu
+            o = [a for a in e.args if not (_is_splat_const(a) and _splat_value(a) == 0.0)]
+            if len(o) != 1 or seen_affine or activation != abi.ACT_NONE:
+                raise Unsupported("matmul epilogue: relu is recognised once, as the last "
+                                  "arithmetic before the store")
+            activation = abi.ACT_RELU
+            e = o[0]
         elif e.name == "arith.mulf":
+            seen_affine = seen_mul = True
             c = [a for a in e.args if _is_splat_const(a)]
             o = [a for a in e.args if not _is_splat_const(a)]
             if len(c) != 1 or len(o) != 1:
@@ -647,6 +660,10 @@ def _launch_matmul(L, handle, sp):
             alpha *= _splat_value(c[0])
             e = o[0]
         elif e.name == "arith.addf":
+            if seen_mul:
+                # (acc + bias) * c is not alpha * acc + bias
+                raise Unsupported("matmul epilogue: a bias add inside a multiply is not recognised")
+            seen_affine = True
             b = [a for a in e.args if _bias_load(a) is not None]
             o = [a for a in e.args if _bias_load(a) is None]
             if len(b) != 1 or len(o) != 1:
@@ -665,7 +682,7 @@ def _launch_matmul(L, handle, sp):
     tl = _tensor_desc(A, L.args, lo0, hi0, 0, A.size1)
     tr = _tensor_desc(B, L.args, 0, B.size0, lo1, hi1)
     to = _tensor_desc(Cr, L.args, lo0, hi0, lo1, hi1)
-    ep = abi.Epilogue(float(alpha), None, abi.F32, 1, abi.ACT_NONE, int(rounding))
+    ep = abi.Epilogue(float(alpha), None, abi.F32, 1, activation, int(rounding))
     if bias_root is not None:
         root, axis = bias_root
         t = L.args[root.arg]

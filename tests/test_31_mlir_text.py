@@ -175,3 +175,41 @@ def test_fixtures_run_on_gpu(handle, ko, pkg):
     ref = ko.matmul_f64(bits(A), 1, bits(B), 1)
     err, _ = ko.max_rel_err(Cd.cpu().double().numpy(), ref)
     assert err <= 1e-2
+
+
+def _gemm_with_epilogue(tail: str) -> str:
+    """gemm_ring_bf16.mlir with the lines between the loop and the store replaced."""
+    text = open(os.path.join(KERNELS, "gemm_ring_bf16.mlir")).read()
+    head, rest = text.split("    %out = arith.truncf %acc", 1)
+    rest = rest.split("\n", 1)[1]
+    return head + tail + rest
+
+
+def test_lift_matmul_epilogues(pkg):
+    """scale, relu and the downcast after the accumulator become the fused
+    epilogue; orders the fused epilogue cannot express are refused."""
+    M, K, N = 128, 64, 96
+    a, b, c = (torch.zeros(s, dtype=torch.bfloat16) for s in ((M, K), (K, N), (M, N)))
+    ok = _gemm_with_epilogue(
+        "    %half = arith.constant dense<5.000000e-01> : tensor<32x32xf32, #values>\n"
+        "    %zero2 = arith.constant dense<0.000000e+00> : tensor<32x32xf32, #values>\n"
+        "    %sc = arith.mulf %acc, %half : tensor<32x32xf32, #values>\n"
+        "    %re = arith.maximumf %sc, %zero2 : tensor<32x32xf32, #values>\n"
+        "    %out = arith.truncf %re : tensor<32x32xf32, #values> to tensor<32x32xbf16, #values>\n")
+    mod = pkg.mlir_text.parse_text(ok)
+    h = FakeHandle()
+    pkg.executor.launch(next(iter(mod.functions.values())), (M // 32, N // 32, 1),
+                        [a, b, c, M, K, N], h, module=mod)
+    kind, tl, tr, to, ep, way = h.log[0]
+    assert kind == "matmul" and ep.alpha == 0.5 and ep.activation == pkg.abi.ACT_RELU
+    # relu before the scale: act(alpha * acc) is not alpha * act(acc) in general
+    bad = _gemm_with_epilogue(
+        "    %half = arith.constant dense<-5.000000e-01> : tensor<32x32xf32, #values>\n"
+        "    %zero2 = arith.constant dense<0.000000e+00> : tensor<32x32xf32, #values>\n"
+        "    %re = arith.maximumf %acc, %zero2 : tensor<32x32xf32, #values>\n"
+        "    %sc = arith.mulf %re, %half : tensor<32x32xf32, #values>\n"
+        "    %out = arith.truncf %sc : tensor<32x32xf32, #values> to tensor<32x32xbf16, #values>\n")
+    mod = pkg.mlir_text.parse_text(bad)
+    with pytest.raises(pkg.executor.Unsupported, match="relu is recognised once"):
+        pkg.executor.launch(next(iter(mod.functions.values())), (M // 32, N // 32, 1),
+                            [a, b, c, M, K, N], FakeHandle(), module=mod)
