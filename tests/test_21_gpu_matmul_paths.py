@@ -93,3 +93,61 @@ def test_cta_pair_kernel(handle, ko, shape, bn, layout):
     finally:
         handle.set_matmul_path("auto")
     check(ko, out, A, B, bias=bias)
+
+
+@pytest.mark.parametrize("K", [64, 192, 256, 320, 1024])
+def test_wide_pair_tile_many_tiles_per_pair(handle, ko, K):
+    """256 x 512 tiles, several per CTA pair, K loops shorter and longer than the
+    skew between the halves at tile boundaries (1, 3, 4, 5 and 16 K blocks)."""
+    M, N = 2048, 8192 + 264          # 8 x 17 tiles on 74 pairs, ragged last column block
+    A, B = normal((M, K), 31, K ** -0.5), normal((K, N), 32)
+    bias = uniform((N,), 33, -0.1, 0.1, torch.bfloat16)
+    handle.set_matmul_path("2cta:512")
+    try:
+        out = handle.matmul(A.cuda(), B.cuda(), bias=bias.cuda())
+        handle.check()
+    finally:
+        handle.set_matmul_path("auto")
+    rows = np.array([0, 127, 128, 255, 256, 1000, 2047], dtype=np.int32)
+    cols = np.concatenate([np.arange(0, 1024), np.arange(4000, 4700), np.arange(8100, N)]).astype(np.int32)
+    check(ko, out, A, B, bias=bias, rows=rows, cols=cols)
+    ref = torch.addmm(bias.cuda().float(), A.cuda().float(), B.cuda().float())
+    assert (out.float() - ref).abs().max().item() <= 2 ** -5 * max(1.0, ref.abs().max().item())
+
+
+@pytest.mark.parametrize("variant", ["f16_out", "f32_out", "alpha", "bias_f32", "row_bias", "relu", "addend", "rz"])
+def test_wide_pair_tile_epilogues(handle, ko, variant):
+    """Every epilogue flavour on the 256 x 512 tile: the register-drain path
+    (16-bit out, scale, optional 16-bit column bias) and the chunked one."""
+    M, N, K = 512, 1280, 384
+    dt = torch.float16 if variant == "f16_out" else torch.bfloat16
+    A, B = normal((M, K), 41, K ** -0.5, dt), normal((K, N), 42, 1.0, dt)
+    kw, okw = {}, {}
+    out_dtype = torch.float32 if variant in ("f32_out", "addend") else dt
+    if variant == "alpha":
+        kw["alpha"] = okw["alpha"] = 0.37
+        bias = uniform((N,), 43, -0.1, 0.1, dt)
+        kw["bias"], okw["bias"] = bias.cuda(), bias
+    if variant == "bias_f32":
+        bias = uniform((N,), 43, -0.1, 0.1, torch.float32)
+        kw["bias"], okw["bias"] = bias.cuda(), bias
+    if variant == "row_bias":
+        bias = uniform((M,), 43, -0.1, 0.1, dt)
+        kw["bias"], okw["bias"] = bias.cuda(), bias
+        kw["bias_axis"] = okw["bias_axis"] = 0
+    if variant == "relu":
+        kw["activation"] = okw["activation"] = 1
+    if variant == "rz":
+        kw["rounding"] = 0
+    acc = None
+    if variant == "addend":
+        acc = normal((M, N), 44, 1.0, torch.float32)
+        kw["acc"], okw["acc"] = acc.cuda(), acc
+    handle.set_matmul_path("2cta:512")
+    try:
+        out = handle.matmul(A.cuda(), B.cuda(), out_dtype=out_dtype, **kw)
+        handle.check()
+        assert handle.last_kernel == "tcgen05_2cta"
+    finally:
+        handle.set_matmul_path("auto")
+    check(ko, out, A, B, **okw)
