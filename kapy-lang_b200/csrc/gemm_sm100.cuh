@@ -106,8 +106,10 @@ struct GemmCfg {
   static constexpr int B_BYTES = BN_CTA * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   // 32-row x 128-byte staging buffers per epilogue warp: two, except where eight
-  // warps and 48 KB stages leave room for one only
-  static constexpr int C_BUFS = (BN == 512 && EPI == 8) ? 1 : 2;
+  // warps and 48 KB stages leave room for one only (the 512-wide pair tile), or
+  // where one buffer buys a fourth stage (256-wide single-CTA tiles with eight
+  // epilogue warps: the short-K shapes, whose main loop is load latency)
+  static constexpr int C_BUFS = ((BN == 512 || (BN == 256 && CTAS == 1)) && EPI == 8) ? 1 : 2;
   static constexpr int C_WARP_BYTES = C_BUFS * 4096;
   static constexpr int C_BYTES = EPI * C_WARP_BYTES;
   static constexpr int THREADS = 64 + 32 * EPI;  // producer warp, MMA warp, EPI epilogue warps
@@ -285,7 +287,7 @@ __device__ __forceinline__ bool epilogue_tile(const GemmParams &p, const TmapArr
   constexpr int CW = OUT32 ? 32 : 64;  // output columns per 128-byte staging row
   constexpr int NH = CW / 32;
   constexpr int CSTEP = EPI / 4;
-  constexpr int C_BUFS = (BN == 512 && EPI == 8) ? 1 : 2;
+  constexpr int C_BUFS = ((BN == 512 || BN == 256) && EPI == 8) ? 1 : 2;
   const int lane = t.lane;
   bool handed_back = false;
   for (int c = t.col_begin / CW + t.cpart; c < t.col_end / CW; c += CSTEP) {
