@@ -39,7 +39,7 @@ CPU_SAMPLE_ROWS = 512                         # rows of the output the CPU arm c
 # dram__bytes_read.sum + dram__bytes_write.sum of one full-size launch of the
 # dominant kernel, from a one-pass ncu capture of this benchmark (command and
 # figures in profiles/gemm_tcgen05_2cta_256x512_bf16_8192x8192x4096.txt).
-NCU_TRAFFIC_BYTES = 901_570_304 + 149_774_336
+NCU_TRAFFIC_BYTES = 869_611_008 + 151_768_576
 
 
 def load_peaks():
