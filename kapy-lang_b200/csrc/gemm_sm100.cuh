@@ -10,9 +10,19 @@
 // mma.sync m16n8k8 chain, MatmulOpToLLVM.cpp:58-266) at whole-problem scope.
 //
 // Warp roles: warp 0 = TMA producer (one lane), warp 1 = TMEM allocator + MMA
-// issuer (one lane), warps 2 .. 2+EPI-1 = epilogue (warp w may touch TMEM lanes
-// 32*(w%4) .. +31; with EPI = 8 two warps share a lane quarter and alternate
-// column chunks, for problems whose K loop is too short to hide the epilogue).
+// issuer (the whole warp walks the loops in step, one elected lane issues, so the
+// descriptor arithmetic stays in uniform registers), warps 2 .. 2+EPI-1 =
+// epilogue (warp w may touch TMEM lanes 32*(w%4) .. +31; with EPI = 8 two warps
+// share a lane quarter and alternate column chunks, for problems whose K loop is
+// too short to hide the epilogue).
+//
+// Operand kinds: kind::f16 (f16 / bf16), kind::tf32 (f32 operands) and
+// kind::f8f6f4 (f8E4M3 / f8E5M2) share the kernel: a shared-memory row is always
+// 128 bytes and a K step 32 bytes, whatever the element width.
+//
+// 512-wide tiles (pairs only) hold two 256-column halves that fill TMEM; the MMA
+// role skews the halves at tile boundaries and the epilogue drains them through
+// registers (see epilogue_two_halves and the MMA role below).
 //
 // CTAS == 2 pairs two CTAs of a cluster on one 256-row tile
 // (tcgen05.mma.cta_group::2): each CTA loads its own 128 rows of A and its own
