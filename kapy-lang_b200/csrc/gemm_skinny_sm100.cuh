@@ -353,21 +353,29 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         seen = __shfl_sync(0xffffffffu, seen, 0);
         if (seen == expected - 1) {
           __threadfence();
-          // Sixteen rows at a time, all loads of a slot issued before anything
-          // depends on them: one L2 round trip per slot and batch.
+          // Sixteen rows at a time and two contributors' slots at a time, all 32
+          // loads issued before anything depends on them: one L2 round trip per
+          // pair of slots and batch (a split tile has two or three contributors).
+          // The slots are still added in CTA order.
+          auto slot_of = [&](int c) {
+            const int slot = static_cast<long long>(c) * p.span > t0 ? 0 : 1;
+            return p.scratch + (static_cast<long long>(c * 2 + slot) * p.m_pad) * 128 + q * 32 + lane;
+          };
           for (int mc = 0; mc < p.M; mc += 16) {
             float sums[16];
 #pragma unroll
             for (int i = 0; i < 16; ++i) sums[i] = 0.0f;
-            for (int c = first; c <= last; ++c) {
-              const int slot = static_cast<long long>(c) * p.span > t0 ? 0 : 1;
-              const float *src = p.scratch + (static_cast<long long>(c * 2 + slot) * p.m_pad) * 128 +
-                                 q * 32 + lane;
-              float part[16];
+            for (int c = first; c <= last; c += 2) {
+              const bool two = c + 1 <= last;
+              const float *src0 = slot_of(c), *src1 = slot_of(two ? c + 1 : c);
+              float part0[16], part1[16];
 #pragma unroll
-              for (int i = 0; i < 16; ++i) part[i] = mc + i < p.M ? __ldcg(src + (mc + i) * 128) : 0.0f;
+              for (int i = 0; i < 16; ++i) part0[i] = mc + i < p.M ? __ldcg(src0 + (mc + i) * 128) : 0.0f;
 #pragma unroll
-              for (int i = 0; i < 16; ++i) sums[i] += part[i];
+              for (int i = 0; i < 16; ++i)
+                part1[i] = (two && mc + i < p.M) ? __ldcg(src1 + (mc + i) * 128) : 0.0f;
+#pragma unroll
+              for (int i = 0; i < 16; ++i) sums[i] = (sums[i] + part0[i]) + part1[i];
             }
             if (n < p.N) {
               if (fast16) {
