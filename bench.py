@@ -237,6 +237,9 @@ def secondary(torch, pkg, h, peaks):
     gbs = 470941696 / t / 1e9
     out["decode_16x28672x8192_bf16"] = {"GB/s": gbs, "frac_of_measured_hbm": gbs / peaks["hbm_gbs"],
                                         "ms": t * 1e3, "kernel": h.last_kernel}
+    # the vendor library on the same buffers, for context only (not on the product path)
+    t_lib = timeit(lambda: torch.mm(Xs, W, out=o))
+    out["decode_16x28672x8192_bf16"]["library_torch_mm_GB/s"] = 470941696 / t_lib / 1e9
     del W, o
     # attention-score shape: batch 64 x 2048 x 2048 x 128, alpha = 1/sqrt(128)
     Q = torch.randn(8, 2048, 128, generator=g).to(torch.bfloat16).cuda().repeat(8, 1, 1)
@@ -247,6 +250,12 @@ def secondary(torch, pkg, h, peaks):
     out["batched_64x2048x2048x128_bf16"] = {"GB/s": gbs, "TFLOP/s": 6.872e10 / t / 1e12,
                                             "frac_of_measured_hbm": gbs / peaks["hbm_gbs"],
                                             "ms": t * 1e3, "kernel": h.last_kernel}
+    # write-dominated (512 MiB out of 576 MiB): a plain fill of the output and the vendor
+    # library's batched matmul on the same buffers, for context only
+    t_fill = timeit(lambda: S.zero_())
+    out["batched_64x2048x2048x128_bf16"]["fill_of_the_output_GB/s"] = S.numel() * 2 / t_fill / 1e9
+    t_lib = timeit(lambda: torch.bmm(Q, Kt, out=S))
+    out["batched_64x2048x2048x128_bf16"]["library_torch_bmm_GB/s"] = 603979776 / t_lib / 1e9
     del Q, Kt, S
     # fp16 1024^3 with column-major B: launch-latency scale, absolute time only
     A1 = (torch.rand(1024, 1024, generator=g) * 2 - 1).to(torch.float16).cuda()
