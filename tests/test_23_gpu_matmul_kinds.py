@@ -156,3 +156,22 @@ def test_kind_diagnostics(handle):
         handle.matmul(A8, A8, out_dtype=torch.float32, impl_way=2)
     with pytest.raises(ValueError, match="same element type unless"):
         handle.matmul(A16, A16.to(torch.bfloat16), out_dtype=torch.float32)
+
+
+@pytest.mark.parametrize("dt", [torch.float32, torch.float8_e4m3fn])
+def test_kinds_through_host_buffers(handle, ko, dt):
+    """kapyb_matmul_host with f32 (tf32) and f8 operands: the chunked upload /
+    compute / download pipeline moves 4- and 1-byte elements as well."""
+    M, N, K = 2304 + 40, 512, 2048
+    A = normal((M, K), 21, K ** -0.5, torch.float32)
+    B = normal((K, N), 22, 1.0, torch.float32)
+    if dt == torch.float32:
+        A, B = tf32_trunc(A), tf32_trunc(B)
+    else:
+        A, B = (A * 16).to(dt), B.to(dt)
+    out = torch.empty((M, N), dtype=torch.bfloat16).pin_memory()
+    handle.matmul_host(A.pin_memory(), B.pin_memory(), out)
+    dev = handle.matmul(A.cuda(), B.cuda(), out_dtype=torch.bfloat16)
+    handle.check()
+    assert torch.equal(dev.cpu(), out)
+    check(ko, out, A, B)
