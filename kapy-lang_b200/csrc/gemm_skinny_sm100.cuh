@@ -168,6 +168,9 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   __syncthreads();
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // set-up done without touching global memory: see gemm_tcgen05_kernel
+  ptx::griddep_launch();
+  ptx::griddep_wait();
 
   const long long total = static_cast<long long>(p.sk_tiles) * p.num_kb;  // units of the split region
   const long long g_begin = min(total, static_cast<long long>(blockIdx.x) * p.span);

@@ -599,6 +599,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
   }
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // Everything above touched only shared and tensor memory: let the next kernel of
+  // the stream start its own set-up while this grid runs, and do not touch global
+  // memory before the kernels ahead of this one are done.
+  ptx::griddep_launch();
+  ptx::griddep_wait();
 
   if (warp == 0 && lane == 0) {
     // ------------------------------------------------------------ producer

@@ -549,13 +549,17 @@ static kapyb_status launch_tcgen05(kapyb_handle h, const MatmulProblem &p, bool 
   cfg.blockDim = dim3(Cfg::THREADS, 1, 1);
   cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = CTAS;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  // the kernel's set-up may overlap the tail of the kernel ahead of it in the
+  // stream; it waits (griddepcontrol.wait) before it touches global memory
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = 2;
   // The tile loop is statically strided, so every CTA (pair) of the grid must be
   // resident at once: a pair that only starts when another retires would run its
   // whole share afterwards.  Pairs need two free SMs in one GPC, which can be
@@ -662,8 +666,17 @@ static kapyb_status launch_skinny_on(kapyb_handle h, const MatmulProblem &p, boo
                                      cudaFuncAttributeMaxDynamicSharedMemorySize, 232448));
     attr_set[h->device] = true;
   }
-  gemm_skinny_kernel<<<grid, kSkinnyThreads, smem, stream>>>(tmW, tmX, sp);
-  CUDA_TRY(h, cudaGetLastError());
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid, 1, 1);
+  cfg.blockDim = dim3(kSkinnyThreads, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;  // see launch_tcgen05
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  CUDA_TRY(h, cudaLaunchKernelEx(&cfg, gemm_skinny_kernel, tmW, tmX, sp));
   h->launches++;
   h->last_kernel = "tcgen05_skinny";
   return KAPYB_OK;

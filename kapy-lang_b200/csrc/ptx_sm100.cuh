@@ -21,6 +21,18 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
   return t;
 }
 
+// Programmatic dependent launch.  griddep_launch: the next kernel in the stream
+// (if it was launched with programmatic stream serialization) may start being
+// scheduled now instead of when this grid has drained; griddep_wait: blocks until
+// every grid this one depends on has completed and its writes are visible.  A
+// kernel launched without the attribute sees both as no-ops.
+__device__ __forceinline__ void griddep_launch() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void griddep_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
 __device__ __forceinline__ bool elect_one() {
   uint32_t pred = 0;
   asm volatile(
