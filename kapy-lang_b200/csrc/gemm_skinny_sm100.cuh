@@ -356,40 +356,50 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         seen = __shfl_sync(0xffffffffu, seen, 0);
         if (seen == expected - 1) {
           __threadfence();
-          // Sixteen rows at a time and two contributors' slots at a time, all 32
-          // loads issued before anything depends on them: one L2 round trip per
-          // pair of slots and batch (a split tile has two or three contributors).
-          // The slots are still added in CTA order.
+          // 32 rows at a time and two contributors' slots at a time, all 64 loads
+          // issued before anything depends on them: one L2 round trip per pair of
+          // slots and batch (a split tile has two or three contributors; under a
+          // full HBM load a round trip is 2-3 us, and this pass must be done
+          // before the CTA's whole tile needs the epilogue warps again).  The
+          // slots are still added in CTA order.
           auto slot_of = [&](int c) {
             const int slot = static_cast<long long>(c) * p.span > t0 ? 0 : 1;
             return p.scratch + (static_cast<long long>(c * 2 + slot) * p.m_pad) * 128 + q * 32 + lane;
           };
-          for (int mc = 0; mc < p.M; mc += 16) {
-            float sums[16];
+          for (int mc = 0; mc < p.M; mc += 32) {
+            float sums[2][16];
 #pragma unroll
-            for (int i = 0; i < 16; ++i) sums[i] = 0.0f;
+            for (int i = 0; i < 32; ++i) sums[i >> 4][i & 15] = 0.0f;
             for (int c = first; c <= last; c += 2) {
               const bool two = c + 1 <= last;
               const float *src0 = slot_of(c), *src1 = slot_of(two ? c + 1 : c);
-              float part0[16], part1[16];
+              float part0[32], part1[32];
 #pragma unroll
-              for (int i = 0; i < 16; ++i) part0[i] = mc + i < p.M ? __ldcg(src0 + (mc + i) * 128) : 0.0f;
+              for (int i = 0; i < 32; ++i) part0[i] = mc + i < p.M ? __ldcg(src0 + (mc + i) * 128) : 0.0f;
 #pragma unroll
-              for (int i = 0; i < 16; ++i)
+              for (int i = 0; i < 32; ++i)
                 part1[i] = (two && mc + i < p.M) ? __ldcg(src1 + (mc + i) * 128) : 0.0f;
 #pragma unroll
-              for (int i = 0; i < 16; ++i) sums[i] = (sums[i] + part0[i]) + part1[i];
+              for (int i = 0; i < 32; ++i)
+                sums[i >> 4][i & 15] = (sums[i >> 4][i & 15] + part0[i]) + part1[i];
             }
             if (n < p.N) {
-              if (fast16) {
-                if (p.out_dtype == KAPYB_BF16)
-                  skinny_store16<KAPYB_BF16>(col16 + mc * p.c_s0, p.c_s0, p.M - mc, sums, p.ep.alpha, bias_n);
-                else
-                  skinny_store16<KAPYB_F16>(col16 + mc * p.c_s0, p.c_s0, p.M - mc, sums, p.ep.alpha, bias_n);
-              } else {
 #pragma unroll
-                for (int i = 0; i < 16; ++i)
-                  if (mc + i < p.M) skinny_finish(p, n, mc + i, sums[i], bias_n);
+              for (int hb = 0; hb < 2; ++hb) {
+                const int m0r = mc + hb * 16;
+                if (m0r >= p.M) break;
+                if (fast16) {
+                  if (p.out_dtype == KAPYB_BF16)
+                    skinny_store16<KAPYB_BF16>(col16 + m0r * p.c_s0, p.c_s0, p.M - m0r, sums[hb],
+                                               p.ep.alpha, bias_n);
+                  else
+                    skinny_store16<KAPYB_F16>(col16 + m0r * p.c_s0, p.c_s0, p.M - m0r, sums[hb],
+                                              p.ep.alpha, bias_n);
+                } else {
+#pragma unroll
+                  for (int i = 0; i < 16; ++i)
+                    if (m0r + i < p.M) skinny_finish(p, n, m0r + i, sums[hb][i], bias_n);
+                }
               }
             }
           }
