@@ -370,6 +370,19 @@ KAPYB_API kapyb_status kapyb_matmul_plan(kapyb_handle h, int32_t sm_count,
                                          const kapyb_tensor2d *out, int32_t batch, char *text,
                                          size_t capacity);
 
+/* Tuned dispatch choices, process-wide.  A file has one problem per line,
+ *     M N K batch dtype k|mn k|mn path        # comment
+ * (dtype of lhs: f16 bf16 f32 f8E4M3 f8E5M2; the majors of lhs and rhs as the
+ * kernel sees them, "k" = K contiguous; path as in kapyb_set_matmul_path, e.g.
+ * "2cta:256" or "1cta:128:e8").  kapyb_matmul consults the table when no path
+ * is forced and the problem matches a line exactly; a choice that does not apply
+ * (say, a tcgen05 path for operands TMA cannot describe) is ignored.  Loading
+ * adds to the table (same problem: the later line wins); errors name the line.
+ * kapyb_matmul_plan shows when a choice came from the table.  The reference
+ * keeps no such cache; `kapy-lang_b200/runtime.py: tune_matmul` writes one. */
+KAPYB_API kapyb_status kapyb_tuning_load(const char *file, int32_t *n_entries);
+KAPYB_API kapyb_status kapyb_tuning_clear(void);
+
 /* Name of the kernel family the last matmul on `h` dispatched to
  * ("tcgen05_1cta", "tcgen05_2cta", "tcgen05_skinny", "simt"). */
 KAPYB_API const char *kapyb_last_kernel(kapyb_handle h);

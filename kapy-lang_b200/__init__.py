@@ -13,7 +13,9 @@ from . import mlir_text  # noqa: F401
 from . import programs  # noqa: F401
 from . import runtime  # noqa: F401
 from .build import build  # noqa: F401
-from .runtime import Handle, KapybError, KapybTimeout, matmul_plan, shard_range, tensor2d  # noqa: F401
+from .runtime import (Handle, KapybError, KapybTimeout, matmul_plan, shard_range, tensor2d,  # noqa: F401
+                      tune_matmul, tuning_clear, tuning_load)
 
-__all__ = ["abi", "dist", "executor", "ir", "mlir_text", "programs", "runtime", "build", "Handle", "KapybError", "KapybTimeout", "matmul_plan", "shard_range",
+__all__ = ["abi", "dist", "executor", "ir", "mlir_text", "programs", "runtime", "build", "Handle", "KapybError", "KapybTimeout", "matmul_plan", "shard_range", "tune_matmul",
+           "tuning_clear", "tuning_load",
            "tensor2d"]

@@ -85,6 +85,8 @@ PROTOTYPES = {
                                     C.POINTER(C.c_int64), C.POINTER(C.c_int64)]),
     "kapyb_last_kernel": (C.c_char_p, [C.c_void_p]),
     "kapyb_launch_count": (C.c_int64, [C.c_void_p]),
+    "kapyb_tuning_load": (C.c_int, [C.c_char_p, C.POINTER(C.c_int32)]),
+    "kapyb_tuning_clear": (C.c_int, []),
     "kapyb_matmul_plan": (C.c_int, [C.c_void_p, C.c_int32, C.POINTER(Tensor2d), C.POINTER(Tensor2d),
                                     C.POINTER(Tensor2d), C.c_int32, C.c_char_p, C.c_size_t]),
     "kapyb_probe_read": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(C.c_uint32), C.c_int32]),

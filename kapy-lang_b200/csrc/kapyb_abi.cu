@@ -9,7 +9,11 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <fstream>
+#include <mutex>
+#include <sstream>
 #include <string>
+#include <vector>
 
 #include "../../include/kapyb.h"
 #include "eltwise.cuh"
@@ -155,52 +159,75 @@ extern "C" KAPYB_API kapyb_status kapyb_probe_read(kapyb_handle h, void *stream,
   return KAPYB_OK;
 }
 
+// A dispatch choice in text form: "auto" | "1cta" | "2cta" | "skinny" | "simt",
+// optionally followed by ":<tile width>" and options ":e<epilogue warps>",
+// ":s<stages>" (skinny), ":d<debug bits>", ":w<wait limit, ms>".
+struct PathChoice {
+  int path = PATH_AUTO, bn = 0, epi = 0, skinny_stages = 0, debug = 0;
+  uint32_t wait_limit_us = 0;
+};
+
+static bool parse_path(const std::string &text, PathChoice &c, const char **why) {
+  c = PathChoice{};
+  auto option = [&](const char *tag, size_t from) -> int {
+    const size_t at = text.find(tag, from);
+    return at == std::string::npos ? -1 : atoi(text.c_str() + at + 2);
+  };
+  const size_t colon = text.find(':');
+  const std::string family = text.substr(0, colon);
+  if (family == "auto")
+    c.path = PATH_AUTO;
+  else if (family == "1cta")
+    c.path = PATH_1CTA;
+  else if (family == "2cta")
+    c.path = PATH_2CTA;
+  else if (family == "skinny")
+    c.path = PATH_SKINNY;
+  else if (family == "simt")
+    c.path = PATH_SIMT;
+  else {
+    *why = "unknown path";
+    return false;
+  }
+  if (colon == std::string::npos) return true;
+  const char first = text[colon + 1];  // text[size()] is the terminator: in bounds
+  if (first >= '0' && first <= '9') {
+    c.bn = atoi(text.c_str() + colon + 1);
+    if (c.bn != 64 && c.bn != 128 && c.bn != 256 && c.bn != 512) {
+      *why = "tile width must be 64/128/256/512";
+      return false;
+    }
+  }
+  c.debug = std::max(0, option(":d", colon));
+  c.epi = std::max(0, option(":e", colon));
+  c.skinny_stages = std::max(0, option(":s", colon));
+  const int w = option(":w", colon);
+  c.wait_limit_us = w > 0 ? 1000u * static_cast<uint32_t>(w) : 0u;
+  return true;
+}
+
 extern "C" KAPYB_API kapyb_status kapyb_set_matmul_path(kapyb_handle h, const char *name) {
   if (!h || !name) return fail(h, KAPYB_INVALID_ARG, "kapyb_set_matmul_path: NULL argument");
-  std::string s(name);
-  h->forced_bn = 0;
-  h->debug = 0;
-  h->wait_limit_us = 0;
-  h->forced_epi = 0;
-  h->skinny_stages = 0;
-  if (s.rfind("skinny", 0) == 0) {
-    size_t cs = s.find(":s");
-    if (cs != std::string::npos) h->skinny_stages = atoi(s.c_str() + cs + 2);
-    size_t cd = s.find(":d");
-    if (cd != std::string::npos) h->debug = atoi(s.c_str() + cd + 2);
-    h->forced_path = PATH_SKINNY;
-    return KAPYB_OK;
-  }
-  size_t colon = s.find(':');
-  if (colon != std::string::npos) {
-    h->forced_bn = atoi(s.c_str() + colon + 1);
-    size_t colon2 = s.find(":d", colon);
-    if (colon2 != std::string::npos) h->debug = atoi(s.c_str() + colon2 + 2);
-    size_t colonw = s.find(":w", colon);
-    if (colonw != std::string::npos) h->wait_limit_us = 1000u * atoi(s.c_str() + colonw + 2);
-    size_t colon3 = s.find(":e", colon);
-    if (colon3 != std::string::npos) h->forced_epi = atoi(s.c_str() + colon3 + 2);
-    s = s.substr(0, colon);
-    const char first_opt = s.c_str()[colon + 1];
-    const bool no_width = first_opt < '0' || first_opt > '9';  // "auto:d128": options only
-    if (!no_width && h->forced_bn != 64 && h->forced_bn != 128 && h->forced_bn != 256 &&
-        h->forced_bn != 512)
-      return fail(h, KAPYB_INVALID_ARG, "kapyb_set_matmul_path: tile width must be 64/128/256/512");
-    if (no_width) h->forced_bn = 0;
-  }
-  if (s == "auto")
-    h->forced_path = PATH_AUTO;
-  else if (s == "1cta")
-    h->forced_path = PATH_1CTA;
-  else if (s == "2cta")
-    h->forced_path = PATH_2CTA;
-  else if (s == "skinny")
-    h->forced_path = PATH_SKINNY;
-  else if (s == "simt")
-    h->forced_path = PATH_SIMT;
-  else
-    return fail(h, KAPYB_INVALID_ARG, "kapyb_set_matmul_path: unknown path '%s'", name);
+  PathChoice c;
+  const char *why = "";
+  if (!parse_path(name, c, &why))
+    return fail(h, KAPYB_INVALID_ARG, "kapyb_set_matmul_path: %s ('%s')", why, name);
+  h->forced_path = c.path;
+  h->forced_bn = c.bn;
+  h->forced_epi = c.epi;
+  h->skinny_stages = c.skinny_stages;
+  h->debug = c.debug;
+  h->wait_limit_us = c.wait_limit_us;
   return KAPYB_OK;
+}
+
+static int dtype_from_name(const std::string &n) {
+  if (n == "f16") return KAPYB_F16;
+  if (n == "bf16") return KAPYB_BF16;
+  if (n == "f32") return KAPYB_F32;
+  if (n == "f8E4M3") return KAPYB_F8E4M3;
+  if (n == "f8E5M2") return KAPYB_F8E5M2;
+  return -1;
 }
 
 extern "C" KAPYB_API kapyb_status kapyb_check(kapyb_handle h, void *stream) {
@@ -698,6 +725,7 @@ static kapyb_status launch_skinny(kapyb_handle h, const MatmulProblem &p, bool a
 struct MatmulPlan {
   int path = PATH_SIMT;        // PATH_SIMT / PATH_SKINNY / PATH_1CTA / PATH_2CTA
   bool transposed = false;     // the transposed problem is computed (out has its unit stride on axis 0)
+  bool tuned = false;          // the choice came from the tuning table
   bool a_mn = false, b_mn = false;  // operand majors as the kernel sees them
   bool tma = false;            // operands and output are TMA-describable
   int bn = 0, epi = 4;         // tile width and epilogue warps (tcgen05 paths)
@@ -709,15 +737,62 @@ struct PlanOptions {
   int forced_path, forced_bn, forced_epi;
 };
 
+// ---- tuned dispatch choices (process-wide; see kapyb_tuning_load)
+struct TuneEntry {
+  int M, N, K, batch, in_dtype, a_mn, b_mn;
+  PathChoice choice;
+};
+static std::mutex g_tune_mu;
+static std::vector<TuneEntry> g_tune;
+
+static bool tuned_choice(const MatmulProblem &p, bool a_mn, bool b_mn, PathChoice &c) {
+  std::lock_guard<std::mutex> lock(g_tune_mu);
+  for (const TuneEntry &e : g_tune)
+    if (e.M == p.M && e.N == p.N && e.K == p.K && e.batch == p.batch && e.in_dtype == p.in_dtype &&
+        e.a_mn == (a_mn ? 1 : 0) && e.b_mn == (b_mn ? 1 : 0)) {
+      c = e.choice;
+      return true;
+    }
+  return false;
+}
+
+static kapyb_status plan_decide(const PlanOptions &o, const MatmulProblem &p, void *const *peer_outs,
+                                int n_peers, MatmulPlan &plan);
+
 // Decides how `p` runs.  `p` is transposed in place when the output's unit
-// stride is on axis 0.
+// stride is on axis 0.  Without a forced path, a tuned choice for exactly this
+// problem (shape, batch, operand type and majors) is tried first; if it does not
+// apply after all, the built-in heuristics decide.
 static kapyb_status plan_matmul(const PlanOptions &o, MatmulProblem &p, void *const *peer_outs,
                                 int n_peers, MatmulPlan &plan) {
   // Put the output's unit stride on axis 1 (compute the transposed problem otherwise).
-  if (p.c_s1 != 1 && p.c_s0 == 1 && n_peers == 0) {
-    transpose_problem(p);
-    plan.transposed = true;
+  const bool transposed = p.c_s1 != 1 && p.c_s0 == 1 && n_peers == 0;
+  if (transposed) transpose_problem(p);
+  if (o.forced_path == PATH_AUTO && o.forced_bn == 0) {
+    const bool a_k = p.a_s1 == 1 || p.K == 1, a_m = p.a_s0 == 1 || p.M == 1;
+    const bool b_n = p.b_s1 == 1 || p.N == 1;
+    PathChoice c;
+    if (tuned_choice(p, !a_k && a_m, b_n, c) && c.path != PATH_AUTO) {
+      PlanOptions t = o;
+      t.forced_path = c.path;
+      t.forced_bn = c.bn;
+      t.forced_epi = c.epi;
+      MatmulPlan tuned;
+      if (plan_decide(t, p, peer_outs, n_peers, tuned) == KAPYB_OK) {
+        plan = tuned;
+        plan.transposed = transposed;
+        plan.tuned = true;
+        return KAPYB_OK;
+      }
+    }
   }
+  const kapyb_status st = plan_decide(o, p, peer_outs, n_peers, plan);
+  plan.transposed = transposed;
+  return st;
+}
+
+static kapyb_status plan_decide(const PlanOptions &o, const MatmulProblem &p, void *const *peer_outs,
+                                int n_peers, MatmulPlan &plan) {
   const bool c_unit = p.c_s1 == 1 || p.N == 1;
   const bool a_k = p.a_s1 == 1 || p.K == 1, a_m = p.a_s0 == 1 || p.M == 1;
   const bool b_n = p.b_s1 == 1 || p.N == 1, b_k = p.b_s0 == 1 || p.K == 1;
@@ -971,6 +1046,56 @@ extern "C" KAPYB_API kapyb_status kapyb_matmul_plan(kapyb_handle h, int32_t sm_c
   }
   add("operands: A %s, B %s%s\n", amaj, bmaj,
       plan.transposed ? "; the transposed problem is computed (out has its unit stride on axis 0)" : "");
+  if (plan.tuned) add("%s\n", "choice: from the tuning table");
+  return KAPYB_OK;
+}
+
+extern "C" KAPYB_API kapyb_status kapyb_tuning_clear(void) {
+  std::lock_guard<std::mutex> lock(g_tune_mu);
+  g_tune.clear();
+  return KAPYB_OK;
+}
+
+extern "C" KAPYB_API kapyb_status kapyb_tuning_load(const char *file, int32_t *n_entries) {
+  if (n_entries) *n_entries = 0;
+  if (!file) return fail(nullptr, KAPYB_INVALID_ARG, "kapyb_tuning_load: NULL file name");
+  std::ifstream in(file);
+  if (!in) return fail(nullptr, KAPYB_INVALID_ARG, "kapyb_tuning_load: cannot read '%s'", file);
+  std::vector<TuneEntry> loaded;
+  std::string line;
+  int lineno = 0;
+  while (std::getline(in, line)) {
+    ++lineno;
+    const size_t hash = line.find('#');
+    if (hash != std::string::npos) line.resize(hash);
+    std::istringstream ls(line);
+    TuneEntry e{};
+    std::string dt, amaj, bmaj, path;
+    if (!(ls >> e.M)) continue;  // blank or comment line
+    const char *why = "";
+    if (!(ls >> e.N >> e.K >> e.batch >> dt >> amaj >> bmaj >> path) || e.M < 1 || e.N < 1 ||
+        e.K < 1 || e.batch < 1 || (e.in_dtype = dtype_from_name(dt)) < 0 ||
+        (amaj != "k" && amaj != "mn") || (bmaj != "k" && bmaj != "mn") ||
+        !parse_path(path, e.choice, &why) || e.choice.debug != 0)
+      return fail(nullptr, KAPYB_INVALID_ARG,
+                  "kapyb_tuning_load: %s line %d is not 'M N K batch dtype k|mn k|mn path'", file,
+                  lineno);
+    e.a_mn = amaj == "mn";
+    e.b_mn = bmaj == "mn";
+    loaded.push_back(e);
+  }
+  std::lock_guard<std::mutex> lock(g_tune_mu);
+  for (const TuneEntry &e : loaded) {
+    bool replaced = false;
+    for (TuneEntry &old : g_tune)
+      if (old.M == e.M && old.N == e.N && old.K == e.K && old.batch == e.batch &&
+          old.in_dtype == e.in_dtype && old.a_mn == e.a_mn && old.b_mn == e.b_mn) {
+        old = e;
+        replaced = true;
+      }
+    if (!replaced) g_tune.push_back(e);
+  }
+  if (n_entries) *n_entries = static_cast<int32_t>(loaded.size());
   return KAPYB_OK;
 }
 

@@ -9,6 +9,7 @@ python/src/passes.cc:72-75).
 from __future__ import annotations
 
 import ctypes as C
+import os
 from typing import Optional, Sequence
 
 from . import _abi as abi
@@ -88,6 +89,71 @@ def matmul_plan(m: int, n: int, k: int, *, dtype=abi.BF16, rhs_dtype=None, out_d
             raise ValueError(msg)
         raise KapybError(st, msg)
     return buf.value.decode()
+
+
+_DTYPE_NAMES = {abi.F16: "f16", abi.BF16: "bf16", abi.F32: "f32", abi.F8E4M3: "f8E4M3",
+                abi.F8E5M2: "f8E5M2"}
+
+
+def tuning_load(path: str) -> int:
+    """Adds the tuned dispatch choices of a file to the process-wide table."""
+    n = C.c_int32(0)
+    lib = abi.load()
+    st = lib.kapyb_tuning_load(os.fsencode(path), C.byref(n))
+    if st != abi.OK:
+        raise ValueError(lib.kapyb_last_error_string(None).decode())
+    return n.value
+
+
+def tuning_clear() -> None:
+    abi.load().kapyb_tuning_clear()
+
+
+def tune_matmul(handle, lhs, rhs, out=None, *, file: Optional[str] = None, iters: int = 10,
+                candidates: Optional[Sequence[str]] = None, **epilogue):
+    """Times the kernel families on this very problem (device tensors, 2-D or
+    batched 3-D) and returns (best path, {path: seconds}).  With `file`, appends
+    the winner as a line kapyb_tuning_load understands."""
+    torch = _torch()
+    batched = lhs.dim() == 3
+    m, k = lhs.shape[-2], lhs.shape[-1]
+    n = rhs.shape[-1]
+    if candidates is None:
+        candidates = ["auto", "1cta:64", "1cta:128", "1cta:256", "2cta:128", "2cta:256", "2cta:512"]
+        if m <= 64 and not batched:
+            candidates.append("skinny")
+    if out is None:
+        out = torch.empty(lhs.shape[:-1] + (n,), device=lhs.device,
+                          dtype=torch.bfloat16 if lhs.dtype.itemsize == 1 else lhs.dtype)
+    times = {}
+    try:
+        for path in candidates:
+            try:
+                handle.set_matmul_path(path)
+                for _ in range(3):
+                    handle.matmul(lhs, rhs, out, **epilogue)
+                handle.check()
+            except (KapybError, ValueError):
+                continue  # this family does not take the problem
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(iters):
+                handle.matmul(lhs, rhs, out, **epilogue)
+            e1.record()
+            e1.synchronize()
+            times[path] = e0.elapsed_time(e1) * 1e-3 / iters
+    finally:
+        handle.set_matmul_path("auto")
+    best = min(times, key=times.get)
+    if file is not None and best != "auto":
+        la, lb = (lhs[0], rhs[0]) if batched else (lhs, rhs)
+        # majors as the kernel sees them (out row-major): K contiguous = "k"
+        amaj = "k" if (la.stride(1) == 1 or k == 1) else "mn"
+        bmaj = "mn" if (lb.stride(1) == 1 or n == 1) else "k"
+        with open(file, "a") as f:
+            f.write(f"{m} {n} {k} {lhs.shape[0] if batched else 1} {_DTYPE_NAMES[dtype_code(lhs.dtype)]} "
+                    f"{amaj} {bmaj} {best}  # {times[best] * 1e6:.1f} us, auto {times.get('auto', 0) * 1e6:.1f} us\n")
+    return best, times
 
 
 class Handle:

@@ -61,3 +61,34 @@ def test_verifier_applies(pkg):
     with pytest.raises(ValueError, match="same element bit width"):
         plan(pkg, 64, 64, 64, dtype=pkg.abi.F32, rhs_dtype=pkg.abi.F16, out_dtype=pkg.abi.F32)
     assert "path: none" in plan(pkg, 0, 64, 64)
+
+
+def test_tuning_table(pkg, tmp_path):
+    """Tuned choices override the heuristics for exactly the listed problem, are
+    ignored where they cannot apply, and bad files are refused with the line."""
+    f = tmp_path / "tuned.txt"
+    f.write_text("# M N K batch dtype lhs rhs path\n"
+                 "2048 2048 2048 1 bf16 k mn 1cta:256:e8   # one-wave problem\n"
+                 "\n"
+                 "512 512 1001 1 bf16 k mn 2cta:256\n")
+    pkg.tuning_clear()
+    try:
+        assert "tile: 256 x 256" in plan(pkg, 2048, 2048, 2048)
+        assert pkg.tuning_load(str(f)) == 2
+        text = plan(pkg, 2048, 2048, 2048)
+        assert "tcgen05_1cta" in text and "tile: 128 x 256" in text and "epilogue warps 8" in text
+        assert "from the tuning table" in text
+        # another problem, another operand type or another major: untouched
+        assert "from the tuning table" not in plan(pkg, 2048, 2048, 1024)
+        assert "from the tuning table" not in plan(pkg, 2048, 2048, 2048, dtype=pkg.abi.F16)
+        assert "from the tuning table" not in plan(pkg, 2048, 2048, 2048, rhs_strides=(1, 2048))
+        # a tuned tcgen05 path for operands TMA cannot describe is ignored
+        assert "path: simt" in plan(pkg, 512, 512, 1001)
+        pkg.tuning_clear()
+        assert "tile: 256 x 256" in plan(pkg, 2048, 2048, 2048)
+        bad = tmp_path / "bad.txt"
+        bad.write_text("128 128 128 1 bf16 k mn 2cta:256\n128 128 128 1 int8 k mn auto\n")
+        with pytest.raises(ValueError, match="line 2"):
+            pkg.tuning_load(str(bad))
+    finally:
+        pkg.tuning_clear()

@@ -151,3 +151,29 @@ def test_wide_pair_tile_epilogues(handle, ko, variant):
     finally:
         handle.set_matmul_path("auto")
     check(ko, out, A, B, **okw)
+
+
+def test_tune_then_dispatch_from_the_table(handle, ko, pkg, tmp_path):
+    """tune_matmul times the kernel families on a problem and records the winner;
+    once loaded, kapyb_matmul takes that choice for exactly that problem."""
+    M, N, K = 1024, 1536, 512
+    A, B = normal((M, K), 51, K ** -0.5).cuda(), normal((K, N), 52).cuda()
+    f = tmp_path / "tuned.txt"
+    best, times = pkg.tune_matmul(handle, A, B, file=str(f), iters=5,
+                                  candidates=["auto", "1cta:128", "2cta:256", "1cta:64"])
+    assert best in times and len(times) == 4
+    # whatever won, force a distinctive entry and see it honoured
+    f.write_text(f"{M} {N} {K} 1 bf16 k mn 1cta:64\n")
+    pkg.tuning_clear()
+    try:
+        assert pkg.tuning_load(str(f)) == 1
+        assert "tile: 128 x 64" in pkg.matmul_plan(M, N, K, handle=handle)
+        out = handle.matmul(A, B)
+        handle.check()
+        assert handle.last_kernel == "tcgen05_1cta"
+        check(ko, out, A.cpu(), B.cpu())
+        ref = handle.matmul(A, B[:, :1024].contiguous())   # another problem: heuristics again
+        handle.check()
+        assert ref.shape == (M, 1024)
+    finally:
+        pkg.tuning_clear()
