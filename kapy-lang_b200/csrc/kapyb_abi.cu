@@ -834,7 +834,7 @@ static kapyb_status plan_decide(const PlanOptions &o, const MatmulProblem &p, vo
     if (p.M <= kSkinnyMaxM && n_peers == 0 && p.batch == 1 && dtype_size(p.in_dtype) == 2 &&
         skinny_supported(o.sm_count, p.M, p.N, p.K))
       path = PATH_SKINNY;
-    else if (p.M >= 256 && p.N >= 256 && p.K >= 512 && pair_tiles * 4 >= o.sm_count && o.forced_bn == 0)
+    else if (p.M >= 256 && p.N >= 256 && p.K >= 512 && pair_tiles * 5 >= o.sm_count && o.forced_bn == 0)
       path = PATH_2CTA;
     else
       path = PATH_1CTA;
@@ -851,19 +851,26 @@ static kapyb_status plan_decide(const PlanOptions &o, const MatmulProblem &p, vo
     plan.path = PATH_SKINNY;
     return KAPYB_OK;
   }
-  // Tile width: the widest tile that still yields about a wave of work.
+  // Tile width for single CTAs: waves of tiles x the time of one tile.  A tile's
+  // main loop is load latency per K block, so a narrower tile is only a little
+  // quicker (measured 1.0 : 0.9 : 0.76 for 256 : 128 : 64 columns); it pays when
+  // it saves a wave or fills more SMs in the only wave there is.
   int bn = o.forced_bn;
   if (bn == 0) {
     const long long tm = (p.M + 127) / 128;
-    auto tiles = [&](int w) { return tm * ((p.N + w - 1) / w) * p.batch; };
-    if (tiles(256) >= o.sm_count || p.N > 128 * 16)
-      bn = 256;
-    else if (tiles(128) >= o.sm_count / 2 || p.N > 64 * 16)
-      bn = 128;
-    else
-      bn = 64;
-    if (p.N <= 64) bn = 64;
-    else if (p.N <= 128 && bn > 128) bn = 128;
+    double best = 0.0;
+    const int widths[3] = {256, 128, 64};
+    const double tile_time[3] = {1.0, 0.9, 0.76};
+    for (int i = 0; i < 3; ++i) {
+      const int w = widths[i];
+      if (w > 64 && p.N <= w / 2) continue;  // mostly padding
+      const long long t = tm * ((p.N + w - 1) / w) * p.batch;
+      const double cost = static_cast<double>((t + o.sm_count - 1) / o.sm_count) * tile_time[i];
+      if (bn == 0 || cost < best - 1e-9) {
+        bn = w;
+        best = cost;
+      }
+    }
   }
   // An N-contiguous B arrives in chunks of 128 bytes of N: the columns one CTA
   // loads for one MMA (tile width / column halves / CTAs) have to hold at least
@@ -884,7 +891,10 @@ static kapyb_status plan_decide(const PlanOptions &o, const MatmulProblem &p, vo
         const long long t = static_cast<long long>((p.M + 255) / 256) * ((p.N + w - 1) / w) * p.batch;
         return static_cast<double>(t) / static_cast<double>((t + pairs - 1) / pairs * pairs);
       };
-      bn = (p.N >= 512 && p.K >= 512 && wave_eff(512) >= 0.8 * wave_eff(256)) ? 512 : 256;
+      bn = (p.N >= 512 && p.K >= 1024 && wave_eff(512) >= 0.8 * wave_eff(256)) ? 512 : 256;
+      // less than half a wave of 256-wide pair tiles: 128-wide ones put more SMs to work
+      const long long t256 = static_cast<long long>((p.M + 255) / 256) * ((p.N + 255) / 256) * p.batch;
+      if (bn == 256 && t256 * 2 <= pairs) bn = 128;
     }
     if (bn == 64) bn = 128;
     if (group_cols(bn, 2) < min_cols) bn = 512;

@@ -92,3 +92,11 @@ def test_tuning_table(pkg, tmp_path):
             pkg.tuning_load(str(bad))
     finally:
         pkg.tuning_clear()
+
+
+def test_few_row_problems_spread_over_the_sms(pkg):
+    """One wave of tiles either way: the narrower tile fills more SMs."""
+    assert "tile: 128 x 64" in plan(pkg, 128, 8192, 8192)        # 128 tiles instead of 32
+    assert "tile: 256 x 128" in plan(pkg, 256, 8192, 8192)       # 64 pair tiles instead of 32
+    assert "tile: 256 x 256" in plan(pkg, 8192, 8192, 512)       # K loop too short for the wide tile
+    assert "tile: 128 x 256" in plan(pkg, 8192, 8192, 64)        # many waves: the widest single-CTA tile
