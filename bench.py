@@ -7,8 +7,13 @@ normal(0, 1/sqrt(K)) from a seed; bias uniform[-0.1, 0.1]).
 
 One step = one pass of the hot path over the whole problem.  N > 1 (under
 torchrun) shards the columns of B and of the output across ranks with no
-collective on the data path; the fused push all-gather is timed separately and
-reported under "gather".  Rank 0 prints one JSON line.
+collective on the data path; rank 0 prints one JSON line.  Beside the headline
+the line carries: the same step held for two seconds ("sustained"), the step end
+to end from host buffers ("e2e"; for N > 1 the upload of A is sharded by rows
+and completed over NVLink), the step with the full output assembled on every
+rank ("gather"), the decode-shape and batched configurations sharded the same
+way ("sharded"), and at N = 1 the other single-GPU configurations ("extra"),
+each with the host cores' time for a bounded sample of the same work.
 
 `--impl reference` times the reference's arithmetic on the host cores (the CPU
 restatement under oracle/, since the reference itself stops at a PTX string and
@@ -20,7 +25,6 @@ import argparse
 import json
 import os
 import statistics
-import subprocess
 import sys
 import threading
 import time
@@ -36,10 +40,21 @@ UNIT = "TFLOP/s"
 FLOPS = 2.0 * M * N * K                       # algorithmic FLOPs of one step
 ALG_BYTES = 3 * M * N * 2 + N * 2             # A + B + C (bf16) + bias
 CPU_SAMPLE_ROWS = 512                         # rows of the output the CPU arm computes per step
-# dram__bytes_read.sum + dram__bytes_write.sum of one full-size launch of the
-# dominant kernel, from a one-pass ncu capture of this benchmark (command and
-# figures in profiles/gemm_tcgen05_2cta_256x512_bf16_8192x8192x4096.txt).
-NCU_TRAFFIC_BYTES = 869_611_008 + 151_768_576
+WORKLOAD = ("bf16 GEMM M=N=K=8192 row-major A/B, fp32 accumulate, bf16 out, "
+            "fused per-column bias")
+# dram__bytes_read.sum + dram__bytes_write.sum of one full-size launch, from a
+# one-pass ncu capture of this benchmark; valid for the kernel and tile named
+# here only (profiles/gemm_tcgen05_2cta_256x512_bf16_8192x8192x4096.txt has the
+# command).  The line carries the figure only while the dispatcher still picks
+# that kernel and tile for the benchmark problem.
+NCU_TRAFFIC = {"bytes": 869_611_008 + 151_768_576, "kernel": "tcgen05_2cta",
+               "tile": "256 x 512", "captured_on": "gemm_tcgen05_kernel<512,2,8>, 8192^3 bf16 + bias"}
+
+C4_M, C4_N, C4_K = 16, 28672, 8192
+C4_BYTES = C4_K * C4_N * 2 + C4_M * C4_K * 2 + C4_M * C4_N * 2
+C5_B, C5_M, C5_N, C5_K = 64, 2048, 2048, 128
+C5_BYTES = C5_B * (C5_M * C5_K * 2 + C5_K * C5_N * 2 + C5_M * C5_N * 2)
+C5_FLOPS = 2.0 * C5_B * C5_M * C5_N * C5_K
 
 
 def load_peaks():
@@ -57,8 +72,9 @@ class ClockSampler:
     """Samples SM clocks and throttle reasons through NVML (read-only queries)
     from a thread while the timed region runs."""
 
-    def __init__(self, index: int):
+    def __init__(self, index: int, period: float = 0.002):
         self.index = index
+        self.period = period
         self.samples = []
         self._stop = threading.Event()
         self.thread = None
@@ -92,7 +108,7 @@ class ClockSampler:
                 except Exception:
                     reasons = nv.nvmlDeviceGetCurrentClocksThrottleReasons(hdl)
                 self.samples.append((time.perf_counter(), mhz, reasons))
-                time.sleep(0.002)
+                time.sleep(self.period)
         except Exception as ex:  # NVML missing: report it, do not fail the run
             self.err = repr(ex)
 
@@ -104,7 +120,7 @@ class ClockSampler:
         while not self.samples and self.err is None and time.perf_counter() - t0 < 3.0:
             time.sleep(0.01)
 
-    def stop(self, t_begin=None, t_end=None):
+    def stop(self, t_begin=None, t_end=None, histogram=False):
         self._stop.set()
         if self.thread is not None:
             self.thread.join(timeout=5)
@@ -121,14 +137,21 @@ class ClockSampler:
             for b, name in bits.items():
                 if r & b:
                     seen.add(name)
-        return {"sm_mhz": statistics.median(m for _, m, _ in rows),
-                "sm_max_mhz": getattr(self, "max_mhz", None), "reasons": sorted(seen),
-                "samples": len(rows)}
+        out = {"sm_mhz": statistics.median(m for _, m, _ in rows),
+               "sm_max_mhz": getattr(self, "max_mhz", None), "reasons": sorted(seen),
+               "samples": len(rows)}
+        if histogram:
+            hist = {}
+            for _, m, _ in rows:
+                key = str(int(round(m / 50.0) * 50))
+                hist[key] = hist.get(key, 0) + 1
+            out["samples_by_sm_mhz"] = dict(sorted(hist.items(), key=lambda kv: int(kv[0])))
+        return out
 
 
 def make_inputs(torch, n_cols_begin=0, n_cols_end=N):
-    """Seeded host tensors (pinned).  Every rank draws the full B so that shards
-    are slices of the same matrix whatever the world size."""
+    """Seeded host tensors.  Every rank draws the full B so that shards are
+    slices of the same matrix whatever the world size."""
     g = torch.Generator(device="cpu").manual_seed(SEED)
     A = (torch.randn(M, K, generator=g) * K ** -0.5).to(torch.bfloat16)
     B = (torch.randn(K, N, generator=g) * K ** -0.5).to(torch.bfloat16)
@@ -138,9 +161,23 @@ def make_inputs(torch, n_cols_begin=0, n_cols_end=N):
     return A, B, bias
 
 
+def np_bits(torch, t):
+    import numpy as np
+    return t.contiguous().view(torch.int16).numpy().view(np.uint16)
+
+
 def cpu_step(ko, A_bits, B_bits, bias_bits, rows):
     return ko.matmul_f32acc(A_bits, ko.BF16, B_bits, ko.BF16, ko.BF16, bias=bias_bits,
                             bias_dtype=ko.BF16, row_begin=0, row_end=rows)
+
+
+def load_oracle():
+    """The CPU checker with every host core it may use (a launcher such as
+    torch.distributed.run exports OMP_NUM_THREADS=1 to its children)."""
+    import oracle as ko
+    ko.build()
+    ko.set_num_threads(0)
+    return ko
 
 
 def run_reference(args):
@@ -148,14 +185,11 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    import numpy as np
     import torch
 
-    import oracle as ko
-    ko.build()
+    ko = load_oracle()
     A, B, bias = make_inputs(torch)
-    bits = lambda t: t.view(torch.int16).numpy().view(np.uint16)
-    Ab, Bb, bb = bits(A), bits(B), bits(bias)
+    Ab, Bb, bb = np_bits(torch, A), np_bits(torch, B), np_bits(torch, bias)
     rows = CPU_SAMPLE_ROWS
     for _ in range(max(1, min(args.warmup, 1))):
         cpu_step(ko, Ab, Bb, bb, 32)
@@ -170,8 +204,7 @@ def run_reference(args):
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": "bf16 GEMM M=N=K=8192 row-major A/B, fp32 accumulate, bf16 out, "
-                               "fused per-column bias", "seed": SEED},
+        "config": {"workload": WORKLOAD, "seed": SEED},
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port",
                          "sample": f"rows [0,{rows}) of the {M}x{N} output per step "
                                    f"(all of B and K), OpenMP on {cores} threads"},
@@ -180,24 +213,25 @@ def run_reference(args):
     print(json.dumps(line))
 
 
-def secondary(torch, pkg, h, peaks):
-    """The other single-GPU configurations, timed with the same hygiene (inputs
-    larger than L2 or L2 flushed between iterations), for context."""
-    out = {}
-    abi = pkg.abi
-    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+class Timer:
+    """Device timing with the hygiene the numbers need: warm-up, CUDA events on
+    the launching stream, inputs larger than L2 or an L2 flush before each launch."""
 
-    def timeit(fn, iters=10, flush_l2=False):
-        """Median over 5 samples of `iters` back-to-back launches (one event pair
-        per sample), or of single launches with an L2 flush before each when the
-        working set would otherwise stay in L2."""
-        for _ in range(3):
+    def __init__(self, torch):
+        self.torch = torch
+        self.flush = None
+
+    def __call__(self, fn, iters=10, flush_l2=False, warmup=3):
+        torch = self.torch
+        if flush_l2 and self.flush is None:
+            self.flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+        for _ in range(warmup):
             fn()
         torch.cuda.synchronize()
         ts = []
         for _ in range(5 if not flush_l2 else iters):
             if flush_l2:
-                flush.zero_()
+                self.flush.zero_()
             s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             s.record()
             for _ in range(1 if flush_l2 else iters):
@@ -207,63 +241,284 @@ def secondary(torch, pkg, h, peaks):
             ts.append(s.elapsed_time(e) * 1e-3 / (1 if flush_l2 else iters))
         return statistics.median(ts)
 
+
+def cpu_time(fn, min_s=0.3):
+    """Seconds per call of a CPU function (one warm call, then enough calls for min_s)."""
+    fn()
+    n, t0 = 0, time.perf_counter()
+    while True:
+        fn()
+        n += 1
+        dt = time.perf_counter() - t0
+        if dt >= min_s:
+            return dt / n
+
+
+def secondary(torch, pkg, h, peaks, ko):
+    """The other single-GPU configurations, timed with the same hygiene (inputs
+    larger than L2 or L2 flushed between iterations), each with the host cores'
+    time for a bounded sample of the same work beside it."""
+    import numpy as np
+    out = {}
+    abi = pkg.abi
+    timeit = Timer(torch)
+    cores = ko.num_threads()
+    hbm = peaks["hbm_gbs"]
+
     g = torch.Generator(device="cpu").manual_seed(1003)
     n = 1 << 28
-    x = torch.randn(1 << 24, generator=g).to(torch.bfloat16).cuda().repeat(16).view(1, n)
+    x_host = torch.randn(1 << 24, generator=g).to(torch.bfloat16)
+    x = x_host.cuda().repeat(16).view(1, n)
     y = torch.empty_like(x)
     prog = pkg.programs.affine_gelu_tanh(abi.BF16, 0.5, 0.1)
     t = timeit(lambda: h.elementwise(prog, [x], y))
     gbs = n * 4 / t / 1e9
-    out["gelu_tanh_affine_2^28_bf16"] = {"GB/s": gbs, "frac_of_measured_hbm": gbs / peaks["hbm_gbs"],
-                                         "ms": t * 1e3, "kernel": h.last_kernel}
+    xb = np_bits(torch, x_host)
+    tc = cpu_time(lambda: ko.affine_gelu_bf16(xb, 0.5, 0.1))
+    out["gelu_tanh_affine_2^28_bf16"] = {
+        "GB/s": gbs, "frac_of_measured_hbm": gbs / hbm, "ms": t * 1e3, "kernel": h.last_kernel,
+        "cpu_baseline": {"value": xb.size * 4 / tc / 1e9, "unit": "GB/s", "cores": cores,
+                         "kind": "port", "sample": "2^24 of the 2^28 elements"}}
     prog_lin = pkg.programs.affine(abi.BF16, 0.5, 0.1)
     t = timeit(lambda: h.elementwise(prog_lin, [x], y))
     gbs = n * 4 / t / 1e9
-    out["affine_2^28_bf16"] = {"GB/s": gbs, "frac_of_measured_hbm": gbs / peaks["hbm_gbs"],
-                               "ms": t * 1e3, "kernel": h.last_kernel}
+    tc = cpu_time(lambda: ko.affine_gelu_bf16(xb, 0.5, 0.1, linear_only=True))
+    out["affine_2^28_bf16"] = {
+        "GB/s": gbs, "frac_of_measured_hbm": gbs / hbm, "ms": t * 1e3, "kernel": h.last_kernel,
+        "cpu_baseline": {"value": xb.size * 4 / tc / 1e9, "unit": "GB/s", "cores": cores,
+                         "kind": "port", "sample": "2^24 of the 2^28 elements"}}
     del y
     X = x.view(65536, 4096)
     s = torch.empty((65536, 1), dtype=torch.float32, device="cuda")
     t = timeit(lambda: h.reduce(X, axis=1, out=s))
     gbs = (65536 * 4096 * 2 + 65536 * 4) / t / 1e9
-    out["rowsum_65536x4096_bf16"] = {"GB/s": gbs, "frac_of_measured_hbm": gbs / peaks["hbm_gbs"],
-                                     "ms": t * 1e3, "kernel": h.last_kernel}
+    xr = xb.reshape(4096, 4096)
+    tc = cpu_time(lambda: ko.rowsum_bf16_f32(xr))
+    out["rowsum_65536x4096_bf16"] = {
+        "GB/s": gbs, "frac_of_measured_hbm": gbs / hbm, "ms": t * 1e3, "kernel": h.last_kernel,
+        "cpu_baseline": {"value": (xr.size * 2 + 4096 * 4) / tc / 1e9, "unit": "GB/s", "cores": cores,
+                         "kind": "port", "sample": "4096 of the 65536 rows"}}
     del x, X, s
     # decode shape: M=16, N=28672, K=8192 (weights 470 MB > L2)
-    Xs = torch.randn(16, 8192, generator=g).to(torch.bfloat16).cuda()
-    W = (torch.randn(8192, 28672 // 8, generator=g) * 0.02).to(torch.bfloat16).cuda().repeat(1, 8)
-    o = torch.empty((16, 28672), dtype=torch.bfloat16, device="cuda")
+    Xs_h = torch.randn(C4_M, C4_K, generator=g).to(torch.bfloat16)
+    W_h = (torch.randn(C4_K, C4_N // 8, generator=g) * 0.02).to(torch.bfloat16)
+    Xs, W = Xs_h.cuda(), W_h.cuda().repeat(1, 8)
+    o = torch.empty((C4_M, C4_N), dtype=torch.bfloat16, device="cuda")
     t = timeit(lambda: h.matmul(Xs, W, out=o))
-    gbs = 470941696 / t / 1e9
-    out["decode_16x28672x8192_bf16"] = {"GB/s": gbs, "frac_of_measured_hbm": gbs / peaks["hbm_gbs"],
-                                        "ms": t * 1e3, "kernel": h.last_kernel}
+    gbs = C4_BYTES / t / 1e9
     # the vendor library on the same buffers, for context only (not on the product path)
     t_lib = timeit(lambda: torch.mm(Xs, W, out=o))
-    out["decode_16x28672x8192_bf16"]["library_torch_mm_GB/s"] = 470941696 / t_lib / 1e9
+    wcols = 1024
+    Xb, Wb = np_bits(torch, Xs_h), np_bits(torch, W_h[:, :wcols])
+    tc = cpu_time(lambda: ko.matmul_f32acc(Xb, ko.BF16, Wb, ko.BF16, ko.BF16))
+    out["decode_16x28672x8192_bf16"] = {
+        "GB/s": gbs, "frac_of_measured_hbm": gbs / hbm, "ms": t * 1e3, "kernel": h.last_kernel,
+        "library_torch_mm_GB/s": C4_BYTES / t_lib / 1e9,
+        "cpu_baseline": {"value": (C4_K * wcols * 2 + C4_M * C4_K * 2 + C4_M * wcols * 2) / tc / 1e9,
+                         "unit": "GB/s", "cores": cores, "kind": "port",
+                         "sample": f"{wcols} of the 28672 weight columns"}}
     del W, o
     # attention-score shape: batch 64 x 2048 x 2048 x 128, alpha = 1/sqrt(128)
-    Q = torch.randn(8, 2048, 128, generator=g).to(torch.bfloat16).cuda().repeat(8, 1, 1)
-    Kt = torch.randn(8, 128, 2048, generator=g).to(torch.bfloat16).cuda().repeat(8, 1, 1)
-    S = torch.empty((64, 2048, 2048), dtype=torch.bfloat16, device="cuda")
+    Q_h = torch.randn(8, C5_M, C5_K, generator=g).to(torch.bfloat16)
+    Kt_h = torch.randn(8, C5_K, C5_N, generator=g).to(torch.bfloat16)
+    Q, Kt = Q_h.cuda().repeat(8, 1, 1), Kt_h.cuda().repeat(8, 1, 1)
+    S = torch.empty((C5_B, C5_M, C5_N), dtype=torch.bfloat16, device="cuda")
     t = timeit(lambda: h.matmul(Q, Kt, out=S, alpha=128 ** -0.5))
-    gbs = 603979776 / t / 1e9
-    out["batched_64x2048x2048x128_bf16"] = {"GB/s": gbs, "TFLOP/s": 6.872e10 / t / 1e12,
-                                            "frac_of_measured_hbm": gbs / peaks["hbm_gbs"],
-                                            "ms": t * 1e3, "kernel": h.last_kernel}
+    gbs = C5_BYTES / t / 1e9
     # write-dominated (512 MiB out of 576 MiB): a plain fill of the output and the vendor
     # library's batched matmul on the same buffers, for context only
     t_fill = timeit(lambda: S.zero_())
-    out["batched_64x2048x2048x128_bf16"]["fill_of_the_output_GB/s"] = S.numel() * 2 / t_fill / 1e9
     t_lib = timeit(lambda: torch.bmm(Q, Kt, out=S))
-    out["batched_64x2048x2048x128_bf16"]["library_torch_bmm_GB/s"] = 603979776 / t_lib / 1e9
+    qb, kb = np_bits(torch, Q_h[0, :512]), np_bits(torch, Kt_h[0])
+    tc = cpu_time(lambda: ko.matmul_f32acc(qb, ko.BF16, kb, ko.BF16, ko.BF16, alpha=128 ** -0.5))
+    out["batched_64x2048x2048x128_bf16"] = {
+        "GB/s": gbs, "TFLOP/s": C5_FLOPS / t / 1e12, "frac_of_measured_hbm": gbs / hbm,
+        "ms": t * 1e3, "kernel": h.last_kernel,
+        "fill_of_the_output_GB/s": S.numel() * 2 / t_fill / 1e9,
+        "library_torch_bmm_GB/s": C5_BYTES / t_lib / 1e9,
+        "cpu_baseline": {"value": (512 * C5_K * 2 + C5_K * C5_N * 2 + 512 * C5_N * 2) / tc / 1e9,
+                         "unit": "GB/s", "cores": cores, "kind": "port",
+                         "sample": "512 rows of one of the 64 batch entries"}}
     del Q, Kt, S
     # fp16 1024^3 with column-major B: launch-latency scale, absolute time only
-    A1 = (torch.rand(1024, 1024, generator=g) * 2 - 1).to(torch.float16).cuda()
-    B1 = (torch.rand(1024, 1024, generator=g) * 2 - 1).to(torch.float16).cuda().t()
+    A1_h = (torch.rand(1024, 1024, generator=g) * 2 - 1).to(torch.float16)
+    B1_h = (torch.rand(1024, 1024, generator=g) * 2 - 1).to(torch.float16)
+    A1, B1 = A1_h.cuda(), B1_h.cuda().t()
     C1 = torch.empty((1024, 1024), dtype=torch.float16, device="cuda")
     t = timeit(lambda: h.matmul(A1, B1, out=C1), iters=20, flush_l2=True)
-    out["fp16_1024^3_colmajorB"] = {"us": t * 1e6, "TFLOP/s": 2.147e9 / t / 1e12,
-                                    "kernel": h.last_kernel}
+    kern = h.last_kernel
+    t_lib = timeit(lambda: torch.mm(A1, B1, out=C1), iters=20, flush_l2=True)
+    a1b = np_bits(torch, A1_h[:256])
+    b1b = np_bits(torch, B1_h).T          # the same column-major view the GPU multiplies by
+    tc = cpu_time(lambda: ko.matmul_f32acc(a1b, ko.F16, b1b, ko.F16, ko.F16))
+    out["fp16_1024^3_colmajorB"] = {
+        "us": t * 1e6, "TFLOP/s": 2.147e9 / t / 1e12, "kernel": kern,
+        "library_torch_mm_us": t_lib * 1e6,
+        "cpu_baseline": {"value": 2.0 * 256 * 1024 * 1024 / tc / 1e12, "unit": "TFLOP/s",
+                         "cores": cores, "kind": "port", "sample": "256 of the 1024 rows"}}
+    h.check()
+    return out
+
+
+def sustained_run(torch, h, step, sec_per_step, rank, local, peaks, seconds=2.2):
+    """The same step back to back for at least two seconds: TFLOP/s over the last
+    second, NVML clock samples binned by clock, and the SM clock the kernel itself
+    measured right afterwards, while the GPU is still at that operating point."""
+    per_batch = max(1, int(0.04 / sec_per_step))
+    batches = max(3, int(seconds / (per_batch * sec_per_step)) + 1)
+    sampler = ClockSampler(local, period=0.01)
+    if rank == 0:
+        sampler.start()
+    evs = [torch.cuda.Event(enable_timing=True) for _ in range(batches + 1)]
+    t_begin = time.perf_counter()
+    evs[0].record()
+    for b in range(batches):
+        for _ in range(per_batch):
+            step()
+        evs[b + 1].record()
+    evs[-1].synchronize()
+    t_end = time.perf_counter()
+    # in-kernel clock: a short continuation with the kernel's own probe switched on
+    mhz = None
+    try:
+        h.set_matmul_path("auto:d128")
+        for _ in range(per_batch):
+            step()
+        cyc, ns = h.probe_clock()
+        if ns:
+            mhz = cyc / ns * 1e3
+    finally:
+        h.set_matmul_path("auto")
+    clocks = sampler.stop(t_begin, t_end, histogram=True) if rank == 0 else None
+    total_s = evs[0].elapsed_time(evs[-1]) * 1e-3
+    # last second: the latest event at least one second before the end
+    k = batches
+    while k > 0 and evs[k].elapsed_time(evs[-1]) * 1e-3 < 1.0:
+        k -= 1
+    tail_s = evs[k].elapsed_time(evs[-1]) * 1e-3
+    tail_steps = (batches - k) * per_batch
+    rate = FLOPS / (tail_s / tail_steps) / 1e12 if tail_steps else None
+    return {"seconds": total_s, "steps": batches * per_batch, "value_last_second": rate,
+            "value_whole_run": FLOPS / (total_s / (batches * per_batch)) / 1e12, "unit": UNIT,
+            "sm_mhz_in_kernel": round(mhz, 1) if mhz else None, "clocks": clocks,
+            "peak": peaks["bf16_sustained"],
+            "peak_kind": "sustained cuBLAS bf16, " + peaks["source"]}, rate
+
+
+def sharded_configs(torch, dist, pkg, h, ko, peaks, world, rank, barrier):
+    """The decode-shape GEMM sharded by weight columns and the batched GEMM
+    sharded by batch: device time (max over ranks), bandwidth per GPU against the
+    measured copy rate, a spot check of this rank's block against the f64
+    checker, and for the decode shape the time to assemble the full output."""
+    import numpy as np
+    out = {}
+    hbm = peaks["hbm_gbs"]
+
+    def timed(fn, iters=10):
+        for _ in range(3):
+            fn()
+        barrier()
+        ts = []
+        for _ in range(5):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(iters):
+                fn()
+            b.record()
+            b.synchronize()
+            ts.append(a.elapsed_time(b) * 1e-3 / iters)
+        t = torch.tensor([statistics.median(ts)], device="cuda")
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def all_true(ok: bool) -> bool:
+        t = torch.tensor([1 if ok else 0], device="cuda")
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        return bool(t.item())
+
+    # ---- decode shape, weight columns dealt in blocks of 128
+    spans = pkg.dist.column_shards(C4_N, world, 128)
+    c0, c1 = spans[rank]
+    n_loc = c1 - c0
+    g = torch.Generator(device="cpu").manual_seed(1005)
+    X_h = torch.randn(C4_M, C4_K, generator=g).to(torch.bfloat16)
+    gw = torch.Generator(device="cpu").manual_seed(2005 + rank)
+    blk = min(n_loc, 3584)
+    W_blk = (torch.randn(C4_K, blk, generator=gw) * 0.02).to(torch.bfloat16)
+    reps = (n_loc + blk - 1) // blk
+    X = X_h.cuda()
+    W = W_blk.cuda().repeat(1, reps)[:, :n_loc].contiguous()
+    o = torch.empty((C4_M, n_loc), dtype=torch.bfloat16, device="cuda")
+    # a shard smaller than L2 would be timed out of cache: flush before each launch then
+    shard_bytes = C4_K * n_loc * 2 + C4_M * C4_K * 2 + C4_M * n_loc * 2
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda") if shard_bytes < (200 << 20) else None
+
+    def c4_step():
+        if flush is not None:
+            flush.zero_()
+        h.matmul(X, W, out=o)
+    t = timed(c4_step)
+    if flush is not None:
+        t_flush = timed(lambda: flush.zero_())
+        t = max(t - t_flush, 1e-9)
+    kern = h.last_kernel
+    cols = np.unique(np.concatenate([np.arange(0, min(128, n_loc)), np.arange(max(0, n_loc - 128), n_loc)]))
+    ref = ko.matmul_f64(np_bits(torch, X_h), ko.BF16, np_bits(torch, W.cpu()), ko.BF16,
+                        cols=cols.astype(np.int32))
+    got = ko.from_bits(np_bits(torch, o.cpu()[:, cols]), ko.BF16)
+    err, _ = ko.max_rel_err(got, ref)
+    entry = {"ms_per_step": t * 1e3, "columns_per_gpu": n_loc, "kernel": kern,
+             "GB/s_per_gpu": shard_bytes / t / 1e9, "frac_of_measured_hbm": shard_bytes / t / 1e9 / hbm,
+             "GB/s_all_gpus": C4_BYTES / t / 1e9 if world > 1 else shard_bytes / t / 1e9,
+             "l2": "flushed before each launch" if flush is not None else "shard larger than L2",
+             "max_rel_err_vs_f64": err, "parity_ok_all_ranks": all_true(err <= 1e-2)}
+    if world > 1:
+        full = torch.empty((C4_M, C4_N), dtype=torch.bfloat16, device="cuda")
+        tg = timed(lambda: pkg.dist.all_gather_columns(o, spans, out=full))
+        entry["all_gather_of_the_output_us"] = tg * 1e6
+        entry["gather_matches_local_block"] = all_true(bool(torch.equal(full[:, c0:c1], o)))
+        del full
+    out["decode_16x28672x8192_bf16_column_sharded"] = entry
+    del W, o, flush
+
+    # ---- batched shape, batch entries dealt to the ranks
+    b0, b1 = pkg.dist.batch_shards(C5_B, world)[rank]
+    nb = b1 - b0
+    gq = torch.Generator(device="cpu").manual_seed(1006 + rank)
+    distinct = min(nb, 8)
+    Q_h = torch.randn(distinct, C5_M, C5_K, generator=gq).to(torch.bfloat16)
+    Kt_h = torch.randn(distinct, C5_K, C5_N, generator=gq).to(torch.bfloat16)
+    reps = (nb + distinct - 1) // distinct
+    Q = Q_h.cuda().repeat(reps, 1, 1)[:nb].contiguous()
+    Kt = Kt_h.cuda().repeat(reps, 1, 1)[:nb].contiguous()
+    S = torch.empty((nb, C5_M, C5_N), dtype=torch.bfloat16, device="cuda")
+    per_gpu_bytes = C5_BYTES // C5_B * nb
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda") if per_gpu_bytes < (200 << 20) else None
+
+    def c5_step():
+        if flush is not None:
+            flush.zero_()
+        h.matmul(Q, Kt, out=S, alpha=128 ** -0.5)
+    t = timed(c5_step)
+    if flush is not None:
+        t = max(t - timed(lambda: flush.zero_()), 1e-9)
+    kern = h.last_kernel
+    rows = np.arange(0, C5_M, 37, dtype=np.int32)
+    worst = 0.0
+    for e in range(distinct):
+        ref = ko.matmul_f64(np_bits(torch, Q_h[e]), ko.BF16, np_bits(torch, Kt_h[e]), ko.BF16,
+                            alpha=128 ** -0.5, rows=rows)
+        got = ko.from_bits(np_bits(torch, S[e].cpu()[rows]), ko.BF16)
+        worst = max(worst, ko.max_rel_err(got, ref)[0])
+    out["batched_64x2048x2048x128_bf16_batch_sharded"] = {
+        "ms_per_step": t * 1e3, "batch_entries_per_gpu": nb, "kernel": kern,
+        "GB/s_per_gpu": per_gpu_bytes / t / 1e9, "frac_of_measured_hbm": per_gpu_bytes / t / 1e9 / hbm,
+        "GB/s_all_gpus": C5_BYTES / t / 1e9, "TFLOP/s_all_gpus": C5_FLOPS / t / 1e12,
+        "l2": "flushed before each launch" if flush is not None else "shard larger than L2",
+        "max_rel_err_vs_f64": worst, "parity_ok_all_ranks": all_true(worst <= 1e-2),
+        "collective": "none (outputs stay with their batch entries)"}
     h.check()
     return out
 
@@ -293,8 +548,11 @@ def run_ours(args):
 
     c0, c1 = pkg.shard_range(N, world, rank, 256)
     A, Bs, bias = make_inputs(torch, c0, c1)
-    A_pin, B_pin, bias_pin = A.pin_memory(), Bs.pin_memory(), bias.pin_memory()
-    Ad, Bd, bd = A_pin.cuda(non_blocking=True), B_pin.cuda(non_blocking=True), bias_pin.cuda(non_blocking=True)
+    r0, r1 = pkg.shard_range(M, world, rank, 256)
+    A_pin = (A if world == 1 else A[r0:r1].contiguous()).pin_memory()
+    B_pin, bias_pin = Bs.pin_memory(), bias.pin_memory()
+    Ad = A.cuda()
+    Bd, bd = B_pin.cuda(non_blocking=True), bias_pin.cuda(non_blocking=True)
     Cd = torch.empty((M, c1 - c0), dtype=torch.bfloat16, device="cuda")
     torch.cuda.synchronize()
 
@@ -309,6 +567,7 @@ def run_ours(args):
     for _ in range(max(3, args.warmup)):
         step()
     h.check()
+    main_kernel = h.last_kernel
     barrier()
     sampler = ClockSampler(local)
     if rank == 0:
@@ -350,15 +609,37 @@ def run_ours(args):
         finally:
             h.set_matmul_path("auto")
 
+    # ---- the same step held for two seconds (every rank runs it; rank 0 reports)
+    sustained = None
+    if not args.no_sustained:
+        barrier()
+        sustained, rate = sustained_run(torch, h, step, sec_per_step, rank, local, peaks)
+        if world > 1:
+            t = torch.tensor([rate or 0.0], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MIN)      # the slowest rank sets the job's rate
+            rate = float(t.item())
+            sustained["value_last_second"] = rate
+        sustained["per_gpu_value"] = (rate or 0.0) / world
+        sustained["frac"] = (rate or 0.0) / world / peaks["bf16_sustained"]
+        barrier()
+
     # ---- end to end through the host-buffer C-ABI call (pinned host memory in,
-    # pinned host memory out, copies inside the timed region)
+    # pinned host memory out, copies inside the timed region).  N > 1: each rank
+    # uploads its own rows of A and its column block of B; the rows of A reach the
+    # other GPUs over NVLink inside the call.
     C_pin = torch.empty((M, c1 - c0), dtype=torch.bfloat16).pin_memory()
-    h.matmul_host(A_pin, B_pin, C_pin, bias=bias_pin)
+    if world == 1:
+        host_step = lambda: h.matmul_host(A_pin, B_pin, C_pin, bias=bias_pin)
+    else:
+        shm = pkg.dist.ShardedHostMatmul(M, K, torch.bfloat16, torch.device("cuda", local))
+        assert shm.rows == (r0, r1)
+        host_step = lambda: shm(h, A_pin, B_pin, C_pin, bias=bias_pin)
+    host_step()
     e2e_steps = max(2, min(args.steps, 5))
     barrier()
     t0 = time.perf_counter()
     for _ in range(e2e_steps):
-        h.matmul_host(A_pin, B_pin, C_pin, bias=bias_pin)
+        host_step()
     torch.cuda.synchronize()
     e2e_t = (time.perf_counter() - t0) / e2e_steps
     if world > 1:
@@ -367,9 +648,22 @@ def run_ours(args):
         e2e_t = float(t.item())
     h2d = A_pin.numel() * 2 + B_pin.numel() * 2 + bias_pin.numel() * 2
     d2h = C_pin.numel() * 2
-    e2e = {"value": FLOPS / e2e_t / 1e12, "unit": UNIT, "h2d_bytes_per_step": h2d,
-           "d2h_bytes_per_step": d2h, "ms_per_step": e2e_t * 1e3}
-    assert torch.equal(C_pin, Cd.cpu()), "host-buffer call and device call disagree"
+    same = bool(torch.equal(C_pin, Cd.cpu()))
+    if world > 1:
+        t = torch.tensor([h2d, d2h, 1 if same else 0], device="cuda", dtype=torch.int64)
+        tmin = t.clone()
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        dist.all_reduce(tmin, op=dist.ReduceOp.MIN)
+        h2d_all, d2h_all, same = int(t[0]), int(t[1]), bool(tmin[2].item())
+    else:
+        h2d_all, d2h_all = h2d, d2h
+    e2e = {"value": FLOPS / e2e_t / 1e12, "unit": UNIT, "h2d_bytes_per_step": h2d_all,
+           "d2h_bytes_per_step": d2h_all, "ms_per_step": e2e_t * 1e3,
+           "h2d_bytes_per_step_per_gpu": h2d, "d2h_bytes_per_step_per_gpu": d2h,
+           "call": "kapyb_matmul_host" if world == 1 else
+                   "kapyb_matmul_host_sharded (rows of A uploaded once per box, completed over NVLink)",
+           "equals_device_path": same}
+    assert same, "host-buffer call and device call disagree"
 
     # ---- N > 1: the same step with the full output assembled on every rank
     gather = None
@@ -393,6 +687,7 @@ def run_ours(args):
             return float(t.item())
 
         iters = max(2, min(args.steps, 10))
+        full = None
         try:
             full = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
 
@@ -401,9 +696,9 @@ def run_ours(args):
                 pkg.dist.all_gather_columns(Cd, spans, out=full)
             tn = timed(nccl_step, iters)
             gather["nccl_all_gather"] = {"value": FLOPS / tn / 1e12, "unit": UNIT, "ms_per_step": tn * 1e3}
-            del full
         except Exception as ex:  # report, keep the main number
             gather["nccl_all_gather"] = {"error": repr(ex)[:200]}
+            full = None
         try:
             pg = pkg.dist.PushGather(M, N, torch.bfloat16, torch.device("cuda", local))
 
@@ -412,46 +707,67 @@ def run_ours(args):
                 pg.wait()
             tp = timed(push_step, iters)
             h.check()
-            ok = bool(torch.equal(pg.full[:, c0:c1], Cd))
+            # every block of the assembled matrix, local and remote, bit for bit
+            # against the NCCL-gathered one, on every rank
+            ok = bool(torch.equal(pg.full, full)) if full is not None else False
+            t = torch.tensor([1 if ok else 0], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MIN)
             gather["fused_push"] = {"value": FLOPS / tp / 1e12, "unit": UNIT, "ms_per_step": tp * 1e3,
-                                    "matches_local_shard": ok}
+                                    "matches_full": bool(t.item()),
+                                    "completion": "kapyb_gather_signal / kapyb_gather_wait (bounded)"}
         except Exception as ex:
             gather["fused_push"] = {"error": repr(ex)[:200]}
+        del full
+
+    del Ad, Bd
+    torch.cuda.empty_cache()
+    ko = load_oracle()
+    sharded = None
+    if world > 1 or args.sharded:
+        try:
+            sharded = sharded_configs(torch, dist, pkg, h, ko, peaks, world, rank, barrier)
+        except Exception as ex:
+            sharded = {"error": repr(ex)[:300]}
 
     line = None
     if rank == 0:
         long_run = elapsed > 1.0
         peak = peaks["bf16_sustained"] if long_run else peaks["bf16_burst"]
         per_gpu = value / world
+        # the captured traffic figure belongs to one kernel and tile on the full problem
+        plan = pkg.matmul_plan(M, c1 - c0, K, handle=h)
+        traffic = NCU_TRAFFIC["bytes"] if (world == 1 and main_kernel == NCU_TRAFFIC["kernel"]
+                                           and NCU_TRAFFIC["tile"] in plan) else None
         roofline = {"bound": "tensor", "achieved": per_gpu, "peak": peak, "unit": UNIT,
                     "frac": per_gpu / peak,
                     "peak_kind": ("sustained" if long_run else "burst") + " cuBLAS bf16, " +
                                  peaks["source"],
                     "frac_of_nominal_2250": per_gpu / 2250.0,
-                    "traffic": NCU_TRAFFIC_BYTES, "algorithmic_bytes": ALG_BYTES,
-                    "kernel": h.last_kernel}
+                    "traffic": traffic, "traffic_captured_on": NCU_TRAFFIC["captured_on"],
+                    "algorithmic_bytes": ALG_BYTES, "kernel": main_kernel,
+                    "plan": plan.splitlines()[1] if len(plan.splitlines()) > 1 else plan}
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world,
             "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": sec_per_step * 1e3,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": "bf16 GEMM M=N=K=8192 row-major A/B, fp32 accumulate, bf16 out, "
-                                   "fused per-column bias", "seed": SEED,
-                       "sharding": f"columns of B and C over {world} rank(s), no collective",
+            "config": {"workload": WORKLOAD, "seed": SEED},
+            "layout": {"sharding": f"columns of B and C over {world} rank(s), no collective",
                        "l2": "A+B+C = 384 MiB per step, larger than the 126 MB L2"},
             "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks, "roofline": roofline,
         }
+        if sustained is not None:
+            line["sustained"] = sustained
         if gather is not None:
             line["gather"] = gather
+        if sharded is not None:
+            line["sharded"] = sharded
 
     # ---- CPU baseline: the checker's fp32-accumulate port on a bounded row sample
     if rank == 0 and world == 1:
         import numpy as np
 
-        import oracle as ko
-        ko.build()
-        bits = lambda t: t.view(torch.int16).numpy().view(np.uint16)
-        Ab, Bb, bb = bits(A), bits(Bs), bits(bias)
+        Ab, Bb, bb = np_bits(torch, A), np_bits(torch, Bs), np_bits(torch, bias)
         cpu_step(ko, Ab, Bb, bb, 32)
         t0 = time.perf_counter()
         got = cpu_step(ko, Ab, Bb, bb, CPU_SAMPLE_ROWS)
@@ -467,9 +783,9 @@ def run_ours(args):
         cpu = torch.from_numpy(got[:CPU_SAMPLE_ROWS].view(np.int16)).view(torch.bfloat16).float()
         line["cpu_baseline"]["max_abs_diff_vs_gpu"] = float((dev - cpu).abs().max())
         if not args.no_extra:
-            del Ad, Bd, Cd
+            del Cd
             torch.cuda.empty_cache()
-            line["extra"] = secondary(torch, pkg, h, peaks)
+            line["extra"] = secondary(torch, pkg, h, peaks, ko)
 
     if world > 1:
         dist.barrier()
@@ -535,6 +851,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--path", default="", help="force a matmul kernel family (tests/profiling)")
     ap.add_argument("--no-extra", action="store_true", help="skip the secondary configurations")
+    ap.add_argument("--no-sustained", action="store_true", help="skip the two-second run")
+    ap.add_argument("--sharded", action="store_true",
+                    help="run the sharded decode / batched configurations at one GPU too")
     ap.add_argument("--profile-case", default="",
                     help="gemm|gelu|rowsum|decode|batched: a small case for a profiler capture")
     args = ap.parse_args()

@@ -45,7 +45,8 @@ typedef enum {
   KAPYB_INVALID_ARG = 1, /* verifier-equivalent rejection (Kapy.cpp:451-574) */
   KAPYB_UNSUPPORTED = 2,
   KAPYB_CUDA_ERROR = 3,
-  KAPYB_NCCL_ERROR = 4,
+  /* 4 is not used: the library calls no communication library; ranks meet
+   * through the flags of kapyb_gather_signal / kapyb_gather_wait */
   KAPYB_TIMEOUT = 5      /* a bounded device-side wait gave up */
 } kapyb_status;
 
@@ -59,7 +60,11 @@ typedef enum {
    * nothing computes in them.  f8E4M3 bytes are read the way the MMA and cvt
    * instructions read them: finite-only, S.1111.111 is NaN, largest value 448. */
   KAPYB_F8E4M3 = 3,
-  KAPYB_F8E5M2 = 4
+  KAPYB_F8E5M2 = 4,
+  /* i1, the result type of arith.cmpf (ir.cc:941-1000): a value inside an
+   * elementwise program only (the condition of a select); no tensor in memory
+   * has it. */
+  KAPYB_I1 = 5
 } kapyb_dtype;
 
 /* Enums.td:52-61 -- value returned for out-of-bounds lanes of ld_global. */
@@ -120,7 +125,9 @@ typedef struct {
   int32_t size0, size1;
   int32_t stride0, stride1;
   int32_t dtype; /* kapyb_dtype */
-  int32_t padding; /* kapyb_padding, used by elementwise loads only */
+  int32_t padding; /* kapyb_padding: what an elementwise load returns out of bounds.
+                      Matmul operands take KAPYB_PAD_ZERO only (anything else is
+                      refused with KAPYB_UNSUPPORTED); outputs ignore it. */
 } kapyb_tensor2d;
 
 /* result = downcast(act(alpha * (lhs . rhs) + bias [+ acc])).
@@ -174,8 +181,32 @@ typedef enum {
   KAPYB_OP_CEIL = 25,
   KAPYB_OP_TANH = 26,  /* elementwise_extern_lib "__nv_tanhf" (Ops.td:459-484) */
   KAPYB_OP_STORE = 27, /* output = a                      (kapy.st_global) */
+  KAPYB_OP_CMP = 28,   /* dst(i1) = a <pred> b, flags = kapyb_cmp_predicate (arith.cmpf;
+                          Builder.create_cmpf_*, ir.cc:941-1000); dtype = KAPYB_I1 */
+  KAPYB_OP_SELECT = 29, /* dst = a(i1) ? b : c            (arith.select, ir.cc:1162) */
+  KAPYB_OP_AND = 30,   /* i1 logic on conditions          (arith.andi / ori / xori on i1) */
+  KAPYB_OP_OR = 31,
+  KAPYB_OP_XOR = 32,
   KAPYB_OP_COUNT_
 } kapyb_opcode;
+
+/* Predicates of arith.cmpf as Builder.create_cmpf_* binds them (ir.cc:941-1000).
+ * "Ordered" predicates are false when either operand is NaN, "unordered" ones
+ * true. */
+typedef enum {
+  KAPYB_CMP_OLT = 0,
+  KAPYB_CMP_OGT = 1,
+  KAPYB_CMP_OLE = 2,
+  KAPYB_CMP_OGE = 3,
+  KAPYB_CMP_OEQ = 4,
+  KAPYB_CMP_ONE = 5,
+  KAPYB_CMP_ULT = 6,
+  KAPYB_CMP_UGT = 7,
+  KAPYB_CMP_ULE = 8,
+  KAPYB_CMP_UGE = 9,
+  KAPYB_CMP_UEQ = 10,
+  KAPYB_CMP_UNE = 11
+} kapyb_cmp_predicate;
 
 #define KAPYB_MAX_REGS 16
 #define KAPYB_MAX_INSTS 64
@@ -213,7 +244,10 @@ KAPYB_API kapyb_status kapyb_destroy(kapyb_handle h);
 KAPYB_API const char *kapyb_last_error_string(kapyb_handle h);
 
 /* Synchronises `stream` and reports what the device recorded: KAPYB_TIMEOUT if
- * a kernel gave up on a bounded wait, KAPYB_CUDA_ERROR on a sticky error. */
+ * a kernel gave up on a bounded wait, KAPYB_CUDA_ERROR on a sticky error.  A
+ * decode-shape matmul that gave up leaves its tile counters in the handle's
+ * workspace half counted; this call clears them, so call it after any launch
+ * that may have timed out and before the next decode-shape matmul on `h`. */
 KAPYB_API kapyb_status kapyb_check(kapyb_handle h, void *stream);
 
 /* Grows the handle's device workspace (split-K partials, host-call staging) to
@@ -273,6 +307,54 @@ KAPYB_API kapyb_status kapyb_matmul_push(
     int32_t out_stride0, int32_t col_begin, int32_t n_total,
     const kapyb_epilogue *epilogue, int32_t impl_way, void *stream);
 
+/* Completion flags between the GPUs of one box; no reference counterpart (the
+ * reference has no multi-GPU code).  Every rank owns an array of n_ranks 32-bit
+ * words in memory all ranks can reach (peer-mapped device memory, or pinned
+ * host memory), zero at the start.  kapyb_gather_signal stores `seq` into word
+ * my_rank of EVERY rank's array (peer_flags[r] = rank r's array), ordered after
+ * everything issued on `stream` before it; kapyb_gather_wait returns (on
+ * `stream`) once every word of this rank's own array has reached `seq` (wrapping
+ * comparison; start at 1 and count up).  Only stores cross the link.  The wait
+ * polls for at most limit_ms (0 = 2000): when that runs out the kernel gives
+ * up, later work on the stream still runs, and kapyb_check returns
+ * KAPYB_TIMEOUT.  A rank must order its own signal before its wait (same stream,
+ * or an event): the wait is never the only thing keeping a kernel of the same
+ * GPU from running. */
+KAPYB_API kapyb_status kapyb_gather_signal(kapyb_handle h, void *const *peer_flags,
+                                           int32_t n_ranks, int32_t my_rank, uint32_t seq,
+                                           void *stream);
+KAPYB_API kapyb_status kapyb_gather_wait(kapyb_handle h, const void *my_flags, int32_t n_ranks,
+                                         uint32_t seq, uint32_t limit_ms, void *stream);
+
+/* What a rank needs to meet its peers in kapyb_matmul_host_sharded. */
+typedef struct {
+  int32_t rank, world;
+  /* [world] device pointers, entry r = rank r's staging area for the whole lhs,
+   * reachable from this GPU (entry [rank] is this GPU's own memory).  Each area
+   * holds TWO copies of [m_total, K], the second starting roundup256(m_total *
+   * K * element size) bytes after the first; calls use them in turn (seq & 1). */
+  void *const *peer_lhs;
+  /* [world] device pointers to every rank's flag array (kapyb_gather_signal). */
+  void *const *peer_flags;
+  uint32_t seq;           /* 1 for the first call, then +1 per call, the same on all ranks */
+  uint32_t wait_limit_ms; /* 0: 2000 */
+} kapyb_shard_ctx;
+
+/* kapyb_matmul_host for `world` GPUs that share one problem: the output is
+ * sharded by columns (this rank computes out[m_total, n_local] = lhs . rhs with
+ * rhs its own [K, n_local] column block of B), and the upload of lhs is sharded
+ * by rows: this rank uploads only rows [row_begin, row_begin + lhs_rows->size0)
+ * from host memory and forwards them to every peer's staging area over NVLink
+ * (copy engines, stores only, no loads of remote memory), so each row of lhs
+ * crosses PCIe once per box instead of once per GPU.  Every rank must make the
+ * matching call (same seq).  Returns when `out` has landed in host memory;
+ * KAPYB_TIMEOUT when a peer's rows did not arrive within the limit.  No
+ * reference counterpart. */
+KAPYB_API kapyb_status kapyb_matmul_host_sharded(
+    kapyb_handle h, const kapyb_tensor2d *lhs_rows, int32_t m_total, int32_t row_begin,
+    const kapyb_tensor2d *rhs, const kapyb_tensor2d *out, const kapyb_epilogue *epilogue,
+    const kapyb_shard_ctx *ctx, int32_t impl_way, void *stream);
+
 /* The decode-shape (few-row) matmul for callers that must not allocate device
  * memory.  No counterpart in the reference.
  *
@@ -298,15 +380,20 @@ KAPYB_API kapyb_status kapyb_matmul_push(
  *    leading dimension a multiple of 16 bytes); there is no fallback kernel;
  *  - the call runs on the CURRENT device.  Its first call on each device looks
  *    up the array's device address (cudaGetSymbolAddress) and the device's
- *    properties; make that first call outside any stream capture;
+ *    properties; make that first call outside any stream capture.  Threads that
+ *    make their first call on one device at the same time are serialised;
  *  - it calls no cudaMalloc/cudaFree and no allocating library routine.  It
- *    clears the counters it will use (cudaMemsetAsync on `stream`), then
- *    launches the kernel on `stream`;
+ *    clears the counters it will use and the time-out word (cudaMemsetAsync on
+ *    `stream`), then launches the kernel on `stream`;
  *  - all calls on one GPU share the one array: two calls whose kernels can
  *    overlap on the GPU (different streams, no dependency) race and give wrong
  *    results.  Keep them on one stream or order them yourself;
- *  - sync_and_check != 0 waits for `stream` and returns KAPYB_TIMEOUT if the
- *    kernel gave up on a bounded wait; with 0 the call returns after launching.
+ *  - sync_and_check != 0 waits for `stream` and returns KAPYB_TIMEOUT if THIS
+ *    call's kernel gave up on a bounded wait; with 0 the call returns after
+ *    launching and a time-out of it goes unreported (the next call starts the
+ *    word from zero again);
+ *  - a tile split between SMs is summed in a fixed order, so the result is the
+ *    same bits as kapyb_matmul's on the same problem and device.
  * Error text: kapyb_last_error_string(NULL) on the calling thread. */
 KAPYB_API kapyb_status kapyb_matmul_decode_static(const kapyb_tensor2d *lhs,
                                                   const kapyb_tensor2d *rhs,
@@ -337,9 +424,12 @@ KAPYB_API kapyb_status kapyb_elementwise(kapyb_handle h, const kapyb_inst *prog,
 
 /* kapy.reduce (Ops.td:441-457; lowering ReduceOpToLLVM.cpp:76-119) over a whole
  * [size0,size1] tensor: axis 1 -> dst [size0,1], axis 0 -> dst [1,size1].
- * src elements are widened to dst->dtype (arith.extf) before combining when
- * the dtypes differ; dst->dtype must be f32 or equal src->dtype.  The order of
- * combination is unspecified, as in the reference. */
+ * dst->dtype must be f32 or equal src->dtype.  The lambda runs at dst's element
+ * type, as the reference calls the region on values of the tensor's type: with
+ * an f32 destination a 16-bit source is widened first (arith.extf) and combined
+ * in f32; with a 16-bit destination every combination is rounded to that type
+ * (reduce_sum.mlir:10-25 adds in f16).  The order of combination is unspecified
+ * in the reference; here it is fixed per shape, so results repeat bit for bit. */
 KAPYB_API kapyb_status kapyb_reduce(kapyb_handle h, const kapyb_tensor2d *src,
                                     const kapyb_tensor2d *dst, int32_t axis,
                                     int32_t combiner, void *stream);
@@ -397,14 +487,21 @@ KAPYB_API int64_t kapyb_launch_count(kapyb_handle h);
  * ratio is the SM clock in GHz while the kernel ran).  Both kernels: words 2..6
  * are readings of the nanosecond timer's low 32 bits: the
  * complement of the earliest CTA start, then the latest, over all CTAs, of: CTA
- * start, first operand stage landed, last MMA issued, epilogue done.  GEMM only:
+ * start, first operand stage landed, last MMA issued, epilogue done.  GEMM only
+ * (zero unless the library was built with -DKAPYB_DEBUG_SWITCHES):
  * words 7..11 = clocks one epilogue warp of the first CTA spent per phase of its
  * chunk loop; words 12, 13 = clocks the first CTA's MMA warp waited for operand
  * stages and for accumulator slots. */
 KAPYB_API kapyb_status kapyb_probe_read(kapyb_handle h, void *stream, uint32_t *words, int32_t n);
 
-/* Forces a kernel family for matmul ("auto", "1cta", "2cta", "skinny",
- * "simt"); for tests and profiling. */
+/* Forces a kernel family for matmul ("auto", "1cta", "2cta", "skinny", "simt"),
+ * optionally ":<tile width>", ":e<epilogue warps>", ":s<stages>", ":w<wait limit
+ * in ms>" and ":d<debug bits>"; for tests and profiling.  Debug bit 16 silences
+ * the producer (every bounded wait then runs out: the test of the time-out
+ * path) and bit 128 switches the probes on; both leave correct kernels
+ * correct.  The bits that make a kernel skip work (1, 2, 4, 8, 32) are refused
+ * with KAPYB_UNSUPPORTED unless the library was built with
+ * -DKAPYB_DEBUG_SWITCHES. */
 KAPYB_API kapyb_status kapyb_set_matmul_path(kapyb_handle h, const char *name);
 
 #ifdef __cplusplus

@@ -12,9 +12,9 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 SO_PATH = os.path.join(_HERE, "libkapyb.so")
 
 # kapyb_status
-OK, INVALID_ARG, UNSUPPORTED, CUDA_ERROR, NCCL_ERROR, TIMEOUT = range(6)
+OK, INVALID_ARG, UNSUPPORTED, CUDA_ERROR, _UNUSED_4, TIMEOUT = range(6)
 # kapyb_dtype
-F16, BF16, F32, F8E4M3, F8E5M2 = 0, 1, 2, 3, 4
+F16, BF16, F32, F8E4M3, F8E5M2, I1 = 0, 1, 2, 3, 4, 5
 # kapyb_padding (Enums.td:52-61)
 PAD_ZERO, PAD_QNAN, PAD_PINF, PAD_NINF = 0, 1, 2, 3
 # kapyb_rounding (Enums.td:102-109)
@@ -29,7 +29,10 @@ MMA_ANY, MMA_M16N8K8_F16, MMA_M16N8K16_F16, MMA_M16N8K8_TF32, MMA_M16N8K16_F8 = 
 # kapyb_opcode
 (OP_LOAD, OP_CONST, OP_CVT, OP_ADD, OP_SUB, OP_MUL, OP_DIV, OP_FMA, OP_MAXIMUM, OP_MINIMUM,
  OP_MAXNUM, OP_MINNUM, OP_CLAMP, OP_ABS, OP_NEG, OP_EXP, OP_EXP2, OP_LOG, OP_LOG2, OP_SQRT,
- OP_RSQRT, OP_ERF, OP_SIN, OP_COS, OP_FLOOR, OP_CEIL, OP_TANH, OP_STORE) = range(28)
+ OP_RSQRT, OP_ERF, OP_SIN, OP_COS, OP_FLOOR, OP_CEIL, OP_TANH, OP_STORE, OP_CMP, OP_SELECT,
+ OP_AND, OP_OR, OP_XOR) = range(33)
+# kapyb_cmp_predicate (arith.cmpf as ir.cc:941-1000 binds it)
+CMP_PREDICATES = ["olt", "ogt", "ole", "oge", "oeq", "one", "ult", "ugt", "ule", "uge", "ueq", "une"]
 
 MAX_REGS, MAX_INSTS, MAX_INPUTS = 16, 64, 4
 
@@ -45,6 +48,12 @@ class Epilogue(C.Structure):
     _fields_ = [("alpha", C.c_float), ("bias", C.c_void_p),
                 ("bias_dtype", C.c_int32), ("bias_axis", C.c_int32),
                 ("activation", C.c_int32), ("rounding", C.c_int32)]
+
+
+class ShardCtx(C.Structure):
+    _fields_ = [("rank", C.c_int32), ("world", C.c_int32),
+                ("peer_lhs", C.POINTER(C.c_void_p)), ("peer_flags", C.POINTER(C.c_void_p)),
+                ("seq", C.c_uint32), ("wait_limit_ms", C.c_uint32)]
 
 
 class Inst(C.Structure):
@@ -74,6 +83,14 @@ PROTOTYPES = {
                                     C.POINTER(C.c_void_p), C.c_int32, C.c_int32, C.c_int32,
                                     C.c_int32, C.c_int32, C.POINTER(Epilogue), C.c_int32,
                                     C.c_void_p]),
+    "kapyb_gather_signal": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p), C.c_int32, C.c_int32,
+                                      C.c_uint32, C.c_void_p]),
+    "kapyb_gather_wait": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_uint32, C.c_uint32,
+                                    C.c_void_p]),
+    "kapyb_matmul_host_sharded": (C.c_int, [C.c_void_p, C.POINTER(Tensor2d), C.c_int32, C.c_int32,
+                                            C.POINTER(Tensor2d), C.POINTER(Tensor2d),
+                                            C.POINTER(Epilogue), C.POINTER(ShardCtx), C.c_int32,
+                                            C.c_void_p]),
     "kapyb_matmul_decode_static": (C.c_int, [C.POINTER(Tensor2d), C.POINTER(Tensor2d),
                                              C.POINTER(Tensor2d), C.POINTER(Epilogue), C.c_int32,
                                              C.c_void_p]),

@@ -34,10 +34,14 @@ def is_stale() -> bool:
 
 
 def build(force: bool = False, verbose: bool = False) -> str:
+    """KAPYB_DEBUG_SWITCHES=1 in the environment compiles the profiling switches
+    that make kernels skip work (and the epilogue's per-phase clock probes) in."""
     if not force and not is_stale():
         return SO_PATH
     nvcc = os.environ.get("NVCC", "nvcc")
     cmd = [nvcc, *NVCC_FLAGS, "-o", SO_PATH, _SRC]
+    if os.environ.get("KAPYB_DEBUG_SWITCHES", "") not in ("", "0"):
+        cmd.insert(1, "-DKAPYB_DEBUG_SWITCHES")
     if verbose:
         cmd.insert(1, "-Xptxas")
         cmd.insert(2, "-v")

@@ -64,6 +64,25 @@ __device__ __forceinline__ float minimum_f(float a, float b) {
   return fminf(a, b);
 }
 
+// arith.cmpf: ordered predicates are false, unordered ones true, when an operand is NaN.
+__device__ __forceinline__ bool cmp_f(int pred, float a, float b) {
+  const bool un = a != a || b != b;
+  switch (pred) {
+  case KAPYB_CMP_OLT: return a < b;
+  case KAPYB_CMP_OGT: return a > b;
+  case KAPYB_CMP_OLE: return a <= b;
+  case KAPYB_CMP_OGE: return a >= b;
+  case KAPYB_CMP_OEQ: return a == b;
+  case KAPYB_CMP_ONE: return !un && a != b;
+  case KAPYB_CMP_ULT: return un || a < b;
+  case KAPYB_CMP_UGT: return un || a > b;
+  case KAPYB_CMP_ULE: return un || a <= b;
+  case KAPYB_CMP_UGE: return un || a >= b;
+  case KAPYB_CMP_UEQ: return un || a == b;
+  default: return un || a != b;  // UNE
+  }
+}
+
 __device__ float interp_one(const EltProgram &P, int i, int j, bool *stored, float *store_val) {
   float r[KAPYB_MAX_REGS];
 #pragma unroll
@@ -120,6 +139,12 @@ __device__ float interp_one(const EltProgram &P, int i, int j, bool *stored, flo
       *stored = true;
       *store_val = a;
       break;
+    // conditions (i1) live in the float registers as 0 / 1
+    case KAPYB_OP_CMP: v = cmp_f(in.flags, a, b) ? 1.0f : 0.0f; break;
+    case KAPYB_OP_SELECT: v = a != 0.0f ? b : c; break;
+    case KAPYB_OP_AND: v = (a != 0.0f && b != 0.0f) ? 1.0f : 0.0f; break;
+    case KAPYB_OP_OR: v = (a != 0.0f || b != 0.0f) ? 1.0f : 0.0f; break;
+    case KAPYB_OP_XOR: v = ((a != 0.0f) != (b != 0.0f)) ? 1.0f : 0.0f; break;
     default: break;
     }
     if (in.op != KAPYB_OP_STORE && in.dst >= 0) r[in.dst & (KAPYB_MAX_REGS - 1)] = v;

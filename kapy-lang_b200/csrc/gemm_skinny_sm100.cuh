@@ -2,14 +2,19 @@
 // HBM-bound weight streaming.  The operands are swapped so the weights fill the
 // 128-row side of tcgen05.mma and the activations its narrow side:
 //   D[n, m] = sum_k W[k, n] * X[m, k]      (instruction shape 128 x M_pad x 16)
-// The (weight tile, k block) units are dealt to the CTAs as equal contiguous
-// spans ("stream-K"), so all SMs stream the same number of bytes whatever the
-// tile count.  A tile that is split between CTAs is accumulated with fp32
-// atomics in scratch memory; the last contributor applies the epilogue, writes
-// the output and leaves the scratch zeroed for the next launch.
+// Whole weight tiles go round-robin to the CTAs while they fill the GPU evenly;
+// the (tile, k block) units of the leftover tiles are dealt out as equal
+// contiguous spans ("stream-K"), so all SMs stream the same number of bytes
+// whatever the tile count.  A tile that is split between CTAs goes through
+// scratch memory: every contributor writes its partial sums with plain stores
+// into its own slot (no initial value needed) and bumps a per-tile counter; the
+// contributor that completes the count adds all slots IN CTA ORDER, applies the
+// epilogue, writes the output and resets the counter.  The counters are the
+// only state that must be zero when a launch starts.
 //
 // Same arithmetic contract as the big-tile kernel (fp32 accumulation of exact
-// products, fused epilogue), but a split tile sums its spans in arrival order.
+// products, fused epilogue).  Because a split tile's slots are added in CTA
+// order, not arrival order, the result is the same bits from run to run.
 #pragma once
 
 #include <cuda.h>
@@ -18,6 +23,19 @@
 #include "ptx_sm100.cuh"
 
 namespace kapyb {
+
+#ifdef KAPYB_DEBUG_SWITCHES
+constexpr int kSkinnyDebugMask = 0xff;
+#else
+constexpr int kSkinnyDebugMask = 128;
+#endif
+template <int BITS>
+__device__ __forceinline__ bool skinny_debug_on(int debug) {
+  if constexpr ((kSkinnyDebugMask & BITS) == 0)
+    return false;
+  else
+    return (debug & (kSkinnyDebugMask & BITS)) != 0;
+}
 
 constexpr int kSkinnyMaxM = 64;
 constexpr int kSkinnyThreads = 192;
@@ -46,10 +64,11 @@ struct SkinnyParams {
   uint32_t idesc;
   uint32_t *status;
   uint32_t wait_limit_us;  // 0: the default limit of a bounded wait
-  int debug;               // profiling only (results are wrong): bit2 skip the epilogue body,
+  int debug;               // bit7: record the timeline probes in status[2..8] (results stay
+                           // right).  Only in a build with -DKAPYB_DEBUG_SWITCHES, for
+                           // profiling (results are wrong): bit2 skip the epilogue body,
                            // bit3 skip the publish/count/owner pass, bit4 skip whole-tile
-                           // stores, bit5 skip the partial-sum stores; bit7 record the
-                           // timeline probes in status[2..8] (results stay right)
+                           // stores, bit5 skip the partial-sum stores
   EpilogueArgs ep;
 };
 
@@ -137,7 +156,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   // the shuffle makes the warp index provably uniform for the compiler
   const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0);
   const int lane = threadIdx.x & 31;
-  const bool probe = (p.debug & 128) != 0;
+  const bool probe = skinny_debug_on<128>(p.debug);
   if (probe && threadIdx.x == 0) {
     const uint32_t t = static_cast<uint32_t>(ptx::globaltimer_ns());
     atomicMax(p.status + 4, ~t);  // earliest start, kept as the largest complement
@@ -296,7 +315,11 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     for (int j = 0; j < work.count(); ++j) {
       int tile, kb_begin, kb_end;
       work.get(j, tile, kb_begin, kb_end);
-      if (!ptx::mbar_wait(ptx::smem_u32(&tfull_bar[acc]), acc_phase, abort_flag)) break;
+      // warp vote after the wait: the lanes leave together or not at all (what
+      // follows is warp-collective)
+      if (!__all_sync(0xffffffffu,
+                      ptx::mbar_wait(ptx::smem_u32(&tfull_bar[acc]), acc_phase, abort_flag)))
+        break;
       ptx::tc_fence_after();
       const bool whole = kb_begin == 0 && kb_end == p.num_kb;
       const int n = tile * 128 + q * 32 + lane;
@@ -312,12 +335,12 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       if (p.ep.bias != nullptr && p.ep.bias_axis == 1 && n < p.N)
         bias_n = load_as_f32(p.ep.bias, p.ep.bias_dtype, n);
       uint16_t *col16 = static_cast<uint16_t *>(p.c) + n * p.c_s1;
-      for (int mc = 0; mc < p.m_pad && !(p.debug & 4); mc += 16) {
+      for (int mc = 0; mc < p.m_pad && !skinny_debug_on<4>(p.debug); mc += 16) {
         uint32_t v[16];
         ptx::tmem_ld_32x16(t_row + static_cast<uint32_t>(mc), v);
         ptx::tmem_ld_wait();
         if (whole) {
-          if (n < p.N && !(p.debug & 16)) {
+          if (n < p.N && !skinny_debug_on<16>(p.debug)) {
             if (fast16) {
               float f[16];
 #pragma unroll
@@ -332,7 +355,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
                 if (mc + i < p.M) skinny_finish(p, n, mc + i, __uint_as_float(v[i]), bias_n);
             }
           }
-        } else if (!(p.debug & 32)) {
+        } else if (!skinny_debug_on<32>(p.debug)) {
 #pragma unroll
           for (int i = 0; i < 16; ++i)
             if (mc + i < p.M) __stcg(scr + (mc + i) * 128, __uint_as_float(v[i]));
@@ -341,7 +364,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       ptx::tc_fence_before();
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&tempty_bar[acc]));
-      if (!whole && !(p.debug & (4 | 8))) {
+      if (!whole && !skinny_debug_on<4 | 8>(p.debug)) {
         // Publish this segment's partial sums (plain stores into this CTA's own
         // slot), then count it.  The contributor that completes the count owns
         // the tile quarter: it adds the slots of all contributors in CTA order

@@ -39,6 +39,28 @@ namespace kapyb {
 
 constexpr int kMaxOutputs = 8;  // own output + up to 7 peers for the push epilogue
 
+// Debug switches (GemmParams::debug).  Bits 0-3 and 5 make a kernel skip part of
+// its work, so its results are garbage: they exist for profiling only and are
+// compiled in only with -DKAPYB_DEBUG_SWITCHES, together with the per-phase
+// clock probes of the epilogue warps.  A normal build keeps bit 4 (the producer
+// stays silent, so that every other role's bounded wait runs out: the test of the
+// time-out path) and bit 7 (timeline and clock probes of the MMA warp; results
+// stay right), and neither costs the epilogue warps a register.
+#ifdef KAPYB_DEBUG_SWITCHES
+constexpr int kDebugMask = 0xff;
+constexpr bool kEpilogueProbes = true;
+#else
+constexpr int kDebugMask = 16 | 128;
+constexpr bool kEpilogueProbes = false;
+#endif
+template <int BITS>
+__device__ __forceinline__ bool debug_on(int debug) {
+  if constexpr ((kDebugMask & BITS) == 0)
+    return false;
+  else
+    return (debug & (kDebugMask & BITS)) != 0;
+}
+
 struct TmapArray {
   CUtensorMap m[kMaxOutputs];
 };
@@ -306,7 +328,8 @@ __device__ __forceinline__ bool epilogue_tile(const GemmParams &p, const TmapArr
     uint8_t *sbuf = t.stg + (C_BUFS == 2 ? buf : 0) * 4096;
     // All loads of the chunk are in flight before the one wait.
     uint32_t v[NH][32];
-    const uint32_t c0 = t.prof ? static_cast<uint32_t>(clock()) : 0u;
+    const bool probing = kEpilogueProbes && t.prof != nullptr;
+    const uint32_t c0 = probing ? static_cast<uint32_t>(clock()) : 0u;
 #pragma unroll
     for (int h = 0; h < NH; ++h)
       ptx::tmem_ld_32x32(t.t_row + static_cast<uint32_t>(c * CW + h * 32), v[h]);
@@ -314,9 +337,9 @@ __device__ __forceinline__ bool epilogue_tile(const GemmParams &p, const TmapArr
     // with a single buffer) must have finished reading it.
     if (lane == 0) ptx::tma_store_wait_read<C_BUFS - 1>();
     __syncwarp();
-    const uint32_t c1 = t.prof ? static_cast<uint32_t>(clock()) : 0u;
+    const uint32_t c1 = probing ? static_cast<uint32_t>(clock()) : 0u;
     ptx::tmem_ld_wait();
-    const uint32_t c2 = t.prof ? static_cast<uint32_t>(clock()) : 0u;
+    const uint32_t c2 = probing ? static_cast<uint32_t>(clock()) : 0u;
     if (c + CSTEP >= t.col_end / CW || t.n0 + (c + CSTEP) * CW >= p.N) {
       // That was this warp's last read of the slot: hand it back now, so the next
       // tile's MMAs do not wait for the arithmetic and the stores below.
@@ -348,13 +371,13 @@ __device__ __forceinline__ bool epilogue_tile(const GemmParams &p, const TmapArr
     }
     ptx::fence_proxy_async_smem();
     __syncwarp();
-    const uint32_t c3 = t.prof ? static_cast<uint32_t>(clock()) : 0u;
-    if (lane == 0 && !(p.debug & 8)) {
+    const uint32_t c3 = probing ? static_cast<uint32_t>(clock()) : 0u;
+    if (lane == 0 && !debug_on<8>(p.debug)) {
       for (int o = 0; o < p.n_out; ++o)
         ptx::tma_store_3d(&tmC.m[o], ptx::smem_u32(sbuf), p.out_col_offset + nc, t.m0, t.b);
       ptx::tma_store_commit();
     }
-    if (t.prof && lane == 0) {
+    if (probing && lane == 0) {
       atomicAdd(t.prof + 0, c2 - c0);  // staging buffer free again, accumulator loads landed
       (void)c1;
       atomicAdd(t.prof + 2, c3 - c2);  // arithmetic, staging, fence
@@ -389,7 +412,7 @@ __device__ __forceinline__ bool epilogue_two_halves(const GemmParams &p, const T
   auto store_chunk = [&](int nc) {
     ptx::fence_proxy_async_smem();
     __syncwarp();
-    if (lane == 0 && !(p.debug & 8)) {
+    if (lane == 0 && !debug_on<8>(p.debug)) {
       for (int o = 0; o < p.n_out; ++o)
         ptx::tma_store_3d(&tmC.m[o], ptx::smem_u32(t.stg), p.out_col_offset + nc, t.m0, t.b);
       ptx::tma_store_commit();
@@ -430,7 +453,9 @@ __device__ __forceinline__ bool epilogue_two_halves(const GemmParams &p, const T
   for (int i = 0; i < 4; ++i) {
     const int hh = i >> 1, j = i & 1;
     if (j == 0) {
-      if (!ptx::mbar_wait(tfull0 + hh * 8, parity, abort_flag)) alive = false;
+      // every lane polls, then the warp votes: a time-out must take all lanes or none,
+      // since the loads, shuffles and __syncwarp below are warp-collective
+      if (!__all_sync(0xffffffffu, ptx::mbar_wait(tfull0 + hh * 8, parity, abort_flag))) alive = false;
       ptx::tc_fence_after();
     }
     const int c = hh * 4 + t.cpart + 2 * j;
@@ -559,7 +584,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
   const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0);
   const int lane = threadIdx.x & 31;
   const uint32_t rank = CTAS == 2 ? ptx::cluster_ctarank() : 0u;
-  const bool timeline = (p.debug & 128) != 0;  // probes: see GemmParams::debug
+  const bool timeline = debug_on<128>(p.debug);  // probes: see GemmParams::debug
   if (timeline && threadIdx.x == 0) {
     const uint32_t t = static_cast<uint32_t>(ptx::globaltimer_ns());
     atomicMax(p.status + 4, ~t);  // earliest CTA start, kept as the largest complement
@@ -610,7 +635,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
-    for (int tile = unit; tile < p.num_tiles && ok && !(p.debug & (16 | 32)); tile += unit_step) {
+    for (int tile = unit; tile < p.num_tiles && ok && !debug_on<16 | 32>(p.debug); tile += unit_step) {
       int b, mb, nb;
       decode_tile(p, tile, b, mb, nb);
       const int m0 = mb * Cfg::TILE_M + static_cast<int>(rank) * Cfg::BM;
@@ -630,7 +655,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
         const int b_chunks = Cfg::BN_CTA / ce;
         const uint32_t a_dst = ptx::smem_u32(sA + stage * Cfg::A_BYTES);
         const uint32_t b_dst = ptx::smem_u32(sB + stage * Cfg::B_BYTES);
-        if (p.debug & 1) {
+        if (debug_on<1>(p.debug)) {
           if (rank == 0) ptx::mbar_arrive(ptx::smem_u32(&full_bar[stage]));
         } else if constexpr (CTAS == 1) {
           const uint32_t fb = ptx::smem_u32(&full_bar[stage]);
@@ -719,7 +744,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
     const uint32_t b_lo0 = b_lo_c | (ptx::smem_u32(sB) >> 4);
     const uint32_t idesc = p.idesc;
     const int kind = p.kind;
-    const bool skip_mma = (p.debug & 2) != 0, free_run = (p.debug & 32) != 0;
+    const bool skip_mma = debug_on<2>(p.debug), free_run = debug_on<32>(p.debug);
     int stage = 0;
     uint32_t phase = 0;
     int acc = 0;
@@ -883,7 +908,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
     int acc = 0;
     uint32_t acc_phase = 0;
     int buf = 0;
-    uint32_t *prof = (timeline && blockIdx.x == 0 && e == 0) ? prof_words : nullptr;
+    uint32_t *prof = (kEpilogueProbes && timeline && blockIdx.x == 0 && e == 0) ? prof_words : nullptr;
     for (int tile = unit; tile < p.num_tiles; tile += unit_step) {
       const uint32_t s0 = prof ? static_cast<uint32_t>(clock()) : 0u;
       int b, mb, nb;
@@ -916,7 +941,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
           et.prof = nullptr;
           if (p.ep.bias != nullptr && p.ep.bias_axis == 0 && row < p.M)
             et.bias_row = load_as_f32(p.ep.bias, p.ep.bias_dtype, row);
-          const bool active = m0 < p.M && !(p.debug & 4);
+          const bool active = m0 < p.M && !debug_on<4>(p.debug);
           const uint32_t tf0 = ptx::smem_u32(&tfull_bar[0]);
           alive = epilogue_two_halves<EPI>(p, tmC, et, tf0, acc_phase, abort_flag, active,
                                            out_kind == 1);
@@ -930,7 +955,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
         // slot: with two halves, half hh of this tile; otherwise the tile's slot
         const int slot = Cfg::HALVES == 2 ? hh : acc;
         const uint32_t w0 = prof ? static_cast<uint32_t>(clock()) : 0u;
-        if (!ptx::mbar_wait(ptx::smem_u32(&tfull_bar[slot]), acc_phase, abort_flag)) {
+        // warp vote after the wait: the lanes leave together or not at all
+        if (!__all_sync(0xffffffffu,
+                        ptx::mbar_wait(ptx::smem_u32(&tfull_bar[slot]), acc_phase, abort_flag))) {
           alive = false;
           break;
         }
@@ -940,7 +967,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
                                (Cfg::HALVES == 2 ? 0u : static_cast<uint32_t>(acc * BN));
         bool handed_back = false;
         const uint32_t slot_bar = tempty_leader + static_cast<uint32_t>(slot * 8);
-        if (m0 < p.M && !(p.debug & 4)) {
+        if (m0 < p.M && !debug_on<4>(p.debug)) {
           EpiTile et;
           et.tempty_addr = slot_bar;
           et.remote_arrive = CTAS == 2;

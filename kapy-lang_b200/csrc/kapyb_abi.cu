@@ -6,6 +6,7 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <atomic>
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
@@ -17,6 +18,7 @@
 
 #include "../../include/kapyb.h"
 #include "eltwise.cuh"
+#include "gather_sync.cuh"
 #include "gemm_simt.cuh"
 #include "gemm_skinny_sm100.cuh"
 #include "gemm_sm100.cuh"
@@ -54,6 +56,10 @@ struct kapyb_context {
   cudaStream_t copy_in = nullptr, copy_out = nullptr;
   cudaEvent_t ev[2 * 16 + 2] = {};
   bool pipe_ready = false;
+  // sharded host-buffer calls: the stream that forwards this rank's rows to its peers
+  cudaStream_t push = nullptr;
+  cudaEvent_t ev_push[16 + 1] = {};
+  bool push_ready = false;
 };
 
 static thread_local std::string g_create_error;
@@ -78,7 +84,7 @@ static kapyb_status fail(kapyb_handle h, kapyb_status st, const char *fmt, ...) 
       return fail(h, KAPYB_CUDA_ERROR, "%s failed: %s", #expr, cudaGetErrorString(e_));    \
   } while (0)
 
-extern "C" KAPYB_API int kapyb_version(void) { return 100; }
+extern "C" KAPYB_API int kapyb_version(void) { return 110; }
 
 extern "C" KAPYB_API kapyb_status kapyb_create(kapyb_handle *out, int device) {
   if (!out) return fail(nullptr, KAPYB_INVALID_ARG, "kapyb_create: out is NULL");
@@ -126,6 +132,11 @@ extern "C" KAPYB_API kapyb_status kapyb_destroy(kapyb_handle h) {
   cudaSetDevice(h->device);
   if (h->workspace) cudaFree(h->workspace);
   if (h->status) cudaFree(h->status);
+  if (h->push_ready) {
+    cudaStreamDestroy(h->push);
+    for (cudaEvent_t e : h->ev_push)
+      if (e) cudaEventDestroy(e);
+  }
   if (h->pipe_ready) {
     cudaStreamDestroy(h->copy_in);
     cudaStreamDestroy(h->copy_out);
@@ -212,6 +223,10 @@ extern "C" KAPYB_API kapyb_status kapyb_set_matmul_path(kapyb_handle h, const ch
   const char *why = "";
   if (!parse_path(name, c, &why))
     return fail(h, KAPYB_INVALID_ARG, "kapyb_set_matmul_path: %s ('%s')", why, name);
+  if (c.debug & ~kDebugMask)
+    return fail(h, KAPYB_UNSUPPORTED,
+                "kapyb_set_matmul_path: debug bits %d make results garbage and exist only in a "
+                "library built with -DKAPYB_DEBUG_SWITCHES ('%s')", c.debug & ~kDebugMask, name);
   h->forced_path = c.path;
   h->forced_bn = c.bn;
   h->forced_epi = c.epi;
@@ -291,6 +306,7 @@ static const char *dtype_name(int d) {
          : d == KAPYB_F32   ? "f32"
          : d == KAPYB_F8E4M3 ? "f8E4M3"
          : d == KAPYB_F8E5M2 ? "f8E5M2"
+         : d == KAPYB_I1     ? "i1"
                              : "?";
 }
 
@@ -312,6 +328,15 @@ static kapyb_status verify_matmul(kapyb_handle h, const kapyb_tensor2d *lhs,
     return fail(h, KAPYB_INVALID_ARG, "matmul: unknown element type");
   if (lhs->size0 < 0 || lhs->size1 < 0 || rhs->size0 < 0 || rhs->size1 < 0)
     return fail(h, KAPYB_INVALID_ARG, "matmul: negative size");
+  // Out-of-bounds lanes of a matmul operand are filled with zeros (TMA fill, and
+  // the zero accumulator contribution that implies).  The other padding options
+  // of ld_global (Enums.td:52-61) would put NaN or infinities into every output
+  // whose K range is ragged against the kernel's tile, which depends on a tile
+  // size the caller cannot see: refuse them instead of ignoring them.
+  if (lhs->padding != KAPYB_PAD_ZERO || rhs->padding != KAPYB_PAD_ZERO)
+    return fail(h, KAPYB_UNSUPPORTED,
+                "matmul: operands are padded with zeros only (padding option %d requested)",
+                lhs->padding != KAPYB_PAD_ZERO ? lhs->padding : rhs->padding);
   if (lhs->size1 != rhs->size0)
     return fail(h, KAPYB_INVALID_ARG,
                 "matmul: number of columns of lhs must be equal to number of rows of rhs");
@@ -1181,6 +1206,16 @@ static size_t span_bytes(const kapyb_tensor2d *t) {
 
 static size_t round256(size_t x) { return (x + 255) & ~static_cast<size_t>(255); }
 
+// Copy streams and events of the host-buffer pipelines, created on first use.
+static kapyb_status ensure_pipe(kapyb_handle h) {
+  if (h->pipe_ready) return KAPYB_OK;
+  CUDA_TRY(h, cudaStreamCreateWithFlags(&h->copy_in, cudaStreamNonBlocking));
+  CUDA_TRY(h, cudaStreamCreateWithFlags(&h->copy_out, cudaStreamNonBlocking));
+  for (cudaEvent_t &e : h->ev) CUDA_TRY(h, cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+  h->pipe_ready = true;
+  return KAPYB_OK;
+}
+
 extern "C" KAPYB_API kapyb_status kapyb_matmul_host(kapyb_handle h, const kapyb_tensor2d *lhs,
                                                     const kapyb_tensor2d *rhs,
                                                     const kapyb_tensor2d *out,
@@ -1205,10 +1240,11 @@ extern "C" KAPYB_API kapyb_status kapyb_matmul_host(kapyb_handle h, const kapyb_
   CUDA_TRY(h, cudaSetDevice(h->device));
   char *w = static_cast<char *>(h->workspace) + skinny_ws;
   char *da = w, *db = da + round256(na), *dc = db + round256(nb), *dbias = dc + round256(nc);
-  const bool pipelined = lhs->stride1 == 1 && out->stride1 == 1 && out->stride0 == out->size1 &&
-                         lhs->stride0 == lhs->size1 && lhs->size0 >= 2048 &&
-                         (static_cast<size_t>(lhs->size0) * lhs->size1 >= (1u << 22));
-  if (!pipelined)
+  // Large row-major problems go up and come back in row chunks (see below).
+  const bool can_pipe = lhs->stride1 == 1 && out->stride1 == 1 && out->stride0 == out->size1 &&
+                        lhs->stride0 == lhs->size1 && lhs->size0 >= 2048 &&
+                        (static_cast<size_t>(lhs->size0) * lhs->size1 >= (1u << 22));
+  if (!can_pipe)
     CUDA_TRY(h, cudaMemcpyAsync(da, elem_ptr(lhs), na, cudaMemcpyHostToDevice, stream));
   CUDA_TRY(h, cudaMemcpyAsync(db, elem_ptr(rhs), nb, cudaMemcpyHostToDevice, stream));
   kapyb_epilogue ep;
@@ -1237,16 +1273,9 @@ extern "C" KAPYB_API kapyb_status kapyb_matmul_host(kapyb_handle h, const kapyb_
   // chunk i+1, the GEMM of chunk i and the download of chunk i-1 (PCIe is full
   // duplex; a single stream would serialise the three).
   constexpr int kMaxChunks = 16;
-  const bool can_pipe = lhs->stride1 == 1 && out->stride1 == 1 && out->stride0 == out->size1 &&
-                        lhs->stride0 == lhs->size1 && lhs->size0 >= 2048 &&
-                        (static_cast<size_t>(lhs->size0) * lhs->size1 >= (1u << 22));
   if (can_pipe) {
-    if (!h->pipe_ready) {
-      CUDA_TRY(h, cudaStreamCreateWithFlags(&h->copy_in, cudaStreamNonBlocking));
-      CUDA_TRY(h, cudaStreamCreateWithFlags(&h->copy_out, cudaStreamNonBlocking));
-      for (cudaEvent_t &e : h->ev) CUDA_TRY(h, cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
-      h->pipe_ready = true;
-    }
+    st = ensure_pipe(h);
+    if (st != KAPYB_OK) return st;
     const int M = lhs->size0;
     const int chunks = std::min(kMaxChunks, std::max(2, M / 1024));
     const int rows_per = ((M + chunks - 1) / chunks + 255) / 256 * 256;
@@ -1311,6 +1340,212 @@ extern "C" KAPYB_API kapyb_status kapyb_matmul_host(kapyb_handle h, const kapyb_
   return kapyb_check(h, stream);
 }
 
+// ------------------------------------------------- cross-GPU completion flags
+
+extern "C" KAPYB_API kapyb_status kapyb_gather_signal(kapyb_handle h, void *const *peer_flags,
+                                                      int32_t n_ranks, int32_t my_rank,
+                                                      uint32_t seq, void *stream) {
+  if (!h) return fail(h, KAPYB_INVALID_ARG, "kapyb_gather_signal: NULL handle");
+  if (!peer_flags || n_ranks < 1 || n_ranks > kMaxGatherRanks || my_rank < 0 || my_rank >= n_ranks)
+    return fail(h, KAPYB_INVALID_ARG, "gather_signal: need 1..%d ranks and a rank inside them",
+                kMaxGatherRanks);
+  GatherFlagPtrs fp;
+  for (int r = 0; r < n_ranks; ++r) {
+    if (!peer_flags[r] || (reinterpret_cast<uintptr_t>(peer_flags[r]) & 3u))
+      return fail(h, KAPYB_INVALID_ARG, "gather_signal: peer_flags[%d] is NULL or misaligned", r);
+    fp.p[r] = static_cast<uint32_t *>(peer_flags[r]);
+  }
+  for (int r = n_ranks; r < kMaxGatherRanks; ++r) fp.p[r] = nullptr;
+  CUDA_TRY(h, cudaSetDevice(h->device));
+  gather_signal_kernel<<<1, kMaxGatherRanks, 0, static_cast<cudaStream_t>(stream)>>>(fp, n_ranks,
+                                                                                      my_rank, seq);
+  CUDA_TRY(h, cudaGetLastError());
+  h->launches++;
+  return KAPYB_OK;
+}
+
+extern "C" KAPYB_API kapyb_status kapyb_gather_wait(kapyb_handle h, const void *my_flags,
+                                                    int32_t n_ranks, uint32_t seq,
+                                                    uint32_t limit_ms, void *stream) {
+  if (!h) return fail(h, KAPYB_INVALID_ARG, "kapyb_gather_wait: NULL handle");
+  if (!my_flags || (reinterpret_cast<uintptr_t>(my_flags) & 3u) || n_ranks < 1 ||
+      n_ranks > kMaxGatherRanks)
+    return fail(h, KAPYB_INVALID_ARG, "gather_wait: need an aligned flag array of 1..%d words",
+                kMaxGatherRanks);
+  CUDA_TRY(h, cudaSetDevice(h->device));
+  const unsigned long long limit_ns = (limit_ms ? limit_ms : 2000u) * 1000000ull;
+  gather_wait_kernel<<<1, kMaxGatherRanks, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint32_t *>(my_flags), n_ranks, seq, limit_ns, h->status);
+  CUDA_TRY(h, cudaGetLastError());
+  h->launches++;
+  return KAPYB_OK;
+}
+
+// ------------------------------------------- host buffers, rows of A sharded
+
+// Rows per GEMM launch of a chunked host call: enough tiles per launch to fill a
+// good part of the GPU (a 256-row x 512-column tile per SM pair), in multiples
+// of 256 rows, at most kMax launches.
+static int host_chunk_rows(int M, int n_cols, int sm_count, int max_chunks) {
+  const int tiles_n = std::max(1, (n_cols + 511) / 512);
+  const int want_tiles = std::max(1, (sm_count / 2) * 2 / 5);
+  int rows = std::max(((want_tiles + tiles_n - 1) / tiles_n) * 256, 1024);
+  const int chunks = std::max(1, std::min(max_chunks, (M + rows - 1) / rows));
+  return std::max(256, ((M + chunks - 1) / chunks + 255) / 256 * 256);  // even chunks
+}
+
+extern "C" KAPYB_API kapyb_status kapyb_matmul_host_sharded(
+    kapyb_handle h, const kapyb_tensor2d *lhs_rows, int32_t m_total, int32_t row_begin,
+    const kapyb_tensor2d *rhs, const kapyb_tensor2d *out, const kapyb_epilogue *epilogue,
+    const kapyb_shard_ctx *ctx, int32_t impl_way, void *stream_) {
+  if (!h) return fail(h, KAPYB_INVALID_ARG, "kapyb_matmul_host_sharded: NULL handle");
+  if (!lhs_rows || !rhs || !out || !ctx)
+    return fail(h, KAPYB_INVALID_ARG, "matmul_host_sharded: NULL argument");
+  const int world = ctx->world, rank = ctx->rank;
+  if (world < 1 || world > kMaxGatherRanks || rank < 0 || rank >= world || !ctx->peer_lhs ||
+      !ctx->peer_flags)
+    return fail(h, KAPYB_INVALID_ARG, "matmul_host_sharded: bad rank / world / peer tables");
+  const int K = lhs_rows->size1, rows_mine = lhs_rows->size0;
+  if (m_total < 0 || row_begin < 0 || rows_mine < 0 || row_begin + rows_mine > m_total)
+    return fail(h, KAPYB_INVALID_ARG, "matmul_host_sharded: rows [%d, %d) outside [0, %d)",
+                row_begin, row_begin + rows_mine, m_total);
+  // the whole problem as the kernels will see it: lhs [m_total, K] in the staging buffer
+  kapyb_tensor2d full = *lhs_rows;
+  full.size0 = m_total;
+  full.stride0 = K;
+  full.stride1 = 1;
+  kapyb_status st = verify_matmul(h, &full, rhs, nullptr, out, epilogue, impl_way);
+  if (st != KAPYB_OK) return st;
+  if ((rows_mine > 0 && (lhs_rows->stride1 != 1 || lhs_rows->stride0 != K)) ||
+      out->stride1 != 1 || out->stride0 != out->size1)
+    return fail(h, KAPYB_UNSUPPORTED,
+                "matmul_host_sharded: this rank's rows of lhs and the output must be dense row-major");
+  if (rhs->stride0 < 0 || rhs->stride1 < 0)
+    return fail(h, KAPYB_UNSUPPORTED, "matmul_host_sharded: negative strides are not supported");
+  const size_t esz_a = dtype_size(lhs_rows->dtype), esz_c = dtype_size(out->dtype);
+  if ((static_cast<size_t>(K) * esz_a) % 16 != 0)
+    return fail(h, KAPYB_UNSUPPORTED, "matmul_host_sharded: a row of lhs must be a multiple of 16 bytes");
+  for (int r = 0; r < world; ++r)
+    if (!ctx->peer_lhs[r] || !ctx->peer_flags[r] || !aligned16(ctx->peer_lhs[r]))
+      return fail(h, KAPYB_INVALID_ARG, "matmul_host_sharded: peer table entry %d is NULL or misaligned", r);
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  CUDA_TRY(h, cudaSetDevice(h->device));
+
+  const size_t nb = span_bytes(rhs), nc = span_bytes(out);
+  size_t nbias = 0;
+  if (epilogue && epilogue->bias)
+    nbias = static_cast<size_t>(epilogue->bias_axis == 1 ? rhs->size1 : m_total) *
+            dtype_size(epilogue->bias_dtype);
+  const size_t skinny_ws = skinny_workspace_bytes();
+  st = kapyb_reserve_workspace(h, skinny_ws + round256(nb) + round256(nc) + round256(nbias));
+  if (st != KAPYB_OK) return st;
+  st = ensure_pipe(h);
+  if (st != KAPYB_OK) return st;
+  if (!h->push_ready) {
+    CUDA_TRY(h, cudaStreamCreateWithFlags(&h->push, cudaStreamNonBlocking));
+    for (cudaEvent_t &e : h->ev_push) CUDA_TRY(h, cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+    h->push_ready = true;
+  }
+  char *w = static_cast<char *>(h->workspace) + skinny_ws;
+  char *db = w, *dc = db + round256(nb), *dbias = dc + round256(nc);
+  // Two staging copies of lhs per rank, used in turn: a peer may still multiply
+  // out of one while the next call's rows arrive in the other (calls are at most
+  // one apart across ranks, because each waits for every peer's rows of ITS call).
+  const size_t a_bytes = static_cast<size_t>(m_total) * K * esz_a;
+  const size_t half = (ctx->seq & 1u) ? ((a_bytes + 255) & ~static_cast<size_t>(255)) : 0;
+  char *da = static_cast<char *>(ctx->peer_lhs[rank]) + half;
+
+  constexpr int kMaxChunks = 16;
+  cudaEvent_t ev_start = h->ev[2 * kMaxChunks], ev_done = h->ev[2 * kMaxChunks + 1];
+  CUDA_TRY(h, cudaEventRecord(ev_start, stream));
+  CUDA_TRY(h, cudaStreamWaitEvent(h->copy_in, ev_start, 0));
+  CUDA_TRY(h, cudaStreamWaitEvent(h->copy_out, ev_start, 0));
+  CUDA_TRY(h, cudaStreamWaitEvent(h->push, ev_start, 0));
+
+  // 1. this rank's rows go up in pieces; each piece is forwarded to every peer's
+  //    staging copy over NVLink (copy engines, stores only) as soon as it has landed
+  const char *ha = static_cast<const char *>(elem_ptr(lhs_rows));
+  const size_t row_bytes = static_cast<size_t>(K) * esz_a;
+  const size_t mine_off = static_cast<size_t>(row_begin) * row_bytes;
+  const int pieces = rows_mine >= 1024 ? 4 : 1;
+  const int rows_per_piece = (rows_mine + pieces - 1) / pieces;
+  int n_pieces = 0;
+  for (int r0 = 0; r0 < rows_mine; r0 += rows_per_piece, ++n_pieces) {
+    const int rows = std::min(rows_per_piece, rows_mine - r0);
+    const size_t off = mine_off + static_cast<size_t>(r0) * row_bytes;
+    const size_t bytes = static_cast<size_t>(rows) * row_bytes;
+    CUDA_TRY(h, cudaMemcpyAsync(da + off, ha + static_cast<size_t>(r0) * row_bytes, bytes,
+                                cudaMemcpyHostToDevice, h->copy_in));
+    CUDA_TRY(h, cudaEventRecord(h->ev_push[n_pieces], h->copy_in));
+    CUDA_TRY(h, cudaStreamWaitEvent(h->push, h->ev_push[n_pieces], 0));
+    for (int i = 1; i < world; ++i) {
+      const int peer = (rank + i) % world;  // ranks start with different peers
+      CUDA_TRY(h, cudaMemcpyAsync(static_cast<char *>(ctx->peer_lhs[peer]) + half + off, da + off,
+                                  bytes, cudaMemcpyDeviceToDevice, h->push));
+    }
+  }
+  st = kapyb_gather_signal(h, ctx->peer_flags, world, rank, ctx->seq, h->push);
+  if (st != KAPYB_OK) return st;
+  // (this rank's own word is set by that kernel: the compute stream is ordered
+  // after it by an event, never by polling for a kernel of the same GPU)
+  CUDA_TRY(h, cudaEventRecord(h->ev_push[15], h->push));
+  // 2. the column shard of rhs and the bias follow on the same PCIe link
+  CUDA_TRY(h, cudaMemcpyAsync(db, elem_ptr(rhs), nb, cudaMemcpyHostToDevice, h->copy_in));
+  kapyb_epilogue ep;
+  if (epilogue)
+    ep = *epilogue;
+  else {
+    ep.alpha = 1.0f;
+    ep.bias = nullptr;
+    ep.bias_dtype = KAPYB_F32;
+    ep.bias_axis = 1;
+    ep.activation = KAPYB_ACT_NONE;
+    ep.rounding = KAPYB_RN;
+  }
+  if (nbias) {
+    CUDA_TRY(h, cudaMemcpyAsync(dbias, ep.bias, nbias, cudaMemcpyHostToDevice, h->copy_in));
+    ep.bias = dbias;
+  }
+  CUDA_TRY(h, cudaEventRecord(h->ev_push[16], h->copy_in));
+  CUDA_TRY(h, cudaStreamWaitEvent(stream, h->ev_push[16], 0));
+  CUDA_TRY(h, cudaStreamWaitEvent(stream, h->ev_push[15], 0));
+  // 3. wait (bounded) until every rank's rows have landed here, then multiply row
+  //    chunk by row chunk, each chunk's download overlapping the next one's GEMM
+  st = kapyb_gather_wait(h, ctx->peer_flags[rank], world, ctx->seq, ctx->wait_limit_ms, stream);
+  if (st != KAPYB_OK) return st;
+  kapyb_tensor2d dl = full, dr = *rhs, dout = *out;
+  dl.ptr = da;
+  dl.offset_elems = 0;
+  dr.ptr = db;
+  dr.offset_elems = 0;
+  dout.ptr = dc;
+  dout.offset_elems = 0;
+  char *hc = static_cast<char *>(const_cast<void *>(elem_ptr(out)));
+  const int rows_per = host_chunk_rows(m_total, rhs->size1, h->sm_count, kMaxChunks);
+  int n_chunks = 0;
+  for (int r0 = 0; r0 < m_total; r0 += rows_per, ++n_chunks) {
+    const int rows = std::min(rows_per, m_total - r0);
+    kapyb_tensor2d cl = dl, co = dout;
+    cl.offset_elems = static_cast<int64_t>(r0) * K;
+    cl.size0 = rows;
+    co.offset_elems = static_cast<int64_t>(r0) * out->stride0;
+    co.size0 = rows;
+    kapyb_epilogue cep = ep;
+    if (cep.bias && cep.bias_axis == 0)
+      cep.bias = static_cast<const char *>(cep.bias) + static_cast<size_t>(r0) * dtype_size(cep.bias_dtype);
+    st = run_matmul(h, make_problem(&cl, &dr, nullptr, &co, &cep), nullptr, 0, stream);
+    if (st != KAPYB_OK) return st;
+    CUDA_TRY(h, cudaEventRecord(h->ev[2 * n_chunks + 1], stream));
+    CUDA_TRY(h, cudaStreamWaitEvent(h->copy_out, h->ev[2 * n_chunks + 1], 0));
+    const size_t c_off = static_cast<size_t>(r0) * out->stride0 * esz_c;
+    CUDA_TRY(h, cudaMemcpyAsync(hc + c_off, dc + c_off, static_cast<size_t>(rows) * out->stride0 * esz_c,
+                                cudaMemcpyDeviceToHost, h->copy_out));
+  }
+  CUDA_TRY(h, cudaEventRecord(ev_done, h->copy_out));
+  CUDA_TRY(h, cudaStreamWaitEvent(stream, ev_done, 0));
+  return kapyb_check(h, stream);
+}
+
 // ------------------------------------------------------------- elementwise
 
 static kapyb_status verify_program(kapyb_handle h, const kapyb_inst *prog, int n_inst,
@@ -1345,7 +1580,12 @@ static kapyb_status verify_program(kapyb_handle h, const kapyb_inst *prog, int n
     case KAPYB_OP_LOAD:
     case KAPYB_OP_CONST: nsrc = 0; break;
     case KAPYB_OP_FMA:
+    case KAPYB_OP_SELECT:
     case KAPYB_OP_CLAMP: nsrc = 3; break;
+    case KAPYB_OP_CMP:
+    case KAPYB_OP_AND:
+    case KAPYB_OP_OR:
+    case KAPYB_OP_XOR:
     case KAPYB_OP_ADD:
     case KAPYB_OP_SUB:
     case KAPYB_OP_MUL:
@@ -1369,13 +1609,41 @@ static kapyb_status verify_program(kapyb_handle h, const kapyb_inst *prog, int n
       ++stores;
       continue;
     }
+    if (in.dst < 0 || in.dst >= KAPYB_MAX_REGS)
+      return fail(h, KAPYB_INVALID_ARG, "elementwise: op %d writes register %d", pc, in.dst);
+    // Conditions: arith.cmpf yields i1 from two operands of one float type;
+    // and/or/xor combine conditions; arith.select picks between two values of
+    // the result type.
+    if (in.op == KAPYB_OP_CMP) {
+      const int ot = reg_dtype[in.a];
+      if (in.dtype != KAPYB_I1 || !valid_dtype(ot) || reg_dtype[in.b] != ot)
+        return fail(h, KAPYB_INVALID_ARG,
+                    "elementwise: op %d (cmpf) needs two operands of one f16/bf16/f32 type and an i1 result", pc);
+      if (in.flags < KAPYB_CMP_OLT || in.flags > KAPYB_CMP_UNE)
+        return fail(h, KAPYB_INVALID_ARG, "elementwise: op %d has an unknown cmpf predicate %d", pc, in.flags);
+      reg_dtype[in.dst] = KAPYB_I1;
+      continue;
+    }
+    if (in.op == KAPYB_OP_AND || in.op == KAPYB_OP_OR || in.op == KAPYB_OP_XOR) {
+      if (in.dtype != KAPYB_I1 || reg_dtype[in.a] != KAPYB_I1 || reg_dtype[in.b] != KAPYB_I1)
+        return fail(h, KAPYB_INVALID_ARG, "elementwise: op %d combines i1 conditions only", pc);
+      reg_dtype[in.dst] = KAPYB_I1;
+      continue;
+    }
+    if (in.op == KAPYB_OP_SELECT) {
+      if (reg_dtype[in.a] != KAPYB_I1)
+        return fail(h, KAPYB_INVALID_ARG, "elementwise: op %d (select) needs an i1 condition", pc);
+      if (!valid_dtype(in.dtype) || reg_dtype[in.b] != in.dtype || reg_dtype[in.c] != in.dtype)
+        return fail(h, KAPYB_INVALID_ARG,
+                    "elementwise: op %d (select) requires the same element type for both values and the result", pc);
+      reg_dtype[in.dst] = in.dtype;
+      continue;
+    }
     if (!valid_operand_dtype(in.dtype))
       return fail(h, KAPYB_INVALID_ARG, "elementwise: op %d has a bad element type", pc);
     // the 8-bit types exist in memory and across casts only
     if (is_fp8(in.dtype) && in.op != KAPYB_OP_LOAD && in.op != KAPYB_OP_CVT)
       return fail(h, KAPYB_INVALID_ARG, "elementwise: op %d cannot compute in an f8 element type", pc);
-    if (in.dst < 0 || in.dst >= KAPYB_MAX_REGS)
-      return fail(h, KAPYB_INVALID_ARG, "elementwise: op %d writes register %d", pc, in.dst);
     if (in.op == KAPYB_OP_LOAD) {
       if (in.flags < 0 || in.flags >= n_inputs)
         return fail(h, KAPYB_INVALID_ARG, "elementwise: ld_global of input %d, but %d given", in.flags, n_inputs);
@@ -1551,12 +1819,50 @@ extern "C" KAPYB_API kapyb_status kapyb_elementwise(kapyb_handle h, const kapyb_
   CUDA_TRY(h, cudaSetDevice(h->device));
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
 
+  // Output against inputs.  The streaming kernels read through the read-only
+  // data path (ld.global.nc, __restrict__), which must not see memory the same
+  // kernel writes.  An input that IS the output (same address, shape, strides
+  // and element type: an in-place update, each element read before it is
+  // written by the same thread) runs on the interpreter kernel, which uses plain
+  // loads; any other overlap would make the result depend on thread timing and
+  // is refused.
+  bool in_place = false;
+  {
+    auto byte_range = [](const kapyb_tensor2d &t, uintptr_t *lo, uintptr_t *hi) {
+      const int64_t e0 = static_cast<int64_t>(t.size0 - 1) * t.stride0;
+      const int64_t e1 = static_cast<int64_t>(t.size1 - 1) * t.stride1;
+      const int64_t mn = std::min<int64_t>(0, e0) + std::min<int64_t>(0, e1);
+      const int64_t mx = std::max<int64_t>(0, e0) + std::max<int64_t>(0, e1);
+      const int64_t esz = dtype_size(t.dtype);
+      const uintptr_t base = reinterpret_cast<uintptr_t>(elem_ptr(&t));
+      *lo = base + mn * esz;
+      *hi = base + (mx + 1) * esz;
+    };
+    uintptr_t olo, ohi;
+    byte_range(*out, &olo, &ohi);
+    for (int k = 0; k < n_inputs; ++k) {
+      const kapyb_tensor2d &t = inputs[k];
+      if (t.size0 == 0 || t.size1 == 0) continue;
+      uintptr_t ilo, ihi;
+      byte_range(t, &ilo, &ihi);
+      if (ihi <= olo || ohi <= ilo) continue;
+      const bool same = elem_ptr(&t) == elem_ptr(out) && t.size0 == out->size0 &&
+                        t.size1 == out->size1 && t.stride0 == out->stride0 &&
+                        t.stride1 == out->stride1 && t.dtype == out->dtype;
+      if (!same)
+        return fail(h, KAPYB_INVALID_ARG,
+                    "elementwise: the output overlaps input %d without being the same tensor "
+                    "(only an exact in-place update is defined)", k);
+      in_place = true;
+    }
+  }
+
   ExprNode nodes[KAPYB_MAX_INSTS];
   int root = -1;
   build_nodes(prog, n_inst, nodes, &root);
 
   // Fused path 0: a bare cast to or from an 8-bit float type, contiguous.
-  if (n_inst == 3 && prog[0].op == KAPYB_OP_LOAD && prog[1].op == KAPYB_OP_CVT &&
+  if (!in_place && n_inst == 3 && prog[0].op == KAPYB_OP_LOAD && prog[1].op == KAPYB_OP_CVT &&
       prog[2].op == KAPYB_OP_STORE && prog[1].a == prog[0].dst && prog[2].a == prog[1].dst &&
       (is_fp8(prog[0].dtype) != is_fp8(prog[1].dtype))) {
     const kapyb_tensor2d &tin = inputs[prog[0].flags];
@@ -1603,7 +1909,7 @@ extern "C" KAPYB_API kapyb_status kapyb_elementwise(kapyb_handle h, const kapyb_
   {
     AffineGelu f;
     int li = -1, din = 0, rn = 1;
-    if (match_affine_gelu(nodes, root, &f, &li, &din, &rn) &&
+    if (!in_place && match_affine_gelu(nodes, root, &f, &li, &din, &rn) &&
         (din == KAPYB_F16 || din == KAPYB_BF16) &&
         nodes[root].dtype == out->dtype && din == out->dtype && (rn == 0 || rn == 1) &&
         contiguous_same(inputs[li], *out) &&
@@ -1633,7 +1939,7 @@ extern "C" KAPYB_API kapyb_status kapyb_elementwise(kapyb_handle h, const kapyb_
     }
   }
   // Fused path 2: z = a (add|sub|mul) b, one element type, contiguous.
-  if (root >= 0 && n_inputs >= 2) {
+  if (!in_place && root >= 0 && n_inputs >= 2) {
     const ExprNode &r = nodes[root];
     if ((r.op == KAPYB_OP_ADD || r.op == KAPYB_OP_SUB || r.op == KAPYB_OP_MUL) && r.a >= 0 &&
         r.b >= 0 && nodes[r.a].op == KAPYB_OP_LOAD && nodes[r.b].op == KAPYB_OP_LOAD &&
@@ -1697,7 +2003,17 @@ extern "C" KAPYB_API kapyb_status kapyb_elementwise(kapyb_handle h, const kapyb_
 // ------------------------------------------------------------------ reduce
 
 template <int COMB, int DT>
-static void launch_reduce_rows(const ReduceParams &p, bool vec, int grid, cudaStream_t stream) {
+static void launch_reduce_rows(const ReduceParams &p, bool vec, bool narrow, int grid,
+                               cudaStream_t stream) {
+  if constexpr (DT != KAPYB_F32) {
+    if (narrow) {
+      if (vec)
+        reduce_rows_kernel<COMB, true, DT, true><<<grid, 256, 0, stream>>>(p);
+      else
+        reduce_rows_kernel<COMB, false, DT, true><<<grid, 256, 0, stream>>>(p);
+      return;
+    }
+  }
   if (vec)
     reduce_rows_kernel<COMB, true, DT><<<grid, 256, 0, stream>>>(p);
   else
@@ -1707,6 +2023,9 @@ static void launch_reduce_rows(const ReduceParams &p, bool vec, int grid, cudaSt
 template <int COMB>
 static void launch_reduce(const ReduceParams &p, bool unit_inner, bool vec, int sm_count,
                           cudaStream_t stream) {
+  // The lambda runs at the destination's element type: a 16-bit destination
+  // (necessarily the source's type) means a rounding to that type per step.
+  const bool narrow = p.dst_dtype != KAPYB_F32;
   if (unit_inner) {
     // One row per warp, as many blocks as that takes (capped far above a resident
     // wave): the block scheduler then walks the SMs through neighbouring rows,
@@ -1715,15 +2034,20 @@ static void launch_reduce(const ReduceParams &p, bool unit_inner, bool vec, int 
     const int grid = static_cast<int>(std::max(1ll, std::min(blocks, 1ll << 22)));
     (void)sm_count;
     if (p.src_dtype == KAPYB_F32)
-      launch_reduce_rows<COMB, KAPYB_F32>(p, vec, grid, stream);
+      launch_reduce_rows<COMB, KAPYB_F32>(p, vec, false, grid, stream);
     else if (p.src_dtype == KAPYB_BF16)
-      launch_reduce_rows<COMB, KAPYB_BF16>(p, vec, grid, stream);
+      launch_reduce_rows<COMB, KAPYB_BF16>(p, vec, narrow, grid, stream);
     else
-      launch_reduce_rows<COMB, KAPYB_F16>(p, vec, grid, stream);
+      launch_reduce_rows<COMB, KAPYB_F16>(p, vec, narrow, grid, stream);
   } else {
     const long long blocks = (static_cast<long long>(p.rows) + 31) / 32;
     const int grid = static_cast<int>(std::max(1ll, std::min(blocks, static_cast<long long>(sm_count) * 8)));
-    reduce_cols_kernel<COMB><<<grid, 256, 0, stream>>>(p);
+    if (narrow && p.dst_dtype == KAPYB_BF16)
+      reduce_cols_kernel<COMB, KAPYB_BF16><<<grid, 256, 0, stream>>>(p);
+    else if (narrow)
+      reduce_cols_kernel<COMB, KAPYB_F16><<<grid, 256, 0, stream>>>(p);
+    else
+      reduce_cols_kernel<COMB><<<grid, 256, 0, stream>>>(p);
   }
 }
 
@@ -1789,13 +2113,44 @@ static __device__ __align__(256) unsigned char g_decode_scratch[kStaticCounterBy
 static __device__ uint32_t g_decode_status;
 
 struct StaticDeviceState {
-  bool ready = false;
+  std::atomic<bool> ready{false};    // written last, with release ordering
   unsigned char *scratch = nullptr;  // device address of g_decode_scratch on this device
   uint32_t *status = nullptr;        // device address of g_decode_status on this device
   int sm_count = 0;
   EncodeTiledFn encode = nullptr;
 };
 static StaticDeviceState g_static_state[kMaxDevices];
+static std::mutex g_static_mu;  // serialises the one-time set-up per device
+
+// First call on device `dev` (which must be current): resolve where the static
+// arrays live there.  In host code the symbol name is only a stand-in, not a
+// device address, so the runtime is asked for the address.  Two threads that make
+// their first call at once are serialised; later calls take no lock.
+static kapyb_status static_state_init(int dev, StaticDeviceState &sd) {
+  std::lock_guard<std::mutex> lock(g_static_mu);
+  if (sd.ready.load(std::memory_order_acquire)) return KAPYB_OK;
+  cudaDeviceProp prop;
+  cudaError_t e = cudaGetDeviceProperties(&prop, dev);
+  if (e != cudaSuccess) return fail(nullptr, KAPYB_CUDA_ERROR, "matmul_decode_static: device properties: %s", cudaGetErrorString(e));
+  if (prop.major != 10)
+    return fail(nullptr, KAPYB_CUDA_ERROR, "matmul_decode_static: device %d is sm_%d%d; kernels are built for sm_100a only", dev, prop.major, prop.minor);
+  void *p_scratch = nullptr, *p_status = nullptr;
+  e = cudaGetSymbolAddress(&p_scratch, g_decode_scratch);
+  if (e != cudaSuccess) return fail(nullptr, KAPYB_CUDA_ERROR, "matmul_decode_static: cudaGetSymbolAddress(scratch): %s", cudaGetErrorString(e));
+  e = cudaGetSymbolAddress(&p_status, g_decode_status);
+  if (e != cudaSuccess) return fail(nullptr, KAPYB_CUDA_ERROR, "matmul_decode_static: cudaGetSymbolAddress(status): %s", cudaGetErrorString(e));
+  cudaDriverEntryPointQueryResult q;
+  void *fn = nullptr;
+  e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
+  if (e != cudaSuccess || fn == nullptr || q != cudaDriverEntryPointSuccess)
+    return fail(nullptr, KAPYB_CUDA_ERROR, "matmul_decode_static: cuTensorMapEncodeTiled not available");
+  sd.scratch = static_cast<unsigned char *>(p_scratch);
+  sd.status = static_cast<uint32_t *>(p_status);
+  sd.sm_count = prop.multiProcessorCount;
+  sd.encode = reinterpret_cast<EncodeTiledFn>(fn);
+  sd.ready.store(true, std::memory_order_release);
+  return KAPYB_OK;
+}
 
 extern "C" KAPYB_API kapyb_status kapyb_matmul_decode_static(const kapyb_tensor2d *lhs,
                                                              const kapyb_tensor2d *rhs,
@@ -1816,30 +2171,9 @@ extern "C" KAPYB_API kapyb_status kapyb_matmul_decode_static(const kapyb_tensor2
   if (dev < 0 || dev >= kMaxDevices)
     return fail(nullptr, KAPYB_UNSUPPORTED, "matmul_decode_static: device index %d not supported", dev);
   StaticDeviceState &sd = g_static_state[dev];
-  if (!sd.ready) {
-    // First call on this device: resolve where the static arrays live there.
-    // The symbol name is only a host-side stand-in, so ask the runtime for the
-    // device address while this device is current.
-    cudaDeviceProp prop;
-    e = cudaGetDeviceProperties(&prop, dev);
-    if (e != cudaSuccess) return fail(nullptr, KAPYB_CUDA_ERROR, "matmul_decode_static: device properties: %s", cudaGetErrorString(e));
-    if (prop.major != 10)
-      return fail(nullptr, KAPYB_CUDA_ERROR, "matmul_decode_static: device %d is sm_%d%d; kernels are built for sm_100a only", dev, prop.major, prop.minor);
-    void *p_scratch = nullptr, *p_status = nullptr;
-    e = cudaGetSymbolAddress(&p_scratch, g_decode_scratch);
-    if (e != cudaSuccess) return fail(nullptr, KAPYB_CUDA_ERROR, "matmul_decode_static: cudaGetSymbolAddress(scratch): %s", cudaGetErrorString(e));
-    e = cudaGetSymbolAddress(&p_status, g_decode_status);
-    if (e != cudaSuccess) return fail(nullptr, KAPYB_CUDA_ERROR, "matmul_decode_static: cudaGetSymbolAddress(status): %s", cudaGetErrorString(e));
-    cudaDriverEntryPointQueryResult q;
-    void *fn = nullptr;
-    e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
-    if (e != cudaSuccess || fn == nullptr || q != cudaDriverEntryPointSuccess)
-      return fail(nullptr, KAPYB_CUDA_ERROR, "matmul_decode_static: cuTensorMapEncodeTiled not available");
-    sd.scratch = static_cast<unsigned char *>(p_scratch);
-    sd.status = static_cast<uint32_t *>(p_status);
-    sd.sm_count = prop.multiProcessorCount;
-    sd.encode = reinterpret_cast<EncodeTiledFn>(fn);
-    sd.ready = true;
+  if (!sd.ready.load(std::memory_order_acquire)) {
+    const kapyb_status ist = static_state_init(dev, sd);
+    if (ist != KAPYB_OK) return ist;
   }
   ctx.device = dev;
   ctx.sm_count = sd.sm_count;
@@ -1880,6 +2214,9 @@ extern "C" KAPYB_API kapyb_status kapyb_matmul_decode_static(const kapyb_tensor2
   // anything after one that was cut short): clear the ones this call uses.  The
   // partial sums are written before they are read and need no clearing.
   e = cudaMemsetAsync(sd.scratch, 0, need_counters, stream);
+  // The status word is shared too: start this call from "no time-out", so that a
+  // checked call never reports what an earlier unchecked call left behind.
+  if (e == cudaSuccess) e = cudaMemsetAsync(sd.status, 0, sizeof(uint32_t), stream);
   if (e != cudaSuccess) return fail(nullptr, KAPYB_CUDA_ERROR, "matmul_decode_static: clearing scratch: %s", cudaGetErrorString(e));
   st = launch_skinny_on(&ctx, p, a_mn, b_mn,
                         reinterpret_cast<float *>(sd.scratch + kStaticCounterBytes),

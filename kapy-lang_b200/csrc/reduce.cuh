@@ -2,8 +2,15 @@
 // within a lane, then butterflies across the warp with shfl.sync.bfly
 // (ReduceOpToLLVM.cpp:76-119); here one warp owns one row (axis 1), reads it
 // with 256-bit coalesced loads, folds in registers and finishes with the same
-// xor-shuffle tree.  Values are widened to f32 before combining; a 16-bit
-// destination is rounded once at the end.
+// xor-shuffle tree.
+//
+// The lambda runs at the element type of the tensor it reduces
+// (ReduceOpToLLVM.cpp:76-119 calls the region on values of that type).  When
+// the destination is f32 the source is widened first (arith.extf ahead of the
+// reduce) and the combiner works in f32.  When source and destination are the
+// same 16-bit type (reduce_sum.mlir:10-25 adds in f16) every combination is
+// rounded to that type, as the reference's add.f16 / fma.rn.bf16 would: the
+// accumulators then hold values of the 16-bit type at every step (NARROW).
 #pragma once
 
 #include "common.cuh"
@@ -18,8 +25,24 @@ struct ReduceParams {
   int src_dtype, dst_dtype, combiner;
 };
 
-template <int COMB>
+// One rounding at a 16-bit type (operands exactly representable in it):
+// add = fma(a, 1, b), mul = fma(a, b, -0) as ElementwiseOpToLLVM.cpp:771-892.
+template <int DT>
+__device__ __forceinline__ float fma16(float a, float b, float c) {
+  if constexpr (DT == KAPYB_BF16)
+    return __bfloat162float(
+        __hfma(__float2bfloat16_rn(a), __float2bfloat16_rn(b), __float2bfloat16_rn(c)));
+  else
+    return __half2float(__hfma(__float2half_rn(a), __float2half_rn(b), __float2half_rn(c)));
+}
+
+// NT: KAPYB_F32 combines in f32; KAPYB_F16 / KAPYB_BF16 round every result to that type.
+template <int COMB, int NT = KAPYB_F32>
 __device__ __forceinline__ float combine(float a, float b) {
+  if constexpr (NT != KAPYB_F32) {
+    if (COMB == KAPYB_RED_ADD) return fma16<NT>(a, 1.0f, b);
+    if (COMB == KAPYB_RED_MUL) return fma16<NT>(a, b, -0.0f);
+  }
   if (COMB == KAPYB_RED_ADD) return __fadd_rn(a, b);
   if (COMB == KAPYB_RED_MUL) return __fmul_rn(a, b);
   if (COMB == KAPYB_RED_MAX) return (a != a || b != b) ? __uint_as_float(0x7fffffffu) : fmaxf(a, b);
@@ -34,10 +57,11 @@ __device__ __forceinline__ float identity() {
   return __uint_as_float(0x7f800000u);
 }
 
-template <int COMB>
+template <int COMB, int NT = KAPYB_F32>
 __device__ __forceinline__ float warp_reduce(float v) {
 #pragma unroll
-  for (int off = 16; off > 0; off >>= 1) v = combine<COMB>(v, __shfl_xor_sync(0xffffffffu, v, off));
+  for (int off = 16; off > 0; off >>= 1)
+    v = combine<COMB, NT>(v, __shfl_xor_sync(0xffffffffu, v, off));
   return v;
 }
 
@@ -55,16 +79,16 @@ __device__ __forceinline__ Vec32B ld_nc_v8(const void *p) {
   return v;
 }
 
-template <int COMB, int DT>
+template <int COMB, int DT, int NT>
 __device__ __forceinline__ float fold_vec(float acc, const Vec32B &v) {
 #pragma unroll
   for (int k = 0; k < 8; ++k) {
     if constexpr (DT == KAPYB_F32) {
-      acc = combine<COMB>(acc, __uint_as_float(v.w[k]));
+      acc = combine<COMB, NT>(acc, __uint_as_float(v.w[k]));
     } else {
       float lo, hi;
       unpack2_16<DT>(v.w[k], lo, hi);
-      acc = combine<COMB>(combine<COMB>(acc, lo), hi);
+      acc = combine<COMB, NT>(combine<COMB, NT>(acc, lo), hi);
     }
   }
   return acc;
@@ -75,9 +99,14 @@ constexpr int kReduceUnroll = 8;
 // One warp per row; the reduced axis is contiguous.  VEC: every row starts on a
 // 32-byte boundary, so the row is read with 256-bit loads, eight in flight per
 // lane (8 KB per warp: one whole row of 4096 16-bit values).  !VEC: scalar loads
-// with any strides.
-template <int COMB, bool VEC, int DT>
+// with any strides.  NARROW: combine at DT (a 16-bit type) with a rounding per step.
+// Order of combination (fixed, so a result is the same bits from run to run):
+// lane l folds its elements in ascending order into up to four accumulators,
+// which are joined as (a0 + a1) + (a2 + a3); the lanes then meet in a butterfly
+// over lane distances 16, 8, 4, 2, 1.
+template <int COMB, bool VEC, int DT, bool NARROW = false>
 __global__ void __launch_bounds__(256) reduce_rows_kernel(const ReduceParams p) {
+  constexpr int NT = NARROW ? DT : KAPYB_F32;
   const int lane = threadIdx.x & 31;
   const int warps_per_block = blockDim.x >> 5;
   const long long warp_global =
@@ -98,17 +127,17 @@ __global__ void __launch_bounds__(256) reduce_rows_kernel(const ReduceParams p) 
 #pragma unroll
         for (int u = 0; u < kReduceUnroll; ++u) v[u] = ld_nc_v8(base + (i + 32 * u) * 32ll);
 #pragma unroll
-        for (int u = 0; u < kReduceUnroll; ++u) acc[u & 3] = fold_vec<COMB, DT>(acc[u & 3], v[u]);
+        for (int u = 0; u < kReduceUnroll; ++u) acc[u & 3] = fold_vec<COMB, DT, NT>(acc[u & 3], v[u]);
       }
-      for (; i < n_vec; i += 32) acc[0] = fold_vec<COMB, DT>(acc[0], ld_nc_v8(base + i * 32ll));
+      for (; i < n_vec; i += 32) acc[0] = fold_vec<COMB, DT, NT>(acc[0], ld_nc_v8(base + i * 32ll));
       for (int e = n_vec * per + lane; e < p.cols; e += 32)
-        acc[1] = combine<COMB>(acc[1], load_as_f32(base, DT, e));
+        acc[1] = combine<COMB, NT>(acc[1], load_as_f32(base, DT, e));
     } else {
       for (int e = lane; e < p.cols; e += 32)
-        acc[0] = combine<COMB>(acc[0], load_as_f32(base, DT, e * p.src_col_stride));
+        acc[0] = combine<COMB, NT>(acc[0], load_as_f32(base, DT, e * p.src_col_stride));
     }
-    float r = combine<COMB>(combine<COMB>(acc[0], acc[1]), combine<COMB>(acc[2], acc[3]));
-    r = warp_reduce<COMB>(r);
+    float r = combine<COMB, NT>(combine<COMB, NT>(acc[0], acc[1]), combine<COMB, NT>(acc[2], acc[3]));
+    r = warp_reduce<COMB, NT>(r);
     if (lane == 0) store_from_f32(p.dst, p.dst_dtype, row * p.dst_stride, r, 1);
   }
 }
@@ -116,7 +145,8 @@ __global__ void __launch_bounds__(256) reduce_rows_kernel(const ReduceParams p) 
 // Reduction along the strided axis (column results of a row-major tensor):
 // 32 consecutive results per warp so loads stay coalesced; the 8 warps of a
 // block split the reduced axis and meet in shared memory.
-template <int COMB>
+// NT as in combine(): KAPYB_F32, or the 16-bit type every combination is rounded to.
+template <int COMB, int NT = KAPYB_F32>
 __global__ void __launch_bounds__(256) reduce_cols_kernel(const ReduceParams p) {
   __shared__ float part[8][33];
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
@@ -126,15 +156,15 @@ __global__ void __launch_bounds__(256) reduce_cols_kernel(const ReduceParams p) 
     float acc = identity<COMB>();
     if (r < p.rows) {
       for (int e = w; e < p.cols; e += 8)
-        acc = combine<COMB>(acc, load_as_f32(p.src, p.src_dtype,
-                                             r * p.src_row_stride + e * p.src_col_stride));
+        acc = combine<COMB, NT>(acc, load_as_f32(p.src, p.src_dtype,
+                                                 r * p.src_row_stride + e * p.src_col_stride));
     }
     part[w][lane] = acc;
     __syncthreads();
     if (w == 0 && r < p.rows) {
       float t = part[0][lane];
 #pragma unroll
-      for (int k = 1; k < 8; ++k) t = combine<COMB>(t, part[k][lane]);
+      for (int k = 1; k < 8; ++k) t = combine<COMB, NT>(t, part[k][lane]);
       store_from_f32(p.dst, p.dst_dtype, r * p.dst_stride, t, 1);
     }
     __syncthreads();

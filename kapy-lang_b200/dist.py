@@ -13,6 +13,10 @@ matrix, in which case there are two ways to assemble it:
     straight into all peers' full-size outputs through peer-mapped pointers
     (``kapyb_matmul_push``), so the transfer overlaps the main loop tile by
     tile and no staging copy exists.  Only stores cross NVLink.
+
+Ranks meet through flag words the library's own kernels write and poll with a
+time limit (``RankFlags``), so a missing peer becomes ``KapybTimeout``.
+``ShardedHostMatmul`` is the end-to-end form for host tensors.
 """
 from __future__ import annotations
 
@@ -70,6 +74,39 @@ def sharded_matmul(handle, lhs, rhs_shard, spans, *, bias_shard=None, gather: st
     raise ValueError("gather must be 'none' or 'nccl' (use PushGather for the fused variant)")
 
 
+class RankFlags:
+    """One flag word per rank in every rank's symmetric memory, and the sequence
+    number the ranks count together (kapyb_gather_signal / kapyb_gather_wait)."""
+
+    def __init__(self, device, group=None):
+        import torch
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+        self.group = group or dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        # 64 words: the array the library's kernels index by rank
+        self.words = symm.empty((64,), dtype=torch.int32, device=device)
+        self.words.zero_()
+        self.hdl = symm.rendezvous(self.words, group=self.group)
+        self.ptrs = [int(p) for p in self.hdl.buffer_ptrs]
+        torch.cuda.synchronize(device)
+        dist.barrier(self.group)      # nobody signals before every array is zero
+        self.seq = 0
+
+    def next(self) -> int:
+        self.seq += 1
+        return self.seq
+
+    def signal_and_wait(self, handle, limit_ms: int = 0, stream=None) -> int:
+        """Announces this rank's work so far on the stream to every rank, then
+        waits (bounded, on the stream) for the same announcement from all."""
+        seq = self.next()
+        handle.gather_signal(self.ptrs, self.rank, seq, stream=stream)
+        handle.gather_wait(self.ptrs[self.rank], self.world, seq, limit_ms, stream=stream)
+        return seq
+
+
 class PushGather:
     """Full-size outputs in symmetric memory plus the fused push epilogue."""
 
@@ -86,15 +123,54 @@ class PushGather:
         r = dist.get_rank(self.group)
         self.peer_ptrs = [ptrs[(r + 1 + i) % len(ptrs)] for i in range(len(ptrs))]
         self.M, self.n_total, self.dtype = M, n_total, dtype
+        self.flags = RankFlags(device, self.group)
+        self._handle = None
 
     def matmul(self, handle, lhs, rhs_shard, col_begin: int, *, bias_shard=None, **epilogue):
         """Runs this rank's shard and stores it into every rank's `full`."""
+        self._handle = handle
         handle.matmul_push(lhs, rhs_shard, self.peer_ptrs, out_dtype=self.dtype,
                            out_stride0=self.n_total, col_begin=col_begin, n_total=self.n_total,
                            bias=bias_shard, **epilogue)
 
-    def wait(self):
-        """Stream-ordered barrier: after it, every peer's stores into `full` have
-        been issued and completed on their streams."""
-        self.hdl.barrier(channel=0)
+    def wait(self, limit_ms: int = 0):
+        """Stream-ordered and bounded: after it, every peer's stores into this
+        rank's `full` have landed.  The ranks meet through the library's flag
+        words; a peer that never arrives surfaces as KapybTimeout in
+        handle.check(), not as a hang."""
+        if self._handle is None:
+            raise RuntimeError("PushGather.wait() before matmul()")
+        self.flags.signal_and_wait(self._handle, limit_ms)
         return self.full
+
+
+class ShardedHostMatmul:
+    """End-to-end matmul on host tensors across the ranks of one box.  The
+    output is sharded by columns; the UPLOAD of lhs is sharded by rows (each rank
+    sends its rows over PCIe once and forwards them to its peers over NVLink),
+    so the host-side traffic per step does not grow with the number of GPUs."""
+
+    def __init__(self, m_total: int, k: int, dtype, device, group=None):
+        import torch
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+        self.group = group or dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        self.m_total, self.k = m_total, k
+        esz = torch.empty((), dtype=dtype).element_size()
+        half = (m_total * k * esz + 255) // 256 * 256
+        # two staging copies of lhs, used in turn (see kapyb_shard_ctx)
+        self.staging = symm.empty((2 * half,), dtype=torch.uint8, device=device)
+        self.hdl = symm.rendezvous(self.staging, group=self.group)
+        self.lhs_ptrs = [int(p) for p in self.hdl.buffer_ptrs]
+        self.flags = RankFlags(device, self.group)
+        self.rows = runtime.shard_range(m_total, self.world, self.rank, 256)
+
+    def __call__(self, handle, lhs_rows, rhs_shard, out, *, wait_limit_ms: int = 0, **epilogue):
+        """lhs_rows: host rows [self.rows[0], self.rows[1]) of lhs; rhs_shard: this
+        rank's host column block of B; out: host [m_total, n_local]."""
+        return handle.matmul_host_sharded(
+            lhs_rows, self.m_total, self.rows[0], rhs_shard, out, peer_lhs_ptrs=self.lhs_ptrs,
+            peer_flag_ptrs=self.flags.ptrs, rank=self.rank, seq=self.flags.next(),
+            wait_limit_ms=wait_limit_ms, **epilogue)

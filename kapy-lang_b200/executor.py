@@ -40,7 +40,8 @@ class Unsupported(NotImplementedError):
 
 
 _DT = {"f16": abi.F16, "bf16": abi.BF16, "f32": abi.F32, "f8e4m3": abi.F8E4M3,
-       "f8e5m2": abi.F8E5M2}  # the f8 types: matmul operands only (the library checks)
+       "f8e5m2": abi.F8E5M2,  # the f8 types: matmul operands only (the library checks)
+       "i1": abi.I1}          # conditions of arith.select inside an elementwise graph
 
 
 _ESZ = {abi.F16: 2, abi.BF16: 2, abi.F32: 4, abi.F8E4M3: 1, abi.F8E5M2: 1}
@@ -131,6 +132,7 @@ _OPCODES = {
     "math.cos": abi.OP_COS, "math.floor": abi.OP_FLOOR, "math.ceil": abi.OP_CEIL,
     "arith.extf": abi.OP_CVT, "arith.truncf": abi.OP_CVT, "kapy.fptofp": abi.OP_CVT,
 }
+_I1_LOGIC = {"arith.andi": abi.OP_AND, "arith.ori": abi.OP_OR, "arith.xori": abi.OP_XOR}
 _COMBINERS = {"arith.addf": abi.RED_ADD, "arith.mulf": abi.RED_MUL,
               "arith.maximumf": abi.RED_MAX, "arith.minimumf": abi.RED_MIN}
 
@@ -287,6 +289,25 @@ class _Lifter:
             shape = t.shape if isinstance(t, ir.TensorType) else (1, 1)
             E[op.results[0]] = Expr("op", _dtype(t), shape, name=n,
                                     args=tuple(self.expr(o) for o in op.operands), attrs=attrs)
+        elif n == "arith.cmpf" and self._register_tensor(op.results[0].type):
+            # a condition over register tensors: part of an elementwise graph
+            t = op.results[0].type
+            pred = str(op.attrs.get("predicate", "")).lower()
+            if pred not in abi.CMP_PREDICATES:
+                raise Unsupported(f"cmpf predicate {pred!r} is not one Builder.create_cmpf_* offers")
+            E[op.results[0]] = Expr("op", abi.I1, t.shape, name=n,
+                                    args=tuple(self.expr(o) for o in op.operands),
+                                    attrs={"predicate": abi.CMP_PREDICATES.index(pred)})
+        elif n in _I1_LOGIC and self._register_tensor(op.results[0].type) and \
+                op.results[0].type.element.kind == "i1":
+            t = op.results[0].type
+            E[op.results[0]] = Expr("op", abi.I1, t.shape, name=n,
+                                    args=tuple(self.expr(o) for o in op.operands), attrs={})
+        elif n == "arith.select" and self._register_tensor(op.results[0].type) and \
+                op.results[0].type.element.is_float():
+            t = op.results[0].type
+            E[op.results[0]] = Expr("op", _dtype(t), t.shape, name=n,
+                                    args=tuple(self.expr(o) for o in op.operands), attrs={})
         elif n == "kapy.elementwise_extern_lib":
             if op.attrs.get("sym_name") != "__nv_tanhf":
                 raise Unsupported(f"extern function {op.attrs.get('sym_name')} is not available")
@@ -328,6 +349,10 @@ class _Lifter:
             pass   # plumbing of the software pipeline; followed structurally by trace_root()
         else:
             raise Unsupported(f"op {n} cannot be lifted")
+
+    @staticmethod
+    def _register_tensor(t) -> bool:
+        return isinstance(t, ir.TensorType) and t.memory == ir.MemorySpace.REGISTER_FILE
 
     # ---- matmul idiom ------------------------------------------------------
     def trace_roots(self, v: ir.Value, seen=None) -> set:
@@ -454,6 +479,12 @@ class _Program:
             s = srcs + [-1] * (3 - len(srcs))
             if e.name == "tanh":
                 code, flags = abi.OP_TANH, 0
+            elif e.name == "arith.cmpf":
+                code, flags = abi.OP_CMP, int(e.attrs["predicate"])
+            elif e.name == "arith.select":
+                code, flags = abi.OP_SELECT, 0
+            elif e.name in _I1_LOGIC:
+                code, flags = _I1_LOGIC[e.name], 0
             else:
                 code = _OPCODES[e.name]
                 flags = e.attrs.get("rounding", 0) if code == abi.OP_CVT else \

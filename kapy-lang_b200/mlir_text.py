@@ -246,9 +246,12 @@ class _Parser:
             return self.add(blk, env, res, ir.Operation(name, [V(parts[1]), V(parts[2])], [rt],
                                                         {"predicate": parts[0]}))
         if name == "arith.select":
-            ops, _, t = rest.rpartition(":")
+            # "%c, %a, %b : T" with a scalar condition, "... : tensor<..xi1>, T" with a
+            # tensor of conditions: the result type is the last one
+            ops, _, t = rest.partition(":")
             return self.add(blk, env, res,
-                            ir.Operation(name, [V(o) for o in _split_top(ops)], [self.ty(t)]))
+                            ir.Operation(name, [V(o) for o in _split_top(ops)],
+                                         [self.ty(_split_top(t)[-1])]))
         if name in _CASTS:
             mm = re.match(r"(%[\w#]+)\s*(\{.*\})?\s*:\s*(.+?)\s+to\s+(.+)$", rest)
             if not mm:

@@ -22,7 +22,7 @@ import numpy as np
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _SO = os.path.join(_HERE, "_build", "libkapy_oracle.so")
 
-F16, BF16, F32, F8E4M3, F8E5M2 = 0, 1, 2, 3, 4
+F16, BF16, F32, F8E4M3, F8E5M2, I1 = 0, 1, 2, 3, 4, 5
 RZ, RN = 0, 1
 PAD_ZERO, PAD_QNAN, PAD_PINF, PAD_NINF = 0, 1, 2, 3
 ACT_NONE, ACT_RELU, ACT_GELU_TANH, ACT_SILU = 0, 1, 2, 3
@@ -68,8 +68,7 @@ _lib = None
 def lib():
     global _lib
     if _lib is None:
-        if not os.path.exists(_SO):
-            build()
+        build()     # compiles only when the source is newer than the library
         L = C.CDLL(_SO)
         L.ko_bf16_to_f32.restype = C.c_float
         L.ko_bf16_to_f32.argtypes = [C.c_uint16]
@@ -102,6 +101,8 @@ def lib():
         L.ko_max_rel_err.restype = C.c_double
         L.ko_max_rel_err.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.POINTER(C.c_double)]
         L.ko_num_threads.restype = C.c_int
+        L.ko_set_num_threads.restype = C.c_int
+        L.ko_set_num_threads.argtypes = [C.c_int]
         _lib = L
     return _lib
 
@@ -272,6 +273,12 @@ def rowsum_bf16_f32(x_bits: np.ndarray) -> np.ndarray:
 
 def num_threads() -> int:
     return int(lib().ko_num_threads())
+
+
+def set_num_threads(n: int = 0) -> int:
+    """Threads the OpenMP loops use from now on (0: every processor this process
+    may run on, whatever OMP_NUM_THREADS a launcher exported)."""
+    return int(lib().ko_set_num_threads(int(n)))
 
 
 def ulp_diff(a_bits: np.ndarray, b_bits: np.ndarray) -> np.ndarray:

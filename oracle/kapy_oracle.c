@@ -311,6 +311,26 @@ static double ko_minnum(double a, double b) {
   return ko_minimum(a, b);
 }
 
+/* arith.cmpf with the predicates Builder.create_cmpf_* binds (ir.cc:941-1000):
+ * ordered predicates are false and unordered ones true when an operand is NaN. */
+static int ko_cmpf(int pred, double a, double b) {
+  const int un = isnan(a) || isnan(b);
+  switch (pred) {
+  case KAPYB_CMP_OLT: return !un && a < b;
+  case KAPYB_CMP_OGT: return !un && a > b;
+  case KAPYB_CMP_OLE: return !un && a <= b;
+  case KAPYB_CMP_OGE: return !un && a >= b;
+  case KAPYB_CMP_OEQ: return !un && a == b;
+  case KAPYB_CMP_ONE: return !un && a != b;
+  case KAPYB_CMP_ULT: return un || a < b;
+  case KAPYB_CMP_UGT: return un || a > b;
+  case KAPYB_CMP_ULE: return un || a <= b;
+  case KAPYB_CMP_UGE: return un || a >= b;
+  case KAPYB_CMP_UEQ: return un || a == b;
+  default: return un || a != b;
+  }
+}
+
 /* The gelu_tanh composite in the form the benchmark graph pins:
  * u / (1 + exp(-2k)), k = c0 * fma(c1*u*u, u, u), evaluated here in double from
  * a given u (transcendental step exact, as the tolerance rule requires). */
@@ -389,6 +409,11 @@ KO_API int ko_eltwise(const kapyb_inst *prog, int n_inst, const kapyb_tensor2d *
         case KAPYB_OP_FLOOR: v = floor(a); break;
         case KAPYB_OP_CEIL: v = ceil(a); break;
         case KAPYB_OP_TANH: v = ko_round_to(tanh(a), in.dtype, 1); break;
+        case KAPYB_OP_CMP: v = ko_cmpf(in.flags, a, b) ? 1.0 : 0.0; break;
+        case KAPYB_OP_SELECT: v = a != 0.0 ? b : c; break; /* arith.select (ir.cc:1162) */
+        case KAPYB_OP_AND: v = (a != 0.0 && b != 0.0) ? 1.0 : 0.0; break;
+        case KAPYB_OP_OR: v = (a != 0.0 || b != 0.0) ? 1.0 : 0.0; break;
+        case KAPYB_OP_XOR: v = ((a != 0.0) != (b != 0.0)) ? 1.0 : 0.0; break;
         case KAPYB_OP_STORE:
           ko_store(out->ptr, out->dtype,
                    out->offset_elems + i * (int64_t)out->stride0 + j * (int64_t)out->stride1, a);
@@ -629,6 +654,20 @@ KO_API double ko_max_rel_err(const double *c, const double *ref, int64_t n, doub
   }
   if (tau_out) *tau_out = tau;
   return worst;
+}
+
+/* Sets the number of OpenMP threads later calls use (n <= 0: one per processor
+ * this process may run on).  A launcher may have exported OMP_NUM_THREADS=1;
+ * the timed CPU baseline must not inherit that. */
+KO_API int ko_set_num_threads(int n) {
+#ifdef _OPENMP
+  if (n <= 0) n = omp_get_num_procs();
+  omp_set_num_threads(n);
+  return n;
+#else
+  (void)n;
+  return 1;
+#endif
 }
 
 KO_API int ko_num_threads(void) {

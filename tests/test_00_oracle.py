@@ -153,6 +153,53 @@ def test_reduce(ko):
     assert np.all(np.abs(fast - s) <= 4 * 2.0 ** -24 * ab)
 
 
+def test_cmpf_select_truth_table(ko):
+    """arith.cmpf predicates (ir.cc:941-1000) and arith.select (ir.cc:1162) in the
+    checker's interpreter against a table written out by hand: ordered
+    predicates are false and unordered ones true as soon as an operand is NaN."""
+    nan = np.float32(np.nan)
+    a = np.array([[1.0, 2.0, 2.0, nan, 1.0, nan, 0.0]], dtype=np.float32)
+    b = np.array([[2.0, 1.0, 2.0, 1.0, nan, nan, -0.0]], dtype=np.float32)
+    #            a<b   a>b  a==b  NaN?  NaN?  NaN?  +0 == -0
+    table = {"olt": [1, 0, 0, 0, 0, 0, 0], "ogt": [0, 1, 0, 0, 0, 0, 0],
+             "ole": [1, 0, 1, 0, 0, 0, 1], "oge": [0, 1, 1, 0, 0, 0, 1],
+             "oeq": [0, 0, 1, 0, 0, 0, 1], "one": [1, 1, 0, 0, 0, 0, 0],
+             "ult": [1, 0, 0, 1, 1, 1, 0], "ugt": [0, 1, 0, 1, 1, 1, 0],
+             "ule": [1, 0, 1, 1, 1, 1, 1], "uge": [0, 1, 1, 1, 1, 1, 1],
+             "ueq": [0, 0, 1, 1, 1, 1, 1], "une": [1, 1, 0, 1, 1, 1, 0]}
+    names = ["olt", "ogt", "ole", "oge", "oeq", "one", "ult", "ugt", "ule", "uge", "ueq", "une"]
+    F, I1 = ko.F32, ko.I1
+    for pred, name in enumerate(names):
+        # out = select(a <pred> b, 10, 20)
+        prog = [(0, F, 0, -1, -1, -1, 0.0, 0), (0, F, 1, -1, -1, -1, 0.0, 1),
+                (28, I1, 2, 0, 1, -1, 0.0, pred),
+                (1, F, 3, -1, -1, -1, 10.0, 0), (1, F, 4, -1, -1, -1, 20.0, 0),
+                (29, F, 5, 2, 3, 4, 0.0, 0), (27, F, -1, 5, -1, -1, 0.0, 0)]
+        got = ko.eltwise(prog, [a, b], [F, F], a.shape, F)
+        want = np.where(np.array(table[name]) == 1, 10.0, 20.0).astype(np.float32).reshape(1, -1)
+        assert np.array_equal(got, want), name
+    # and / or / xor on conditions
+    for op, fn in ((30, np.logical_and), (31, np.logical_or), (32, np.logical_xor)):
+        prog = [(0, F, 0, -1, -1, -1, 0.0, 0), (0, F, 1, -1, -1, -1, 0.0, 1),
+                (28, I1, 2, 0, 1, -1, 0.0, 0), (28, I1, 3, 0, 1, -1, 0.0, 4),
+                (op, I1, 4, 2, 3, -1, 0.0, 0), (1, F, 5, -1, -1, -1, 1.0, 0),
+                (1, F, 6, -1, -1, -1, 0.0, 0), (29, F, 7, 4, 5, 6, 0.0, 0),
+                (27, F, -1, 7, -1, -1, 0.0, 0)]
+        got = ko.eltwise(prog, [a, b], [F, F], a.shape, F)
+        want = fn(np.array(table["olt"]) == 1, np.array(table["oeq"]) == 1).astype(np.float32)
+        assert np.array_equal(got.ravel(), want), op
+
+
+def test_thread_count_can_be_set(ko):
+    """The timed CPU baseline must not inherit a launcher's OMP_NUM_THREADS=1."""
+    import os
+    before = ko.num_threads()
+    assert ko.set_num_threads(1) == 1 and ko.num_threads() == 1
+    n = ko.set_num_threads(0)
+    assert n == ko.num_threads() and 1 <= n <= (os.cpu_count() or 1)
+    ko.set_num_threads(before)
+
+
 def test_f8_decode_tables(ko):
     """The checker's f8E4M3 / f8E5M2 decoders against torch's conversions, all
     256 bit patterns each (an independent implementation of the two formats)."""

@@ -166,6 +166,107 @@ def test_verifier_rejections(handle, pkg):
         handle.elementwise([(A.OP_LOAD, A.BF16, 0, -1, -1, -1, 0.0, 0)], [x], y)
 
 
+# ------------------------------------------------------------ cmpf / select
+
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16, torch.float16])
+def test_cmpf_select_every_predicate(handle, ko, pkg, dt):
+    """arith.cmpf with each predicate Builder.create_cmpf_* offers (ir.cc:941-1000)
+    feeding arith.select (ir.cc:1162): bit-exact, NaN operands included (ordered
+    predicates false, unordered true), equal values and signed zeros too."""
+    A = pkg.abi
+    D = pkg.runtime.dtype_code(dt)
+    a = normal((6, 300), 71, dtype=dt)
+    b = normal((6, 300), 72, dtype=dt)
+    b[:, ::7] = a[:, ::7]                      # equal pairs
+    a[0, 5], b[1, 9] = float("nan"), float("nan")
+    a[2, 11], b[2, 11] = float("nan"), float("nan")
+    a[3, 1], b[3, 1] = 0.0, -0.0
+    for pred in range(len(A.CMP_PREDICATES)):
+        prog = [(A.OP_LOAD, D, 0, -1, -1, -1, 0.0, 0), (A.OP_LOAD, D, 1, -1, -1, -1, 0.0, 1),
+                (A.OP_CMP, A.I1, 2, 0, 1, -1, 0.0, pred),
+                (A.OP_SELECT, D, 3, 2, 0, 1, 0.0, 0), (A.OP_STORE, D, -1, 3, -1, -1, 0.0, 0)]
+        got, want = run_both(handle, ko, prog, [a, b], (6, 300), dt)
+        assert handle.last_kernel == "elt_interp"
+        same = (got.view(np.uint32) == want.view(np.uint32)) if dt == torch.float32 else got == want
+        assert same.all(), (A.CMP_PREDICATES[pred], int((~same).sum()))
+
+
+def test_select_graph_with_condition_logic(handle, ko, pkg):
+    """y = (x > lo and not (x >= hi)) ? x * 2 : -1, conditions combined with
+    andi / xori on i1 values."""
+    A = pkg.abi
+    F = A.F32
+    x = normal((5, 777), 73, dtype=torch.float32)
+    prog = [(A.OP_LOAD, F, 0, -1, -1, -1, 0.0, 0),
+            (A.OP_CONST, F, 1, -1, -1, -1, -0.5, 0), (A.OP_CONST, F, 2, -1, -1, -1, 0.75, 0),
+            (A.OP_CMP, A.I1, 3, 0, 1, -1, 0.0, A.CMP_PREDICATES.index("ogt")),
+            (A.OP_CMP, A.I1, 4, 0, 2, -1, 0.0, A.CMP_PREDICATES.index("oge")),
+            (A.OP_XOR, A.I1, 5, 3, 4, -1, 0.0, 0),      # in (lo, hi): exactly one holds
+            (A.OP_AND, A.I1, 6, 5, 3, -1, 0.0, 0),
+            (A.OP_CONST, F, 7, -1, -1, -1, 2.0, 0), (A.OP_MUL, F, 8, 0, 7, -1, 0.0, 0),
+            (A.OP_CONST, F, 9, -1, -1, -1, -1.0, 0),
+            (A.OP_SELECT, F, 10, 6, 8, 9, 0.0, 0), (A.OP_STORE, F, -1, 10, -1, -1, 0.0, 0)]
+    got, want = run_both(handle, ko, prog, [x], (5, 777), torch.float32)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    ref = torch.where((x > -0.5) & ~(x >= 0.75), x * 2, torch.full_like(x, -1.0))
+    assert np.array_equal(got, ref.numpy())
+
+
+def test_cmpf_select_rules(handle, pkg):
+    A = pkg.abi
+    x = torch.zeros((1, 8), dtype=torch.float32, device="cuda")
+    y = torch.zeros((1, 8), dtype=torch.float32, device="cuda")
+    ld = [(A.OP_LOAD, A.F32, 0, -1, -1, -1, 0.0, 0)]
+    with pytest.raises(ValueError, match="i1 condition"):
+        handle.elementwise(ld + [(A.OP_SELECT, A.F32, 1, 0, 0, 0, 0.0, 0),
+                                 (A.OP_STORE, A.F32, -1, 1, -1, -1, 0.0, 0)], [x], y)
+    with pytest.raises(ValueError, match="unknown cmpf predicate"):
+        handle.elementwise(ld + [(A.OP_CMP, A.I1, 1, 0, 0, -1, 0.0, 12),
+                                 (A.OP_SELECT, A.F32, 2, 1, 0, 0, 0.0, 0),
+                                 (A.OP_STORE, A.F32, -1, 2, -1, -1, 0.0, 0)], [x], y)
+    with pytest.raises(ValueError, match="st_global source is"):
+        handle.elementwise(ld + [(A.OP_CMP, A.I1, 1, 0, 0, -1, 0.0, 0),
+                                 (A.OP_STORE, A.F32, -1, 1, -1, -1, 0.0, 0)], [x], y)
+    with pytest.raises(ValueError, match="same element type"):    # arithmetic on a condition
+        handle.elementwise(ld + [(A.OP_CMP, A.I1, 1, 0, 0, -1, 0.0, 0),
+                                 (A.OP_ADD, A.F32, 2, 0, 1, -1, 0.0, 0),
+                                 (A.OP_STORE, A.F32, -1, 2, -1, -1, 0.0, 0)], [x], y)
+
+
+# ------------------------------------------------------ output against inputs
+
+def test_in_place_and_overlap(handle, ko, pkg):
+    """An input that is exactly the output runs in place (on the interpreter: the
+    streaming kernels read through the read-only path) and gives the same bits
+    as the out-of-place call; a partial overlap is refused."""
+    A = pkg.abi
+    x = normal((1, 1 << 15), 81)
+    prog = pkg.programs.affine_gelu_tanh(A.BF16, 0.5, 0.1)
+    xd = x.cuda()
+    y = torch.empty_like(xd)
+    handle.elementwise(prog, [xd], y)
+    assert handle.last_kernel == "elt_affine_gelu"
+    handle.elementwise(prog, [xd], xd)
+    assert handle.last_kernel == "elt_interp"
+    handle.check()
+    assert torch.equal(xd, y)
+    # binary op accumulating into its first operand
+    a, b = normal((1, 4096), 82), normal((1, 4096), 83)
+    ad, bd = a.cuda(), b.cuda()
+    handle.elementwise(pkg.programs.binary(A.OP_ADD, A.BF16), [ad, bd], ad)
+    assert handle.last_kernel == "elt_interp"
+    handle.check()
+    want = ko.eltwise(pkg.programs.binary(A.OP_ADD, A.BF16), [bits(a), bits(b)], [1, 1], (1, 4096), 1)
+    assert np.array_equal(bits(ad.cpu()), want)
+    # shifted by one element: every output element is some other thread's input
+    buf = torch.zeros((1, 4097), dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(ValueError, match="overlaps input 0"):
+        handle.elementwise(pkg.programs.affine(A.BF16, 0.5, 0.1), [buf[:, 1:]], buf[:, :4096])
+    # disjoint halves of one allocation are fine
+    handle.elementwise(pkg.programs.affine(A.BF16, 0.5, 0.1), [buf[:, :2048]], buf[:, 2048:4096])
+    handle.check()
+
+
 # ------------------------------------------------------------------ f8 casts
 
 F8_TORCH = {3: torch.float8_e4m3fn, 4: torch.float8_e5m2}

@@ -1,6 +1,8 @@
 """kapy.reduce against the f64 checker.  The reference fixes no combination
-order (ReduceOpToLLVM.cpp:76-119), so sums are held to 4*eps_f32*sum|x| (plus
-one rounding of a 16-bit result); max/min are exact."""
+order (ReduceOpToLLVM.cpp:76-119), so f32 sums are held to 4*eps_f32*sum|x|;
+a sum whose lambda runs at a 16-bit type (source and result f16 or bf16) rounds
+at every step, which any order keeps within n*u*sum|x| (u the type's unit
+roundoff); max/min are exact."""
 import numpy as np
 import pytest
 import torch
@@ -15,7 +17,9 @@ def check_sum(ko, got64, X, dt, axis, out_dtype):
     ref, ab = ko.reduce_f64(bits(X), code(dt), axis)
     tol = 4 * EPS32 * ab + 1e-30
     if out_dtype != torch.float32:
-        tol = tol + np.abs(ref) * (2.0 ** -8 if out_dtype == torch.bfloat16 else 2.0 ** -11)
+        # a rounding to the 16-bit type per combination, in whatever order
+        n = X.shape[axis]
+        tol = n * (2.0 ** -8 if out_dtype == torch.bfloat16 else 2.0 ** -11) * ab + 1e-30
     assert np.all(np.abs(got64 - ref) <= tol), np.abs(got64 - ref).max()
 
 
@@ -37,6 +41,43 @@ def test_reduce_sum_mlir_shape(handle, ko):
     handle.check()
     assert out.dtype == torch.float16 and out.shape == (128, 1)
     check_sum(ko, out.cpu().double().numpy().ravel(), X, torch.float16, 1, torch.float16)
+
+
+def _add_at(ko, a, b, dt):
+    """Elementwise a + b with one rounding at the 16-bit type `dt` (the checker's add)."""
+    prog = [(0, dt, 0, -1, -1, -1, 0.0, 0), (0, dt, 1, -1, -1, -1, 0.0, 1),
+            (3, dt, 2, 0, 1, -1, 0.0, 0), (27, dt, -1, 2, -1, -1, 0.0, 0)]
+    return ko.eltwise(prog, [np.ascontiguousarray(a), np.ascontiguousarray(b)], [dt, dt], a.shape, dt)
+
+
+@pytest.mark.parametrize("dt", [torch.float16, torch.bfloat16])
+def test_sixteen_bit_sum_rounds_at_every_step(handle, ko, dt):
+    """The lambda of reduce_sum.mlir:10-25 adds at the tensor's 16-bit type.  For
+    a [n, 256] tensor whose rows start on 32-byte boundaries the kernel's order
+    is: lanes 0..15 each add 16 consecutive elements in ascending order, then
+    meet in a butterfly over lane distances 8, 4, 2, 1.  Restated with the
+    checker's single-rounding add, that order must give the same bits."""
+    X = normal((128, 256), 5, dtype=dt)
+    out = handle.reduce(X.cuda(), axis=1)
+    handle.check()
+    assert out.dtype == dt
+    xb = bits(X)
+    code_dt = code(dt)
+    lanes = []
+    for lane in range(16):
+        acc = xb[:, 16 * lane:16 * lane + 1].copy()
+        for e in range(1, 16):
+            acc = _add_at(ko, acc, xb[:, 16 * lane + e:16 * lane + e + 1], code_dt)
+        lanes.append(acc)
+    v = np.concatenate(lanes, axis=1)                      # [128, 16]
+    for off in (8, 4, 2, 1):
+        v = _add_at(ko, v, v[:, np.arange(16) ^ off], code_dt)
+    want = v[:, 0]
+    got = bits(out.cpu()).ravel()
+    assert np.array_equal(got, want), int((got != want).sum())
+    # and it differs from the sum formed in f32 and rounded once, in some rows at least
+    once = handle.reduce(X.cuda(), axis=1, out_dtype=torch.float32).cpu().ravel().to(dt)
+    assert (bits(once).ravel() != got).any()
 
 
 @pytest.mark.parametrize("shape", [(300, 37), (4096, 64), (7, 1)])

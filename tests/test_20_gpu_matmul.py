@@ -165,6 +165,28 @@ def test_verifier_rejections(handle):
     assert e.shape == (0, 8)
 
 
+def test_operand_padding_is_zero_only(handle, pkg):
+    """ld_global's QNAN / +-INF padding (Enums.td:52-61) has no whole-problem
+    meaning for a matmul operand (it would poison every output whose K range is
+    ragged against a tile size the caller cannot see): refused, not ignored."""
+    import ctypes as C
+    a = torch.zeros((64, 72), dtype=torch.bfloat16, device="cuda")
+    b = torch.zeros((72, 64), dtype=torch.bfloat16, device="cuda")
+    c = torch.zeros((64, 64), dtype=torch.bfloat16, device="cuda")
+    lib = pkg.abi.load()
+    ep = pkg.abi.Epilogue(1.0, None, pkg.abi.F32, 1, 0, pkg.abi.RN)
+    for pad_l, pad_r in ((pkg.abi.PAD_QNAN, 0), (0, pkg.abi.PAD_PINF), (pkg.abi.PAD_NINF, pkg.abi.PAD_NINF)):
+        tl, tr, to = pkg.tensor2d(a, pad_l), pkg.tensor2d(b, pad_r), pkg.tensor2d(c)
+        st = lib.kapyb_matmul(handle._h, C.byref(tl), C.byref(tr), None, C.byref(to), C.byref(ep), 0,
+                              handle._stream())
+        assert st == pkg.abi.UNSUPPORTED
+        assert "padded with zeros only" in lib.kapyb_last_error_string(handle._h).decode()
+    tl, tr, to = pkg.tensor2d(a), pkg.tensor2d(b), pkg.tensor2d(c)
+    assert lib.kapyb_matmul(handle._h, C.byref(tl), C.byref(tr), None, C.byref(to), C.byref(ep), 0,
+                            handle._stream()) == pkg.abi.OK
+    handle.check()
+
+
 def test_host_buffers(handle, ko):
     """kapyb_matmul_host: host tensors in, host tensor out."""
     M, N, K = 256, 384, 512

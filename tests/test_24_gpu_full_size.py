@@ -68,7 +68,9 @@ def test_config5_batched_full_size(handle, ko):
     assert S.shape == (64, 2048, 2048) and S.dtype == torch.bfloat16
     groups = S.view(8, 8, 2048, 2048).view(torch.int16)
     assert torch.equal(groups, groups[0:1].expand(8, -1, -1, -1)), "a batch's result depends on its index"
-    ref = ko.matmul_f64(bits(Q8[0]), code(torch.bfloat16), bits(K8[0]), code(torch.bfloat16),
-                        alpha=128 ** -0.5)
-    err, tau = ko.max_rel_err(S[0].cpu().double().numpy(), ref)
-    assert err <= 1e-2, f"max rel err {err:.3e} (tau {tau:.3e})"
+    # every one of the eight distinct batch entries against the f64 checker
+    for e in range(8):
+        ref = ko.matmul_f64(bits(Q8[e]), code(torch.bfloat16), bits(K8[e]), code(torch.bfloat16),
+                            alpha=128 ** -0.5)
+        err, tau = ko.max_rel_err(S[e].cpu().double().numpy(), ref)
+        assert err <= 1e-2, f"batch entry {e}: max rel err {err:.3e} (tau {tau:.3e})"

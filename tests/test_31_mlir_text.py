@@ -1,8 +1,9 @@
 """The textual kapy IR reader and the lifting of parsed kernels.
 
 The fixtures under tests/golden/kernels/ are kernels written for this test in
-the reference's assembly syntax.  When the reference checkout is present (it is
-not on the GPU box) its own three test inputs are parsed and lifted too."""
+the reference's assembly syntax; tests/golden/ref_inputs/ holds the three kernel
+inputs of the reference's own test suite, which are parsed, lifted and run on
+the GPU unchanged."""
 import glob
 import os
 
@@ -15,11 +16,8 @@ from util import bits, normal
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 KERNELS = os.path.join(HERE, "golden", "kernels")
-# the reference checkout, when it sits beside this repository (or where
-# KAPY_REFERENCE_DIR points)
-REF = os.path.join(os.environ.get("KAPY_REFERENCE_DIR",
-                                  os.path.join(HERE, "..", "..", "reference")),
-                   "test", "Conversion", "KapyToKgpu")
+# the reference's own test inputs (test/Conversion/KapyToKgpu/*.mlir), unchanged
+REF = os.path.join(HERE, "golden", "ref_inputs")
 
 
 def load(pkg, name):
@@ -48,6 +46,23 @@ def test_lift_scale_shift(pkg):
     assert kind == "elementwise" and (tout.size0, tout.size1) == (1, 4096)
     assert [t[0] for t in insts] == [A.OP_LOAD, A.OP_CVT, A.OP_CONST, A.OP_CONST, A.OP_FMA,
                                      A.OP_CVT, A.OP_STORE]
+
+
+def test_lift_leaky_relu_select(pkg):
+    """arith.cmpf feeding arith.select over register tensors becomes part of the
+    elementwise program (KAPYB_OP_CMP / KAPYB_OP_SELECT)."""
+    mod, fn = load(pkg, "leaky_relu_f32.mlir")
+    n = 2048
+    x, y = torch.zeros(n), torch.zeros(n)
+    h = FakeHandle()
+    pkg.executor.launch(fn, (n // 512, 1, 1), [x, y, n], h, module=mod)
+    kind, insts, tin, tout = h.log[0]
+    A = pkg.abi
+    ops = [t[0] for t in insts]
+    assert kind == "elementwise" and (tout.size0, tout.size1) == (1, n)
+    assert ops.count(A.OP_CMP) == 1 and ops.count(A.OP_SELECT) == 1 and ops[-1] == A.OP_STORE
+    cmp_inst = insts[ops.index(A.OP_CMP)]
+    assert cmp_inst[1] == A.I1 and cmp_inst[7] == A.CMP_PREDICATES.index("ogt")
 
 
 def test_lift_row_max(pkg):
@@ -111,7 +126,6 @@ def test_lift_gemm_ring_f8_and_tf32(pkg):
         assert (tl.size0, tl.size1, tl.stride0) == (M, K, K) and (tr.size0, tr.size1) == (K, N)
 
 
-@pytest.mark.skipif(not os.path.isdir(REF), reason="reference checkout not present")
 def test_reference_inputs_parse_and_lift(pkg):
     """elementwise_add.mlir, reduce_sum.mlir and matmul.mlir run unchanged: each
     becomes one library call over the region its grid covers."""
@@ -144,6 +158,50 @@ def test_reference_inputs_parse_and_lift(pkg):
 
 
 @pytest.mark.gpu
+def test_reference_inputs_run_on_gpu(handle, ko, pkg):
+    """The reference's three kernels, launched on the grids their tile sizes
+    imply, on seeded data, against the CPU checker."""
+    # elementwise_add.mlir:9-25: z = x + y in f16, one program per 512 elements
+    mod = pkg.mlir_text.parse_file(os.path.join(REF, "elementwise_add.mlir"))
+    n = 512 * 41
+    x, y = normal((n,), 21, dtype=torch.float16), normal((n,), 22, dtype=torch.float16)
+    zd = torch.zeros(n, dtype=torch.float16, device="cuda")
+    ran = pkg.executor.launch(mod, (n // 512, 1, 1), [x.cuda(), y.cuda(), zd, n], handle)
+    handle.check()
+    assert ran == ["elt_binary"]
+    want = ko.eltwise(pkg.programs.binary(pkg.abi.OP_ADD, pkg.abi.F16),
+                      [bits(x).reshape(1, -1), bits(y).reshape(1, -1)], [0, 0], (1, n), 0)
+    assert np.array_equal(bits(zd.cpu()).reshape(1, -1), want)
+
+    # reduce_sum.mlir:10-25: row sums of [rows, 256] f16 with an f16 addf lambda,
+    # one program per 4 rows; every addition rounds to f16, in whatever order
+    mod = pkg.mlir_text.parse_file(os.path.join(REF, "reduce_sum.mlir"))
+    rows = 4 * 50
+    src = normal((rows, 256), 23, dtype=torch.float16)
+    dst = torch.zeros(rows, dtype=torch.float16, device="cuda")
+    ran = pkg.executor.launch(mod, (rows // 4, 1, 1), [src.cuda(), dst, rows], handle)
+    handle.check()
+    assert ran == ["reduce_rows"]
+    ref, ab = ko.reduce_f64(bits(src), 0, 1)
+    got = dst.cpu().double().numpy()
+    assert np.all(np.abs(got - ref) <= 256 * 2.0 ** -11 * ab + 1e-30)
+
+    # matmul.mlir:1-134: the pipelined f16 GEMM, grid (M/128, N/128), 4 warps
+    mod = pkg.mlir_text.parse_file(os.path.join(REF, "matmul.mlir"))
+    M, K, N = 512, 768, 640
+    A = normal((M, K), 24, K ** -0.5, dtype=torch.float16)
+    B = normal((K, N), 25, dtype=torch.float16)
+    Cd = torch.zeros((M, N), dtype=torch.float16, device="cuda")
+    ran = pkg.executor.launch(mod, (M // 128, N // 128, 1), [A.cuda(), B.cuda(), Cd, M, K, N],
+                              handle)
+    handle.check()
+    assert ran[0].startswith("tcgen05")
+    ref = ko.matmul_f64(bits(A), 0, bits(B), 0)
+    err, _ = ko.max_rel_err(Cd.cpu().double().numpy(), ref)
+    assert err <= 1e-2, err
+
+
+@pytest.mark.gpu
 def test_fixtures_run_on_gpu(handle, ko, pkg):
     # scale + shift, bit-exact
     mod, fn = load(pkg, "scale_shift_bf16.mlir")
@@ -155,6 +213,14 @@ def test_fixtures_run_on_gpu(handle, ko, pkg):
     want = ko.eltwise(pkg.programs.affine(pkg.abi.BF16, 0.5, 0.1), [bits(x).reshape(1, -1)], [1],
                       (1, n), 1)
     assert np.array_equal(bits(yd.cpu()).reshape(1, -1), want)
+    # leaky relu through cmpf + select, bit-exact
+    mod, fn = load(pkg, "leaky_relu_f32.mlir")
+    n = 512 * 19
+    x = normal((n,), 9, dtype=torch.float32)
+    yd = torch.zeros(n, dtype=torch.float32, device="cuda")
+    assert pkg.executor.launch(fn, (19, 1, 1), [x.cuda(), yd, n], handle, module=mod) == ["elt_interp"]
+    handle.check()
+    assert torch.equal(yd.cpu(), torch.where(x > 0, x, x * torch.tensor(0.1, dtype=torch.float32)))
     # row max, exact
     mod, fn = load(pkg, "row_max_f32.mlir")
     m = 8 * 25
