@@ -533,9 +533,14 @@ def run_ours(args):
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
+    saved_stdout = None
     if world > 1:
-        # NCCL prints its version banner on stdout; the JSON line must be alone there
+        # NCCL prints its version banner on stdout; the JSON line must be alone there:
+        # everything but that line goes to stderr
         os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
+        sys.stdout.flush()
+        saved_stdout = os.dup(1)
+        os.dup2(2, 1)
         torch.cuda.set_device(local)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     else:
@@ -713,8 +718,18 @@ def run_ours(args):
             t = torch.tensor([1 if ok else 0], device="cuda")
             dist.all_reduce(t, op=dist.ReduceOp.MIN)
             gather["fused_push"] = {"value": FLOPS / tp / 1e12, "unit": UNIT, "ms_per_step": tp * 1e3,
-                                    "matches_full": bool(t.item()),
+                                    "matches_full": bool(t.item()), "kernel_plan": "dispatcher's choice",
                                     "completion": "kapyb_gather_signal / kapyb_gather_wait (bounded)"}
+            # the same step with each pair-tile width forced: what the dispatcher chose between
+            by_tile = {}
+            for path in ("2cta:512", "2cta:256", "2cta:128"):
+                h.set_matmul_path(path)
+                try:
+                    by_tile[path] = timed(push_step, iters) * 1e3
+                finally:
+                    h.set_matmul_path("auto")
+            h.check()
+            gather["fused_push"]["ms_per_step_by_forced_tile"] = by_tile
         except Exception as ex:
             gather["fused_push"] = {"error": repr(ex)[:200]}
         del full
@@ -790,6 +805,9 @@ def run_ours(args):
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+        sys.stdout.flush()
+        os.dup2(saved_stdout, 1)
+        os.close(saved_stdout)
     if rank == 0:
         print(json.dumps(line))
 

@@ -274,6 +274,23 @@ KAPYB_API kapyb_status kapyb_matmul(kapyb_handle h, const kapyb_tensor2d *lhs,
                                     const kapyb_epilogue *epilogue,
                                     int32_t impl_way, void *stream);
 
+/* kapyb_matmul with a kapy.reduce (Ops.td:441-457) of its result fused into the
+ * epilogue: besides `out`, the f32 values the epilogue produces (scale, bias,
+ * activation; before the downcast to out's type) are summed along `axis` into
+ * `reduced`, a dense f32 vector of shape [M,1] (axis 1: one sum per row) or
+ * [1,N] (axis 0: one per column).  This is what a kernel that follows its
+ * matmul chain with `kapy.reduce ... lambda addf` on the accumulator tile
+ * computes, without a second pass over the output.  `reduced` is cleared on
+ * `stream` and then accumulated with fp32 atomic adds, so the order of
+ * combination is unspecified (as in the reference, ReduceOpToLLVM.cpp:76-119)
+ * and may differ from run to run in the last bits.  Only the addf lambda
+ * (KAPYB_RED_ADD) is fused; operands and output must be TMA-describable. */
+KAPYB_API kapyb_status kapyb_matmul_reduce(kapyb_handle h, const kapyb_tensor2d *lhs,
+                                           const kapyb_tensor2d *rhs, const kapyb_tensor2d *out,
+                                           const kapyb_tensor2d *reduced, int32_t axis,
+                                           int32_t combiner, const kapyb_epilogue *epilogue,
+                                           int32_t impl_way, void *stream);
+
 /* `batch` independent matmuls; operand b of batch i starts batch_stride_*
  * elements after batch i-1.  In the reference the batch is the grid's z axis
  * (kapy.program_id axis 2, ir.cc:1091-1096). */
@@ -336,7 +353,8 @@ typedef struct {
   void *const *peer_lhs;
   /* [world] device pointers to every rank's flag array (kapyb_gather_signal). */
   void *const *peer_flags;
-  uint32_t seq;           /* 1 for the first call, then +1 per call, the same on all ranks */
+  uint32_t seq;           /* 1 for the first call, then +1 per call, the same on all ranks
+                             (the flag words carry seq * 64 + a piece number) */
   uint32_t wait_limit_ms; /* 0: 2000 */
 } kapyb_shard_ctx;
 
@@ -346,8 +364,11 @@ typedef struct {
  * by rows: this rank uploads only rows [row_begin, row_begin + lhs_rows->size0)
  * from host memory and forwards them to every peer's staging area over NVLink
  * (copy engines, stores only, no loads of remote memory), so each row of lhs
- * crosses PCIe once per box instead of once per GPU.  Every rank must make the
- * matching call (same seq).  Returns when `out` has landed in host memory;
+ * crosses PCIe once per box instead of once per GPU.  The rows travel in up to
+ * four pieces per rank; the product of a piece and the download of its rows of
+ * `out` overlap the upload of the next piece.  m_total must be a multiple of
+ * world and rank r must own the r-th block of m_total / world rows.  Every rank
+ * must make the matching call (same seq).  Returns when `out` has landed in host memory;
  * KAPYB_TIMEOUT when a peer's rows did not arrive within the limit.  No
  * reference counterpart. */
 KAPYB_API kapyb_status kapyb_matmul_host_sharded(

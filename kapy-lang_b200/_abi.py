@@ -73,6 +73,9 @@ PROTOTYPES = {
     "kapyb_matmul": (C.c_int, [C.c_void_p, C.POINTER(Tensor2d), C.POINTER(Tensor2d),
                                C.POINTER(Tensor2d), C.POINTER(Tensor2d), C.POINTER(Epilogue),
                                C.c_int32, C.c_void_p]),
+    "kapyb_matmul_reduce": (C.c_int, [C.c_void_p, C.POINTER(Tensor2d), C.POINTER(Tensor2d),
+                                      C.POINTER(Tensor2d), C.POINTER(Tensor2d), C.c_int32,
+                                      C.c_int32, C.POINTER(Epilogue), C.c_int32, C.c_void_p]),
     "kapyb_matmul_batched": (C.c_int, [C.c_void_p, C.POINTER(Tensor2d), C.POINTER(Tensor2d),
                                        C.POINTER(Tensor2d), C.c_int32, C.c_int64, C.c_int64,
                                        C.c_int64, C.POINTER(Epilogue), C.c_int32, C.c_void_p]),

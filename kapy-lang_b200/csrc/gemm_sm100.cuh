@@ -126,6 +126,12 @@ struct GemmParams {
               // status[14], [15]: clocks the first CTA's MMA warp waited for operand stages
               // and for accumulator slots
   EpilogueArgs ep;
+  // kapy.reduce fused after the epilogue (REDUCE instantiations only): the f32
+  // values the epilogue produces, before the downcast, are also summed along
+  // red_axis (1: over the columns, one sum per row; 0: over the rows, one per
+  // column) into the zero-initialised vector `red` with fp32 atomics.
+  float *red;
+  int red_axis;
 };
 
 template <int BN, int CTAS, int EPI = 4>
@@ -244,7 +250,7 @@ struct EpiTile {
 // The fused arithmetic on 32 consecutive accumulator columns of one row
 // (columns col0 .. col0+31 of row t.row): scale, bias, addend, activation.
 // LEVEL 0: scale only; 1: scale and bias; 2: scale, bias, addend, activation.
-template <int LEVEL>
+template <int LEVEL, bool REDUCE = false>
 __device__ __forceinline__ void finish32(const GemmParams &p, const EpiTile &t, float (&f)[32],
                                          int col0) {
   const int lane = t.lane;
@@ -287,6 +293,28 @@ __device__ __forceinline__ void finish32(const GemmParams &p, const EpiTile &t, 
       for (int i = 0; i < 32; ++i) f[i] = apply_activation(p.ep.activation, f[i]);
     }
   }
+  if constexpr (REDUCE) {
+    // Lane l holds row t.row, columns col0 .. col0+31.  Rows and columns outside
+    // the problem hold the products of TMA's zero fill plus bias: leave them out.
+    const bool row_ok = t.row < p.M;
+    if (p.red_axis == 1) {
+      float s = 0.0f;
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (col0 + i < p.N) s += f[i];
+      if (row_ok) atomicAdd(p.red + t.row, s);
+    } else {
+      float mine = 0.0f;
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        float v = row_ok ? f[i] : 0.0f;
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+        if (lane == i) mine = v;
+      }
+      if (col0 + lane < p.N) atomicAdd(p.red + col0 + lane, mine);
+    }
+  }
 }
 
 // 32 finished columns -> 16 packed bf16 or f16 pairs, rounded to nearest.
@@ -312,7 +340,7 @@ __device__ __forceinline__ void stage_packed16(uint8_t *srow, const uint32_t (&w
 // OUTK: 0 f32, 1/2 bf16 rn/rz, 3/4 f16 rn/rz.  PLAIN: the epilogue is only the
 // scale (no bias, addend or activation), so none of those are even tested.
 // Returns whether the slot was handed back (false when this warp had no chunk).
-template <int BN, int EPI, int OUTK, bool PLAIN>
+template <int BN, int EPI, int OUTK, bool PLAIN, bool REDUCE = false>
 __device__ __forceinline__ bool epilogue_tile(const GemmParams &p, const TmapArray &tmC,
                                               const EpiTile &t, int &buf) {
   constexpr bool OUT32 = OUTK == 0;
@@ -360,7 +388,7 @@ __device__ __forceinline__ bool epilogue_tile(const GemmParams &p, const TmapArr
       float f[32];
 #pragma unroll
       for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(v[h][i]);
-      finish32<PLAIN ? 0 : 2>(p, t, f, col0);
+      finish32<PLAIN ? 0 : 2, REDUCE>(p, t, f, col0);
       // Row `lane` of the staging tile, 128-byte swizzle: 16-byte chunk j of row
       // r lives at chunk position j ^ (r & 7).
       if constexpr (OUTK == 0) stage_half_f32(srow, f, lane);
@@ -557,7 +585,7 @@ __device__ __forceinline__ void issue_kblock(uint32_t d_tmem, uint32_t a_lo, uin
   }
 }
 
-template <int BN, int CTAS, int EPI>
+template <int BN, int CTAS, int EPI, bool REDUCE = false>
 __global__ void __launch_bounds__(64 + 32 * EPI, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
                     const __grid_constant__ CUtensorMap tmB,
@@ -903,7 +931,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
     const bool bias_fast = bias_col && p.ep.bias_dtype != KAPYB_F32 &&
                            (reinterpret_cast<uintptr_t>(p.ep.bias) & 15u) == 0;
     // "plain": nothing but the scale between the accumulator and the downcast
-    const bool plain = p.ep.bias == nullptr && p.ep.acc == nullptr &&
+    const bool plain = !REDUCE && p.ep.bias == nullptr && p.ep.acc == nullptr &&
                        p.ep.activation == KAPYB_ACT_NONE;
     int acc = 0;
     uint32_t acc_phase = 0;
@@ -990,15 +1018,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
           // One specialised copy of the chunk loop per (output kind, plain/full
           // epilogue): the switch runs once per slot, the loops inside are tight.
           switch (out_kind * 2 + (plain ? 1 : 0)) {
-          case 0: handed_back = epilogue_tile<BN, EPI, 0, false>(p, tmC, et, buf); break;
+          case 0: handed_back = epilogue_tile<BN, EPI, 0, false, REDUCE>(p, tmC, et, buf); break;
           case 1: handed_back = epilogue_tile<BN, EPI, 0, true>(p, tmC, et, buf); break;
-          case 2: handed_back = epilogue_tile<BN, EPI, 1, false>(p, tmC, et, buf); break;
+          case 2: handed_back = epilogue_tile<BN, EPI, 1, false, REDUCE>(p, tmC, et, buf); break;
           case 3: handed_back = epilogue_tile<BN, EPI, 1, true>(p, tmC, et, buf); break;
-          case 4: handed_back = epilogue_tile<BN, EPI, 2, false>(p, tmC, et, buf); break;
+          case 4: handed_back = epilogue_tile<BN, EPI, 2, false, REDUCE>(p, tmC, et, buf); break;
           case 5: handed_back = epilogue_tile<BN, EPI, 2, true>(p, tmC, et, buf); break;
-          case 6: handed_back = epilogue_tile<BN, EPI, 3, false>(p, tmC, et, buf); break;
+          case 6: handed_back = epilogue_tile<BN, EPI, 3, false, REDUCE>(p, tmC, et, buf); break;
           case 7: handed_back = epilogue_tile<BN, EPI, 3, true>(p, tmC, et, buf); break;
-          case 8: handed_back = epilogue_tile<BN, EPI, 4, false>(p, tmC, et, buf); break;
+          case 8: handed_back = epilogue_tile<BN, EPI, 4, false, REDUCE>(p, tmC, et, buf); break;
           default: handed_back = epilogue_tile<BN, EPI, 4, true>(p, tmC, et, buf); break;
           }
         }

@@ -7,6 +7,8 @@
 
 #include <algorithm>
 #include <atomic>
+#include <chrono>
+#include <cstdlib>
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
@@ -521,9 +523,10 @@ static kapyb_status launch_simt(kapyb_handle h, const MatmulProblem &p, cudaStre
   return KAPYB_OK;
 }
 
-template <int BN, int CTAS, int EPI>
+template <int BN, int CTAS, int EPI, bool REDUCE = false>
 static kapyb_status launch_tcgen05(kapyb_handle h, const MatmulProblem &p, bool a_mn, bool b_mn,
-                                   void *const *outs, int n_out, cudaStream_t stream) {
+                                   void *const *outs, int n_out, cudaStream_t stream,
+                                   float *red = nullptr, int red_axis = 1) {
   using Cfg = GemmCfg<BN, CTAS, EPI>;
   CUtensorMap tmA, tmB;
   TmapArray tmC;
@@ -588,8 +591,10 @@ static kapyb_status launch_tcgen05(kapyb_handle h, const MatmulProblem &p, bool 
   gp.debug = h->debug;
   gp.wait_limit_us = h->wait_limit_us;
   gp.ep = p.ep;
+  gp.red = red;
+  gp.red_axis = red_axis;
 
-  auto kern = gemm_tcgen05_kernel<BN, CTAS, EPI>;
+  auto kern = gemm_tcgen05_kernel<BN, CTAS, EPI, REDUCE>;
   static bool attr_set[kMaxDevices] = {};
   if (!attr_set[h->device]) {
     CUDA_TRY(h, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -920,6 +925,23 @@ static kapyb_status plan_decide(const PlanOptions &o, const MatmulProblem &p, vo
       // less than half a wave of 256-wide pair tiles: 128-wide ones put more SMs to work
       const long long t256 = static_cast<long long>((p.M + 255) / 256) * ((p.N + 255) / 256) * p.batch;
       if (bn == 256 && t256 * 2 <= pairs) bn = 128;
+      // Push epilogue to peers: a tile's stores leave only when its K loop is over,
+      // so with a single wave of tiles the whole transfer follows the whole
+      // computation.  Take the widest tile that still gives three waves (the
+      // stores of one wave then cross NVLink under the main loops of the next),
+      // else the narrowest.
+      if (n_peers > 1) {
+        auto waves = [&](int w) {
+          const long long t = static_cast<long long>((p.M + 255) / 256) * ((p.N + w - 1) / w) * p.batch;
+          return static_cast<double>(t) / pairs;
+        };
+        bn = 128;
+        for (int w : {512, 256})
+          if ((w != 512 || (p.N >= 512 && p.K >= 1024)) && waves(w) >= 3.0) {
+            bn = w;
+            break;
+          }
+      }
     }
     if (bn == 64) bn = 128;
     if (group_cols(bn, 2) < min_cols) bn = 512;
@@ -1145,6 +1167,48 @@ extern "C" KAPYB_API kapyb_status kapyb_matmul(kapyb_handle h, const kapyb_tenso
   if (st != KAPYB_OK) return st;
   return run_matmul(h, make_problem(lhs, rhs, acc, out, epilogue), nullptr, 0,
                     static_cast<cudaStream_t>(stream));
+}
+
+extern "C" KAPYB_API kapyb_status kapyb_matmul_reduce(
+    kapyb_handle h, const kapyb_tensor2d *lhs, const kapyb_tensor2d *rhs, const kapyb_tensor2d *out,
+    const kapyb_tensor2d *reduced, int32_t axis, int32_t combiner, const kapyb_epilogue *epilogue,
+    int32_t impl_way, void *stream_) {
+  if (!h) return fail(h, KAPYB_INVALID_ARG, "kapyb_matmul_reduce: NULL handle");
+  kapyb_status st = verify_matmul(h, lhs, rhs, nullptr, out, epilogue, impl_way);
+  if (st != KAPYB_OK) return st;
+  if (!reduced || axis < 0 || axis > 1)
+    return fail(h, KAPYB_INVALID_ARG, "matmul_reduce: axis must be 0 or 1 and `reduced` given");
+  if (combiner != KAPYB_RED_ADD)
+    return fail(h, KAPYB_UNSUPPORTED, "matmul_reduce: only the addf lambda is fused (combiner %d)", combiner);
+  // ReduceOp::inferReturnTypes (Kapy.cpp:613-626): the reduced axis becomes 1
+  const int want0 = axis == 0 ? 1 : out->size0, want1 = axis == 1 ? 1 : out->size1;
+  if (reduced->size0 != want0 || reduced->size1 != want1)
+    return fail(h, KAPYB_INVALID_ARG, "matmul_reduce: result shape must be [%d, %d]", want0, want1);
+  const int len = axis == 1 ? out->size0 : out->size1;
+  const int rstride = axis == 1 ? reduced->stride0 : reduced->stride1;
+  if (reduced->dtype != KAPYB_F32 || (len > 1 && rstride != 1) || (len > 0 && !reduced->ptr))
+    return fail(h, KAPYB_UNSUPPORTED, "matmul_reduce: `reduced` must be a dense f32 vector");
+  if (len == 0) return KAPYB_OK;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  CUDA_TRY(h, cudaSetDevice(h->device));
+  float *red = static_cast<float *>(const_cast<void *>(elem_ptr(reduced)));
+  // the sums are formed with atomic adds: they start from zero (and stay zero
+  // when there is nothing to sum)
+  CUDA_TRY(h, cudaMemsetAsync(red, 0, static_cast<size_t>(len) * sizeof(float), stream));
+  if (out->size0 == 0 || out->size1 == 0) return KAPYB_OK;
+  MatmulProblem p = make_problem(lhs, rhs, nullptr, out, epilogue);
+  MatmulPlan plan;
+  const PlanOptions opt{h->sm_count, PATH_1CTA, 128, 4};
+  st = plan_decide(opt, p, nullptr, 0, plan);
+  if (st != KAPYB_OK) return fail(h, st, "%s", plan.error);
+  if (plan.path != PATH_1CTA || !plan.tma || p.c_s1 != 1 || p.K < 1)
+    return fail(h, KAPYB_UNSUPPORTED,
+                "matmul_reduce: operands and a row-major output must be TMA-describable "
+                "(unit strides, 16-byte aligned bases and leading dimensions), K >= 1");
+  void *own[1] = {p.c};
+  if (plan.bn == 256)
+    return launch_tcgen05<256, 1, 4, true>(h, p, plan.a_mn, plan.b_mn, own, 1, stream, red, axis);
+  return launch_tcgen05<128, 1, 4, true>(h, p, plan.a_mn, plan.b_mn, own, 1, stream, red, axis);
 }
 
 extern "C" KAPYB_API kapyb_status kapyb_matmul_batched(
@@ -1383,16 +1447,28 @@ extern "C" KAPYB_API kapyb_status kapyb_gather_wait(kapyb_handle h, const void *
 
 // ------------------------------------------- host buffers, rows of A sharded
 
-// Rows per GEMM launch of a chunked host call: enough tiles per launch to fill a
-// good part of the GPU (a 256-row x 512-column tile per SM pair), in multiples
-// of 256 rows, at most kMax launches.
-static int host_chunk_rows(int M, int n_cols, int sm_count, int max_chunks) {
-  const int tiles_n = std::max(1, (n_cols + 511) / 512);
-  const int want_tiles = std::max(1, (sm_count / 2) * 2 / 5);
-  int rows = std::max(((want_tiles + tiles_n - 1) / tiles_n) * 256, 1024);
-  const int chunks = std::max(1, std::min(max_chunks, (M + rows - 1) / rows));
-  return std::max(256, ((M + chunks - 1) / chunks + 255) / 256 * 256);  // even chunks
-}
+// KAPYB_TRACE=1 in the environment makes the sharded host call print, per phase,
+// the host time at which the phase's work had been issued and the time at which
+// the stream it runs on had drained (the drain serialises the phases: a
+// diagnosis aid, never on in a timed run).
+struct HostTrace {
+  bool on;
+  int rank;
+  std::chrono::steady_clock::time_point t0;
+  HostTrace(int rank_) : rank(rank_), t0(std::chrono::steady_clock::now()) {
+    const char *e = getenv("KAPYB_TRACE");
+    on = e && e[0] && e[0] != '0';
+  }
+  double ms() const {
+    return std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
+  }
+  void mark(const char *what, cudaStream_t s) {
+    if (!on) return;
+    const double issued = ms();
+    cudaStreamSynchronize(s);
+    fprintf(stderr, "[kapyb trace r%d] %-28s issued %7.3f ms, drained %7.3f ms\n", rank, what, issued, ms());
+  }
+};
 
 extern "C" KAPYB_API kapyb_status kapyb_matmul_host_sharded(
     kapyb_handle h, const kapyb_tensor2d *lhs_rows, int32_t m_total, int32_t row_begin,
@@ -1462,34 +1538,38 @@ extern "C" KAPYB_API kapyb_status kapyb_matmul_host_sharded(
   CUDA_TRY(h, cudaStreamWaitEvent(h->copy_out, ev_start, 0));
   CUDA_TRY(h, cudaStreamWaitEvent(h->push, ev_start, 0));
 
-  // 1. this rank's rows go up in pieces; each piece is forwarded to every peer's
-  //    staging copy over NVLink (copy engines, stores only) as soon as it has landed
-  const char *ha = static_cast<const char *>(elem_ptr(lhs_rows));
-  const size_t row_bytes = static_cast<size_t>(K) * esz_a;
-  const size_t mine_off = static_cast<size_t>(row_begin) * row_bytes;
-  const int pieces = rows_mine >= 1024 ? 4 : 1;
-  const int rows_per_piece = (rows_mine + pieces - 1) / pieces;
-  int n_pieces = 0;
-  for (int r0 = 0; r0 < rows_mine; r0 += rows_per_piece, ++n_pieces) {
-    const int rows = std::min(rows_per_piece, rows_mine - r0);
-    const size_t off = mine_off + static_cast<size_t>(r0) * row_bytes;
-    const size_t bytes = static_cast<size_t>(rows) * row_bytes;
-    CUDA_TRY(h, cudaMemcpyAsync(da + off, ha + static_cast<size_t>(r0) * row_bytes, bytes,
-                                cudaMemcpyHostToDevice, h->copy_in));
-    CUDA_TRY(h, cudaEventRecord(h->ev_push[n_pieces], h->copy_in));
-    CUDA_TRY(h, cudaStreamWaitEvent(h->push, h->ev_push[n_pieces], 0));
-    for (int i = 1; i < world; ++i) {
-      const int peer = (rank + i) % world;  // ranks start with different peers
-      CUDA_TRY(h, cudaMemcpyAsync(static_cast<char *>(ctx->peer_lhs[peer]) + half + off, da + off,
-                                  bytes, cudaMemcpyDeviceToDevice, h->push));
-    }
+  HostTrace trace(rank);
+  // The rows of lhs travel in `pieces` pieces per rank, and the staging copy keeps
+  // them PIECE-MAJOR: piece j of every rank side by side (staging row of rank r,
+  // piece j, row i = (j * world + r) * P + i).  Every rank uploads its piece j at
+  // about the same time, so piece j of the whole matrix is complete long before
+  // piece j+1, and its product and download overlap the upload of the next piece
+  // (PCIe is full duplex; the download is the longer leg when all GPUs of a box
+  // transfer at once).  A per-row bias would have to be permuted the same way, and
+  // ragged row blocks do not tile: both run as one piece (natural row order).
+  const int R = world > 0 ? m_total / world : 0;
+  const bool uniform = m_total % world == 0 && rows_mine == R && row_begin == rank * R;
+  if (!uniform) {
+    // every rank must own the same number of rows for the staging layout to tile
+    return fail(h, KAPYB_UNSUPPORTED,
+                "matmul_host_sharded: every rank must own m_total / world rows, rank r the r-th block");
   }
-  st = kapyb_gather_signal(h, ctx->peer_flags, world, rank, ctx->seq, h->push);
-  if (st != KAPYB_OK) return st;
-  // (this rank's own word is set by that kernel: the compute stream is ordered
-  // after it by an event, never by polling for a kernel of the same GPU)
-  CUDA_TRY(h, cudaEventRecord(h->ev_push[15], h->push));
-  // 2. the column shard of rhs and the bias follow on the same PCIe link
+  int pieces = 1;
+  const bool row_bias = epilogue && epilogue->bias && epilogue->bias_axis == 0;
+  if (!row_bias)
+    for (int p : {4, 2})
+      if (R % p == 0 && (R / p) % 64 == 0 && static_cast<long long>(R / p) * world >= 1024) {
+        pieces = p;
+        break;
+      }
+  const int P = R / pieces;                      // rows per rank and piece
+  const size_t row_bytes = static_cast<size_t>(K) * esz_a;
+  const size_t piece_bytes = static_cast<size_t>(P) * row_bytes;
+  const char *ha = static_cast<const char *>(elem_ptr(lhs_rows));
+  // flag words carry (seq, piece): they only ever grow
+  auto flag_value = [&](int j) { return (ctx->seq << 6) | static_cast<uint32_t>(j + 1); };
+
+  // 1. the column shard of rhs and the bias go up first: every product needs them
   CUDA_TRY(h, cudaMemcpyAsync(db, elem_ptr(rhs), nb, cudaMemcpyHostToDevice, h->copy_in));
   kapyb_epilogue ep;
   if (epilogue)
@@ -1508,11 +1588,31 @@ extern "C" KAPYB_API kapyb_status kapyb_matmul_host_sharded(
   }
   CUDA_TRY(h, cudaEventRecord(h->ev_push[16], h->copy_in));
   CUDA_TRY(h, cudaStreamWaitEvent(stream, h->ev_push[16], 0));
-  CUDA_TRY(h, cudaStreamWaitEvent(stream, h->ev_push[15], 0));
-  // 3. wait (bounded) until every rank's rows have landed here, then multiply row
-  //    chunk by row chunk, each chunk's download overlapping the next one's GEMM
-  st = kapyb_gather_wait(h, ctx->peer_flags[rank], world, ctx->seq, ctx->wait_limit_ms, stream);
-  if (st != KAPYB_OK) return st;
+  trace.mark("rhs shard uploaded", h->copy_in);
+  // 2. this rank's rows, piece by piece; each piece is forwarded to every peer's
+  //    staging copy over NVLink (copy engines, stores only) as soon as it has
+  //    landed, and announced
+  for (int j = 0; j < pieces; ++j) {
+    const size_t off = (static_cast<size_t>(j) * world + rank) * piece_bytes;
+    CUDA_TRY(h, cudaMemcpyAsync(da + off, ha + static_cast<size_t>(j) * piece_bytes, piece_bytes,
+                                cudaMemcpyHostToDevice, h->copy_in));
+    CUDA_TRY(h, cudaEventRecord(h->ev_push[j], h->copy_in));
+    CUDA_TRY(h, cudaStreamWaitEvent(h->push, h->ev_push[j], 0));
+    for (int i = 1; i < world; ++i) {
+      const int peer = (rank + i) % world;  // ranks start with different peers
+      CUDA_TRY(h, cudaMemcpyAsync(static_cast<char *>(ctx->peer_lhs[peer]) + half + off, da + off,
+                                  piece_bytes, cudaMemcpyDeviceToDevice, h->push));
+    }
+    st = kapyb_gather_signal(h, ctx->peer_flags, world, rank, flag_value(j), h->push);
+    if (st != KAPYB_OK) return st;
+    // (this rank's own word is set by that kernel: the compute stream is ordered
+    // after it by an event, never by polling for a kernel of the same GPU)
+    CUDA_TRY(h, cudaEventRecord(h->ev_push[8 + j], h->push));
+  }
+  trace.mark("own rows uploaded", h->copy_in);
+  trace.mark("own rows forwarded", h->push);
+  // 3. per piece: wait (bounded) until every rank's rows of the piece have landed
+  //    here, multiply, and send the piece's rows of the output home
   kapyb_tensor2d dl = full, dr = *rhs, dout = *out;
   dl.ptr = da;
   dl.offset_elems = 0;
@@ -1521,29 +1621,37 @@ extern "C" KAPYB_API kapyb_status kapyb_matmul_host_sharded(
   dout.ptr = dc;
   dout.offset_elems = 0;
   char *hc = static_cast<char *>(const_cast<void *>(elem_ptr(out)));
-  const int rows_per = host_chunk_rows(m_total, rhs->size1, h->sm_count, kMaxChunks);
-  int n_chunks = 0;
-  for (int r0 = 0; r0 < m_total; r0 += rows_per, ++n_chunks) {
-    const int rows = std::min(rows_per, m_total - r0);
-    kapyb_tensor2d cl = dl, co = dout;
-    cl.offset_elems = static_cast<int64_t>(r0) * K;
-    cl.size0 = rows;
-    co.offset_elems = static_cast<int64_t>(r0) * out->stride0;
-    co.size0 = rows;
-    kapyb_epilogue cep = ep;
-    if (cep.bias && cep.bias_axis == 0)
-      cep.bias = static_cast<const char *>(cep.bias) + static_cast<size_t>(r0) * dtype_size(cep.bias_dtype);
-    st = run_matmul(h, make_problem(&cl, &dr, nullptr, &co, &cep), nullptr, 0, stream);
+  const size_t out_row_bytes = static_cast<size_t>(out->stride0) * esz_c;
+  for (int j = 0; j < pieces; ++j) {
+    CUDA_TRY(h, cudaStreamWaitEvent(stream, h->ev_push[8 + j], 0));
+    st = kapyb_gather_wait(h, ctx->peer_flags[rank], world, flag_value(j), ctx->wait_limit_ms, stream);
     if (st != KAPYB_OK) return st;
-    CUDA_TRY(h, cudaEventRecord(h->ev[2 * n_chunks + 1], stream));
-    CUDA_TRY(h, cudaStreamWaitEvent(h->copy_out, h->ev[2 * n_chunks + 1], 0));
-    const size_t c_off = static_cast<size_t>(r0) * out->stride0 * esz_c;
-    CUDA_TRY(h, cudaMemcpyAsync(hc + c_off, dc + c_off, static_cast<size_t>(rows) * out->stride0 * esz_c,
-                                cudaMemcpyDeviceToHost, h->copy_out));
+    const int rows = P * world;                  // piece j of every rank, adjacent in staging
+    const int64_t first = static_cast<int64_t>(j) * rows;
+    kapyb_tensor2d cl = dl, co = dout;
+    cl.offset_elems = first * K;
+    cl.size0 = rows;
+    co.offset_elems = first * out->stride0;
+    co.size0 = rows;
+    st = run_matmul(h, make_problem(&cl, &dr, nullptr, &co, &ep), nullptr, 0, stream);
+    if (st != KAPYB_OK) return st;
+    CUDA_TRY(h, cudaEventRecord(h->ev[2 * j + 1], stream));
+    CUDA_TRY(h, cudaStreamWaitEvent(h->copy_out, h->ev[2 * j + 1], 0));
+    for (int r = 0; r < world; ++r) {
+      // staging rows of (rank r, piece j) -> rows r * R + j * P of the caller's output
+      const size_t src = (static_cast<size_t>(first) + static_cast<size_t>(r) * P) * out_row_bytes;
+      const size_t dst = (static_cast<size_t>(r) * R + static_cast<size_t>(j) * P) * out_row_bytes;
+      CUDA_TRY(h, cudaMemcpyAsync(hc + dst, dc + src, static_cast<size_t>(P) * out_row_bytes,
+                                  cudaMemcpyDeviceToHost, h->copy_out));
+    }
   }
+  trace.mark("products launched", stream);
+  trace.mark("output downloaded", h->copy_out);
   CUDA_TRY(h, cudaEventRecord(ev_done, h->copy_out));
   CUDA_TRY(h, cudaStreamWaitEvent(stream, ev_done, 0));
-  return kapyb_check(h, stream);
+  const kapyb_status done = kapyb_check(h, stream);
+  if (trace.on) fprintf(stderr, "[kapyb trace r%d] call returns at %7.3f ms\n", rank, trace.ms());
+  return done;
 }
 
 // ------------------------------------------------------------- elementwise

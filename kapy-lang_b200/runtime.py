@@ -283,6 +283,28 @@ class Handle:
             self._raise(st)
         return out
 
+    def matmul_reduce(self, lhs, rhs, axis: int, out=None, reduced=None, *, alpha: float = 1.0,
+                      bias=None, bias_axis: int = 1, activation: int = abi.ACT_NONE,
+                      rounding: int = abi.RN, out_dtype=None, combiner: int = abi.RED_ADD,
+                      impl_way: int = abi.MMA_ANY, stream=None):
+        """matmul whose epilogue also sums its f32 result along `axis` (kapy.reduce
+        with an addf lambda on the accumulator tile).  Returns (out, reduced)."""
+        torch = _torch()
+        if out is None:
+            out = torch.empty((lhs.shape[0], rhs.shape[1]), device=lhs.device,
+                              dtype=out_dtype or lhs.dtype)
+        if reduced is None:
+            shape = (1, rhs.shape[1]) if axis == 0 else (lhs.shape[0], 1)
+            reduced = torch.empty(shape, device=lhs.device, dtype=torch.float32)
+        tl, tr, to, td = tensor2d(lhs), tensor2d(rhs), tensor2d(out), tensor2d(reduced)
+        ep = self._epilogue(alpha, bias, bias_axis, activation, rounding)
+        st = self._lib.kapyb_matmul_reduce(self._h, C.byref(tl), C.byref(tr), C.byref(to),
+                                           C.byref(td), int(axis), int(combiner), C.byref(ep),
+                                           impl_way, self._stream(stream))
+        if st != abi.OK:
+            self._raise(st)
+        return out, reduced
+
     def _matmul_batched(self, lhs, rhs, out, *, alpha, bias, bias_axis, activation, rounding,
                         out_dtype, impl_way, stream):
         torch = _torch()

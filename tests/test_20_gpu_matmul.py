@@ -165,6 +165,51 @@ def test_verifier_rejections(handle):
     assert e.shape == (0, 8)
 
 
+@pytest.mark.parametrize("axis", [0, 1])
+@pytest.mark.parametrize("shape", [(512, 384, 256), (200, 264, 136), (1000, 72, 64)])
+def test_reduce_fused_into_the_epilogue(handle, ko, pkg, axis, shape):
+    """kapy.reduce with an addf lambda on the accumulator tile, after scale, bias
+    and relu: the f32 values are summed along `axis` by the epilogue itself.
+    Checked against the f64 matmul summed in f64 (the order of the f32 atomic adds
+    is unspecified: bound = 1e-5 * sum|c| per result), and `out` against the same
+    tolerance as any matmul; ragged tiles must not leak their padding into the sums."""
+    M, N, K = shape
+    A, B = normal((M, K), 61, K ** -0.5), normal((K, N), 62)
+    bias = uniform((N,), 63, -0.5, 0.5, torch.bfloat16)
+    ep = dict(alpha=0.75, bias=bias.cuda(), activation=pkg.abi.ACT_RELU)
+    out, red = handle.matmul_reduce(A.cuda(), B.cuda(), axis, **ep)
+    handle.check()
+    assert handle.last_kernel == "tcgen05_1cta"
+    assert red.shape == ((1, N) if axis == 0 else (M, 1)) and red.dtype == torch.float32
+    ref = ko.matmul_f64(bits(A), 1, bits(B), 1, alpha=0.75, bias=bits(bias), bias_dtype=1,
+                        activation=pkg.abi.ACT_RELU)
+    err, _ = ko.max_rel_err(out.cpu().double().numpy(), ref)
+    assert err <= TOL
+    want, scale = ref.sum(axis=axis), np.abs(ref).sum(axis=axis)
+    got = red.cpu().double().numpy().ravel()
+    assert np.all(np.abs(got - want) <= 1e-5 * scale + 1e-12), np.abs(got - want).max()
+    # the unfused pair of calls gives the same sums to the same bound
+    plain = handle.matmul(A.cuda(), B.cuda(), out_dtype=torch.float32, **ep)
+    two_pass = handle.reduce(plain, axis=axis).cpu().double().numpy().ravel()
+    assert np.all(np.abs(got - two_pass) <= 1e-5 * scale + 1e-12)
+    # a second call starts from zero again (the sums are cleared, not accumulated)
+    out2, red2 = handle.matmul_reduce(A.cuda(), B.cuda(), axis, out=out, reduced=red, **ep)
+    handle.check()
+    assert np.all(np.abs(red2.cpu().double().numpy().ravel() - want) <= 1e-5 * scale + 1e-12)
+
+
+def test_reduce_epilogue_rules(handle, pkg):
+    z = lambda s, d=torch.bfloat16: torch.zeros(s, dtype=d, device="cuda")
+    with pytest.raises(ValueError, match="result shape"):
+        handle.matmul_reduce(z((64, 64)), z((64, 128)), 1, reduced=z((1, 128), torch.float32))
+    with pytest.raises(pkg.KapybError, match="only the addf lambda"):
+        handle.matmul_reduce(z((64, 64)), z((64, 128)), 1, combiner=pkg.abi.RED_MAX)
+    with pytest.raises(pkg.KapybError, match="dense f32 vector"):
+        handle.matmul_reduce(z((64, 64)), z((64, 128)), 1, reduced=z((64, 1)))
+    o, r = handle.matmul_reduce(z((0, 64)), z((64, 128)), 0)
+    assert o.shape == (0, 128) and r.shape == (1, 128)
+
+
 def test_operand_padding_is_zero_only(handle, pkg):
     """ld_global's QNAN / +-INF padding (Enums.td:52-61) has no whole-problem
     meaning for a matmul operand (it would poison every output whose K range is
