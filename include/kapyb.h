@@ -75,6 +75,34 @@ typedef enum {
   KAPYB_PAD_NINF = 3
 } kapyb_padding;
 
+/* Enums.td:63-76: the cache operator of ld_global / st_global (PTX .ca .cg .cs
+ * .wb .wt .lu .cv). */
+typedef enum {
+  KAPYB_CACHE_NONE = 0,
+  KAPYB_CACHE_CA = 1,
+  KAPYB_CACHE_CG = 2,
+  KAPYB_CACHE_CS = 3,
+  KAPYB_CACHE_WB = 4,
+  KAPYB_CACHE_WT = 5,
+  KAPYB_CACHE_LU = 6,
+  KAPYB_CACHE_CV = 7
+} kapyb_cache_modifier;
+
+/* Enums.td:78-88: the eviction priority of ld_global / st_global. */
+typedef enum {
+  KAPYB_EVICT_NORMAL = 0,
+  KAPYB_EVICT_FIRST = 1,
+  KAPYB_EVICT_LAST = 2,
+  KAPYB_EVICT_UNCHANGED = 3,
+  KAPYB_NO_ALLOCATE = 4
+} kapyb_evict_priority;
+
+/* kapyb_tensor2d.cache: cache operator, eviction priority and the volatile flag
+ * of the ld_global / st_global that touches the tensor
+ * (LdGlobalOpToLLVM.cpp:101-110, StGlobalOpToLLVM.cpp:100-108). */
+#define KAPYB_CACHE_HINTS(modifier, priority, is_volatile) \
+  ((int32_t)(modifier) | ((int32_t)(priority) << 8) | ((is_volatile) ? (1 << 16) : 0))
+
 /* Enums.td:90-100.  Names an sm_80 instruction; validated against the operand
  * dtypes exactly as MatmulOp::verify does (Kapy.cpp:491-565) and otherwise
  * ignored: scheduling on sm_100a is tcgen05. */
@@ -128,6 +156,17 @@ typedef struct {
   int32_t padding; /* kapyb_padding: what an elementwise load returns out of bounds.
                       Matmul operands take KAPYB_PAD_ZERO only (anything else is
                       refused with KAPYB_UNSUPPORTED); outputs ignore it. */
+  int32_t cache;   /* KAPYB_CACHE_HINTS(...), 0 = none.  Hints never change a
+                      result.  Elementwise programs on the general kernel issue the
+                      very ld / st forms the reference emits (a cache operator
+                      wins over a priority, volatile over both).  Matmul operands
+                      map the priority to an L2 policy on their TMA loads:
+                      EVICT_FIRST -> L2::evict_first, EVICT_LAST -> L2::evict_last,
+                      NO_ALLOCATE -> L2::evict_first (a tile is never loaded
+                      around L2); other values leave the default.  The fused
+                      streaming kernels and kapyb_reduce keep their own policy
+                      (read-once loads that bypass L1, streaming stores). */
+  int32_t reserved_; /* keeps the struct a multiple of 8 bytes; set to 0 */
 } kapyb_tensor2d;
 
 /* result = downcast(act(alpha * (lhs . rhs) + bias [+ acc])).

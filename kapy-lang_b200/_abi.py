@@ -17,6 +17,16 @@ OK, INVALID_ARG, UNSUPPORTED, CUDA_ERROR, _UNUSED_4, TIMEOUT = range(6)
 F16, BF16, F32, F8E4M3, F8E5M2, I1 = 0, 1, 2, 3, 4, 5
 # kapyb_padding (Enums.td:52-61)
 PAD_ZERO, PAD_QNAN, PAD_PINF, PAD_NINF = 0, 1, 2, 3
+# kapyb_cache_modifier / kapyb_evict_priority (Enums.td:63-88)
+CACHE_NONE, CACHE_CA, CACHE_CG, CACHE_CS, CACHE_WB, CACHE_WT, CACHE_LU, CACHE_CV = range(8)
+EVICT_NORMAL, EVICT_FIRST, EVICT_LAST, EVICT_UNCHANGED, NO_ALLOCATE = range(5)
+
+
+def cache_hints(modifier: int = 0, priority: int = 0, is_volatile: bool = False) -> int:
+    """KAPYB_CACHE_HINTS: the `cache` field of a tensor descriptor."""
+    return int(modifier) | (int(priority) << 8) | ((1 << 16) if is_volatile else 0)
+
+
 # kapyb_rounding (Enums.td:102-109)
 RZ, RN = 0, 1
 # kapyb_activation
@@ -41,7 +51,8 @@ class Tensor2d(C.Structure):
     _fields_ = [("ptr", C.c_void_p), ("offset_elems", C.c_int64),
                 ("size0", C.c_int32), ("size1", C.c_int32),
                 ("stride0", C.c_int32), ("stride1", C.c_int32),
-                ("dtype", C.c_int32), ("padding", C.c_int32)]
+                ("dtype", C.c_int32), ("padding", C.c_int32),
+                ("cache", C.c_int32), ("reserved_", C.c_int32)]
 
 
 class Epilogue(C.Structure):

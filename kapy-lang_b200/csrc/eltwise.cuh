@@ -21,7 +21,120 @@ struct EltTensor {
   int size0, size1;
   int dtype;
   int padding;
+  int cache;        // KAPYB_CACHE_HINTS of the ld_global / st_global on this tensor
 };
+
+// ld.global / st.global in the forms the reference emits for a cache operator or
+// an eviction priority (LdGlobalOpToLLVM.cpp:101-110, StGlobalOpToLLVM.cpp:100-108):
+// volatile wins, then the cache operator, then "L1::<priority>".  A hint never
+// changes the value moved.
+// X(form index, qualifier before ".global", qualifier after it)
+#define KAPYB_LD_FORMS(X)                                                                    \
+  X(0, "", "") X(1, "", ".ca") X(2, "", ".cg") X(3, "", ".cs") X(4, "", ".lu") X(5, "", ".cv") \
+  X(6, ".volatile", "") X(7, "", ".L1::evict_first") X(8, "", ".L1::evict_last")             \
+  X(9, "", ".L1::evict_unchanged") X(10, "", ".L1::no_allocate")
+#define KAPYB_ST_FORMS(X)                                                                    \
+  X(0, "", "") X(1, "", ".wb") X(2, "", ".cg") X(3, "", ".cs") X(4, "", ".wt")               \
+  X(6, ".volatile", "") X(7, "", ".L1::evict_first") X(8, "", ".L1::evict_last")             \
+  X(9, "", ".L1::evict_unchanged") X(10, "", ".L1::no_allocate")
+
+// form index of a load (0 = plain) from the packed hints
+__host__ __device__ inline int ld_form(int cache) {
+  if (cache & (1 << 16)) return 6;
+  switch (cache & 0xff) {
+  case KAPYB_CACHE_CA: return 1;
+  case KAPYB_CACHE_CG: return 2;
+  case KAPYB_CACHE_CS: return 3;
+  case KAPYB_CACHE_LU: return 4;
+  case KAPYB_CACHE_CV: return 5;
+  default: break;  // NONE; WB / WT are store operators
+  }
+  switch ((cache >> 8) & 0xff) {
+  case KAPYB_EVICT_FIRST: return 7;
+  case KAPYB_EVICT_LAST: return 8;
+  case KAPYB_EVICT_UNCHANGED: return 9;
+  case KAPYB_NO_ALLOCATE: return 10;
+  default: return 0;
+  }
+}
+__host__ __device__ inline int st_form(int cache) {
+  if (cache & (1 << 16)) return 6;
+  switch (cache & 0xff) {
+  case KAPYB_CACHE_WB: return 1;
+  case KAPYB_CACHE_CG: return 2;
+  case KAPYB_CACHE_CS: return 3;
+  case KAPYB_CACHE_WT: return 4;
+  default: break;  // NONE; CA / LU / CV are load operators
+  }
+  switch ((cache >> 8) & 0xff) {
+  case KAPYB_EVICT_FIRST: return 7;
+  case KAPYB_EVICT_LAST: return 8;
+  case KAPYB_EVICT_UNCHANGED: return 9;
+  case KAPYB_NO_ALLOCATE: return 10;
+  default: return 0;
+  }
+}
+
+// the bits of one element (8, 16 or 32 of them), loaded / stored with form `form`
+__device__ __forceinline__ uint32_t ld_bits_form(const void *p, int bytes, int form) {
+  uint32_t v = 0;
+  uint16_t h = 0;
+#define KAPYB_X(ID, PRE, POST)                                                                    \
+  case ID:                                                                                  \
+    if (bytes == 4)                                                                         \
+      asm volatile("ld" PRE ".global" POST ".u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");      \
+    else if (bytes == 2) {                                                                  \
+      asm volatile("ld" PRE ".global" POST ".u16 %0, [%1];" : "=h"(h) : "l"(p) : "memory");      \
+      v = h;                                                                                \
+    } else {                                                                                \
+      asm volatile("ld" PRE ".global" POST ".u8 %0, [%1];" : "=h"(h) : "l"(p) : "memory");       \
+      v = h & 0xffu;                                                                        \
+    }                                                                                       \
+    break;
+  switch (form) { KAPYB_LD_FORMS(KAPYB_X) default: break; }
+#undef KAPYB_X
+  return v;
+}
+__device__ __forceinline__ void st_bits_form(void *p, int bytes, int form, uint32_t v) {
+  const uint16_t h = static_cast<uint16_t>(v);
+#define KAPYB_X(ID, PRE, POST)                                                                    \
+  case ID:                                                                                  \
+    if (bytes == 4)                                                                         \
+      asm volatile("st" PRE ".global" POST ".u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");         \
+    else if (bytes == 2)                                                                    \
+      asm volatile("st" PRE ".global" POST ".u16 [%0], %1;" ::"l"(p), "h"(h) : "memory");         \
+    else                                                                                    \
+      asm volatile("st" PRE ".global" POST ".u8 [%0], %1;" ::"l"(p), "h"(h) : "memory");          \
+    break;
+  switch (form) { KAPYB_ST_FORMS(KAPYB_X) default: break; }
+#undef KAPYB_X
+}
+
+__device__ __forceinline__ float load_as_f32_form(const void *base, int dtype, long long idx,
+                                                  int form) {
+  if (form == 0) return load_as_f32(base, dtype, idx);
+  const int bytes = dtype_size(dtype);
+  const uint32_t v = ld_bits_form(static_cast<const char *>(base) + idx * bytes, bytes, form);
+  if (dtype == KAPYB_F32) return __uint_as_float(v);
+  if (is_fp8_dtype(dtype)) return cvt_fp8_to_f32(static_cast<uint8_t>(v), dtype);
+  return cvt_16_to_f32(static_cast<uint16_t>(v), dtype);
+}
+__device__ __forceinline__ void store_from_f32_form(void *base, int dtype, long long idx, float x,
+                                                    int rn, int form) {
+  if (form == 0) {
+    store_from_f32(base, dtype, idx, x, rn);
+    return;
+  }
+  const int bytes = dtype_size(dtype);
+  uint32_t v;
+  if (dtype == KAPYB_F32)
+    v = __float_as_uint(x);
+  else if (is_fp8_dtype(dtype))
+    v = cvt_f32_to_fp8(x, dtype, rn);
+  else
+    v = cvt_f32_to_16(x, dtype, rn);
+  st_bits_form(static_cast<char *>(base) + idx * bytes, bytes, form, v);
+}
 
 struct EltProgram {
   kapyb_inst inst[KAPYB_MAX_INSTS];
@@ -102,7 +215,7 @@ __device__ float interp_one(const EltProgram &P, int i, int j, bool *stored, flo
       if (ii >= t.size0 || jj >= t.size1)
         v = pad_value(t.padding);
       else
-        v = load_as_f32(t.ptr, t.dtype, ii * t.s0 + jj * t.s1);
+        v = load_as_f32_form(t.ptr, t.dtype, ii * t.s0 + jj * t.s1, ld_form(t.cache));
       break;
     }
     case KAPYB_OP_CONST: v = round_to_dtype(in.imm, dt, 1); break;
@@ -176,7 +289,8 @@ __global__ void __launch_bounds__(256) elt_interp_kernel(const EltProgram P) {
       // the stored register already holds a value of the output's type
       // (f8E5M2: the truncating encoder, which keeps an infinity; the rounding
       // one saturates it)
-      store_from_f32(o, P.out.dtype, idx, sv, P.out.dtype == KAPYB_F8E5M2 ? 0 : 1);
+      store_from_f32_form(o, P.out.dtype, idx, sv, P.out.dtype == KAPYB_F8E5M2 ? 0 : 1,
+                          st_form(P.out.cache));
     }
   }
 }

@@ -70,6 +70,7 @@ struct SkinnyParams {
                            // bit3 skip the publish/count/owner pass, bit4 skip whole-tile
                            // stores, bit5 skip the partial-sum stores
   EpilogueArgs ep;
+  int w_l2, x_l2;  // L2 policy of the weight / activation tile loads: 0 default, 1 evict_first, 2 evict_last
 };
 
 // The work of one CTA, as a list of per-tile segments.  The first `sk_tiles`
@@ -202,6 +203,14 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     uint32_t phase = 0;
     const uint32_t stage_bytes = W_BYTES + p.x_bytes;
     bool ok = true;
+    const uint64_t pol_w = p.w_l2 ? ptx::make_l2_policy(p.w_l2) : 0ull;
+    const uint64_t pol_x = p.x_l2 ? ptx::make_l2_policy(p.x_l2) : 0ull;
+    auto load1 = [](uint64_t pol, uint32_t dst, const CUtensorMap *tm, uint32_t bar, int x, int y) {
+      if (pol)
+        ptx::tma_load_3d_hint(dst, tm, bar, x, y, 0, pol);
+      else
+        ptx::tma_load_3d(dst, tm, bar, x, y, 0);
+    };
     for (int j = 0; j < work.count() && ok; ++j) {
       int tile, kb_begin, kb_end;
       work.get(j, tile, kb_begin, kb_end);
@@ -216,15 +225,15 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         const uint32_t w_dst = ptx::smem_u32(sW + stage * W_BYTES);
         const uint32_t x_dst = ptx::smem_u32(sX + stage * p.x_bytes);
         if (p.w_mn_major) {
-          ptx::tma_load_3d(w_dst, &tmW, fb, n0, k0, 0);
-          ptx::tma_load_3d(w_dst + 8192, &tmW, fb, n0 + 64, k0, 0);
+          load1(pol_w, w_dst, &tmW, fb, n0, k0);
+          load1(pol_w, w_dst + 8192, &tmW, fb, n0 + 64, k0);
         } else {
-          ptx::tma_load_3d(w_dst, &tmW, fb, k0, n0, 0);
+          load1(pol_w, w_dst, &tmW, fb, k0, n0);
         }
         if (p.x_mn_major)
-          ptx::tma_load_3d(x_dst, &tmX, fb, 0, k0, 0);
+          load1(pol_x, x_dst, &tmX, fb, 0, k0);
         else
-          ptx::tma_load_3d(x_dst, &tmX, fb, k0, 0, 0);
+          load1(pol_x, x_dst, &tmX, fb, k0, 0);
         if (++stage == p.stages) {
           stage = 0;
           phase ^= 1u;

@@ -132,6 +132,9 @@ struct GemmParams {
   // column) into the zero-initialised vector `red` with fp32 atomics.
   float *red;
   int red_axis;
+  // L2 policy of the TMA traffic per tensor (from the descriptors' eviction
+  // priority): 0 default, 1 evict_first, 2 evict_last
+  int a_l2, b_l2, c_l2;
 };
 
 template <int BN, int CTAS, int EPI = 4>
@@ -401,8 +404,14 @@ __device__ __forceinline__ bool epilogue_tile(const GemmParams &p, const TmapArr
     __syncwarp();
     const uint32_t c3 = probing ? static_cast<uint32_t>(clock()) : 0u;
     if (lane == 0 && !debug_on<8>(p.debug)) {
-      for (int o = 0; o < p.n_out; ++o)
-        ptx::tma_store_3d(&tmC.m[o], ptx::smem_u32(sbuf), p.out_col_offset + nc, t.m0, t.b);
+      if (p.c_l2) {
+        const uint64_t pol = ptx::make_l2_policy(p.c_l2);
+        for (int o = 0; o < p.n_out; ++o)
+          ptx::tma_store_3d_hint(&tmC.m[o], ptx::smem_u32(sbuf), p.out_col_offset + nc, t.m0, t.b, pol);
+      } else {
+        for (int o = 0; o < p.n_out; ++o)
+          ptx::tma_store_3d(&tmC.m[o], ptx::smem_u32(sbuf), p.out_col_offset + nc, t.m0, t.b);
+      }
       ptx::tma_store_commit();
     }
     if (probing && lane == 0) {
@@ -441,8 +450,14 @@ __device__ __forceinline__ bool epilogue_two_halves(const GemmParams &p, const T
     ptx::fence_proxy_async_smem();
     __syncwarp();
     if (lane == 0 && !debug_on<8>(p.debug)) {
-      for (int o = 0; o < p.n_out; ++o)
-        ptx::tma_store_3d(&tmC.m[o], ptx::smem_u32(t.stg), p.out_col_offset + nc, t.m0, t.b);
+      if (p.c_l2) {
+        const uint64_t pol = ptx::make_l2_policy(p.c_l2);
+        for (int o = 0; o < p.n_out; ++o)
+          ptx::tma_store_3d_hint(&tmC.m[o], ptx::smem_u32(t.stg), p.out_col_offset + nc, t.m0, t.b, pol);
+      } else {
+        for (int o = 0; o < p.n_out; ++o)
+          ptx::tma_store_3d(&tmC.m[o], ptx::smem_u32(t.stg), p.out_col_offset + nc, t.m0, t.b);
+      }
       ptx::tma_store_commit();
     }
   };
@@ -663,6 +678,23 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
+    const uint64_t pol_a = p.a_l2 ? ptx::make_l2_policy(p.a_l2) : 0ull;
+    const uint64_t pol_b = p.b_l2 ? ptx::make_l2_policy(p.b_l2) : 0ull;
+    // one tile load of A or B (pol == 0: the plain form)
+    auto load1 = [](uint64_t pol, uint32_t dst, const CUtensorMap *tm, uint32_t bar, int x, int y,
+                    int z) {
+      if (pol)
+        ptx::tma_load_3d_hint(dst, tm, bar, x, y, z, pol);
+      else
+        ptx::tma_load_3d(dst, tm, bar, x, y, z);
+    };
+    auto load2 = [](uint64_t pol, uint32_t dst, const CUtensorMap *tm, uint32_t bar, int x, int y,
+                    int z) {
+      if (pol)
+        ptx::tma_load_3d_pair_hint(dst, tm, bar, x, y, z, pol);
+      else
+        ptx::tma_load_3d_pair(dst, tm, bar, x, y, z);
+    };
     for (int tile = unit; tile < p.num_tiles && ok && !debug_on<16 | 32>(p.debug); tile += unit_step) {
       int b, mb, nb;
       decode_tile(p, tile, b, mb, nb);
@@ -689,19 +721,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
           const uint32_t fb = ptx::smem_u32(&full_bar[stage]);
           ptx::mbar_arrive_expect_tx(fb, Cfg::STAGE_BYTES);
           if (!p.a_mn_major) {
-            ptx::tma_load_3d(a_dst, &tmA, fb, k0, m0, b);
+            load1(pol_a, a_dst, &tmA, fb, k0, m0, b);
           } else {
             for (int j = 0; j < a_chunks; ++j)
-              ptx::tma_load_3d(a_dst + j * p.mn_lbo, &tmA, fb, m0 + ce * j, k0, b);
+              load1(pol_a, a_dst + j * p.mn_lbo, &tmA, fb, m0 + ce * j, k0, b);
           }
           if (!p.b_mn_major) {
             // one box of kGroupCols rows per column half
 #pragma unroll
             for (int hh = 0; hh < Cfg::SPLIT; ++hh)
-              ptx::tma_load_3d(b_dst + hh * (kGroupCols * 128), &tmB, fb, k0, nB0 + hh * Cfg::MMA_N, b);
+              load1(pol_b, b_dst + hh * (kGroupCols * 128), &tmB, fb, k0, nB0 + hh * Cfg::MMA_N, b);
           } else {
             for (int j = 0; j < b_chunks; ++j)
-              ptx::tma_load_3d(b_dst + j * p.mn_lbo, &tmB, fb, nB0 + ce * j, k0, b);
+              load1(pol_b, b_dst + j * p.mn_lbo, &tmB, fb, nB0 + ce * j, k0, b);
           }
         } else {
           // Both CTAs' loads report their bytes to the leader's barrier; the
@@ -711,22 +743,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
           if (rank == 0)
             ptx::mbar_arrive_expect_tx(ptx::smem_u32(&full_bar[stage]), 2 * Cfg::STAGE_BYTES);
           if (!p.a_mn_major) {
-            ptx::tma_load_3d_pair(a_dst, &tmA, fb, k0, m0, b);
+            load2(pol_a, a_dst, &tmA, fb, k0, m0, b);
           } else {
             for (int j = 0; j < a_chunks; ++j)
-              ptx::tma_load_3d_pair(a_dst + j * p.mn_lbo, &tmA, fb, m0 + ce * j, k0, b);
+              load2(pol_a, a_dst + j * p.mn_lbo, &tmA, fb, m0 + ce * j, k0, b);
           }
           if (!p.b_mn_major) {
             // one box of kGroupCols rows per half
 #pragma unroll
             for (int hh = 0; hh < Cfg::SPLIT; ++hh)
-              ptx::tma_load_3d_pair(b_dst + hh * (kGroupCols * 128), &tmB, fb, k0,
-                                    nB0 + hh * Cfg::MMA_N, b);
+              load2(pol_b, b_dst + hh * (kGroupCols * 128), &tmB, fb, k0, nB0 + hh * Cfg::MMA_N, b);
           } else {
             for (int j = 0; j < b_chunks; ++j) {
               const int hh = (j * ce) / kGroupCols, within = (j * ce) % kGroupCols;
-              ptx::tma_load_3d_pair(b_dst + j * p.mn_lbo, &tmB, fb,
-                                    nB0 + hh * Cfg::MMA_N + within, k0, b);
+              load2(pol_b, b_dst + j * p.mn_lbo, &tmB, fb, nB0 + hh * Cfg::MMA_N + within, k0, b);
             }
           }
         }

@@ -298,6 +298,11 @@ extern "C" KAPYB_API kapyb_status kapyb_shard_range(int64_t total, int32_t parts
 
 // --------------------------------------------------------------- validation
 
+// kapyb_tensor2d.cache: cache operator 0..7, eviction priority 0..4, volatile bit
+static bool valid_cache(int c) {
+  return (c & ~0x1ffff) == 0 && (c & 0xff) <= KAPYB_CACHE_CV && ((c >> 8) & 0xff) <= KAPYB_NO_ALLOCATE;
+}
+
 static bool valid_dtype(int d) { return d == KAPYB_F16 || d == KAPYB_BF16 || d == KAPYB_F32; }
 static bool is_fp8(int d) { return d == KAPYB_F8E4M3 || d == KAPYB_F8E5M2; }
 static bool valid_operand_dtype(int d) { return valid_dtype(d) || is_fp8(d); }
@@ -335,6 +340,8 @@ static kapyb_status verify_matmul(kapyb_handle h, const kapyb_tensor2d *lhs,
   // of ld_global (Enums.td:52-61) would put NaN or infinities into every output
   // whose K range is ragged against the kernel's tile, which depends on a tile
   // size the caller cannot see: refuse them instead of ignoring them.
+  if (!valid_cache(lhs->cache) || !valid_cache(rhs->cache) || !valid_cache(out->cache))
+    return fail(h, KAPYB_INVALID_ARG, "matmul: unknown cache operator or eviction priority");
   if (lhs->padding != KAPYB_PAD_ZERO || rhs->padding != KAPYB_PAD_ZERO)
     return fail(h, KAPYB_UNSUPPORTED,
                 "matmul: operands are padded with zeros only (padding option %d requested)",
@@ -455,7 +462,19 @@ struct MatmulProblem {
   long long a_s0, a_s1, a_bs, b_s0, b_s1, b_bs, c_s0, c_s1, c_bs;
   int in_dtype, in_dtype_b, out_dtype;
   EpilogueArgs ep;
+  int a_l2 = 0, b_l2 = 0, c_l2 = 0;  // L2 policy of each tensor's TMA traffic (see l2_policy_of)
 };
+
+// kapyb_tensor2d.cache -> L2 policy of the tensor's TMA loads / stores: 0 default,
+// 1 evict_first, 2 evict_last.  Tiles always pass through L2, so NO_ALLOCATE (and a
+// streaming cache operator) become evict_first.
+static int l2_policy_of(int cache) {
+  const int mod = cache & 0xff, prio = (cache >> 8) & 0xff;
+  if (prio == KAPYB_EVICT_FIRST || prio == KAPYB_NO_ALLOCATE) return 1;
+  if (prio == KAPYB_EVICT_LAST) return 2;
+  if (mod == KAPYB_CACHE_CS || mod == KAPYB_CACHE_LU) return 1;
+  return 0;
+}
 
 static EpilogueArgs make_ep(const kapyb_epilogue *ep, const kapyb_tensor2d *acc) {
   EpilogueArgs e;
@@ -486,6 +505,7 @@ static void transpose_problem(MatmulProblem &p) {
   p.b_s1 = a0;
   p.b_bs = ab;
   std::swap(p.c_s0, p.c_s1);
+  std::swap(p.a_l2, p.b_l2);
   std::swap(p.ep.acc_stride0, p.ep.acc_stride1);
   p.ep.bias_axis ^= 1;
 }
@@ -593,6 +613,9 @@ static kapyb_status launch_tcgen05(kapyb_handle h, const MatmulProblem &p, bool 
   gp.ep = p.ep;
   gp.red = red;
   gp.red_axis = red_axis;
+  gp.a_l2 = p.a_l2;
+  gp.b_l2 = p.b_l2;
+  gp.c_l2 = p.c_l2;
 
   auto kern = gemm_tcgen05_kernel<BN, CTAS, EPI, REDUCE>;
   static bool attr_set[kMaxDevices] = {};
@@ -682,6 +705,8 @@ static kapyb_status launch_skinny_on(kapyb_handle h, const MatmulProblem &p, boo
   sp.wait_limit_us = h->wait_limit_us;
   sp.debug = h->debug;
   sp.ep = p.ep;
+  sp.w_l2 = p.b_l2;
+  sp.x_l2 = p.a_l2;
   // Whole tiles round-robin while they fill the GPU evenly; the leftover tiles
   // (all of them when there are fewer tiles than SMs) are split into equal spans.
   int grid;
@@ -925,23 +950,6 @@ static kapyb_status plan_decide(const PlanOptions &o, const MatmulProblem &p, vo
       // less than half a wave of 256-wide pair tiles: 128-wide ones put more SMs to work
       const long long t256 = static_cast<long long>((p.M + 255) / 256) * ((p.N + 255) / 256) * p.batch;
       if (bn == 256 && t256 * 2 <= pairs) bn = 128;
-      // Push epilogue to peers: a tile's stores leave only when its K loop is over,
-      // so with a single wave of tiles the whole transfer follows the whole
-      // computation.  Take the widest tile that still gives three waves (the
-      // stores of one wave then cross NVLink under the main loops of the next),
-      // else the narrowest.
-      if (n_peers > 1) {
-        auto waves = [&](int w) {
-          const long long t = static_cast<long long>((p.M + 255) / 256) * ((p.N + w - 1) / w) * p.batch;
-          return static_cast<double>(t) / pairs;
-        };
-        bn = 128;
-        for (int w : {512, 256})
-          if ((w != 512 || (p.N >= 512 && p.K >= 1024)) && waves(w) >= 3.0) {
-            bn = w;
-            break;
-          }
-      }
     }
     if (bn == 64) bn = 128;
     if (group_cols(bn, 2) < min_cols) bn = 512;
@@ -1028,6 +1036,9 @@ static MatmulProblem make_problem(const kapyb_tensor2d *lhs, const kapyb_tensor2
   p.in_dtype_b = rhs->dtype;
   p.out_dtype = out->dtype;
   p.ep = make_ep(ep, acc);
+  p.a_l2 = l2_policy_of(lhs->cache);
+  p.b_l2 = l2_policy_of(rhs->cache);
+  p.c_l2 = l2_policy_of(out->cache);
   return p;
 }
 
@@ -1249,6 +1260,8 @@ extern "C" KAPYB_API kapyb_status kapyb_matmul_push(
   out.stride1 = 1;
   out.dtype = out_dtype;
   out.padding = 0;
+  out.cache = 0;
+  out.reserved_ = 0;
   kapyb_status st = verify_matmul(h, lhs, rhs, nullptr, &out, epilogue, impl_way);
   if (st != KAPYB_OK) return st;
   void *outs[kMaxOutputs];
@@ -1447,26 +1460,53 @@ extern "C" KAPYB_API kapyb_status kapyb_gather_wait(kapyb_handle h, const void *
 
 // ------------------------------------------- host buffers, rows of A sharded
 
-// KAPYB_TRACE=1 in the environment makes the sharded host call print, per phase,
-// the host time at which the phase's work had been issued and the time at which
-// the stream it runs on had drained (the drain serialises the phases: a
-// diagnosis aid, never on in a timed run).
+// KAPYB_TRACE=1 in the environment makes the sharded host call record a timing
+// event on the stream of each phase as the phase is issued and, when the call is
+// over, print when each one completed on the device (milliseconds after the
+// call's first event) next to the host time at which it had been issued.
+// Nothing is synchronised while the call runs, so the overlap is the real one.
+// A diagnosis aid: events are created per call, so leave it off in timed runs.
 struct HostTrace {
   bool on;
   int rank;
   std::chrono::steady_clock::time_point t0;
-  HostTrace(int rank_) : rank(rank_), t0(std::chrono::steady_clock::now()) {
+  struct Mark {
+    const char *what;
+    int index;
+    cudaEvent_t ev;
+    double issued_ms;
+  };
+  std::vector<Mark> marks;
+  explicit HostTrace(int rank_) : rank(rank_), t0(std::chrono::steady_clock::now()) {
     const char *e = getenv("KAPYB_TRACE");
     on = e && e[0] && e[0] != '0';
   }
   double ms() const {
     return std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
   }
-  void mark(const char *what, cudaStream_t s) {
+  void mark(const char *what, cudaStream_t s, int index = -1) {
     if (!on) return;
-    const double issued = ms();
-    cudaStreamSynchronize(s);
-    fprintf(stderr, "[kapyb trace r%d] %-28s issued %7.3f ms, drained %7.3f ms\n", rank, what, issued, ms());
+    cudaEvent_t ev;
+    if (cudaEventCreate(&ev) != cudaSuccess) return;
+    cudaEventRecord(ev, s);
+    marks.push_back(Mark{what, index, ev, ms()});
+  }
+  // call after everything has completed
+  void report() {
+    if (!on || marks.empty()) return;
+    for (const Mark &m : marks) {
+      float dev_ms = 0.0f;
+      cudaEventElapsedTime(&dev_ms, marks[0].ev, m.ev);
+      if (m.index >= 0)
+        fprintf(stderr, "[kapyb trace r%d] %-22s %d  issued %7.3f ms, done on device %7.3f ms\n", rank,
+                m.what, m.index, m.issued_ms, dev_ms);
+      else
+        fprintf(stderr, "[kapyb trace r%d] %-24s issued %7.3f ms, done on device %7.3f ms\n", rank,
+                m.what, m.issued_ms, dev_ms);
+    }
+    fprintf(stderr, "[kapyb trace r%d] call returns at %7.3f ms (host)\n", rank, ms());
+    for (const Mark &m : marks) cudaEventDestroy(m.ev);
+    marks.clear();
   }
 };
 
@@ -1539,6 +1579,7 @@ extern "C" KAPYB_API kapyb_status kapyb_matmul_host_sharded(
   CUDA_TRY(h, cudaStreamWaitEvent(h->push, ev_start, 0));
 
   HostTrace trace(rank);
+  trace.mark("start", stream);
   // The rows of lhs travel in `pieces` pieces per rank, and the staging copy keeps
   // them PIECE-MAJOR: piece j of every rank side by side (staging row of rank r,
   // piece j, row i = (j * world + r) * P + i).  Every rank uploads its piece j at
@@ -1597,6 +1638,7 @@ extern "C" KAPYB_API kapyb_status kapyb_matmul_host_sharded(
     CUDA_TRY(h, cudaMemcpyAsync(da + off, ha + static_cast<size_t>(j) * piece_bytes, piece_bytes,
                                 cudaMemcpyHostToDevice, h->copy_in));
     CUDA_TRY(h, cudaEventRecord(h->ev_push[j], h->copy_in));
+    trace.mark("own piece uploaded", h->copy_in, j);
     CUDA_TRY(h, cudaStreamWaitEvent(h->push, h->ev_push[j], 0));
     for (int i = 1; i < world; ++i) {
       const int peer = (rank + i) % world;  // ranks start with different peers
@@ -1608,9 +1650,8 @@ extern "C" KAPYB_API kapyb_status kapyb_matmul_host_sharded(
     // (this rank's own word is set by that kernel: the compute stream is ordered
     // after it by an event, never by polling for a kernel of the same GPU)
     CUDA_TRY(h, cudaEventRecord(h->ev_push[8 + j], h->push));
+    trace.mark("own piece forwarded", h->push, j);
   }
-  trace.mark("own rows uploaded", h->copy_in);
-  trace.mark("own rows forwarded", h->push);
   // 3. per piece: wait (bounded) until every rank's rows of the piece have landed
   //    here, multiply, and send the piece's rows of the output home
   kapyb_tensor2d dl = full, dr = *rhs, dout = *out;
@@ -1626,6 +1667,7 @@ extern "C" KAPYB_API kapyb_status kapyb_matmul_host_sharded(
     CUDA_TRY(h, cudaStreamWaitEvent(stream, h->ev_push[8 + j], 0));
     st = kapyb_gather_wait(h, ctx->peer_flags[rank], world, flag_value(j), ctx->wait_limit_ms, stream);
     if (st != KAPYB_OK) return st;
+    trace.mark("piece complete here", stream, j);
     const int rows = P * world;                  // piece j of every rank, adjacent in staging
     const int64_t first = static_cast<int64_t>(j) * rows;
     kapyb_tensor2d cl = dl, co = dout;
@@ -1636,6 +1678,7 @@ extern "C" KAPYB_API kapyb_status kapyb_matmul_host_sharded(
     st = run_matmul(h, make_problem(&cl, &dr, nullptr, &co, &ep), nullptr, 0, stream);
     if (st != KAPYB_OK) return st;
     CUDA_TRY(h, cudaEventRecord(h->ev[2 * j + 1], stream));
+    trace.mark("piece multiplied", stream, j);
     CUDA_TRY(h, cudaStreamWaitEvent(h->copy_out, h->ev[2 * j + 1], 0));
     for (int r = 0; r < world; ++r) {
       // staging rows of (rank r, piece j) -> rows r * R + j * P of the caller's output
@@ -1644,13 +1687,15 @@ extern "C" KAPYB_API kapyb_status kapyb_matmul_host_sharded(
       CUDA_TRY(h, cudaMemcpyAsync(hc + dst, dc + src, static_cast<size_t>(P) * out_row_bytes,
                                   cudaMemcpyDeviceToHost, h->copy_out));
     }
+    trace.mark("piece downloaded", h->copy_out, j);
   }
-  trace.mark("products launched", stream);
-  trace.mark("output downloaded", h->copy_out);
   CUDA_TRY(h, cudaEventRecord(ev_done, h->copy_out));
   CUDA_TRY(h, cudaStreamWaitEvent(stream, ev_done, 0));
   const kapyb_status done = kapyb_check(h, stream);
-  if (trace.on) fprintf(stderr, "[kapyb trace r%d] call returns at %7.3f ms\n", rank, trace.ms());
+  if (trace.on) {
+    cudaDeviceSynchronize();
+    trace.report();
+  }
   return done;
 }
 
@@ -1666,6 +1711,8 @@ static kapyb_status verify_program(kapyb_handle h, const kapyb_inst *prog, int n
   if (!out || !valid_operand_dtype(out->dtype) || out->size0 < 0 || out->size1 < 0 ||
       (!out->ptr && out->size0 != 0 && out->size1 != 0))
     return fail(h, KAPYB_INVALID_ARG, "elementwise: bad output descriptor");
+  if (!valid_cache(out->cache))
+    return fail(h, KAPYB_INVALID_ARG, "elementwise: unknown cache operator or eviction priority on the output");
   for (int k = 0; k < n_inputs; ++k) {
     const kapyb_tensor2d &t = inputs[k];
     if (!valid_operand_dtype(t.dtype) || t.size0 < 0 || t.size1 < 0 ||
@@ -1673,6 +1720,8 @@ static kapyb_status verify_program(kapyb_handle h, const kapyb_inst *prog, int n
       return fail(h, KAPYB_INVALID_ARG, "elementwise: bad input descriptor %d", k);
     if (t.padding < KAPYB_PAD_ZERO || t.padding > KAPYB_PAD_NINF)
       return fail(h, KAPYB_INVALID_ARG, "elementwise: bad padding option on input %d", k);
+    if (!valid_cache(t.cache))
+      return fail(h, KAPYB_INVALID_ARG, "elementwise: unknown cache operator or eviction priority on input %d", k);
     if (t.dtype == KAPYB_F8E4M3 && (t.padding == KAPYB_PAD_PINF || t.padding == KAPYB_PAD_NINF))
       return fail(h, KAPYB_INVALID_ARG, "elementwise: f8E4M3 has no infinity to pad input %d with", k);
   }
@@ -2091,6 +2140,7 @@ extern "C" KAPYB_API kapyb_status kapyb_elementwise(kapyb_handle h, const kapyb_
     P.in[k].size1 = inputs[k].size1;
     P.in[k].dtype = inputs[k].dtype;
     P.in[k].padding = inputs[k].padding;
+    P.in[k].cache = inputs[k].cache;
   }
   P.out.ptr = elem_ptr(out);
   P.out.s0 = out->stride0;
@@ -2099,6 +2149,7 @@ extern "C" KAPYB_API kapyb_status kapyb_elementwise(kapyb_handle h, const kapyb_
   P.out.size1 = out->size1;
   P.out.dtype = out->dtype;
   P.out.padding = 0;
+  P.out.cache = out->cache;
   const int grid = static_cast<int>(std::max(1ll, std::min((total + 255) / 256,
                                                             static_cast<long long>(h->sm_count) * 32)));
   elt_interp_kernel<<<grid, 256, 0, stream>>>(P);

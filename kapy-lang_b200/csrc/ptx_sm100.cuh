@@ -162,6 +162,39 @@ __device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const void *tmap,
       : "memory");
 }
 
+// L2 eviction policy for TMA traffic (createpolicy): 1 = evict_first (data read
+// or written once), 2 = evict_last (data other CTAs will come back for).
+__device__ __forceinline__ uint64_t make_l2_policy(int kind) {
+  uint64_t pol;
+  if (kind == 2)
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
+  else
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
+
+// The loads above with an L2 cache hint.
+__device__ __forceinline__ void tma_load_3d_hint(uint32_t dst, const void *tmap, uint32_t bar,
+                                                 int x, int y, int z, uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+      " [%0], [%1, {%3, %4, %5}], [%2], %6;"
+      :
+      : "r"(dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(x), "r"(y), "r"(z),
+        "l"(policy)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_3d_pair_hint(uint32_t dst, const void *tmap, uint32_t bar,
+                                                      int x, int y, int z, uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      ".L2::cache_hint [%0], [%1, {%3, %4, %5}], [%2], %6;"
+      :
+      : "r"(dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(x), "r"(y), "r"(z),
+        "l"(policy)
+      : "memory");
+}
+
 // shared -> global tile store (bulk async-group completion); clips at the
 // tensor's bounds.
 __device__ __forceinline__ void tma_store_3d(const void *tmap, uint32_t src, int x, int y, int z) {
@@ -169,6 +202,15 @@ __device__ __forceinline__ void tma_store_3d(const void *tmap, uint32_t src, int
       "cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
       :
       : "l"(reinterpret_cast<uint64_t>(tmap)), "r"(src), "r"(x), "r"(y), "r"(z)
+      : "memory");
+}
+
+__device__ __forceinline__ void tma_store_3d_hint(const void *tmap, uint32_t src, int x, int y,
+                                                  int z, uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.global.shared::cta.bulk_group.L2::cache_hint [%0, {%2, %3, %4}], [%1], %5;"
+      :
+      : "l"(reinterpret_cast<uint64_t>(tmap)), "r"(src), "r"(x), "r"(y), "r"(z), "l"(policy)
       : "memory");
 }
 

@@ -137,6 +137,13 @@ _COMBINERS = {"arith.addf": abi.RED_ADD, "arith.mulf": abi.RED_MUL,
               "arith.maximumf": abi.RED_MAX, "arith.minimumf": abi.RED_MIN}
 
 
+def _cache_of(op: ir.Operation) -> int:
+    """Cache operator, eviction priority and volatile flag of a ld_global / st_global
+    (ir.cc:1035-1049) packed as kapyb_tensor2d.cache wants them."""
+    return abi.cache_hints(int(op.attrs.get("cache_modifier", 0)), int(op.attrs.get("evict_priority", 0)),
+                           bool(op.attrs.get("is_volatile", False)))
+
+
 class _Lifter:
     def __init__(self, func: ir.FuncOp, grid, args, num_warps: int):
         self.func = func
@@ -145,6 +152,7 @@ class _Lifter:
         self.ranges: Dict[str, int] = {"pid0": gx, "pid1": gy, "pid2": gz, "wid": num_warps}
         self.env: Dict[ir.Value, object] = {}
         self.stores: List[Tuple[Expr, GlobalView]] = []
+        self.store_cache: Dict[int, int] = {}      # id(target view) -> cache hints of its st_global
         self.cp_async: List[Tuple[GlobalView, ir.Value]] = []   # (global source, shared target value)
         self.matmuls: List[ir.Operation] = []
         self.loops: List[ir.Operation] = []
@@ -263,7 +271,8 @@ class _Lifter:
             t = op.results[0].type
             if isinstance(src, GlobalView):
                 E[op.results[0]] = Expr("load", _dtype(t), t.shape, view=src,
-                                        attrs={"padding": int(op.attrs.get("padding_option", 0))})
+                                        attrs={"padding": int(op.attrs.get("padding_option", 0)),
+                                               "cache": _cache_of(op)})
             elif isinstance(src, tuple):
                 E[op.results[0]] = Expr("load-unknown", _dtype(t), t.shape, attrs={"root": src[1]})
             else:
@@ -273,6 +282,7 @@ class _Lifter:
             if not isinstance(tgt, GlobalView):
                 raise Unsupported("st_global target must be a sub-view with launch-time bounds")
             self.stores.append((self.expr(op.operands[0]), tgt))
+            self.store_cache[id(tgt)] = _cache_of(op)
         elif n in ("kapy.splat", "kapy.broadcast"):
             src = self.expr(op.operands[0])
             t = op.results[0].type
@@ -427,7 +437,7 @@ class _Program:
 
     def __init__(self):
         self.insts: List[tuple] = []
-        self.inputs: List[Tuple[GlobalView, int]] = []   # (view, padding)
+        self.inputs: List[Tuple[GlobalView, int, int]] = []   # (view, padding, cache hints)
         self.memo: Dict[int, int] = {}
         self.free = list(range(abi.MAX_REGS - 1, -1, -1))
         self.uses: Dict[int, int] = {}
@@ -453,13 +463,13 @@ class _Program:
             return self.memo[id(e)]
         if e.kind == "load":
             key = None
-            for i, (v, pad) in enumerate(self.inputs):
+            for i, (v, pad, _) in enumerate(self.inputs):
                 if v is e.view:
                     key = i
             if key is None:
                 if len(self.inputs) >= abi.MAX_INPUTS:
                     raise Unsupported(f"more than {abi.MAX_INPUTS} input tensors")
-                self.inputs.append((e.view, e.attrs["padding"]))
+                self.inputs.append((e.view, e.attrs["padding"], e.attrs.get("cache", 0)))
                 key = len(self.inputs) - 1
             r = self.alloc()
             self.insts.append((abi.OP_LOAD, e.dtype, r, -1, -1, -1, 0.0, key))
@@ -496,7 +506,7 @@ class _Program:
         return r
 
 
-def _tensor_desc(root: GlobalRoot, tensors, lo0, hi0, lo1, hi1, padding=abi.PAD_ZERO):
+def _tensor_desc(root: GlobalRoot, tensors, lo0, hi0, lo1, hi1, padding=abi.PAD_ZERO, cache=0):
     t = tensors[root.arg]
     s0 = max(0, min(hi0, root.size0) - lo0)
     s1 = max(0, min(hi1, root.size1) - lo1)
@@ -505,7 +515,8 @@ def _tensor_desc(root: GlobalRoot, tensors, lo0, hi0, lo1, hi1, padding=abi.PAD_
         raise ValueError(f"argument {root.arg} has {t.element_size()}-byte elements but the kernel "
                          f"declares a {esz}-byte element type")
     off = root.offset + lo0 * root.stride0 + lo1 * root.stride1
-    return abi.Tensor2d(t.data_ptr(), off, s0, s1, root.stride0, root.stride1, root.dtype, padding)
+    return abi.Tensor2d(t.data_ptr(), off, s0, s1, root.stride0, root.stride1, root.dtype, padding,
+                        int(cache), 0)
 
 
 def launch(func, grid: Sequence[int], args: Sequence, handle, num_warps: Optional[int] = None,
@@ -567,7 +578,7 @@ def _launch_elementwise(L, expr, tgt, region, handle, sp, out_override=None):
     out_dtype = expr.dtype
     prog.insts.append((abi.OP_STORE, out_dtype, -1, src, -1, -1, 0.0, 0))
     tin = (abi.Tensor2d * max(1, len(prog.inputs)))()
-    for i, (view, pad) in enumerate(prog.inputs):
+    for i, (view, pad, cache) in enumerate(prog.inputs):
         _check_aligned(view, tgt)
         b0 = view.shape[0] == 1 and tgt.shape[0] != 1
         b1 = view.shape[1] == 1 and tgt.shape[1] != 1
@@ -575,13 +586,13 @@ def _launch_elementwise(L, expr, tgt, region, handle, sp, out_override=None):
             (lo0 - tgt.start0.const + view.start0.const, hi0 - tgt.start0.const + view.start0.const)
         v1 = (view.start1.const, view.start1.const + 1) if b1 else \
             (lo1 - tgt.start1.const + view.start1.const, hi1 - tgt.start1.const + view.start1.const)
-        tin[i] = _tensor_desc(view.root, L.args, v0[0], v0[1], v1[0], v1[1], pad)
+        tin[i] = _tensor_desc(view.root, L.args, v0[0], v0[1], v1[0], v1[1], pad, cache)
     if out_override is not None:
         tout = out_override
     else:
         if tgt.root.dtype != out_dtype:
             raise ValueError("st_global: source and target element types differ")
-        tout = _tensor_desc(tgt.root, L.args, lo0, hi0, lo1, hi1)
+        tout = _tensor_desc(tgt.root, L.args, lo0, hi0, lo1, hi1, cache=L.store_cache.get(id(tgt), 0))
     insts = (abi.Inst * len(prog.insts))(*[abi.Inst(*t) for t in prog.insts])
     st = handle._lib.kapyb_elementwise(handle._h, insts, len(prog.insts), tin, len(prog.inputs),
                                        C.byref(tout), sp)

@@ -51,8 +51,9 @@ def torch_dtype(code: int):
             abi.F8E4M3: torch.float8_e4m3fn, abi.F8E5M2: torch.float8_e5m2}[code]
 
 
-def tensor2d(t, padding: int = abi.PAD_ZERO) -> abi.Tensor2d:
-    """kapy.mk_global over a 2-D torch tensor (any strides that fit i32)."""
+def tensor2d(t, padding: int = abi.PAD_ZERO, cache: int = 0) -> abi.Tensor2d:
+    """kapy.mk_global over a 2-D torch tensor (any strides that fit i32).  `cache`:
+    abi.cache_hints(...) of the ld_global / st_global that touches the tensor."""
     if t.dim() != 2:
         raise ValueError("kapy tensors are rank 2")
     s0, s1 = t.stride()
@@ -60,7 +61,7 @@ def tensor2d(t, padding: int = abi.PAD_ZERO) -> abi.Tensor2d:
         if v >= 2 ** 31:
             raise ValueError("sizes and strides must fit i32")
     return abi.Tensor2d(t.data_ptr(), 0, t.shape[0], t.shape[1], s0, s1, dtype_code(t.dtype),
-                        padding)
+                        padding, int(cache), 0)
 
 
 def matmul_plan(m: int, n: int, k: int, *, dtype=abi.BF16, rhs_dtype=None, out_dtype=None,
@@ -263,8 +264,11 @@ class Handle:
     # --------------------------------------------------------------- matmul
     def matmul(self, lhs, rhs, out=None, *, acc=None, alpha: float = 1.0, bias=None,
                bias_axis: int = 1, activation: int = abi.ACT_NONE, rounding: int = abi.RN,
-               out_dtype=None, impl_way: int = abi.MMA_ANY, stream=None):
-        """kapy.matmul at whole-problem scope; 3-D operands run as a batch."""
+               out_dtype=None, impl_way: int = abi.MMA_ANY, stream=None,
+               cache=(0, 0, 0)):
+        """kapy.matmul at whole-problem scope; 3-D operands run as a batch.  `cache`:
+        abi.cache_hints(...) for lhs, rhs and out (their eviction priority becomes the
+        L2 policy of the tile loads / stores)."""
         torch = _torch()
         if lhs.dim() == 3:
             return self._matmul_batched(lhs, rhs, out, alpha=alpha, bias=bias, bias_axis=bias_axis,
@@ -273,7 +277,8 @@ class Handle:
         if out is None:
             out = torch.empty((lhs.shape[0], rhs.shape[1]), device=lhs.device,
                               dtype=out_dtype or lhs.dtype)
-        tl, tr, to = tensor2d(lhs), tensor2d(rhs), tensor2d(out)
+        tl, tr, to = tensor2d(lhs, cache=cache[0]), tensor2d(rhs, cache=cache[1]), \
+            tensor2d(out, cache=cache[2])
         ta = tensor2d(acc) if acc is not None else None
         ep = self._epilogue(alpha, bias, bias_axis, activation, rounding)
         st = self._lib.kapyb_matmul(self._h, C.byref(tl), C.byref(tr),
@@ -399,15 +404,17 @@ class Handle:
 
     # ---------------------------------------------------- elementwise/reduce
     def elementwise(self, insts, inputs, out, paddings: Optional[Sequence[int]] = None,
-                    stream=None):
-        """Runs a recorded op list [(op,dtype,dst,a,b,c,imm,flags), ...]."""
+                    stream=None, caches: Optional[Sequence[int]] = None, out_cache: int = 0):
+        """Runs a recorded op list [(op,dtype,dst,a,b,c,imm,flags), ...].  `caches` /
+        `out_cache`: abi.cache_hints(...) per input / for the output."""
         prog = (abi.Inst * max(1, len(insts)))()
         for i, t in enumerate(insts):
             prog[i] = abi.Inst(*t)
         tin = (abi.Tensor2d * max(1, len(inputs)))()
         for i, t in enumerate(inputs):
-            tin[i] = tensor2d(t, paddings[i] if paddings else abi.PAD_ZERO)
-        to = tensor2d(out)
+            tin[i] = tensor2d(t, paddings[i] if paddings else abi.PAD_ZERO,
+                              caches[i] if caches else 0)
+        to = tensor2d(out, cache=out_cache)
         st = self._lib.kapyb_elementwise(self._h, prog, len(insts), tin, len(inputs),
                                          C.byref(to), self._stream(stream))
         if st != abi.OK:

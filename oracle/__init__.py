@@ -33,7 +33,8 @@ class Tensor2d(C.Structure):
     _fields_ = [("ptr", C.c_void_p), ("offset_elems", C.c_int64),
                 ("size0", C.c_int32), ("size1", C.c_int32),
                 ("stride0", C.c_int32), ("stride1", C.c_int32),
-                ("dtype", C.c_int32), ("padding", C.c_int32)]
+                ("dtype", C.c_int32), ("padding", C.c_int32),
+                ("cache", C.c_int32), ("reserved_", C.c_int32)]
 
 
 class Epilogue(C.Structure):

@@ -27,7 +27,7 @@ def test_header_symbols_exported(pkg):
 
 def test_struct_layout_matches_header(pkg):
     abi = pkg.abi
-    assert C.sizeof(abi.Tensor2d) == 40
+    assert C.sizeof(abi.Tensor2d) == 48
     assert C.sizeof(abi.Epilogue) == 32
     assert C.sizeof(abi.Inst) == 32
 

@@ -233,6 +233,50 @@ def test_cmpf_select_rules(handle, pkg):
                                  (A.OP_STORE, A.F32, -1, 2, -1, -1, 0.0, 0)], [x], y)
 
 
+# ---------------------------------------------------------------- cache hints
+
+def test_cache_hints_never_change_a_result(handle, ko, pkg):
+    """Every cache operator, eviction priority and the volatile flag of ld_global /
+    st_global (Enums.td:63-88) on the general kernel: the ld / st forms differ,
+    the bits do not.  All three element widths are loaded and stored."""
+    A = pkg.abi
+    x32 = normal((7, 333), 91, dtype=torch.float32)
+    y16 = normal((7, 333), 92)
+    # z = select(x > y, x, y) in f32, stored as bf16: loads of 4 and 2 bytes, store of 2
+    prog = [(A.OP_LOAD, A.F32, 0, -1, -1, -1, 0.0, 0), (A.OP_LOAD, A.BF16, 1, -1, -1, -1, 0.0, 1),
+            (A.OP_CVT, A.F32, 2, 1, -1, -1, 0.0, A.RN), (A.OP_CMP, A.I1, 3, 0, 2, -1, 0.0, 1),
+            (A.OP_SELECT, A.F32, 4, 3, 0, 2, 0.0, 0), (A.OP_CVT, A.BF16, 5, 4, -1, -1, 0.0, A.RN),
+            (A.OP_STORE, A.BF16, -1, 5, -1, -1, 0.0, 0)]
+    xd, yd = x32.cuda(), y16.cuda()
+    base = torch.empty((7, 333), dtype=torch.bfloat16, device="cuda")
+    handle.elementwise(prog, [xd, yd], base)
+    assert handle.last_kernel == "elt_interp"
+    want = ko.eltwise(prog, [bits(x32), bits(y16)], [2, 1], (7, 333), 1)
+    assert np.array_equal(bits(base.cpu()), want)
+    hints = [A.cache_hints(m, 0, False) for m in range(8)] + \
+            [A.cache_hints(0, p, False) for p in range(5)] + \
+            [A.cache_hints(0, 0, True), A.cache_hints(A.CACHE_CG, A.EVICT_LAST, False)]
+    for hint in hints:
+        out = torch.zeros_like(base)
+        handle.elementwise(prog, [xd, yd], out, caches=[hint, hint], out_cache=hint)
+        handle.check()
+        assert torch.equal(out, base), hex(hint)
+    # one-byte elements: an f8 cast through the general kernel (column-major output)
+    f8 = torch.arange(256, dtype=torch.uint8).repeat(4, 1).view(torch.float8_e5m2).cuda()
+    up = [(0, 4, 0, -1, -1, -1, 0.0, 0), (2, A.F16, 1, 0, -1, -1, 0.0, 1), (27, A.F16, -1, 1, -1, -1, 0.0, 0)]
+    o0 = torch.empty((256, 4), dtype=torch.float16, device="cuda").t()
+    handle.elementwise(up, [f8], o0)
+    o1 = torch.empty((256, 4), dtype=torch.float16, device="cuda").t()
+    handle.elementwise(up, [f8], o1, caches=[A.cache_hints(A.CACHE_CS)], out_cache=A.cache_hints(A.CACHE_WT))
+    handle.check()
+    assert handle.last_kernel == "elt_interp"
+    assert torch.equal(o0.view(torch.int16), o1.view(torch.int16))
+    with pytest.raises(ValueError, match="cache operator or eviction priority"):
+        handle.elementwise(prog, [xd, yd], base, caches=[A.cache_hints(9), 0])
+    with pytest.raises(ValueError, match="cache operator or eviction priority"):
+        handle.elementwise(prog, [xd, yd], base, out_cache=A.cache_hints(0, 5))
+
+
 # ------------------------------------------------------ output against inputs
 
 def test_in_place_and_overlap(handle, ko, pkg):

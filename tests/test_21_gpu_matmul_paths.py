@@ -177,3 +177,26 @@ def test_tune_then_dispatch_from_the_table(handle, ko, pkg, tmp_path):
         assert ref.shape == (M, 1024)
     finally:
         pkg.tuning_clear()
+
+
+@pytest.mark.parametrize("path", ["1cta:128", "2cta:256", "2cta:512", "skinny"])
+def test_eviction_priorities_become_l2_policies(handle, pkg, path):
+    """EvictPriority on a matmul operand or on the output (Enums.td:78-88) turns
+    into an L2 policy of the tile loads / stores: same bits with any of them."""
+    A_ = pkg.abi
+    M, N, K = (48, 1024, 1024) if path == "skinny" else (512, 1024, 1024)
+    X, W = normal((M, K), 71, K ** -0.5).cuda(), normal((K, N), 72).cuda()
+    handle.set_matmul_path(path)
+    try:
+        want = handle.matmul(X, W)
+        for a, b, c in ((A_.EVICT_LAST, A_.EVICT_FIRST, A_.EVICT_FIRST),
+                        (A_.EVICT_FIRST, A_.EVICT_LAST, A_.NO_ALLOCATE),
+                        (A_.EVICT_UNCHANGED, A_.EVICT_NORMAL, A_.EVICT_LAST)):
+            got = handle.matmul(X, W, cache=(A_.cache_hints(0, a), A_.cache_hints(0, b),
+                                             A_.cache_hints(0, c)))
+            handle.check()
+            assert torch.equal(got, want), (a, b, c)
+    finally:
+        handle.set_matmul_path("auto")
+    with pytest.raises(ValueError, match="cache operator or eviction priority"):
+        handle.matmul(X, W, cache=(A_.cache_hints(0, 7), 0, 0))

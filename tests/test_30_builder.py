@@ -104,6 +104,37 @@ def test_lifting_elementwise_to_one_call(pkg):
     assert h2.log[0][3].size1 == n
 
 
+def test_cache_hints_reach_the_descriptors(pkg):
+    """CacheModifier / EvictPriority / volatile given to create_ld_global and
+    create_st_global (ir.cc:1035-1049) arrive in kapyb_tensor2d.cache."""
+    ir = pkg.ir
+    b = ir.Builder(ir.MLIRContext())
+    mod = b.create_module()
+    mod.set_attr("kapy.num_warps", 1)
+    ptr, i32 = b.get_pointer_type(1), b.get_int32_type()
+    fn = b.get_or_create_function(mod, "k", b.get_function_type([ptr, ptr, i32], []), "public", False)
+    mod.push_back(fn)
+    b.set_insertion_point_to_start(fn.add_entry_block())
+    x, y, n = fn.get_argument(0), fn.get_argument(1), fn.get_argument(2)
+    f32 = b.get_float32_type()
+    c0, c1, c256 = b.create_constant_int32(0), b.create_constant_int32(1), b.create_constant_int32(256)
+    gx, gy = b.create_mk_global(x, c0, c1, n, n, c1, f32), b.create_mk_global(y, c0, c1, n, n, c1, f32)
+    lo = b.create_muli(b.create_program_id(0), c256)
+    hi = b.create_addi(lo, c256)
+    vx, vy = b.create_sv_global(gx, c0, c1, lo, hi, [1, 256]), b.create_sv_global(gy, c0, c1, lo, hi, [1, 256])
+    t = b.create_ld_global(vx, ir.PaddingOption.ZERO, ir.CacheModifier.NONE, ir.EvictPriority.EVICT_FIRST, False)
+    b.create_st_global(b.create_absf(t), vy, ir.CacheModifier.CS, ir.EvictPriority.EVICT_NORMAL, False)
+    b.create_return([])
+    fn.finalize()
+    h = FakeHandle()
+    xs, ys = torch.zeros(1024), torch.zeros(1024)
+    pkg.executor.launch(fn, (4, 1, 1), [xs, ys, 1024], h, module=mod)
+    _, insts, tin, tout = h.log[0]
+    A = pkg.abi
+    assert tin[0].cache == A.cache_hints(A.CACHE_NONE, A.EVICT_FIRST, False)
+    assert tout.cache == A.cache_hints(A.CACHE_CS, A.EVICT_NORMAL, False)
+
+
 def test_lifting_rejects_what_it_cannot_lift(pkg):
     ir = pkg.ir
     b = ir.Builder()
