@@ -19,6 +19,8 @@
 
 #include <cuda.h>
 
+#include <type_traits>
+
 #include "common.cuh"
 #include "ptx_sm100.cuh"
 
@@ -203,14 +205,21 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     uint32_t phase = 0;
     const uint32_t stage_bytes = W_BYTES + p.x_bytes;
     bool ok = true;
-    const uint64_t pol_w = p.w_l2 ? ptx::make_l2_policy(p.w_l2) : 0ull;
-    const uint64_t pol_x = p.x_l2 ? ptx::make_l2_policy(p.x_l2) : 0ull;
-    auto load1 = [](uint64_t pol, uint32_t dst, const CUtensorMap *tm, uint32_t bar, int x, int y) {
-      if (pol)
-        ptx::tma_load_3d_hint(dst, tm, bar, x, y, 0, pol);
-      else
-        ptx::tma_load_3d(dst, tm, bar, x, y, 0);
-    };
+    // Two copies of the loop, plain loads and loads with an L2 policy per tensor: see
+    // the producer of gemm_tcgen05_kernel.
+#define KAPYB_LOAD1(POL, DST, TM, BAR, X, Y)                       \
+  do {                                                             \
+    if constexpr (HINTED)                                          \
+      ptx::tma_load_3d_hint(DST, &TM, BAR, X, Y, 0, POL);          \
+    else                                                           \
+      ptx::tma_load_3d(DST, &TM, BAR, X, Y, 0);                    \
+  } while (0)
+    auto produce = [&](auto hinted) {
+    constexpr bool HINTED = decltype(hinted)::value;
+    const uint64_t pol_w = HINTED ? ptx::make_l2_policy(p.w_l2) : 0ull;
+    const uint64_t pol_x = HINTED ? ptx::make_l2_policy(p.x_l2) : 0ull;
+    (void)pol_w;
+    (void)pol_x;
     for (int j = 0; j < work.count() && ok; ++j) {
       int tile, kb_begin, kb_end;
       work.get(j, tile, kb_begin, kb_end);
@@ -225,21 +234,27 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         const uint32_t w_dst = ptx::smem_u32(sW + stage * W_BYTES);
         const uint32_t x_dst = ptx::smem_u32(sX + stage * p.x_bytes);
         if (p.w_mn_major) {
-          load1(pol_w, w_dst, &tmW, fb, n0, k0);
-          load1(pol_w, w_dst + 8192, &tmW, fb, n0 + 64, k0);
+          KAPYB_LOAD1(pol_w, w_dst, tmW, fb, n0, k0);
+          KAPYB_LOAD1(pol_w, w_dst + 8192, tmW, fb, n0 + 64, k0);
         } else {
-          load1(pol_w, w_dst, &tmW, fb, k0, n0);
+          KAPYB_LOAD1(pol_w, w_dst, tmW, fb, k0, n0);
         }
         if (p.x_mn_major)
-          load1(pol_x, x_dst, &tmX, fb, 0, k0);
+          KAPYB_LOAD1(pol_x, x_dst, tmX, fb, 0, k0);
         else
-          load1(pol_x, x_dst, &tmX, fb, k0, 0);
+          KAPYB_LOAD1(pol_x, x_dst, tmX, fb, k0, 0);
         if (++stage == p.stages) {
           stage = 0;
           phase ^= 1u;
         }
       }
     }
+    };  // produce
+    if (p.w_l2 | p.x_l2)
+      produce(std::true_type{});
+    else
+      produce(std::false_type{});
+#undef KAPYB_LOAD1
   } else if (warp == 1) {
     // ---------------------------------------------------------- MMA issuer
     // The whole warp walks the loops in step and one elected lane issues (uniform

@@ -32,6 +32,8 @@
 
 #include <cuda.h>
 
+#include <type_traits>
+
 #include "common.cuh"
 #include "ptx_sm100.cuh"
 
@@ -678,23 +680,35 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
-    const uint64_t pol_a = p.a_l2 ? ptx::make_l2_policy(p.a_l2) : 0ull;
-    const uint64_t pol_b = p.b_l2 ? ptx::make_l2_policy(p.b_l2) : 0ull;
-    // one tile load of A or B (pol == 0: the plain form)
-    auto load1 = [](uint64_t pol, uint32_t dst, const CUtensorMap *tm, uint32_t bar, int x, int y,
-                    int z) {
-      if (pol)
-        ptx::tma_load_3d_hint(dst, tm, bar, x, y, z, pol);
-      else
-        ptx::tma_load_3d(dst, tm, bar, x, y, z);
-    };
-    auto load2 = [](uint64_t pol, uint32_t dst, const CUtensorMap *tm, uint32_t bar, int x, int y,
-                    int z) {
-      if (pol)
-        ptx::tma_load_3d_pair_hint(dst, tm, bar, x, y, z, pol);
-      else
-        ptx::tma_load_3d_pair(dst, tm, bar, x, y, z);
-    };
+    // The tile loop exists twice: with plain loads, and with loads that carry an L2
+    // policy per tensor (from the descriptors' eviction priority).  Choosing the
+    // form per load inside one loop cost the benchmark kernel 6 % although the
+    // choice never changed: this thread's issue rate is on the critical path.
+    // (The loads are macros, not helpers taking the map's address: the maps are
+    // __grid_constant__ parameters, named where the TMA instruction is issued.)
+#define KAPYB_LOAD1(POL, DST, TM, BAR, X, Y, Z)                    \
+  do {                                                             \
+    if constexpr (HINTED)                                          \
+      ptx::tma_load_3d_hint(DST, &TM, BAR, X, Y, Z, POL);          \
+    else                                                           \
+      ptx::tma_load_3d(DST, &TM, BAR, X, Y, Z);                    \
+  } while (0)
+#define KAPYB_LOAD2(POL, DST, TM, BAR, X, Y, Z)                    \
+  do {                                                             \
+    if constexpr (HINTED)                                          \
+      ptx::tma_load_3d_pair_hint(DST, &TM, BAR, X, Y, Z, POL);     \
+    else                                                           \
+      ptx::tma_load_3d_pair(DST, &TM, BAR, X, Y, Z);               \
+  } while (0)
+    auto produce = [&](auto hinted, auto chunk_elems) {
+    constexpr bool HINTED = decltype(hinted)::value;
+    // elements per 128-byte row of shared memory (64 / 32 / 128 for 2- / 4- / 1-byte
+    // operands) as a constant, so that the chunk loops below unroll
+    constexpr int ce = decltype(chunk_elems)::value;
+    const uint64_t pol_a = HINTED ? ptx::make_l2_policy(p.a_l2) : 0ull;
+    const uint64_t pol_b = HINTED ? ptx::make_l2_policy(p.b_l2) : 0ull;
+    (void)pol_a;
+    (void)pol_b;
     for (int tile = unit; tile < p.num_tiles && ok && !debug_on<16 | 32>(p.debug); tile += unit_step) {
       int b, mb, nb;
       decode_tile(p, tile, b, mb, nb);
@@ -709,10 +723,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
           ok = false;
           break;
         }
-        const int k0 = kb * p.bk_elems;
-        const int ce = p.bk_elems;                       // elements per 128-byte MN chunk
-        const int a_chunks = Cfg::BM / ce;
-        const int b_chunks = Cfg::BN_CTA / ce;
+        const int k0 = kb * ce;
+        constexpr int a_chunks = Cfg::BM / ce;
+        constexpr int b_chunks = Cfg::BN_CTA / ce;
         const uint32_t a_dst = ptx::smem_u32(sA + stage * Cfg::A_BYTES);
         const uint32_t b_dst = ptx::smem_u32(sB + stage * Cfg::B_BYTES);
         if (debug_on<1>(p.debug)) {
@@ -721,19 +734,21 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
           const uint32_t fb = ptx::smem_u32(&full_bar[stage]);
           ptx::mbar_arrive_expect_tx(fb, Cfg::STAGE_BYTES);
           if (!p.a_mn_major) {
-            load1(pol_a, a_dst, &tmA, fb, k0, m0, b);
+            KAPYB_LOAD1(pol_a, a_dst, tmA, fb, k0, m0, b);
           } else {
+#pragma unroll
             for (int j = 0; j < a_chunks; ++j)
-              load1(pol_a, a_dst + j * p.mn_lbo, &tmA, fb, m0 + ce * j, k0, b);
+              KAPYB_LOAD1(pol_a, a_dst + j * p.mn_lbo, tmA, fb, m0 + ce * j, k0, b);
           }
           if (!p.b_mn_major) {
             // one box of kGroupCols rows per column half
 #pragma unroll
             for (int hh = 0; hh < Cfg::SPLIT; ++hh)
-              load1(pol_b, b_dst + hh * (kGroupCols * 128), &tmB, fb, k0, nB0 + hh * Cfg::MMA_N, b);
+              KAPYB_LOAD1(pol_b, b_dst + hh * (kGroupCols * 128), tmB, fb, k0, nB0 + hh * Cfg::MMA_N, b);
           } else {
+#pragma unroll
             for (int j = 0; j < b_chunks; ++j)
-              load1(pol_b, b_dst + j * p.mn_lbo, &tmB, fb, nB0 + ce * j, k0, b);
+              KAPYB_LOAD1(pol_b, b_dst + j * p.mn_lbo, tmB, fb, nB0 + ce * j, k0, b);
           }
         } else {
           // Both CTAs' loads report their bytes to the leader's barrier; the
@@ -743,20 +758,23 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
           if (rank == 0)
             ptx::mbar_arrive_expect_tx(ptx::smem_u32(&full_bar[stage]), 2 * Cfg::STAGE_BYTES);
           if (!p.a_mn_major) {
-            load2(pol_a, a_dst, &tmA, fb, k0, m0, b);
+            KAPYB_LOAD2(pol_a, a_dst, tmA, fb, k0, m0, b);
           } else {
+#pragma unroll
             for (int j = 0; j < a_chunks; ++j)
-              load2(pol_a, a_dst + j * p.mn_lbo, &tmA, fb, m0 + ce * j, k0, b);
+              KAPYB_LOAD2(pol_a, a_dst + j * p.mn_lbo, tmA, fb, m0 + ce * j, k0, b);
           }
           if (!p.b_mn_major) {
             // one box of kGroupCols rows per half
 #pragma unroll
             for (int hh = 0; hh < Cfg::SPLIT; ++hh)
-              load2(pol_b, b_dst + hh * (kGroupCols * 128), &tmB, fb, k0, nB0 + hh * Cfg::MMA_N, b);
+              KAPYB_LOAD2(pol_b, b_dst + hh * (kGroupCols * 128), tmB, fb, k0, nB0 + hh * Cfg::MMA_N, b);
           } else {
+#pragma unroll
             for (int j = 0; j < b_chunks; ++j) {
-              const int hh = (j * ce) / kGroupCols, within = (j * ce) % kGroupCols;
-              load2(pol_b, b_dst + j * p.mn_lbo, &tmB, fb, nB0 + hh * Cfg::MMA_N + within, k0, b);
+              constexpr int per_group = kGroupCols >= ce ? kGroupCols / ce : 1;  // chunks per column half
+              const int hh = j / per_group, within = (j % per_group) * ce;
+              KAPYB_LOAD2(pol_b, b_dst + j * p.mn_lbo, tmB, fb, nB0 + hh * Cfg::MMA_N + within, k0, b);
             }
           }
         }
@@ -766,6 +784,26 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
         }
       }
     }
+    };  // produce
+    const bool hinted = (p.a_l2 | p.b_l2) != 0;
+    if (p.bk_elems == 64) {
+      if (hinted)
+        produce(std::true_type{}, std::integral_constant<int, 64>{});
+      else
+        produce(std::false_type{}, std::integral_constant<int, 64>{});
+    } else if (p.bk_elems == 32) {
+      if (hinted)
+        produce(std::true_type{}, std::integral_constant<int, 32>{});
+      else
+        produce(std::false_type{}, std::integral_constant<int, 32>{});
+    } else {
+      if (hinted)
+        produce(std::true_type{}, std::integral_constant<int, 128>{});
+      else
+        produce(std::false_type{}, std::integral_constant<int, 128>{});
+    }
+#undef KAPYB_LOAD1
+#undef KAPYB_LOAD2
   } else if (warp == 1 && rank == 0) {
     // ---------------------------------------------------------- MMA issuer
     // The whole warp walks the loops in step and one elected lane issues: with

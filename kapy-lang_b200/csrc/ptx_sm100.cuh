@@ -164,12 +164,15 @@ __device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const void *tmap,
 
 // L2 eviction policy for TMA traffic (createpolicy): 1 = evict_first (data read
 // or written once), 2 = evict_last (data other CTAs will come back for).
+// (0 = evict_normal, for the tensor without a hint when another one has one.)
 __device__ __forceinline__ uint64_t make_l2_policy(int kind) {
   uint64_t pol;
   if (kind == 2)
     asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
-  else
+  else if (kind == 1)
     asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+  else
+    asm volatile("createpolicy.fractional.L2::evict_normal.b64 %0, 1.0;" : "=l"(pol));
   return pol;
 }
 
