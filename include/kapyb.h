@@ -283,10 +283,7 @@ KAPYB_API kapyb_status kapyb_destroy(kapyb_handle h);
 KAPYB_API const char *kapyb_last_error_string(kapyb_handle h);
 
 /* Synchronises `stream` and reports what the device recorded: KAPYB_TIMEOUT if
- * a kernel gave up on a bounded wait, KAPYB_CUDA_ERROR on a sticky error.  A
- * decode-shape matmul that gave up leaves its tile counters in the handle's
- * workspace half counted; this call clears them, so call it after any launch
- * that may have timed out and before the next decode-shape matmul on `h`. */
+ * a kernel gave up on a bounded wait, KAPYB_CUDA_ERROR on a sticky error. */
 KAPYB_API kapyb_status kapyb_check(kapyb_handle h, void *stream);
 
 /* Grows the handle's device workspace (split-K partials, host-call staging) to
@@ -423,19 +420,18 @@ KAPYB_API kapyb_status kapyb_matmul_host_sharded(
  * steals from the pool), a latency-critical loop that cannot afford the
  * device-wide synchronisation cudaMalloc/cudaFree imply, or an embedding that
  * forbids allocation after start-up.  kapyb_matmul on this shape splits weight
- * tiles between SMs and sums the pieces in scratch memory taken from the
+ * tiles between SMs and passes the pieces through scratch memory taken from the
  * handle's workspace (a cudaMalloc); this variant takes no handle and keeps that
  * scratch in a fixed array inside the library image instead.
  *
  *   out[M,N] = epilogue(lhs[M,K] . rhs[K,N]),  1 <= M <= 64, f16/bf16 operands.
  *
  * Limits and rules:
- *  - the fixed scratch is 10 MiB of partial sums + 16 KiB of counters per GPU
- *    (held by every GPU that loads the library, until exit); a call needs
- *    ceil(N/128) * 16 bytes of counters (N <= 131072) and 2 * SMs *
- *    roundup16(M) * 512 bytes of partial sums (M = 64 fits on up to 160 SMs).
- *    Larger problems are refused with KAPYB_UNSUPPORTED and a message saying
- *    so; nothing is launched;
+ *  - the fixed scratch is 10 MiB of partial sums per GPU (held by every GPU that
+ *    loads the library, until exit); a call needs SMs * roundup16(M) * 1024
+ *    bytes of it (M = 64 fits on up to 160 SMs).  Larger problems, and M > 64,
+ *    are refused with KAPYB_UNSUPPORTED and a message saying so; nothing is
+ *    launched;
  *  - operands must be TMA-describable (one unit stride, 16-byte aligned base,
  *    leading dimension a multiple of 16 bytes); there is no fallback kernel;
  *  - the call runs on the CURRENT device.  Its first call on each device looks
@@ -443,8 +439,10 @@ KAPYB_API kapyb_status kapyb_matmul_host_sharded(
  *    properties; make that first call outside any stream capture.  Threads that
  *    make their first call on one device at the same time are serialised;
  *  - it calls no cudaMalloc/cudaFree and no allocating library routine.  It
- *    clears the counters it will use and the time-out word (cudaMemsetAsync on
- *    `stream`), then launches the kernel on `stream`;
+ *    clears the time-out word (cudaMemsetAsync on `stream`), then launches the
+ *    kernel on `stream`.  The array keeps the previous call's partial sums and
+ *    needs no clearing: each one carries the number of the call that wrote it,
+ *    and a call only accepts its own;
  *  - all calls on one GPU share the one array: two calls whose kernels can
  *    overlap on the GPU (different streams, no dependency) race and give wrong
  *    results.  Keep them on one stream or order them yourself;

@@ -6,11 +6,18 @@
 // the (tile, k block) units of the leftover tiles are dealt out as equal
 // contiguous spans ("stream-K"), so all SMs stream the same number of bytes
 // whatever the tile count.  A tile that is split between CTAs goes through
-// scratch memory: every contributor writes its partial sums with plain stores
-// into its own slot (no initial value needed) and bumps a per-tile counter; the
-// contributor that completes the count adds all slots IN CTA ORDER, applies the
-// epilogue, writes the output and resets the counter.  The counters are the
-// only state that must be zero when a launch starts.
+// scratch memory without a counter, a fence or an atomic: every contributor but
+// the first writes its partial sums as (value, launch number) pairs, one 8-byte
+// store each, into its own slot; the FIRST contributor of the tile (whose span
+// ends with the tile, so it is among the last to finish) reads the others'
+// pairs until each carries this launch's number, adds them to its own
+// accumulator IN CTA ORDER, applies the epilogue and writes the output.  A pair
+// is written in one piece, so a reader sees either an older launch's pair and
+// tries again, or the value.  The critical path after the last MMA is one L2
+// round trip and the output stores (the counter scheme it replaces needed
+// four round trips, 5-6 us of a 17 us launch when every tile is split).
+// Nothing in the scratch has to be zero or reset between launches: launch
+// numbers only grow.
 //
 // Same arithmetic contract as the big-tile kernel (fp32 accumulation of exact
 // products, fused epilogue).  Because a split tile's slots are added in CTA
@@ -41,8 +48,12 @@ __device__ __forceinline__ bool skinny_debug_on(int debug) {
 
 constexpr int kSkinnyMaxM = 64;
 constexpr int kSkinnyThreads = 192;
-constexpr int kSkinnyMaxStages = 12;
-constexpr int kSkinnyCounterBytes = 64 * 1024;  // 4 counters per weight tile
+constexpr int kSkinnyMaxStages = 12;   // barrier slots; see kSkinnyStages for the depth used
+// Pipeline depth actually used.  Measured on the decode shape (M = 16, N = 28672,
+// K = 8192): 12 stages stream 5.89 TB/s, 8 stages 6.28 TB/s, 6 stages 6.16 TB/s;
+// the same optimum at M = 1 .. 64 and for narrower shards.  More bytes in flight
+// than the memory system needs only scatter its accesses.
+constexpr int kSkinnyStages = 8;
 constexpr size_t kSkinnyScratchBytes = 16u << 20;
 
 struct SkinnyParams {
@@ -52,7 +63,8 @@ struct SkinnyParams {
   int n_tiles;    // ceil(N / 128)
   int span;       // k-block units of the split region per CTA
   int sk_tiles;   // the first sk_tiles weight tiles are split between CTAs ...
-  int dp_per_cta; // ... the rest are whole tiles, this many per CTA (tile = sk_tiles + cta + i * grid)
+  int dp_per_cta; // ... the rest are whole tiles, up to this many per CTA (tile = sk_tiles + cta +
+                  // i * grid while that is < n_tiles: the last round may be ragged)
   int stages;
   int w_mn_major;  // weights N-contiguous ([K,N] row-major)
   int x_mn_major;  // activations M-contiguous
@@ -61,14 +73,14 @@ struct SkinnyParams {
   int out_dtype;
   long long c_s0, c_s1;
   void *c;
-  float *scratch;      // [grid][2][m_pad][128] fp32 partial sums, two slots per CTA
-  uint32_t *counters;  // [n_tiles][4], zero between launches
+  uint2 *scratch;      // [grid][m_pad][128] (fp32 partial sum, launch number): one slot per CTA
+  uint32_t epoch;      // this launch's number: never 0, different from any number still in scratch
   uint32_t idesc;
   uint32_t *status;
   uint32_t wait_limit_us;  // 0: the default limit of a bounded wait
   int debug;               // bit7: record the timeline probes in status[2..8] (results stay
                            // right).  Only in a build with -DKAPYB_DEBUG_SWITCHES, for
-                           // profiling (results are wrong): bit2 skip the epilogue body,
+                           // profiling (results are wrong): bit1 skip the MMAs, bit2 skip the epilogue body,
                            // bit3 skip the publish/count/owner pass, bit4 skip whole-tile
                            // stores, bit5 skip the partial-sum stores
   EpilogueArgs ep;
@@ -85,7 +97,8 @@ struct SkinnyParams {
 struct SkinnyWork {
   int first_tile, n_split_segs, head_kb, tail_kb, num_kb;
   int dp_first, dp_stride, dp_count;
-  __device__ SkinnyWork(long long g_begin, long long g_end, int num_kb_, int sk_tiles, int dp_per_cta)
+  __device__ SkinnyWork(long long g_begin, long long g_end, int num_kb_, int sk_tiles, int dp_per_cta,
+                        int n_tiles)
       : num_kb(num_kb_) {
     first_tile = static_cast<int>(g_begin / num_kb);
     const int last_tile = g_end > g_begin ? static_cast<int>((g_end - 1) / num_kb) : first_tile;
@@ -94,7 +107,9 @@ struct SkinnyWork {
     tail_kb = static_cast<int>(g_end - static_cast<long long>(last_tile) * num_kb);
     dp_first = sk_tiles + static_cast<int>(blockIdx.x);
     dp_stride = static_cast<int>(gridDim.x);
-    dp_count = dp_per_cta;
+    dp_count = 0;
+    for (int i = 0; i < dp_per_cta; ++i)
+      if (dp_first + i * dp_stride < n_tiles) dp_count = i + 1;
   }
   __device__ int count() const { return n_split_segs + dp_count; }
   // j-th segment in processing order
@@ -165,6 +180,48 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     atomicMax(p.status + 4, ~t);  // earliest start, kept as the largest complement
     atomicMax(p.status + 5, t);   // latest start
   }
+  const long long total = static_cast<long long>(p.sk_tiles) * p.num_kb;  // units of the split region
+  const long long g_begin = min(total, static_cast<long long>(blockIdx.x) * p.span);
+  const long long g_end = min(total, g_begin + p.span);
+  const SkinnyWork work(g_begin, g_end, p.num_kb, p.sk_tiles, p.dp_per_cta, p.n_tiles);
+  constexpr uint32_t kWBytes = 128 * 64 * 2;
+
+  // One stage's loads: a 128-column x 64-k weight tile and the activations of the same
+  // k block (plain form, or with the tensors' L2 policies when HINTED).
+  auto issue_stage = [&](auto hinted, int st, int tile, int kb, uint64_t pol_w, uint64_t pol_x) {
+    constexpr bool HINTED = decltype(hinted)::value;
+    (void)pol_w;
+    (void)pol_x;
+#define KAPYB_LOAD1(POL, DST, TM, BAR, X, Y)                       \
+  do {                                                             \
+    if constexpr (HINTED)                                          \
+      ptx::tma_load_3d_hint(DST, &TM, BAR, X, Y, 0, POL);          \
+    else                                                           \
+      ptx::tma_load_3d(DST, &TM, BAR, X, Y, 0);                    \
+  } while (0)
+    const uint32_t fb = ptx::smem_u32(&full_bar[st]);
+    ptx::mbar_arrive_expect_tx(fb, kWBytes + p.x_bytes);
+    const int k0 = kb * 64, n0 = tile * 128;
+    const uint32_t w_dst = ptx::smem_u32(sW + st * kWBytes);
+    const uint32_t x_dst = ptx::smem_u32(sX + st * p.x_bytes);
+    if (p.w_mn_major) {
+      KAPYB_LOAD1(pol_w, w_dst, tmW, fb, n0, k0);
+      KAPYB_LOAD1(pol_w, w_dst + 8192, tmW, fb, n0 + 64, k0);
+    } else {
+      KAPYB_LOAD1(pol_w, w_dst, tmW, fb, k0, n0);
+    }
+    if (p.x_mn_major)
+      KAPYB_LOAD1(pol_x, x_dst, tmX, fb, 0, k0);
+    else
+      KAPYB_LOAD1(pol_x, x_dst, tmX, fb, k0, 0);
+#undef KAPYB_LOAD1
+  };
+
+  // Thread 0 sets the barriers up and, without waiting for the rest of the CTA
+  // (TMEM allocation, the CTA-wide barrier), already fills the pipeline: the first
+  // bytes are then on their way a microsecond earlier, which is most of what a
+  // short launch has to lose.  The producer loop below carries on after them.
+  int prefilled = 0;
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.stages; ++s) {
       ptx::mbar_init(ptx::smem_u32(&full_bar[s]), 1);
@@ -177,10 +234,23 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     abort_flag[0] = 0u;
     abort_flag[1] = p.wait_limit_us;
     ptx::fence_barrier_init();
-  }
-  if (warp == 0 && lane == 0) {
     ptx::prefetch_tensormap(&tmW);
     ptx::prefetch_tensormap(&tmX);
+    // nothing above touched global memory; the loads below do
+    ptx::griddep_wait();
+    const bool hinted = (p.w_l2 | p.x_l2) != 0;
+    const uint64_t pol_w = hinted ? ptx::make_l2_policy(p.w_l2) : 0ull;
+    const uint64_t pol_x = hinted ? ptx::make_l2_policy(p.x_l2) : 0ull;
+    for (int j = 0; j < work.count() && prefilled < p.stages; ++j) {
+      int tile, kb_begin, kb_end;
+      work.get(j, tile, kb_begin, kb_end);
+      for (int kb = kb_begin; kb < kb_end && prefilled < p.stages; ++kb, ++prefilled) {
+        if (hinted)
+          issue_stage(std::true_type{}, prefilled, tile, kb, pol_w, pol_x);
+        else
+          issue_stage(std::false_type{}, prefilled, tile, kb, 0ull, 0ull);
+      }
+    }
   }
   if (warp == 1) {
     ptx::tmem_alloc<1>(ptx::smem_u32(tmem_slot), p.tmem_cols);
@@ -190,71 +260,49 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   __syncthreads();
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  // set-up done without touching global memory: see gemm_tcgen05_kernel
+  // let the next kernel of the stream start its own set-up; every thread that reads
+  // global memory first waits for the kernels ahead (see gemm_tcgen05_kernel)
   ptx::griddep_launch();
   ptx::griddep_wait();
 
-  const long long total = static_cast<long long>(p.sk_tiles) * p.num_kb;  // units of the split region
-  const long long g_begin = min(total, static_cast<long long>(blockIdx.x) * p.span);
-  const long long g_end = min(total, g_begin + p.span);
-  const SkinnyWork work(g_begin, g_end, p.num_kb, p.sk_tiles, p.dp_per_cta);
-
   if (warp == 0 && lane == 0) {
     // ------------------------------------------------------------ producer
-    int stage = 0;
-    uint32_t phase = 0;
-    const uint32_t stage_bytes = W_BYTES + p.x_bytes;
-    bool ok = true;
     // Two copies of the loop, plain loads and loads with an L2 policy per tensor: see
-    // the producer of gemm_tcgen05_kernel.
-#define KAPYB_LOAD1(POL, DST, TM, BAR, X, Y)                       \
-  do {                                                             \
-    if constexpr (HINTED)                                          \
-      ptx::tma_load_3d_hint(DST, &TM, BAR, X, Y, 0, POL);          \
-    else                                                           \
-      ptx::tma_load_3d(DST, &TM, BAR, X, Y, 0);                    \
-  } while (0)
+    // the producer of gemm_tcgen05_kernel.  The first `prefilled` k blocks are
+    // already in flight.
+    int stage = prefilled == p.stages ? 0 : prefilled;
+    uint32_t phase = prefilled == p.stages ? 1u : 0u;
+    bool ok = true;
     auto produce = [&](auto hinted) {
-    constexpr bool HINTED = decltype(hinted)::value;
-    const uint64_t pol_w = HINTED ? ptx::make_l2_policy(p.w_l2) : 0ull;
-    const uint64_t pol_x = HINTED ? ptx::make_l2_policy(p.x_l2) : 0ull;
-    (void)pol_w;
-    (void)pol_x;
-    for (int j = 0; j < work.count() && ok; ++j) {
-      int tile, kb_begin, kb_end;
-      work.get(j, tile, kb_begin, kb_end);
-      for (int kb = kb_begin; kb < kb_end; ++kb) {
-        if (!ptx::mbar_wait(ptx::smem_u32(&empty_bar[stage]), phase ^ 1u, abort_flag)) {
-          ok = false;
-          break;
+      constexpr bool HINTED = decltype(hinted)::value;
+      const uint64_t pol_w = HINTED ? ptx::make_l2_policy(p.w_l2) : 0ull;
+      const uint64_t pol_x = HINTED ? ptx::make_l2_policy(p.x_l2) : 0ull;
+      int skip = prefilled;
+      for (int j = 0; j < work.count() && ok; ++j) {
+        int tile, kb_begin, kb_end;
+        work.get(j, tile, kb_begin, kb_end);
+        if (skip > 0) {
+          const int d = min(skip, kb_end - kb_begin);
+          kb_begin += d;
+          skip -= d;
         }
-        const uint32_t fb = ptx::smem_u32(&full_bar[stage]);
-        ptx::mbar_arrive_expect_tx(fb, stage_bytes);
-        const int k0 = kb * 64, n0 = tile * 128;
-        const uint32_t w_dst = ptx::smem_u32(sW + stage * W_BYTES);
-        const uint32_t x_dst = ptx::smem_u32(sX + stage * p.x_bytes);
-        if (p.w_mn_major) {
-          KAPYB_LOAD1(pol_w, w_dst, tmW, fb, n0, k0);
-          KAPYB_LOAD1(pol_w, w_dst + 8192, tmW, fb, n0 + 64, k0);
-        } else {
-          KAPYB_LOAD1(pol_w, w_dst, tmW, fb, k0, n0);
-        }
-        if (p.x_mn_major)
-          KAPYB_LOAD1(pol_x, x_dst, tmX, fb, 0, k0);
-        else
-          KAPYB_LOAD1(pol_x, x_dst, tmX, fb, k0, 0);
-        if (++stage == p.stages) {
-          stage = 0;
-          phase ^= 1u;
+        for (int kb = kb_begin; kb < kb_end; ++kb) {
+          if (!ptx::mbar_wait(ptx::smem_u32(&empty_bar[stage]), phase ^ 1u, abort_flag)) {
+            ok = false;
+            break;
+          }
+          issue_stage(hinted, stage, tile, kb, pol_w, pol_x);
+          if (++stage == p.stages) {
+            stage = 0;
+            phase ^= 1u;
+          }
         }
       }
-    }
-    };  // produce
+    };
     if (p.w_l2 | p.x_l2)
       produce(std::true_type{});
     else
       produce(std::false_type{});
-#undef KAPYB_LOAD1
   } else if (warp == 1) {
     // ---------------------------------------------------------- MMA issuer
     // The whole warp walks the loops in step and one elected lane issues (uniform
@@ -304,6 +352,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         if (ptx::elect_one()) {
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
+            if (skinny_debug_on<2>(p.debug)) break;  // (debug builds) stream without multiplying
             const uint64_t wdesc = (static_cast<uint64_t>(desc_hi) << 32) | (w_lo + k * w_kstep);
             const uint64_t xdesc = (static_cast<uint64_t>(desc_hi) << 32) | (x_lo + k * x_kstep);
             ptx::umma_k<1, 0>(d_tmem, wdesc, xdesc, idesc, k == 0 ? first : 1u);
@@ -336,7 +385,8 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
                         p.out_dtype != KAPYB_F32 && p.ep.rounding == KAPYB_RN;
     int acc = 0;
     uint32_t acc_phase = 0;
-    for (int j = 0; j < work.count(); ++j) {
+    bool alive = true;
+    for (int j = 0; j < work.count() && alive; ++j) {
       int tile, kb_begin, kb_end;
       work.get(j, tile, kb_begin, kb_end);
       // warp vote after the wait: the lanes leave together or not at all (what
@@ -346,114 +396,112 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         break;
       ptx::tc_fence_after();
       const bool whole = kb_begin == 0 && kb_end == p.num_kb;
+      // A split tile is finished by its first contributor (the segment that starts
+      // the tile); every other contributor publishes its partial sums.
+      const bool owner = !whole && kb_begin == 0;
       const int n = tile * 128 + q * 32 + lane;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
                              static_cast<uint32_t>(acc * p.m_pad);
-      // A CTA's span holds at most two partial segments: one that starts inside a
-      // tile (slot 0) and one that starts a tile but does not finish it (slot 1).
       const long long t0 = static_cast<long long>(tile) * p.num_kb;
-      const int my_slot = kb_begin > 0 ? 0 : 1;
-      float *scr = p.scratch + (static_cast<long long>(blockIdx.x * 2 + my_slot) * p.m_pad) * 128 +
-                   q * 32 + lane;
+      // contributors of a split tile: CTAs first .. last, this one included
+      const int first = whole ? 0 : static_cast<int>(t0 / p.span);
+      const int last = whole ? 0 : static_cast<int>((t0 + p.num_kb - 1) / p.span);
+      auto slot_of = [&](int c) {
+        return p.scratch + (static_cast<long long>(c) * p.m_pad) * 128 + q * 32 + lane;
+      };
       float bias_n = 0.0f;
       if (p.ep.bias != nullptr && p.ep.bias_axis == 1 && n < p.N)
         bias_n = load_as_f32(p.ep.bias, p.ep.bias_dtype, n);
       uint16_t *col16 = static_cast<uint16_t *>(p.c) + n * p.c_s1;
-      for (int mc = 0; mc < p.m_pad && !skinny_debug_on<4>(p.debug); mc += 16) {
+      for (int mc = 0; mc < p.m_pad && alive && !skinny_debug_on<4>(p.debug); mc += 16) {
         uint32_t v[16];
         ptx::tmem_ld_32x16(t_row + static_cast<uint32_t>(mc), v);
         ptx::tmem_ld_wait();
-        if (whole) {
-          if (n < p.N && !skinny_debug_on<16>(p.debug)) {
-            if (fast16) {
-              float f[16];
+        if (!whole && !owner) {
+          // publish: one 8-byte store per element, the value and this launch's number
+          if (!skinny_debug_on<32>(p.debug)) {
+            uint2 *scr = slot_of(static_cast<int>(blockIdx.x));
 #pragma unroll
-              for (int i = 0; i < 16; ++i) f[i] = __uint_as_float(v[i]);
-              if (p.out_dtype == KAPYB_BF16)
-                skinny_store16<KAPYB_BF16>(col16 + mc * p.c_s0, p.c_s0, p.M - mc, f, p.ep.alpha, bias_n);
-              else
-                skinny_store16<KAPYB_F16>(col16 + mc * p.c_s0, p.c_s0, p.M - mc, f, p.ep.alpha, bias_n);
-            } else {
-#pragma unroll
-              for (int i = 0; i < 16; ++i)
-                if (mc + i < p.M) skinny_finish(p, n, mc + i, __uint_as_float(v[i]), bias_n);
-            }
+            for (int i = 0; i < 16; ++i)
+              if (mc + i < p.M) __stcg(scr + (mc + i) * 128, make_uint2(v[i], p.epoch));
           }
-        } else if (!skinny_debug_on<32>(p.debug)) {
+          continue;
+        }
+        float f[16];
 #pragma unroll
-          for (int i = 0; i < 16; ++i)
-            if (mc + i < p.M) __stcg(scr + (mc + i) * 128, __uint_as_float(v[i]));
+        for (int i = 0; i < 16; ++i) f[i] = __uint_as_float(v[i]);
+        if (owner && !skinny_debug_on<8>(p.debug)) {
+          // Add the other contributors' rows mc .. mc+15, two slots per batch: all 32
+          // loads of a batch are issued before anything looks at them (one L2 round
+          // trip per batch), then every pair must carry this launch's number, else
+          // the batch is read again.  CTA order: own sums first, then first+1, ...
+          constexpr int CB = 2;
+          for (int c = first + 1; c <= last && alive; c += CB) {
+            uint2 part[CB][16];
+            uint64_t spin_t0 = 0;
+            for (uint32_t it = 1;; ++it) {
+              // every round reads memory afresh (other CTAs are writing it)
+              asm volatile("" ::: "memory");
+#pragma unroll
+              for (int bb = 0; bb < CB; ++bb) {
+                const bool have = c + bb <= last;
+                const uint2 *src = slot_of(have ? c + bb : c);
+#pragma unroll
+                for (int i = 0; i < 16; ++i)
+                  part[bb][i] = (have && mc + i < p.M) ? __ldcg(src + (mc + i) * 128)   // L2, never L1
+                                                       : make_uint2(0u, p.epoch);
+              }
+              bool good = true;
+#pragma unroll
+              for (int bb = 0; bb < CB; ++bb)
+#pragma unroll
+                for (int i = 0; i < 16; ++i) good = good && part[bb][i].y == p.epoch;
+              if (__all_sync(0xffffffffu, good)) break;
+              // bounded: give up like any other wait of this kernel
+              bool give_up = false;
+              if ((it & 15u) == 0u) {
+                if (*abort_flag != 0u) {
+                  give_up = true;
+                } else {
+                  const uint64_t now = ptx::globaltimer_ns();
+                  if (spin_t0 == 0) spin_t0 = now;
+                  const uint32_t lim_us = abort_flag[1];
+                  if (now - spin_t0 > (lim_us ? static_cast<uint64_t>(lim_us) * 1000ull : ptx::kWaitLimitNs)) {
+                    *abort_flag = 1u;
+                    give_up = true;
+                  }
+                }
+              }
+              if (__any_sync(0xffffffffu, give_up)) {
+                alive = false;
+                break;
+              }
+              __nanosleep(100);
+            }
+            if (!alive) break;
+#pragma unroll
+            for (int bb = 0; bb < CB; ++bb)
+#pragma unroll
+              for (int i = 0; i < 16; ++i) f[i] += __uint_as_float(part[bb][i].x);
+          }
+          if (!alive) break;
+        }
+        if (n < p.N && !skinny_debug_on<16>(p.debug)) {
+          if (fast16) {
+            if (p.out_dtype == KAPYB_BF16)
+              skinny_store16<KAPYB_BF16>(col16 + mc * p.c_s0, p.c_s0, p.M - mc, f, p.ep.alpha, bias_n);
+            else
+              skinny_store16<KAPYB_F16>(col16 + mc * p.c_s0, p.c_s0, p.M - mc, f, p.ep.alpha, bias_n);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+              if (mc + i < p.M) skinny_finish(p, n, mc + i, f[i], bias_n);
+          }
         }
       }
       ptx::tc_fence_before();
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&tempty_bar[acc]));
-      if (!whole && !skinny_debug_on<4 | 8>(p.debug)) {
-        // Publish this segment's partial sums (plain stores into this CTA's own
-        // slot), then count it.  The contributor that completes the count owns
-        // the tile quarter: it adds the slots of all contributors in CTA order
-        // (so the sum does not depend on who came last) and applies the epilogue.
-        const int first = static_cast<int>(t0 / p.span);
-        const int last = static_cast<int>((t0 + p.num_kb - 1) / p.span);
-        const uint32_t expected = static_cast<uint32_t>(last - first + 1);
-        __threadfence();
-        __syncwarp();
-        uint32_t seen = 0;
-        if (lane == 0) seen = atomicAdd(p.counters + tile * 4 + q, 1u);
-        seen = __shfl_sync(0xffffffffu, seen, 0);
-        if (seen == expected - 1) {
-          __threadfence();
-          // 32 rows at a time and two contributors' slots at a time, all 64 loads
-          // issued before anything depends on them: one L2 round trip per pair of
-          // slots and batch (a split tile has two or three contributors; under a
-          // full HBM load a round trip is 2-3 us, and this pass must be done
-          // before the CTA's whole tile needs the epilogue warps again).  The
-          // slots are still added in CTA order.
-          auto slot_of = [&](int c) {
-            const int slot = static_cast<long long>(c) * p.span > t0 ? 0 : 1;
-            return p.scratch + (static_cast<long long>(c * 2 + slot) * p.m_pad) * 128 + q * 32 + lane;
-          };
-          for (int mc = 0; mc < p.M; mc += 32) {
-            float sums[2][16];
-#pragma unroll
-            for (int i = 0; i < 32; ++i) sums[i >> 4][i & 15] = 0.0f;
-            for (int c = first; c <= last; c += 2) {
-              const bool two = c + 1 <= last;
-              const float *src0 = slot_of(c), *src1 = slot_of(two ? c + 1 : c);
-              float part0[32], part1[32];
-#pragma unroll
-              for (int i = 0; i < 32; ++i) part0[i] = mc + i < p.M ? __ldcg(src0 + (mc + i) * 128) : 0.0f;
-#pragma unroll
-              for (int i = 0; i < 32; ++i)
-                part1[i] = (two && mc + i < p.M) ? __ldcg(src1 + (mc + i) * 128) : 0.0f;
-#pragma unroll
-              for (int i = 0; i < 32; ++i)
-                sums[i >> 4][i & 15] = (sums[i >> 4][i & 15] + part0[i]) + part1[i];
-            }
-            if (n < p.N) {
-#pragma unroll
-              for (int hb = 0; hb < 2; ++hb) {
-                const int m0r = mc + hb * 16;
-                if (m0r >= p.M) break;
-                if (fast16) {
-                  if (p.out_dtype == KAPYB_BF16)
-                    skinny_store16<KAPYB_BF16>(col16 + m0r * p.c_s0, p.c_s0, p.M - m0r, sums[hb],
-                                               p.ep.alpha, bias_n);
-                  else
-                    skinny_store16<KAPYB_F16>(col16 + m0r * p.c_s0, p.c_s0, p.M - m0r, sums[hb],
-                                              p.ep.alpha, bias_n);
-                } else {
-#pragma unroll
-                  for (int i = 0; i < 16; ++i)
-                    if (m0r + i < p.M) skinny_finish(p, n, m0r + i, sums[hb][i], bias_n);
-                }
-              }
-            }
-          }
-          __syncwarp();
-          if (lane == 0) atomicExch(p.counters + tile * 4 + q, 0u);
-        }
-      }
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1u;
     }

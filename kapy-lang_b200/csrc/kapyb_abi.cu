@@ -53,7 +53,9 @@ struct kapyb_context {
   int debug = 0;
   uint32_t wait_limit_us = 0;
   int forced_epi = 0;  // 0: by K; 4 or 8: that many epilogue warps (single-CTA kernels)
-  int skinny_stages = 0;  // 0: as many as fit
+  int skinny_stages = 0;  // 0: the default depth
+  uint32_t skinny_epoch = 0;  // number of the last decode-kernel launch that used the workspace
+  int skinny_split = -1;  // -1: by shape; 0: whole weight tiles only; 1: split leftover tiles between SMs
   // host-buffer calls: copy streams and events for the chunked pipeline
   cudaStream_t copy_in = nullptr, copy_out = nullptr;
   cudaEvent_t ev[2 * 16 + 2] = {};
@@ -174,9 +176,10 @@ extern "C" KAPYB_API kapyb_status kapyb_probe_read(kapyb_handle h, void *stream,
 
 // A dispatch choice in text form: "auto" | "1cta" | "2cta" | "skinny" | "simt",
 // optionally followed by ":<tile width>" and options ":e<epilogue warps>",
-// ":s<stages>" (skinny), ":d<debug bits>", ":w<wait limit, ms>".
+// ":s<stages>" and ":k<0|1>" (skinny: whole tiles only | split leftover tiles),
+// ":d<debug bits>", ":w<wait limit, ms>".
 struct PathChoice {
-  int path = PATH_AUTO, bn = 0, epi = 0, skinny_stages = 0, debug = 0;
+  int path = PATH_AUTO, bn = 0, epi = 0, skinny_stages = 0, skinny_split = -1, debug = 0;
   uint32_t wait_limit_us = 0;
 };
 
@@ -214,6 +217,7 @@ static bool parse_path(const std::string &text, PathChoice &c, const char **why)
   c.debug = std::max(0, option(":d", colon));
   c.epi = std::max(0, option(":e", colon));
   c.skinny_stages = std::max(0, option(":s", colon));
+  c.skinny_split = option(":k", colon);
   const int w = option(":w", colon);
   c.wait_limit_us = w > 0 ? 1000u * static_cast<uint32_t>(w) : 0u;
   return true;
@@ -233,6 +237,7 @@ extern "C" KAPYB_API kapyb_status kapyb_set_matmul_path(kapyb_handle h, const ch
   h->forced_bn = c.bn;
   h->forced_epi = c.epi;
   h->skinny_stages = c.skinny_stages;
+  h->skinny_split = c.skinny_split;
   h->debug = c.debug;
   h->wait_limit_us = c.wait_limit_us;
   return KAPYB_OK;
@@ -255,9 +260,6 @@ extern "C" KAPYB_API kapyb_status kapyb_check(kapyb_handle h, void *stream) {
   CUDA_TRY(h, cudaMemcpy(&st, h->status, sizeof(st), cudaMemcpyDeviceToHost));
   if (st != kStatusOk) {
     cudaMemset(h->status, 0, sizeof(uint32_t));
-    // a kernel that gave up may have left tile counters behind
-    if (h->workspace)
-      cudaMemset(h->workspace, 0, std::min<size_t>(h->workspace_bytes, kSkinnyCounterBytes));
     return fail(h, KAPYB_TIMEOUT, "a kernel gave up on a bounded wait (status %u)", st);
   }
   return KAPYB_OK;
@@ -275,8 +277,8 @@ extern "C" KAPYB_API kapyb_status kapyb_reserve_workspace(kapyb_handle h, size_t
   }
   size_t want = (bytes + (1u << 20) - 1) & ~static_cast<size_t>((1u << 20) - 1);
   CUDA_TRY(h, cudaMalloc(&h->workspace, want));
-  // Split-K partial sums and tile counters must start at zero; kernels that use
-  // them leave them zeroed again when they finish.
+  // The decode kernel's partial sums carry the number of the launch that wrote
+  // them; zero is the one number no launch uses.
   CUDA_TRY(h, cudaMemset(h->workspace, 0, want));
   h->workspace_bytes = want;
   return KAPYB_OK;
@@ -662,25 +664,37 @@ static kapyb_status launch_tcgen05(kapyb_handle h, const MatmulProblem &p, bool 
   return KAPYB_OK;
 }
 
-static size_t skinny_workspace_bytes() { return kSkinnyCounterBytes + kSkinnyScratchBytes; }
+static size_t skinny_workspace_bytes() { return kSkinnyScratchBytes; }
 
-// Partial sums of split weight tiles: two slots of [roundup16(M)][128] fp32 per CTA.
+// Partial sums of split weight tiles: one slot of [roundup16(M)][128] (fp32, launch
+// number) pairs per CTA.
 static size_t skinny_partial_bytes(int sm_count, int M) {
   const int m_pad = (M + 15) / 16 * 16;
-  return static_cast<size_t>(sm_count) * 2 * m_pad * 128 * sizeof(float);
+  return static_cast<size_t>(sm_count) * m_pad * 128 * sizeof(uint2);
 }
 
 static bool skinny_supported(int sm_count, int M, int N, int K) {
-  const long long n_tiles = (N + 127) / 128;
-  return M >= 1 && M <= kSkinnyMaxM && K >= 1 &&
-         n_tiles * 4 * sizeof(uint32_t) <= kSkinnyCounterBytes &&
+  return M >= 1 && M <= kSkinnyMaxM && K >= 1 && N >= 1 &&
          skinny_partial_bytes(sm_count, M) <= kSkinnyScratchBytes;
 }
 
-// Launches the weight-streaming kernel.  `counters` must be zero on entry and
-// are zero again when the kernel has finished; `scratch` needs no initial value.
+// Whether leftover weight tiles are split between SMs (stream-K) or every tile
+// stays whole.  forced: -1 decide here, 0 never, 1 always.
+static bool skinny_splits(int forced, int n_tiles, int sm_count) {
+  if (forced == 0) return false;
+  if (forced == 1) return true;
+  // One whole tile per SM on 80-100 % of the SMs streams as fast as all SMs on
+  // equal spans, and has no reduction at its end (measured at M = 16, K = 8192: 130
+  // tiles 41.9 us whole against 46.4 us split; 112 tiles 40.4 / 41.0; 100 tiles
+  // 40.3 / 38.0).  Everything else splits the leftover tiles.
+  return !(n_tiles <= sm_count && n_tiles * 5 > sm_count * 4);
+}
+
+// Launches the weight-streaming kernel.  `scratch` holds (partial sum, launch
+// number) pairs; `epoch` is this launch's number: not 0 and not a number that
+// may still sit in the scratch (callers count up).
 static kapyb_status launch_skinny_on(kapyb_handle h, const MatmulProblem &p, bool a_mn, bool b_mn,
-                                     float *scratch, uint32_t *counters, cudaStream_t stream) {
+                                     uint2 *scratch, uint32_t epoch, cudaStream_t stream) {
   SkinnyParams sp;
   sp.M = p.M;
   sp.N = p.N;
@@ -699,7 +713,7 @@ static kapyb_status launch_skinny_on(kapyb_handle h, const MatmulProblem &p, boo
   sp.c_s1 = p.c_s1;
   sp.c = p.c;
   sp.scratch = scratch;
-  sp.counters = counters;
+  sp.epoch = epoch;
   sp.idesc = ptx::make_idesc_f16(p.in_dtype == KAPYB_BF16, b_mn, a_mn, 128, sp.m_pad);
   sp.status = h->status;
   sp.wait_limit_us = h->wait_limit_us;
@@ -710,7 +724,14 @@ static kapyb_status launch_skinny_on(kapyb_handle h, const MatmulProblem &p, boo
   // Whole tiles round-robin while they fill the GPU evenly; the leftover tiles
   // (all of them when there are fewer tiles than SMs) are split into equal spans.
   int grid;
-  if (sp.n_tiles >= h->sm_count) {
+  const bool split = skinny_splits(h->skinny_split, sp.n_tiles, h->sm_count);
+  if (!split) {
+    // whole tiles only, dealt round-robin (the last round may be ragged)
+    grid = std::min(sp.n_tiles, h->sm_count);
+    sp.dp_per_cta = (sp.n_tiles + grid - 1) / grid;
+    sp.sk_tiles = 0;
+    sp.span = 0;
+  } else if (sp.n_tiles >= h->sm_count) {
     grid = h->sm_count;
     sp.dp_per_cta = sp.n_tiles / grid;
     sp.sk_tiles = sp.n_tiles % grid;
@@ -727,7 +748,7 @@ static kapyb_status launch_skinny_on(kapyb_handle h, const MatmulProblem &p, boo
   const int stage_bytes = 128 * 64 * 2 + sp.x_bytes;
   const int budget = 232448 - 1024 - 1024;
   sp.stages = std::max(2, std::min(kSkinnyMaxStages, budget / stage_bytes));
-  if (h->skinny_stages >= 2) sp.stages = std::min(sp.stages, h->skinny_stages);
+  sp.stages = std::min(sp.stages, h->skinny_stages >= 2 ? h->skinny_stages : kSkinnyStages);
   const int smem = 1024 + sp.stages * stage_bytes + 1024;
 
   CUtensorMap tmW, tmX;
@@ -770,9 +791,8 @@ static kapyb_status launch_skinny(kapyb_handle h, const MatmulProblem &p, bool a
     return fail(h, KAPYB_UNSUPPORTED, "matmul: shape outside the skinny kernel's range");
   kapyb_status st = kapyb_reserve_workspace(h, skinny_workspace_bytes());
   if (st != KAPYB_OK) return st;
-  uint32_t *counters = static_cast<uint32_t *>(h->workspace);
-  float *scratch = reinterpret_cast<float *>(static_cast<char *>(h->workspace) + kSkinnyCounterBytes);
-  return launch_skinny_on(h, p, a_mn, b_mn, scratch, counters, stream);
+  if (++h->skinny_epoch == 0) ++h->skinny_epoch;  // 0 marks scratch no launch has written
+  return launch_skinny_on(h, p, a_mn, b_mn, static_cast<uint2 *>(h->workspace), h->skinny_epoch, stream);
 }
 
 // What run_matmul decided for a problem: the kernel family, the tile, and the
@@ -1085,9 +1105,11 @@ extern "C" KAPYB_API kapyb_status kapyb_matmul_plan(kapyb_handle h, int32_t sm_c
         (p.M + 63) / 64, p.batch);
   } else if (plan.path == PATH_SKINNY) {
     const int num_kb = (p.K + 63) / 64, n_tiles = (p.N + 127) / 128;
-    const int grid = std::min<long long>(opt.sm_count, static_cast<long long>(n_tiles) * num_kb);
-    const int dp = n_tiles >= opt.sm_count ? n_tiles / opt.sm_count : 0;
-    const int sk = n_tiles >= opt.sm_count ? n_tiles % opt.sm_count : n_tiles;
+    const bool split = skinny_splits(h ? h->skinny_split : -1, n_tiles, opt.sm_count);
+    const int grid = split ? static_cast<int>(std::min<long long>(opt.sm_count, static_cast<long long>(n_tiles) * num_kb))
+                           : std::min(n_tiles, opt.sm_count);
+    const int dp = !split ? (n_tiles + grid - 1) / grid : n_tiles >= opt.sm_count ? n_tiles / opt.sm_count : 0;
+    const int sk = !split ? 0 : n_tiles >= opt.sm_count ? n_tiles % opt.sm_count : n_tiles;
     add("path: %s\n", "tcgen05_skinny (weights on the 128-row side of the MMA, activations on its N side)");
     add("tile: 128 weight columns x %d rows x 64 k; %d weight tiles x %d k-blocks on %d CTAs\n",
         (p.M + 15) / 16 * 16, n_tiles, num_kb, grid);
@@ -2262,13 +2284,13 @@ extern "C" KAPYB_API kapyb_status kapyb_reduce(kapyb_handle h, const kapyb_tenso
 
 // ------------------------------------------- decode matmul without allocation
 
-// Fixed scratch for kapyb_matmul_decode_static: tile counters followed by the
-// fp32 partial sums of split weight tiles (two slots per CTA; 10 MiB hold them
+// Fixed scratch for kapyb_matmul_decode_static: the partial sums of split weight
+// tiles, as (fp32 value, launch number) pairs, one slot per CTA (10 MiB hold them
 // for 64 rows on a GPU of up to 160 SMs).  It lives in the library image, so
-// every GPU that loads the library carries these bytes until the process exits.
-constexpr size_t kStaticCounterBytes = 16 * 1024;
+// every GPU that loads the library carries these bytes until the process exits;
+// it starts zeroed, and zero is the one launch number never used.
 constexpr size_t kStaticPartialBytes = 10u << 20;
-static __device__ __align__(256) unsigned char g_decode_scratch[kStaticCounterBytes + kStaticPartialBytes];
+static __device__ __align__(256) unsigned char g_decode_scratch[kStaticPartialBytes];
 static __device__ uint32_t g_decode_status;
 
 struct StaticDeviceState {
@@ -2277,6 +2299,7 @@ struct StaticDeviceState {
   uint32_t *status = nullptr;        // device address of g_decode_status on this device
   int sm_count = 0;
   EncodeTiledFn encode = nullptr;
+  std::atomic<uint32_t> epoch{0};    // launches so far on this device: the numbers in the scratch
 };
 static StaticDeviceState g_static_state[kMaxDevices];
 static std::mutex g_static_mu;  // serialises the one-time set-up per device
@@ -2343,20 +2366,16 @@ extern "C" KAPYB_API kapyb_status kapyb_matmul_decode_static(const kapyb_tensor2
   if (st != KAPYB_OK) return bail(st);
   MatmulProblem p = make_problem(lhs, rhs, nullptr, out, epilogue);
   if (p.M == 0 || p.N == 0) return KAPYB_OK;
-  const long long n_tiles = (p.N + 127) / 128;
   if (dtype_size(p.in_dtype) != 2)
     return bail(fail(&ctx, KAPYB_UNSUPPORTED, "matmul_decode_static: operands must be f16 or bf16"));
   if (p.M > kSkinnyMaxM || p.K < 1)
     return bail(fail(&ctx, KAPYB_UNSUPPORTED, "matmul_decode_static: needs 1 <= M <= %d and K >= 1 (got M=%d, K=%d)", kSkinnyMaxM, p.M, p.K));
-  const size_t need_counters = static_cast<size_t>(n_tiles) * 4 * sizeof(uint32_t);
   const size_t need_partial = skinny_partial_bytes(ctx.sm_count, p.M);
-  if (need_counters > kStaticCounterBytes || need_partial > kStaticPartialBytes)
+  if (need_partial > kStaticPartialBytes)
     return bail(fail(&ctx, KAPYB_UNSUPPORTED,
-                     "matmul_decode_static: problem needs %zu bytes of counters and %zu of partial sums; "
-                     "the fixed scratch holds %zu and %zu (N <= %zu; 2 * SMs * roundup16(M) * 512 "
-                     "bytes of partial sums)",
-                     need_counters, need_partial, kStaticCounterBytes, kStaticPartialBytes,
-                     kStaticCounterBytes / 16 * 128));
+                     "matmul_decode_static: problem needs %zu bytes of partial sums (SMs * roundup16(M) * "
+                     "1024); the fixed scratch holds %zu",
+                     need_partial, kStaticPartialBytes));
   if (p.c_s1 != 1 && p.N != 1)
     return bail(fail(&ctx, KAPYB_UNSUPPORTED, "matmul_decode_static: out must be row-major (unit stride on axis 1)"));
   const bool a_k = p.a_s1 == 1 || p.K == 1, a_m = p.a_s0 == 1 || p.M == 1;
@@ -2369,17 +2388,16 @@ extern "C" KAPYB_API kapyb_status kapyb_matmul_decode_static(const kapyb_tensor2
                      "matmul_decode_static: operands need a unit stride, 16-byte aligned bases and "
                      "leading dimensions that are multiples of 16 bytes"));
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-  // The counters keep whatever the previous call left (zeros after a clean run,
-  // anything after one that was cut short): clear the ones this call uses.  The
-  // partial sums are written before they are read and need no clearing.
-  e = cudaMemsetAsync(sd.scratch, 0, need_counters, stream);
-  // The status word is shared too: start this call from "no time-out", so that a
-  // checked call never reports what an earlier unchecked call left behind.
-  if (e == cudaSuccess) e = cudaMemsetAsync(sd.status, 0, sizeof(uint32_t), stream);
-  if (e != cudaSuccess) return fail(nullptr, KAPYB_CUDA_ERROR, "matmul_decode_static: clearing scratch: %s", cudaGetErrorString(e));
-  st = launch_skinny_on(&ctx, p, a_mn, b_mn,
-                        reinterpret_cast<float *>(sd.scratch + kStaticCounterBytes),
-                        reinterpret_cast<uint32_t *>(sd.scratch), stream);
+  // The array keeps the last call's contents.  Nothing in it has to be cleared:
+  // every partial sum carries the number of the call that wrote it, and this
+  // call only accepts its own number.  The status word is shared too and does
+  // start from zero, so that a checked call never reports what an earlier
+  // unchecked call left behind.
+  e = cudaMemsetAsync(sd.status, 0, sizeof(uint32_t), stream);
+  if (e != cudaSuccess) return fail(nullptr, KAPYB_CUDA_ERROR, "matmul_decode_static: clearing the status word: %s", cudaGetErrorString(e));
+  uint32_t epoch = sd.epoch.fetch_add(1, std::memory_order_relaxed) + 1;
+  if (epoch == 0) epoch = sd.epoch.fetch_add(1, std::memory_order_relaxed) + 1;
+  st = launch_skinny_on(&ctx, p, a_mn, b_mn, reinterpret_cast<uint2 *>(sd.scratch), epoch, stream);
   if (st != KAPYB_OK) return bail(st);
   if (sync_and_check) {
     e = cudaStreamSynchronize(stream);
