@@ -55,6 +55,7 @@ struct kapyb_context {
   int forced_epi = 0;  // 0: by K; 4 or 8: that many epilogue warps (single-CTA kernels)
   int skinny_stages = 0;  // 0: the default depth
   uint32_t skinny_epoch = 0;  // number of the last decode-kernel launch that used the workspace
+  int forced_group_m = 0; // 0: the default raster group (row blocks walked together); else that many
   int skinny_split = -1;  // -1: by shape; 0: whole weight tiles only; 1: split leftover tiles between SMs
   // host-buffer calls: copy streams and events for the chunked pipeline
   cudaStream_t copy_in = nullptr, copy_out = nullptr;
@@ -177,9 +178,10 @@ extern "C" KAPYB_API kapyb_status kapyb_probe_read(kapyb_handle h, void *stream,
 // A dispatch choice in text form: "auto" | "1cta" | "2cta" | "skinny" | "simt",
 // optionally followed by ":<tile width>" and options ":e<epilogue warps>",
 // ":s<stages>" and ":k<0|1>" (skinny: whole tiles only | split leftover tiles),
+// ":g<n>" (tcgen05: row blocks per raster group),
 // ":d<debug bits>", ":w<wait limit, ms>".
 struct PathChoice {
-  int path = PATH_AUTO, bn = 0, epi = 0, skinny_stages = 0, skinny_split = -1, debug = 0;
+  int path = PATH_AUTO, bn = 0, epi = 0, skinny_stages = 0, skinny_split = -1, debug = 0, group_m = 0;
   uint32_t wait_limit_us = 0;
 };
 
@@ -218,6 +220,7 @@ static bool parse_path(const std::string &text, PathChoice &c, const char **why)
   c.epi = std::max(0, option(":e", colon));
   c.skinny_stages = std::max(0, option(":s", colon));
   c.skinny_split = option(":k", colon);
+  c.group_m = std::max(0, option(":g", colon));
   const int w = option(":w", colon);
   c.wait_limit_us = w > 0 ? 1000u * static_cast<uint32_t>(w) : 0u;
   return true;
@@ -238,6 +241,7 @@ extern "C" KAPYB_API kapyb_status kapyb_set_matmul_path(kapyb_handle h, const ch
   h->forced_epi = c.epi;
   h->skinny_stages = c.skinny_stages;
   h->skinny_split = c.skinny_split;
+  h->forced_group_m = c.group_m;
   h->debug = c.debug;
   h->wait_limit_us = c.wait_limit_us;
   return KAPYB_OK;
@@ -605,6 +609,7 @@ static kapyb_status launch_tcgen05(kapyb_handle h, const MatmulProblem &p, bool 
   };
   gp.idesc = ptx::make_idesc(fmt(p.in_dtype), fmt(p.in_dtype_b), a_mn, b_mn, Cfg::TILE_M, Cfg::MMA_N);
   if (BN == 512) gp.group_m = std::max(1, std::min(gp.tiles_m, 12));
+  if (h->forced_group_m > 0) gp.group_m = std::max(1, std::min(gp.tiles_m, h->forced_group_m));
   gp.div_per_batch = FastDiv::make(static_cast<uint32_t>(gp.tiles_m * gp.tiles_n));
   gp.div_in_group = FastDiv::make(static_cast<uint32_t>(gp.group_m * gp.tiles_n));
   gp.div_group_m = FastDiv::make(static_cast<uint32_t>(gp.group_m));
