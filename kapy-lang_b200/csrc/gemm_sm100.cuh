@@ -137,6 +137,61 @@ struct GemmParams {
   // L2 policy of the TMA traffic per tensor (from the descriptors' eviction
   // priority): 0 default, 1 evict_first, 2 evict_last
   int a_l2, b_l2, c_l2;
+  // SPLIT instantiations only.  Tiles below sk_first_tile are dealt to the CTAs
+  // (pairs) whole, round-robin; the K blocks of the tiles from there on, sk_total in
+  // all, are dealt out as one contiguous span per CTA (pair), so a last wave that
+  // would fill only part of the GPU keeps all of it busy.  A CTA whose span starts
+  // inside a tile leaves its fp32 partial accumulator in its slot of sk_scratch
+  // ([CTA][128 x BN] floats) and sets its warps' words of sk_flags to sk_epoch, the
+  // number of this launch; the CTA that did the tile's first K blocks adds the
+  // partial sums to its own in CTA order (the same bits on every run) and runs the
+  // epilogue.
+  int sk_first_tile, sk_total;
+  float *sk_scratch;
+  uint32_t *sk_flags;
+  uint32_t sk_epoch;
+};
+
+// First K block (in the numbering that runs through all split tiles) of CTA (pair)
+// `unit` of `units`.
+__device__ __forceinline__ int sk_span_begin(const GemmParams &p, int unit, int units) {
+  return static_cast<int>(static_cast<long long>(unit) * p.sk_total / units);
+}
+
+// The work of one CTA (pair), item by item: tile `tile`, K blocks [kb0, kb1).
+template <bool SK>
+struct WorkIter {
+  int tile, kb0, kb1;
+  int next_tile, step, lin, lin_end;
+  __device__ __forceinline__ WorkIter(const GemmParams &p, int unit, int units)
+      : tile(0), kb0(0), kb1(p.num_kb), next_tile(unit), step(units), lin(0), lin_end(0) {
+    if constexpr (SK) {
+      lin = sk_span_begin(p, unit, units);
+      lin_end = sk_span_begin(p, unit + 1, units);
+    }
+  }
+  __device__ __forceinline__ bool next(const GemmParams &p) {
+    if constexpr (!SK) {
+      tile = next_tile;
+      next_tile += step;
+      return tile < p.num_tiles;
+    } else {
+      if (next_tile < p.sk_first_tile) {
+        tile = next_tile;
+        next_tile += step;
+        kb0 = 0;
+        kb1 = p.num_kb;
+        return true;
+      }
+      if (lin >= lin_end) return false;
+      const int t = lin / p.num_kb;
+      kb0 = lin - t * p.num_kb;
+      kb1 = min(p.num_kb, kb0 + (lin_end - lin));
+      tile = p.sk_first_tile + t;
+      lin += kb1 - kb0;
+      return true;
+    }
+  }
 };
 
 template <int BN, int CTAS, int EPI = 4>
@@ -437,12 +492,19 @@ __device__ __forceinline__ bool epilogue_tile(const GemmParams &p, const TmapArr
 // chunk by chunk.  Returns false when a wait ran out.
 // One copy serves bf16 and f16 outputs, with or without a bias: separate copies
 // inlined into one kernel made the register allocator spill.
-template <int EPI>
+// MODE 1 / 2: the output is bf16 / f16, known at compile time, and a column bias
+// kept in registers is of the same type (one type throughout, the usual case).
+// The drain is bound by the instructions these warps issue, and choosing the
+// conversions per element at run time tripled them; two specialised copies
+// inlined into one kernel made the register allocator spill, so the kernel
+// itself is instantiated per MODE (its DRAIN parameter).
+template <int EPI, int MODE>
 __device__ __forceinline__ bool epilogue_two_halves(const GemmParams &p, const TmapArray &tmC,
-                                                    EpiTile &t, uint32_t tfull0, uint32_t parity,
-                                                    volatile uint32_t *abort_flag, bool active,
-                                                    bool bf16) {
+                                                 EpiTile &t, uint32_t tfull0, uint32_t parity,
+                                                 volatile uint32_t *abort_flag, bool active) {
   static_assert(EPI == 8, "register drain: eight epilogue warps");
+  static_assert(MODE == 1 || MODE == 2, "bf16 or f16");
+  constexpr bool bf16 = MODE == 1;
   const int lane = t.lane;
   uint8_t *srow = t.stg + lane * 128;
   // Chunk i = hh*2 + j covers tile columns (hh*4 + cpart + 2*j) * 64 ..  Chunk 0
@@ -466,8 +528,10 @@ __device__ __forceinline__ bool epilogue_two_halves(const GemmParams &p, const T
   // A 16-bit column bias is fetched before the accumulator is awaited, so its
   // latency hides behind the main loop: lane l keeps the eight values of columns
   // (l & 7) * 8 .. +7 of chunk l >> 3; the pieces below pick them up by shuffle.
-  const bool bias_regs = t.bias_col && t.bias_fast;
-  const bool bias_bf16 = p.ep.bias_dtype == KAPYB_BF16;
+  constexpr bool bias_bf16 = MODE == 1;
+  const bool bias_regs = t.bias_col && t.bias_fast &&
+                         p.ep.bias_dtype == (MODE == 1 ? KAPYB_BF16 : KAPYB_F16);
+  const float alpha = p.ep.alpha;
   uint4 bv = make_uint4(0u, 0u, 0u, 0u);
   if (bias_regs) {
     const int ci = lane >> 3;
@@ -484,7 +548,19 @@ __device__ __forceinline__ bool epilogue_two_halves(const GemmParams &p, const T
     }
   }
   bool alive = true;  // false once a wait has run out: nothing more is read or stored
+  uint32_t ld_clocks = 0, drain_c0 = 0;
+  // debug builds, timeline on: when the first CTA's first epilogue warp saw half 0
+  // published, handed it back, saw half 1 published, handed it back, issued its last
+  // store (of the CTA's last tile) -> status[9..13]
+  auto stamp = [&](int word) {
+    if constexpr (kEpilogueProbes) {
+      if (t.prof != nullptr && lane == 0)
+        t.prof[word] = static_cast<uint32_t>(ptx::globaltimer_ns());
+    }
+  };
+  uint32_t hb_clocks = 0, st_clocks = 0;
   auto hand_back = [&](int hh) {
+    const uint32_t k0 = (kEpilogueProbes && t.prof) ? static_cast<uint32_t>(clock()) : 0u;
     ptx::tc_fence_before();
     __syncwarp();
     if (lane == 0) {
@@ -493,6 +569,7 @@ __device__ __forceinline__ bool epilogue_two_halves(const GemmParams &p, const T
       else
         ptx::mbar_arrive(t.tempty_addr + hh * 8);
     }
+    if (kEpilogueProbes && t.prof) hb_clocks += static_cast<uint32_t>(clock()) - k0;
   };
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
@@ -502,6 +579,10 @@ __device__ __forceinline__ bool epilogue_two_halves(const GemmParams &p, const T
       // since the loads, shuffles and __syncwarp below are warp-collective
       if (!__all_sync(0xffffffffu, ptx::mbar_wait(tfull0 + hh * 8, parity, abort_flag))) alive = false;
       ptx::tc_fence_after();
+      if (hh == 0) {
+        stamp(0);
+        drain_c0 = static_cast<uint32_t>(clock());
+      }
     }
     const int c = hh * 4 + t.cpart + 2 * j;
     const int nc = t.n0 + c * 64;
@@ -516,18 +597,25 @@ __device__ __forceinline__ bool epilogue_two_halves(const GemmParams &p, const T
       }
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
+        const uint32_t k0 = (kEpilogueProbes && t.prof) ? static_cast<uint32_t>(clock()) : 0u;
         ptx::tmem_ld_32x32(t.t_row + static_cast<uint32_t>(c * 64 + h * 32), v);
         ptx::tmem_ld_wait();
-        if (j == 1 && h == 1) hand_back(hh);  // this warp's last read of half hh
+        if (kEpilogueProbes && t.prof) ld_clocks += static_cast<uint32_t>(clock()) - k0;
+        if (j == 1 && h == 1) {
+          hand_back(hh);  // this warp's last read of half hh
+          if (kEpilogueProbes && t.prof && hh == 1 && lane == 0) {
+            t.prof[3] = hb_clocks;
+            t.prof[4] = st_clocks;
+            t.prof[1] = ld_clocks;                                   // clocks in tcgen05.ld + wait::ld, 8 pieces
+            t.prof[2] = static_cast<uint32_t>(clock()) - drain_c0;   // clocks from half 0 seen to half 1 handed back
+          }
+        }
         float f[32];
 #pragma unroll
         for (int k = 0; k < 32; ++k) f[k] = __uint_as_float(v[k]);
         if (bias_regs) {
-          // the piece's 32 bias values sit in lanes i*8 + h*4 .. +3, eight per lane
-          if (p.ep.alpha != 1.0f) {
-#pragma unroll
-            for (int k = 0; k < 32; ++k) f[k] *= p.ep.alpha;
-          }
+          // the piece's 32 bias values sit in lanes i*8 + h*4 .. +3, eight per lane;
+          // scale and bias are one fused multiply-add per element
 #pragma unroll
           for (int jj = 0; jj < 4; ++jj) {
             const int src = i * 8 + h * 4 + jj;
@@ -542,8 +630,8 @@ __device__ __forceinline__ bool epilogue_two_halves(const GemmParams &p, const T
                 unpack2_16<KAPYB_BF16>(ws[e], lo, hi);
               else
                 unpack2_16<KAPYB_F16>(ws[e], lo, hi);
-              f[8 * jj + 2 * e] += lo;
-              f[8 * jj + 2 * e + 1] += hi;
+              f[8 * jj + 2 * e] = fmaf(f[8 * jj + 2 * e], alpha, lo);
+              f[8 * jj + 2 * e + 1] = fmaf(f[8 * jj + 2 * e + 1], alpha, hi);
             }
           }
         } else {
@@ -557,9 +645,16 @@ __device__ __forceinline__ bool epilogue_two_halves(const GemmParams &p, const T
           pack32_rn(f, pk[i == 0 ? 0 : i - 1][h], bf16);
         }
       }
-      if (i == 0) store_chunk(nc);
     } else if (j == 1) {
       hand_back(hh);
+    }
+    if (i == 1 && alive && active && t.n0 + t.cpart * 64 < p.N) {
+      // chunk 0 sits in the staging buffer: its store goes out now that half 0 is
+      // back with the MMA thread (the fence and the store's issue cost that thread
+      // several hundred clocks when they came first)
+      const uint32_t k0 = (kEpilogueProbes && t.prof) ? static_cast<uint32_t>(clock()) : 0u;
+      store_chunk(t.n0 + t.cpart * 64);
+      if (kEpilogueProbes && t.prof) st_clocks += static_cast<uint32_t>(clock()) - k0;
     }
   }
 #pragma unroll
@@ -602,7 +697,7 @@ __device__ __forceinline__ void issue_kblock(uint32_t d_tmem, uint32_t a_lo, uin
   }
 }
 
-template <int BN, int CTAS, int EPI, bool REDUCE = false>
+template <int BN, int CTAS, int EPI, bool REDUCE = false, bool SK = false, int DRAIN = 1>
 __global__ void __launch_bounds__(64 + 32 * EPI, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
                     const __grid_constant__ CUtensorMap tmB,
@@ -709,16 +804,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
     const uint64_t pol_b = HINTED ? ptx::make_l2_policy(p.b_l2) : 0ull;
     (void)pol_a;
     (void)pol_b;
-    for (int tile = unit; tile < p.num_tiles && ok && !debug_on<16 | 32>(p.debug); tile += unit_step) {
+    for (WorkIter<SK> w(p, unit, unit_step); ok && !debug_on<16 | 32>(p.debug) && w.next(p);) {
       int b, mb, nb;
-      decode_tile(p, tile, b, mb, nb);
+      decode_tile(p, w.tile, b, mb, nb);
       const int m0 = mb * Cfg::TILE_M + static_cast<int>(rank) * Cfg::BM;
       // first B column this CTA loads; with a split tile its columns are two groups
       // of MMA_N / CTAS, one per column half, so that accumulator column c of the
       // pair's MMA is tile column c
       const int nB0 = nb * BN + static_cast<int>(rank) * (Cfg::MMA_N / CTAS);
       constexpr int kGroupCols = Cfg::MMA_N / CTAS;   // columns per half this CTA owns
-      for (int kb = 0; kb < p.num_kb; ++kb) {
+      for (int kb = w.kb0; kb < w.kb1; ++kb) {
         if (!ptx::mbar_wait(ptx::smem_u32(&empty_bar[stage]), phase ^ 1u, abort_flag)) {
           ok = false;
           break;
@@ -851,7 +946,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
     const long long probe_c0 = probe ? clock64() : 0;
     const uint64_t probe_t0 = probe ? ptx::globaltimer_ns() : 0;
     uint32_t stall_full = 0, stall_drain = 0;  // probe: clocks this thread waited for operands / for TMEM
-    for (int tile = unit; tile < p.num_tiles && ok; tile += unit_step) {
+    for (WorkIter<SK> w(p, unit, unit_step); ok && w.next(p);) {
       // ---- helpers (every lane runs them; one elected lane issues)
       // waits for the next operand stage; returns its index, or -1 when the wait ran out
       auto wait_stage = [&]() -> int {
@@ -916,7 +1011,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
         constexpr int kSkew = 2;
         static_assert(kSkew < STAGES, "the skewed blocks stay resident until both halves used them");
         const uint32_t d_tmem = tmem_base;
-        const int n = p.num_kb;
+        const int n = w.kb1 - w.kb0;
         const int skew = n >= 2 * kSkew ? kSkew : 0;
         int held[kSkew];
         if (!wait_drained(0)) break;
@@ -957,7 +1052,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       } else {
         if (!wait_drained(acc)) break;
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
-        for (int kb = 0; kb < p.num_kb; ++kb) {
+        const int n = w.kb1 - w.kb0;
+        for (int kb = 0; kb < n; ++kb) {
           const int st = wait_stage();
           if (st < 0) {
             ok = false;
@@ -1005,17 +1101,158 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
     uint32_t acc_phase = 0;
     int buf = 0;
     uint32_t *prof = (kEpilogueProbes && timeline && blockIdx.x == 0 && e == 0) ? prof_words : nullptr;
-    for (int tile = unit; tile < p.num_tiles; tile += unit_step) {
+    for (WorkIter<SK> w(p, unit, unit_step); w.next(p);) {
       const uint32_t s0 = prof ? static_cast<uint32_t>(clock()) : 0u;
       int b, mb, nb;
-      decode_tile(p, tile, b, mb, nb);
+      decode_tile(p, w.tile, b, mb, nb);
       if (prof && lane == 0) atomicAdd(prof + 1, static_cast<uint32_t>(clock()) - s0);  // tile decode
       const int m0 = mb * Cfg::TILE_M + static_cast<int>(rank) * Cfg::BM + q * 32;
       const int n0 = nb * BN;
       const int row = m0 + lane;
       bool alive = true;
+      if constexpr (SK) {
+        // A tile whose K blocks are shared between CTAs (pairs).  Its pieces: 32 rows
+        // (this warp's TMEM lanes) x 32 columns, 4 KB each, piece (c32, q) of CTA
+        // `rank` of pair `u` at sk_scratch + ((u * CTAS + rank) * BN / 32 * 4 + c32 * 4 + q) KB * 4,
+        // lane l holding row l as eight float4 at [j * 32 + l].
+        // With eight epilogue warps two warps share a lane quarter: each takes the
+        // columns it will drain in the epilogue proper (alternate chunks of 64
+        // columns, of 32 for a 32-bit output), so the sums a warp writes back to TMEM
+        // are read by that warp only.
+        constexpr int CSTEP = EPI / 4;
+        constexpr int kSlotPieces = Cfg::SLOT_COLS / 32;
+        const int pw = out32 ? 1 : 2;  // pieces per chunk
+        auto mine_piece = [&](int c32) { return CSTEP == 1 || ((c32 / pw) & 1) == cpart; };
+        const uint32_t t_row0 = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+        auto pieces_of = [&](int u) {
+          return p.sk_scratch + (static_cast<size_t>(u) * CTAS + rank) * (128 * BN);
+        };
+        if (w.kb0 != 0) {
+          // Not the tile's first K blocks: leave the accumulator for the CTA that did those.
+          float *mine = pieces_of(unit);
+#pragma unroll 1
+          for (int hh = 0; hh < Cfg::HALVES; ++hh) {
+            const int slot = Cfg::HALVES == 2 ? hh : acc;
+            if (!__all_sync(0xffffffffu,
+                            ptx::mbar_wait(ptx::smem_u32(&tfull_bar[slot]), acc_phase, abort_flag))) {
+              alive = false;
+              break;
+            }
+            ptx::tc_fence_after();
+            const uint32_t t_row = t_row0 + (Cfg::HALVES == 2 ? 0u : static_cast<uint32_t>(acc * BN));
+            if (m0 < p.M) {
+              for (int c32 = hh * kSlotPieces; c32 < (hh + 1) * kSlotPieces; ++c32) {
+                if (n0 + c32 * 32 >= p.N) break;
+                if (!mine_piece(c32)) continue;
+                uint32_t v[32];
+                ptx::tmem_ld_32x32(t_row + static_cast<uint32_t>(c32 * 32), v);
+                ptx::tmem_ld_wait();
+                float4 *dst = reinterpret_cast<float4 *>(mine + (c32 * 4 + q) * 1024) + lane;
+#ifndef SK_NO_DUMP_STORES
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                  __stcg(dst + j * 32, make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
+                                                   __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3])));
+#else
+                (void)dst;
+#endif
+              }
+            }
+            ptx::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+              const uint32_t slot_bar = tempty_leader + static_cast<uint32_t>(slot * 8);
+              if constexpr (CTAS == 2)
+                ptx::mbar_arrive_cluster(slot_bar);
+              else
+                ptx::mbar_arrive(slot_bar);
+            }
+          }
+          if (!alive) break;
+          // every lane's stores, then the warp's word: release by one lane after the
+          // warp barrier covers them all
+          __syncwarp();
+          if (lane == 0) {
+            __threadfence();
+            ptx::st_release_gpu(p.sk_flags + (static_cast<size_t>(unit) * CTAS + rank) * 8 + e, p.sk_epoch);
+          }
+          if constexpr (Cfg::HALVES == 2) {
+            acc_phase ^= 1u;
+          } else {
+            acc ^= 1;
+            if (acc == 0) acc_phase ^= 1u;
+          }
+          continue;
+        }
+        if (w.kb1 != p.num_kb) {
+          // The tile's first K blocks, the rest done elsewhere: add the other CTAs'
+          // partial sums into the accumulator (in CTA order), then carry on as usual.
+#pragma unroll 1
+          for (int hh = 0; hh < Cfg::HALVES && alive; ++hh) {
+            const int slot = Cfg::HALVES == 2 ? hh : acc;
+            if (!__all_sync(0xffffffffu,
+                            ptx::mbar_wait(ptx::smem_u32(&tfull_bar[slot]), acc_phase, abort_flag)))
+              alive = false;
+          }
+          if (!alive) break;
+          ptx::tc_fence_after();
+          const uint32_t t_row = t_row0 + (Cfg::HALVES == 2 ? 0u : static_cast<uint32_t>(acc * BN));
+          const int tile_end = (w.tile - p.sk_first_tile + 1) * p.num_kb;
+#pragma unroll 1
+          for (int u = unit + 1; u < unit_step && sk_span_begin(p, u, unit_step) < tile_end; ++u) {
+            const uint32_t *flag = p.sk_flags + (static_cast<size_t>(u) * CTAS + rank) * 8 + e;
+            bool here = ptx::ld_acquire_gpu(flag) == p.sk_epoch;
+            uint64_t t0 = 0;
+            for (uint32_t it = 1; !here; ++it) {
+              __nanosleep(64);
+              here = ptx::ld_acquire_gpu(flag) == p.sk_epoch;
+              if (!here && (it & 63u) == 0u) {
+                if (*abort_flag != 0u) break;
+                const uint64_t now = ptx::globaltimer_ns();
+                if (t0 == 0) t0 = now;
+                const uint32_t lim_us = abort_flag[1];
+                if (now - t0 > (lim_us ? static_cast<uint64_t>(lim_us) * 1000ull : ptx::kWaitLimitNs)) {
+                  *abort_flag = 1u;
+                  break;
+                }
+              }
+            }
+            if (!__all_sync(0xffffffffu, here)) {
+              alive = false;
+              break;
+            }
+            if (m0 >= p.M) continue;
+            const float *theirs = pieces_of(u);
+            for (int c32 = 0; c32 < BN / 32; ++c32) {
+              if (n0 + c32 * 32 >= p.N) break;
+              if (!mine_piece(c32)) continue;
+              const float4 *src = reinterpret_cast<const float4 *>(theirs + (c32 * 4 + q) * 1024) + lane;
+              float4 add[8];
+#pragma unroll
+#ifndef SK_NO_FIXUP_LOADS
+              for (int j = 0; j < 8; ++j) add[j] = __ldcg(src + j * 32);
+#else
+              for (int j = 0; j < 8; ++j) add[j] = make_float4(0.f, 0.f, 0.f, float(reinterpret_cast<uintptr_t>(src) & 1));
+#endif
+              uint32_t v[32];
+              ptx::tmem_ld_32x32(t_row + static_cast<uint32_t>(c32 * 32), v);
+              ptx::tmem_ld_wait();
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                v[4 * j] = __float_as_uint(__uint_as_float(v[4 * j]) + add[j].x);
+                v[4 * j + 1] = __float_as_uint(__uint_as_float(v[4 * j + 1]) + add[j].y);
+                v[4 * j + 2] = __float_as_uint(__uint_as_float(v[4 * j + 2]) + add[j].z);
+                v[4 * j + 3] = __float_as_uint(__uint_as_float(v[4 * j + 3]) + add[j].w);
+              }
+              ptx::tmem_st_32x32(t_row + static_cast<uint32_t>(c32 * 32), v);
+            }
+            ptx::tmem_st_wait();
+          }
+          if (!alive) break;
+        }
+      }
       if constexpr (Cfg::HALVES == 2 && EPI == 8) {
-        if ((out_kind == 1 || out_kind == 3) && p.ep.acc == nullptr &&
+        if (out_kind == (DRAIN == 1 ? 1 : 3) && p.ep.acc == nullptr &&
             p.ep.activation == KAPYB_ACT_NONE) {
           // 16-bit output of a two-half tile: drain to registers, store afterwards
           EpiTile et;
@@ -1034,13 +1271,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
           et.bias_col = bias_col;
           et.bias_fast = bias_fast;
           et.bias_row = 0.0f;
-          et.prof = nullptr;
+          et.prof = (kEpilogueProbes && timeline && blockIdx.x == 0 && e == 0) ? p.status + 9 : nullptr;
           if (p.ep.bias != nullptr && p.ep.bias_axis == 0 && row < p.M)
             et.bias_row = load_as_f32(p.ep.bias, p.ep.bias_dtype, row);
           const bool active = m0 < p.M && !debug_on<4>(p.debug);
           const uint32_t tf0 = ptx::smem_u32(&tfull_bar[0]);
-          alive = epilogue_two_halves<EPI>(p, tmC, et, tf0, acc_phase, abort_flag, active,
-                                           out_kind == 1);
+          alive = epilogue_two_halves<EPI, DRAIN>(p, tmC, et, tf0, acc_phase, abort_flag, active);
           if (!alive) break;
           acc_phase ^= 1u;
           continue;
@@ -1128,7 +1364,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
   ptx::tc_fence_before();
   __syncthreads();
   if (timeline && blockIdx.x == 0 && threadIdx.x == 0) {
-    for (int i = 0; i < 5; ++i) p.status[9 + i] = prof_words[i];
+    for (int i = 0; i < 5; ++i) atomicAdd(p.status + 9 + i, prof_words[i]);
   }
   if (*abort_flag != 0u) {
     if (threadIdx.x == 0) atomicExch(p.status, kStatusTimeout);

@@ -57,6 +57,10 @@ struct kapyb_context {
   uint32_t skinny_epoch = 0;  // number of the last decode-kernel launch that used the workspace
   int forced_group_m = 0; // 0: the default raster group (row blocks walked together); else that many
   int skinny_split = -1;  // -1: by shape; 0: whole weight tiles only; 1: split leftover tiles between SMs
+  int tile_split = -1;    // tcgen05 kernels, the same three choices for the last wave's tiles
+  void *split_scratch = nullptr;  // their partial accumulators and flag words
+  size_t split_scratch_bytes = 0;
+  uint32_t split_epoch = 0;       // number of the last launch that used them
   // host-buffer calls: copy streams and events for the chunked pipeline
   cudaStream_t copy_in = nullptr, copy_out = nullptr;
   cudaEvent_t ev[2 * 16 + 2] = {};
@@ -136,6 +140,7 @@ extern "C" KAPYB_API kapyb_status kapyb_destroy(kapyb_handle h) {
   if (!h) return KAPYB_OK;
   cudaSetDevice(h->device);
   if (h->workspace) cudaFree(h->workspace);
+  if (h->split_scratch) cudaFree(h->split_scratch);
   if (h->status) cudaFree(h->status);
   if (h->push_ready) {
     cudaStreamDestroy(h->push);
@@ -178,10 +183,12 @@ extern "C" KAPYB_API kapyb_status kapyb_probe_read(kapyb_handle h, void *stream,
 // A dispatch choice in text form: "auto" | "1cta" | "2cta" | "skinny" | "simt",
 // optionally followed by ":<tile width>" and options ":e<epilogue warps>",
 // ":s<stages>" and ":k<0|1>" (skinny: whole tiles only | split leftover tiles),
-// ":g<n>" (tcgen05: row blocks per raster group),
+// ":g<n>" (tcgen05: row blocks per raster group), ":x<0|1>" (tcgen05: the tiles of a
+// partly filled last wave stay whole | are split between the CTAs),
 // ":d<debug bits>", ":w<wait limit, ms>".
 struct PathChoice {
   int path = PATH_AUTO, bn = 0, epi = 0, skinny_stages = 0, skinny_split = -1, debug = 0, group_m = 0;
+  int tile_split = -1;
   uint32_t wait_limit_us = 0;
 };
 
@@ -221,6 +228,7 @@ static bool parse_path(const std::string &text, PathChoice &c, const char **why)
   c.skinny_stages = std::max(0, option(":s", colon));
   c.skinny_split = option(":k", colon);
   c.group_m = std::max(0, option(":g", colon));
+  c.tile_split = option(":x", colon);
   const int w = option(":w", colon);
   c.wait_limit_us = w > 0 ? 1000u * static_cast<uint32_t>(w) : 0u;
   return true;
@@ -242,6 +250,7 @@ extern "C" KAPYB_API kapyb_status kapyb_set_matmul_path(kapyb_handle h, const ch
   h->skinny_stages = c.skinny_stages;
   h->skinny_split = c.skinny_split;
   h->forced_group_m = c.group_m;
+  h->tile_split = c.tile_split;
   h->debug = c.debug;
   h->wait_limit_us = c.wait_limit_us;
   return KAPYB_OK;
@@ -549,7 +558,106 @@ static kapyb_status launch_simt(kapyb_handle h, const MatmulProblem &p, cudaStre
   return KAPYB_OK;
 }
 
-template <int BN, int CTAS, int EPI, bool REDUCE = false>
+// The last wave of a tcgen05 launch: `leftover` tiles for `units` CTAs (pairs).
+// Split between all of them (each takes one contiguous span of the tiles' K
+// blocks), the wave takes leftover / units of a tile's time plus the hand-over of
+// the partial sums, instead of a whole tile's time on part of the GPU.
+struct TileSplit {
+  bool on = false;
+  int first_tile = 0;   // tiles below are dealt whole
+  int k_blocks = 0;     // K blocks of the split tiles, all together
+};
+constexpr int kSplitMinSpan = 8;  // K blocks per CTA below which a split is not worth its hand-over
+
+// the instantiations the split variant of the kernel is built for
+constexpr bool split_built(int bn, int ctas, int epi) {
+  return ctas == 2 ? (bn == 512 || epi == 4) : (bn == 256);
+}
+
+static TileSplit tile_split_of(int forced, long long tiles, int num_kb, int units, int bn, int ctas,
+                               int epi) {
+  TileSplit s;
+  const int leftover = static_cast<int>(tiles % units);
+  const long long blocks = static_cast<long long>(leftover) * num_kb;
+  if (forced == 0 || leftover == 0 || !split_built(bn, ctas, epi) || blocks < units ||
+      blocks > 0x3fffffff)
+    return s;
+  // by shape: a wave that is at least 90 % full stays whole
+  if (forced < 0 && (leftover * 10 > units * 9 || blocks / units < kSplitMinSpan)) return s;
+  s.on = true;
+  s.first_tile = static_cast<int>(tiles - leftover);
+  s.k_blocks = static_cast<int>(blocks);
+  return s;
+}
+
+constexpr size_t kSplitFlagBytes = 65536;  // 8 words per CTA, up to 2048 CTAs
+
+static kapyb_status reserve_split_scratch(kapyb_handle h, size_t bytes) {
+  if (bytes <= h->split_scratch_bytes) return KAPYB_OK;
+  CUDA_TRY(h, cudaDeviceSynchronize());
+  if (h->split_scratch) {
+    cudaFree(h->split_scratch);
+    h->split_scratch = nullptr;
+    h->split_scratch_bytes = 0;
+  }
+  CUDA_TRY(h, cudaMalloc(&h->split_scratch, bytes));
+  // flag words carry launch numbers; zero is the one number no launch uses
+  CUDA_TRY(h, cudaMemset(h->split_scratch, 0, kSplitFlagBytes));
+  h->split_scratch_bytes = bytes;
+  return KAPYB_OK;
+}
+
+template <int BN, int CTAS, int EPI>
+static void tcgen05_launch_config(cudaLaunchConfig_t &cfg, cudaLaunchAttribute (&attr)[2],
+                                  cudaStream_t stream) {
+  using Cfg = GemmCfg<BN, CTAS, EPI>;
+  cfg.blockDim = dim3(Cfg::THREADS, 1, 1);
+  cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+  cfg.stream = stream;
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = CTAS;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  // the kernel's set-up may overlap the tail of the kernel ahead of it in the
+  // stream; it waits (griddepcontrol.wait) before it touches global memory
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 2;
+}
+
+// CTAs (pairs) of this instantiation the device holds at once.  The tile loop is
+// statically strided, so every CTA (pair) of the grid must be resident: a pair
+// that only starts when another retires would run its whole share afterwards.
+// Pairs need two free SMs in one GPC, which can be fewer than sm_count / 2.
+template <int BN, int CTAS, int EPI, bool REDUCE, bool SK, int DRAIN>
+static kapyb_status tcgen05_resident(kapyb_handle h, int &resident) {
+  using Cfg = GemmCfg<BN, CTAS, EPI>;
+  auto kern = gemm_tcgen05_kernel<BN, CTAS, EPI, REDUCE, SK, DRAIN>;
+  static int cached[kMaxDevices] = {};
+  if (cached[h->device] == 0) {
+    CUDA_TRY(h, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     Cfg::SMEM_BYTES));
+    int n = h->sm_count / CTAS;
+    if (CTAS == 2) {
+      cudaLaunchConfig_t cfg = {};
+      cudaLaunchAttribute attr[2];
+      tcgen05_launch_config<BN, CTAS, EPI>(cfg, attr, nullptr);
+      cfg.gridDim = dim3(h->sm_count / CTAS * CTAS, 1, 1);
+      int clusters = 0;
+      CUDA_TRY(h, cudaOccupancyMaxActiveClusters(&clusters, kern, &cfg));
+      n = std::min(n, std::max(1, clusters));
+    }
+    cached[h->device] = std::max(1, n);
+  }
+  resident = cached[h->device];
+  return KAPYB_OK;
+}
+
+// DRAIN: the 16-bit output type the register-drain epilogue of the 512-wide tile is
+// compiled for (1 bf16, 2 f16); other outputs of that tile, and every other tile,
+// go chunk by chunk whatever it says.
+template <int BN, int CTAS, int EPI, bool REDUCE = false, bool SK = false, int DRAIN = 1>
 static kapyb_status launch_tcgen05(kapyb_handle h, const MatmulProblem &p, bool a_mn, bool b_mn,
                                    void *const *outs, int n_out, cudaStream_t stream,
                                    float *red = nullptr, int red_axis = 1) {
@@ -557,6 +665,23 @@ static kapyb_status launch_tcgen05(kapyb_handle h, const MatmulProblem &p, bool 
   CUtensorMap tmA, tmB;
   TmapArray tmC;
   kapyb_status st;
+  if constexpr (BN == 512 && EPI == 8 && DRAIN == 1) {
+    if (p.out_dtype == KAPYB_F16)
+      return launch_tcgen05<BN, CTAS, EPI, REDUCE, SK, 2>(h, p, a_mn, b_mn, outs, n_out, stream, red,
+                                                         red_axis);
+  }
+  if constexpr (!SK && !REDUCE && split_built(BN, CTAS, EPI)) {
+    // the same kernel with the last wave's tiles split between the CTAs, when that pays
+    int resident = 0;
+    st = tcgen05_resident<BN, CTAS, EPI, false, true, DRAIN>(h, resident);
+    if (st != KAPYB_OK) return st;
+    const long long tiles = static_cast<long long>((p.M + Cfg::TILE_M - 1) / Cfg::TILE_M) *
+                            ((p.N + BN - 1) / BN) * p.batch;
+    const int num_kb = (p.K + 128 / static_cast<int>(dtype_size(p.in_dtype)) - 1) /
+                       (128 / static_cast<int>(dtype_size(p.in_dtype)));
+    if (tile_split_of(h->tile_split, tiles, num_kb, resident, BN, CTAS, EPI).on)
+      return launch_tcgen05<BN, CTAS, EPI, false, true, DRAIN>(h, p, a_mn, b_mn, outs, n_out, stream);
+  }
   // A shared-memory row is 128 bytes: `ce` elements of the operand type.
   // A: K-major -> inner K, rows M, box {ce, 128}; MN-major -> inner M, rows K, box {ce, ce}.
   const uint32_t ce = 128 / dtype_size(p.in_dtype);
@@ -624,48 +749,40 @@ static kapyb_status launch_tcgen05(kapyb_handle h, const MatmulProblem &p, bool 
   gp.b_l2 = p.b_l2;
   gp.c_l2 = p.c_l2;
 
-  auto kern = gemm_tcgen05_kernel<BN, CTAS, EPI, REDUCE>;
-  static bool attr_set[kMaxDevices] = {};
-  if (!attr_set[h->device]) {
-    CUDA_TRY(h, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     Cfg::SMEM_BYTES));
-    attr_set[h->device] = true;
-  }
+  gp.sk_first_tile = gp.num_tiles;
+  gp.sk_total = 0;
+  gp.sk_scratch = nullptr;
+  gp.sk_flags = nullptr;
+  gp.sk_epoch = 0;
+
+  int resident = 0;
+  st = tcgen05_resident<BN, CTAS, EPI, REDUCE, SK, DRAIN>(h, resident);
+  if (st != KAPYB_OK) return st;
+  auto kern = gemm_tcgen05_kernel<BN, CTAS, EPI, REDUCE, SK, DRAIN>;
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(h->sm_count / CTAS * CTAS, 1, 1);
-  cfg.blockDim = dim3(Cfg::THREADS, 1, 1);
-  cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
-  cfg.stream = stream;
   cudaLaunchAttribute attr[2];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = CTAS;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  // the kernel's set-up may overlap the tail of the kernel ahead of it in the
-  // stream; it waits (griddepcontrol.wait) before it touches global memory
-  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[1].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 2;
-  // The tile loop is statically strided, so every CTA (pair) of the grid must be
-  // resident at once: a pair that only starts when another retires would run its
-  // whole share afterwards.  Pairs need two free SMs in one GPC, which can be
-  // fewer than sm_count / 2.
-  int resident = h->sm_count / CTAS;
-  if (CTAS == 2) {
-    static int max_clusters[kMaxDevices] = {};
-    if (max_clusters[h->device] == 0) {
-      int n = 0;
-      CUDA_TRY(h, cudaOccupancyMaxActiveClusters(&n, kern, &cfg));
-      max_clusters[h->device] = std::max(1, n);
-    }
-    resident = std::min(resident, max_clusters[h->device]);
+  tcgen05_launch_config<BN, CTAS, EPI>(cfg, attr, stream);
+  int units = std::min(gp.num_tiles, resident);
+  if constexpr (SK) {
+    const TileSplit ts = tile_split_of(h->tile_split, gp.num_tiles, gp.num_kb, resident, BN, CTAS, EPI);
+    units = resident;
+    const size_t slot_bytes = static_cast<size_t>(CTAS) * 128 * BN * sizeof(float);
+    st = reserve_split_scratch(h, kSplitFlagBytes + static_cast<size_t>(units) * slot_bytes);
+    if (st != KAPYB_OK) return st;
+    if (static_cast<size_t>(units) * CTAS * 8 * sizeof(uint32_t) > kSplitFlagBytes)
+      return fail(h, KAPYB_UNSUPPORTED, "matmul: more CTAs than the split tiles' flag words cover");
+    gp.sk_first_tile = ts.first_tile;
+    gp.sk_total = ts.k_blocks;
+    gp.sk_flags = static_cast<uint32_t *>(h->split_scratch);
+    gp.sk_scratch = reinterpret_cast<float *>(static_cast<char *>(h->split_scratch) + kSplitFlagBytes);
+    if (++h->split_epoch == 0) h->split_epoch = 1;
+    gp.sk_epoch = h->split_epoch;
   }
-  const int units = std::min(gp.num_tiles, resident);
   cfg.gridDim = dim3(units * CTAS, 1, 1);
   CUDA_TRY(h, cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmC, gp));
   h->launches++;
-  h->last_kernel = CTAS == 2 ? "tcgen05_2cta" : "tcgen05_1cta";
+  h->last_kernel = CTAS == 2 ? (SK ? "tcgen05_2cta_split" : "tcgen05_2cta")
+                             : (SK ? "tcgen05_1cta_split" : "tcgen05_1cta");
   return KAPYB_OK;
 }
 
@@ -1135,6 +1252,14 @@ extern "C" KAPYB_API kapyb_status kapyb_matmul_plan(kapyb_handle h, int32_t sm_c
     add("grid: %d x %d x %d = %lld tile(s) on %d %s: %lld wave(s), %.0f %% of their slots used\n",
         tiles_m, tiles_n, p.batch, tiles, units, ctas == 2 ? "CTA pairs" : "CTAs", waves,
         100.0 * static_cast<double>(tiles) / static_cast<double>(waves * units));
+    const int num_kb = (p.K + 128 / static_cast<int>(dtype_size(p.in_dtype)) - 1) /
+                       (128 / static_cast<int>(dtype_size(p.in_dtype)));
+    const TileSplit ts = tile_split_of(h ? h->tile_split : -1, tiles, num_kb, units, plan.bn, ctas, plan.epi);
+    if (ts.on)
+      add("last wave: %lld tile(s) x %d k-blocks split between the %d %s in spans of %d-%d k-blocks "
+          "(partial sums added in CTA order)\n",
+          tiles - ts.first_tile, num_kb, units, ctas == 2 ? "CTA pairs" : "CTAs", ts.k_blocks / units,
+          (ts.k_blocks + units - 1) / units);
     add("lanes: accumulator row r of a tile -> CTA r / 128 of the %s, TMEM lane r %% 128; "
         "column c -> TMEM column c%s\n",
         ctas == 2 ? "pair" : "tile (always 0)", plan.bn == 512 ? "" : " + slot * tile width");

@@ -63,7 +63,7 @@ def test_row_major_bf16(handle, ko, path, shape):
         A, B = normal((M, K), 1, K ** -0.5), normal((K, N), 2)
         out = handle.matmul(A.cuda(), B.cuda())
         handle.check()
-        assert handle.last_kernel == ("simt" if path == "simt" else "tcgen05_1cta")
+        assert handle.last_kernel.startswith("simt" if path == "simt" else "tcgen05_1cta")
         check(ko, out, A, B)
     finally:
         handle.set_matmul_path("auto")
@@ -179,7 +179,7 @@ def test_reduce_fused_into_the_epilogue(handle, ko, pkg, axis, shape):
     ep = dict(alpha=0.75, bias=bias.cuda(), activation=pkg.abi.ACT_RELU)
     out, red = handle.matmul_reduce(A.cuda(), B.cuda(), axis, **ep)
     handle.check()
-    assert handle.last_kernel == "tcgen05_1cta"
+    assert handle.last_kernel.startswith("tcgen05_1cta")
     assert red.shape == ((1, N) if axis == 0 else (M, 1)) and red.dtype == torch.float32
     ref = ko.matmul_f64(bits(A), 1, bits(B), 1, alpha=0.75, bias=bits(bias), bias_dtype=1,
                         activation=pkg.abi.ACT_RELU)

@@ -89,7 +89,7 @@ def test_cta_pair_kernel(handle, ko, shape, bn, layout):
     try:
         out = handle.matmul(A.cuda(), Bd, bias=bias.cuda())
         handle.check()
-        assert handle.last_kernel == "tcgen05_2cta"
+        assert handle.last_kernel in ("tcgen05_2cta", "tcgen05_2cta_split")
     finally:
         handle.set_matmul_path("auto")
     check(ko, out, A, B, bias=bias)
@@ -147,7 +147,7 @@ def test_wide_pair_tile_epilogues(handle, ko, variant):
     try:
         out = handle.matmul(A.cuda(), B.cuda(), out_dtype=out_dtype, **kw)
         handle.check()
-        assert handle.last_kernel == "tcgen05_2cta"
+        assert handle.last_kernel in ("tcgen05_2cta", "tcgen05_2cta_split")
     finally:
         handle.set_matmul_path("auto")
     check(ko, out, A, B, **okw)
@@ -170,7 +170,7 @@ def test_tune_then_dispatch_from_the_table(handle, ko, pkg, tmp_path):
         assert "tile: 128 x 64" in pkg.matmul_plan(M, N, K, handle=handle)
         out = handle.matmul(A, B)
         handle.check()
-        assert handle.last_kernel == "tcgen05_1cta"
+        assert handle.last_kernel in ("tcgen05_1cta", "tcgen05_1cta_split")
         check(ko, out, A.cpu(), B.cpu())
         ref = handle.matmul(A, B[:, :1024].contiguous())   # another problem: heuristics again
         handle.check()
