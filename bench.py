@@ -848,6 +848,27 @@ def run_profile_case(args):
         W = (torch.randn(8192, 14336, generator=g) * 0.02).to(torch.bfloat16).cuda()
         o = torch.empty((16, 14336), dtype=torch.bfloat16, device="cuda")
         fn = lambda: h.matmul(X, W, out=o)
+    elif case == "raster":
+        # 8192 x 8192 x 2048 + bias, one launch per raster group size and per set of
+        # eviction priorities: DRAM bytes by setting (see profiles/)
+        M, N, K = 8192, 8192, 2048
+        A = (torch.randn(M, K, device="cuda") * K ** -0.5).bfloat16()
+        B = torch.randn(K, N, device="cuda").bfloat16()
+        bias = torch.randn(N, device="cuda").bfloat16()
+        out = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
+        abi = pkg.abi
+        L, F = abi.EVICT_LAST, abi.EVICT_FIRST
+        settings = [("auto:g%d" % g, (0, 0, 0)) for g in (1, 2, 4, 8, 12, 16, 32)]
+        settings += [("auto", tuple(abi.cache_hints(0, x) for x in combo))
+                     for combo in ((L, F, F), (L, 0, 0), (0, 0, F), (L, L, F), (F, F, F))]
+        for path, cache in settings:
+            h.set_matmul_path(path)
+            h.matmul(A, B, out=out, bias=bias, cache=cache)
+            torch.cuda.synchronize()
+        h.set_matmul_path("auto")
+        print(json.dumps({"profile_case": case, "kernel": h.last_kernel, "launches": h.launch_count}))
+        h.check()
+        return
     elif case == "batched":
         Q = torch.randn(32, 2048, 128, generator=g).to(torch.bfloat16).cuda()
         Kt = torch.randn(32, 128, 2048, generator=g).to(torch.bfloat16).cuda()
@@ -873,7 +894,7 @@ def main():
     ap.add_argument("--sharded", action="store_true",
                     help="run the sharded decode / batched configurations at one GPU too")
     ap.add_argument("--profile-case", default="",
-                    help="gemm|gelu|rowsum|decode|batched: a small case for a profiler capture")
+                    help="gemm|gelu|rowsum|decode|batched|raster: a small case for a profiler capture")
     args = ap.parse_args()
     if args.profile_case:
         run_profile_case(args)

@@ -548,13 +548,21 @@ KAPYB_API int64_t kapyb_launch_count(kapyb_handle h);
  * start, first operand stage landed, last MMA issued, epilogue done.  GEMM only
  * (zero unless the library was built with -DKAPYB_DEBUG_SWITCHES):
  * words 7..11 = clocks one epilogue warp of the first CTA spent per phase of its
- * chunk loop; words 12, 13 = clocks the first CTA's MMA warp waited for operand
+ * chunk loop (for the register drain of the 256 x 512 tile: timer at which it saw
+ * half 0, clocks in tcgen05.ld, clocks from there to handing half 1 back, clocks
+ * in the two hand-overs, clocks issuing the first store); words 12, 13 = clocks the first CTA's MMA warp waited for operand
  * stages and for accumulator slots. */
 KAPYB_API kapyb_status kapyb_probe_read(kapyb_handle h, void *stream, uint32_t *words, int32_t n);
 
 /* Forces a kernel family for matmul ("auto", "1cta", "2cta", "skinny", "simt"),
- * optionally ":<tile width>", ":e<epilogue warps>", ":s<stages>", ":w<wait limit
- * in ms>" and ":d<debug bits>"; for tests and profiling.  Debug bit 16 silences
+ * optionally ":<tile width>", ":e<epilogue warps>", ":s<stages>", ":k<0|1>"
+ * (decode kernel: whole weight tiles only | leftover tiles split between SMs),
+ * ":g<row blocks per raster group>", ":x<0|1>" (tcgen05 kernels: the tiles of a
+ * partly filled last wave stay whole, the default | are split between the CTAs,
+ * their partial sums added in CTA order: the same bits on every run, though not
+ * the bits of the whole-tile schedule; the first such call allocates 40 MB of
+ * scratch, so make it before any stream capture), ":w<wait limit in ms>" and
+ * ":d<debug bits>"; for tests and profiling.  Debug bit 16 silences
  * the producer (every bounded wait then runs out: the test of the time-out
  * path) and bit 128 switches the probes on; both leave correct kernels
  * correct.  The bits that make a kernel skip work (1, 2, 4, 8, 32) are refused

@@ -170,6 +170,13 @@ struct WorkIter {
       lin_end = sk_span_begin(p, unit + 1, units);
     }
   }
+  // after next() returned true: whether that item is this CTA's last
+  __device__ __forceinline__ bool last(const GemmParams &p) const {
+    if constexpr (!SK)
+      return next_tile >= p.num_tiles;
+    else
+      return next_tile >= p.sk_first_tile && lin >= lin_end;
+  }
   __device__ __forceinline__ bool next(const GemmParams &p) {
     if constexpr (!SK) {
       tile = next_tile;
@@ -293,6 +300,22 @@ __device__ __forceinline__ void add_bias32(float (&f)[32], const uint4 *bp) {
   }
 }
 
+// The same from four 128-bit words already in registers.
+template <int DT>
+__device__ __forceinline__ void add_bias32_regs(float (&f)[32], const uint4 (&b)[4]) {
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const uint32_t ws[4] = {b[j].x, b[j].y, b[j].z, b[j].w};
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      float lo, hi;
+      unpack2_16<DT>(ws[t], lo, hi);
+      f[8 * j + 2 * t] += lo;
+      f[8 * j + 2 * t + 1] += hi;
+    }
+  }
+}
+
 // What one epilogue warp needs to drain its share of one accumulator tile.
 struct EpiTile {
   int b, m0, n0, row, lane, cpart;
@@ -310,9 +333,11 @@ struct EpiTile {
 // The fused arithmetic on 32 consecutive accumulator columns of one row
 // (columns col0 .. col0+31 of row t.row): scale, bias, addend, activation.
 // LEVEL 0: scale only; 1: scale and bias; 2: scale, bias, addend, activation.
+// `pre`: the 32 column-bias values (16-bit, as fetched ahead of the accumulator
+// wait), or nullptr to fetch them here.
 template <int LEVEL, bool REDUCE = false>
 __device__ __forceinline__ void finish32(const GemmParams &p, const EpiTile &t, float (&f)[32],
-                                         int col0) {
+                                         int col0, const uint4 (*pre)[4] = nullptr) {
   const int lane = t.lane;
   if (p.ep.alpha != 1.0f) {
 #pragma unroll
@@ -320,7 +345,12 @@ __device__ __forceinline__ void finish32(const GemmParams &p, const EpiTile &t, 
   }
   if constexpr (LEVEL >= 1) {
     if (t.bias_col) {
-      if (t.bias_fast && col0 + 32 <= p.N) {
+      if (pre != nullptr) {
+        if (p.ep.bias_dtype == KAPYB_BF16)
+          add_bias32_regs<KAPYB_BF16>(f, *pre);
+        else
+          add_bias32_regs<KAPYB_F16>(f, *pre);
+      } else if (t.bias_fast && col0 + 32 <= p.N) {
         const uint4 *bp =
             reinterpret_cast<const uint4 *>(static_cast<const uint16_t *>(p.ep.bias) + col0);
         if (p.ep.bias_dtype == KAPYB_BF16)
@@ -414,6 +444,19 @@ __device__ __forceinline__ bool epilogue_tile(const GemmParams &p, const TmapArr
     const int nc = t.n0 + c * CW;
     if (nc >= p.N) break;
     uint8_t *sbuf = t.stg + (C_BUFS == 2 ? buf : 0) * 4096;
+    // A 16-bit column bias is fetched first: its latency hides behind the
+    // accumulator loads and the wait for the staging buffer.  (Only where the
+    // registers are there: 192-thread CTAs; with eight epilogue warps a thread has
+    // 168 and the extra 32 spilled.)
+    const bool bias_ahead = EPI == 4 && !PLAIN && t.bias_col && t.bias_fast && nc + CW <= p.N;
+    uint4 braw[EPI == 4 ? NH : 1][4];
+    if (bias_ahead) {
+      const uint4 *bp = reinterpret_cast<const uint4 *>(static_cast<const uint16_t *>(p.ep.bias) + nc);
+#pragma unroll
+      for (int h = 0; h < NH; ++h)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) braw[h][j] = __ldg(bp + h * 4 + j);
+    }
     // All loads of the chunk are in flight before the one wait.
     uint32_t v[NH][32];
     const bool probing = kEpilogueProbes && t.prof != nullptr;
@@ -448,7 +491,7 @@ __device__ __forceinline__ bool epilogue_tile(const GemmParams &p, const TmapArr
       float f[32];
 #pragma unroll
       for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(v[h][i]);
-      finish32<PLAIN ? 0 : 2, REDUCE>(p, t, f, col0);
+      finish32<PLAIN ? 0 : 2, REDUCE>(p, t, f, col0, bias_ahead ? &braw[EPI == 4 ? h : 0] : nullptr);
       // Row `lane` of the staging tile, 128-byte swizzle: 16-byte chunk j of row
       // r lives at chunk position j ^ (r & 7).
       if constexpr (OUTK == 0) stage_half_f32(srow, f, lane);
@@ -501,7 +544,8 @@ __device__ __forceinline__ bool epilogue_tile(const GemmParams &p, const TmapArr
 template <int EPI, int MODE>
 __device__ __forceinline__ bool epilogue_two_halves(const GemmParams &p, const TmapArray &tmC,
                                                  EpiTile &t, uint32_t tfull0, uint32_t parity,
-                                                 volatile uint32_t *abort_flag, bool active) {
+                                                 volatile uint32_t *abort_flag, bool active,
+                                                 uint8_t *spare) {
   static_assert(EPI == 8, "register drain: eight epilogue warps");
   static_assert(MODE == 1 || MODE == 2, "bf16 or f16");
   constexpr bool bf16 = MODE == 1;
@@ -510,20 +554,23 @@ __device__ __forceinline__ bool epilogue_two_halves(const GemmParams &p, const T
   // Chunk i = hh*2 + j covers tile columns (hh*4 + cpart + 2*j) * 64 ..  Chunk 0
   // goes straight through the (idle) staging buffer; 1..3 wait in registers.
   uint32_t pk[3][2][16];
+  // lane 0, after the staged bytes were fenced towards the async proxy
+  auto issue_store = [&](const uint8_t *src, int nc) {
+    if (debug_on<8>(p.debug)) return;
+    if (p.c_l2) {
+      const uint64_t pol = ptx::make_l2_policy(p.c_l2);
+      for (int o = 0; o < p.n_out; ++o)
+        ptx::tma_store_3d_hint(&tmC.m[o], ptx::smem_u32(src), p.out_col_offset + nc, t.m0, t.b, pol);
+    } else {
+      for (int o = 0; o < p.n_out; ++o)
+        ptx::tma_store_3d(&tmC.m[o], ptx::smem_u32(src), p.out_col_offset + nc, t.m0, t.b);
+    }
+    ptx::tma_store_commit();
+  };
   auto store_chunk = [&](int nc) {
     ptx::fence_proxy_async_smem();
     __syncwarp();
-    if (lane == 0 && !debug_on<8>(p.debug)) {
-      if (p.c_l2) {
-        const uint64_t pol = ptx::make_l2_policy(p.c_l2);
-        for (int o = 0; o < p.n_out; ++o)
-          ptx::tma_store_3d_hint(&tmC.m[o], ptx::smem_u32(t.stg), p.out_col_offset + nc, t.m0, t.b, pol);
-      } else {
-        for (int o = 0; o < p.n_out; ++o)
-          ptx::tma_store_3d(&tmC.m[o], ptx::smem_u32(t.stg), p.out_col_offset + nc, t.m0, t.b);
-      }
-      ptx::tma_store_commit();
-    }
+    if (lane == 0) issue_store(t.stg, nc);
   };
   // A 16-bit column bias is fetched before the accumulator is awaited, so its
   // latency hides behind the main loop: lane l keeps the eight values of columns
@@ -656,6 +703,30 @@ __device__ __forceinline__ bool epilogue_two_halves(const GemmParams &p, const T
       store_chunk(t.n0 + t.cpart * 64);
       if (kEpilogueProbes && t.prof) st_clocks += static_cast<uint32_t>(clock()) - k0;
     }
+  }
+  if (spare != nullptr) {
+    // The CTA's last tile: every MMA has read its operands (half 1 was published
+    // after the last of them), so the operand ring is free.  The three chunks go
+    // through 4 KB of it each and leave together instead of taking turns in the one
+    // staging buffer, each waiting for the store before it to have read that.
+    if (alive && active) {
+#pragma unroll
+      for (int i = 1; i < 4; ++i) {
+        uint8_t *row = spare + (i - 1) * 4096 + lane * 128;
+        stage_packed16(row, pk[i - 1][0], lane, 0);
+        stage_packed16(row, pk[i - 1][1], lane, 1);
+      }
+      ptx::fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+#pragma unroll
+        for (int i = 1; i < 4; ++i) {
+          const int nc = t.n0 + ((i >> 1) * 4 + t.cpart + 2 * (i & 1)) * 64;
+          if (nc < p.N) issue_store(spare + (i - 1) * 4096, nc);
+        }
+      }
+    }
+    return alive;
   }
 #pragma unroll
   for (int i = 1; i < 4; ++i) {
@@ -1148,14 +1219,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
                 ptx::tmem_ld_32x32(t_row + static_cast<uint32_t>(c32 * 32), v);
                 ptx::tmem_ld_wait();
                 float4 *dst = reinterpret_cast<float4 *>(mine + (c32 * 4 + q) * 1024) + lane;
-#ifndef SK_NO_DUMP_STORES
 #pragma unroll
                 for (int j = 0; j < 8; ++j)
                   __stcg(dst + j * 32, make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
                                                    __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3])));
-#else
-                (void)dst;
-#endif
               }
             }
             ptx::tc_fence_before();
@@ -1229,11 +1296,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
               const float4 *src = reinterpret_cast<const float4 *>(theirs + (c32 * 4 + q) * 1024) + lane;
               float4 add[8];
 #pragma unroll
-#ifndef SK_NO_FIXUP_LOADS
               for (int j = 0; j < 8; ++j) add[j] = __ldcg(src + j * 32);
-#else
-              for (int j = 0; j < 8; ++j) add[j] = make_float4(0.f, 0.f, 0.f, float(reinterpret_cast<uintptr_t>(src) & 1));
-#endif
               uint32_t v[32];
               ptx::tmem_ld_32x32(t_row + static_cast<uint32_t>(c32 * 32), v);
               ptx::tmem_ld_wait();
@@ -1276,7 +1339,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
             et.bias_row = load_as_f32(p.ep.bias, p.ep.bias_dtype, row);
           const bool active = m0 < p.M && !debug_on<4>(p.debug);
           const uint32_t tf0 = ptx::smem_u32(&tfull_bar[0]);
-          alive = epilogue_two_halves<EPI, DRAIN>(p, tmC, et, tf0, acc_phase, abort_flag, active);
+          // 12 KB of the operand ring per warp, once the CTA's last tile has let go of it
+          static_assert(Cfg::STAGES * Cfg::STAGE_BYTES >= EPI * 12288, "operand ring too small");
+          uint8_t *spare = w.last(p) ? smem + e * 12288 : nullptr;
+          alive = epilogue_two_halves<EPI, DRAIN>(p, tmC, et, tf0, acc_phase, abort_flag, active, spare);
           if (!alive) break;
           acc_phase ^= 1u;
           continue;

@@ -560,14 +560,21 @@ static kapyb_status launch_simt(kapyb_handle h, const MatmulProblem &p, cudaStre
 
 // The last wave of a tcgen05 launch: `leftover` tiles for `units` CTAs (pairs).
 // Split between all of them (each takes one contiguous span of the tiles' K
-// blocks), the wave takes leftover / units of a tile's time plus the hand-over of
-// the partial sums, instead of a whole tile's time on part of the GPU.
+// blocks), every SM works to the end instead of a part of them for a whole
+// tile's time.  Measured on the column shards of the 8192^3 problem (34, 54 and
+// 64 tiles of 256 x 512 left for 74 pairs) this does NOT pay on a B200: the part
+// runs at its power cap, so SMs that sit out the last wave hand their share of
+// the power to the rest as clock, and the split adds traffic (a 512 KB partial
+// accumulator per tile through L2, read back on the critical path) and scatters
+// the tiles' K offsets, which costs operand reuse in L2: 8192 x 1024 x 8192 took
+// 110 us split against 97 us whole, and 96.6 us with the partial sums' traffic
+// compiled out.  So the split runs only when asked for (":x1"); the default
+// keeps whole tiles.
 struct TileSplit {
   bool on = false;
   int first_tile = 0;   // tiles below are dealt whole
   int k_blocks = 0;     // K blocks of the split tiles, all together
 };
-constexpr int kSplitMinSpan = 8;  // K blocks per CTA below which a split is not worth its hand-over
 
 // the instantiations the split variant of the kernel is built for
 constexpr bool split_built(int bn, int ctas, int epi) {
@@ -582,8 +589,7 @@ static TileSplit tile_split_of(int forced, long long tiles, int num_kb, int unit
   if (forced == 0 || leftover == 0 || !split_built(bn, ctas, epi) || blocks < units ||
       blocks > 0x3fffffff)
     return s;
-  // by shape: a wave that is at least 90 % full stays whole
-  if (forced < 0 && (leftover * 10 > units * 9 || blocks / units < kSplitMinSpan)) return s;
+  if (forced < 0) return s;  // not by default: see above
   s.on = true;
   s.first_tile = static_cast<int>(tiles - leftover);
   s.k_blocks = static_cast<int>(blocks);

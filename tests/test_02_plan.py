@@ -102,14 +102,10 @@ def test_few_row_problems_spread_over_the_sms(pkg):
     assert "tile: 128 x 256" in plan(pkg, 8192, 8192, 64)        # many waves: the widest single-CTA tile
 
 
-def test_partly_filled_last_wave_is_split(pkg):
+def test_partly_filled_last_wave_stays_whole_unless_asked(pkg):
     """The column shards of the 8192^3 problem on 2, 4 and 8 GPUs leave 34, 54 and
-    64 tiles of 256 x 512 for 74 CTA pairs in their last wave: those tiles' K
-    blocks are dealt out evenly.  8192^3 itself ends on 68 of 74: left whole."""
-    assert "last wave: 64 tile(s) x 128 k-blocks split between the 74 CTA pairs in spans of 110-111" in \
-        plan(pkg, 8192, 1024, 8192)
-    assert "last wave: 54 tile(s)" in plan(pkg, 8192, 2048, 8192)
-    assert "last wave: 34 tile(s)" in plan(pkg, 8192, 4096, 8192)
-    assert "last wave" not in plan(pkg, 8192, 8192, 8192)
-    # spans of fewer than eight K blocks are not worth the hand-over
-    assert "last wave" not in plan(pkg, 2048, 2048, 256)
+    64 tiles of 256 x 512 for 74 CTA pairs in their last wave.  Splitting those
+    tiles' K blocks between all pairs was measured slower on a power-capped part,
+    so the plan keeps whole tiles; the split is there on request."""
+    for n in (1024, 2048, 4096, 8192):
+        assert "last wave" not in plan(pkg, 8192, n, 8192)
