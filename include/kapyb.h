@@ -163,7 +163,10 @@ typedef struct {
                       map the priority to an L2 policy on their TMA loads:
                       EVICT_FIRST -> L2::evict_first, EVICT_LAST -> L2::evict_last,
                       NO_ALLOCATE -> L2::evict_first (a tile is never loaded
-                      around L2); other values leave the default.  The fused
+                      around L2); other values leave the default, which is no
+                      hint, except for the weight operand of the decode-shape
+                      kernel (M <= 64): read once per call, it streams as
+                      evict_first unless a priority is named.  The fused
                       streaming kernels and kapyb_reduce keep their own policy
                       (read-once loads that bypass L1, streaming stores). */
   int32_t reserved_; /* keeps the struct a multiple of 8 bytes; set to 0 */
