@@ -1516,9 +1516,11 @@ extern "C" KAPYB_API kapyb_status kapyb_matmul_host(kapyb_handle h, const kapyb_
     st = ensure_pipe(h);
     if (st != KAPYB_OK) return st;
     const int M = lhs->size0;
-    // what is left exposed at the end is one chunk's GEMM and download: 512-row
-    // chunks (a GEMM of 45 us at K = N = 8192 against 150 us of upload per chunk)
-    const int chunks = std::min(kMaxChunks, std::max(2, M / 512));
+    // 1024-row chunks: what is left exposed at the end is one chunk's GEMM and
+    // download; smaller chunks lose more in copy and event overhead than they save
+    // there (8192^3 bf16: 5.87 ms with 1024 rows, 6.05 with 512, 6.00 with 2048;
+    // the upload alone takes 4.92 ms)
+    const int chunks = std::min(kMaxChunks, std::max(2, M / 1024));
     const int rows_per = ((M + chunks - 1) / chunks + 255) / 256 * 256;
     cudaEvent_t ev_start = h->ev[2 * kMaxChunks], ev_done = h->ev[2 * kMaxChunks + 1];
     // B and the bias are already on their way on `stream`; A goes up chunk by chunk
@@ -1529,8 +1531,12 @@ extern "C" KAPYB_API kapyb_status kapyb_matmul_host(kapyb_handle h, const kapyb_
     const char *ha = static_cast<const char *>(elem_ptr(lhs));
     char *hc = static_cast<char *>(const_cast<void *>(elem_ptr(out)));
     int n_chunks = 0;
-    for (int r0 = 0; r0 < M; r0 += rows_per, ++n_chunks) {
-      const int rows = std::min(rows_per, M - r0);
+    for (int r0 = 0, rows = 0; r0 < M; r0 += rows, ++n_chunks) {
+      rows = std::min(rows_per, M - r0);
+      // a last chunk of a few rows would go to the decode kernel, whose sums run in
+      // another order than the tiles': it joins the chunk before it, so the result has
+      // the bits of the device-resident call
+      if (M - (r0 + rows) < 256) rows = M - r0;
       const size_t a_off = static_cast<size_t>(r0) * lhs->stride0 * esz_a;
       const size_t c_off = static_cast<size_t>(r0) * out->stride0 * esz_c;
       CUDA_TRY(h, cudaMemcpyAsync(da + a_off, ha + a_off,
