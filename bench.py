@@ -47,8 +47,8 @@ WORKLOAD = ("bf16 GEMM M=N=K=8192 row-major A/B, fp32 accumulate, bf16 out, "
 # here only (profiles/gemm_tcgen05_2cta_256x512_bf16_8192x8192x4096.txt has the
 # command).  The line carries the figure only while the dispatcher still picks
 # that kernel and tile for the benchmark problem.
-NCU_TRAFFIC = {"bytes": 869_267_456 + 153_600_512, "kernel": "tcgen05_2cta",
-               "tile": "256 x 512", "captured_on": "gemm_tcgen05_kernel<512,2,8,0>, 8192^3 bf16 + bias"}
+NCU_TRAFFIC = {"bytes": 877_727_744 + 148_817_664, "kernel": "tcgen05_2cta",
+               "tile": "256 x 512", "captured_on": "gemm_tcgen05_kernel<512,2,8,0,0,1>, 8192^3 bf16 + bias"}
 
 C4_M, C4_N, C4_K = 16, 28672, 8192
 C4_BYTES = C4_K * C4_N * 2 + C4_M * C4_K * 2 + C4_M * C4_N * 2
@@ -356,6 +356,39 @@ def secondary(torch, pkg, h, peaks, ko):
         "library_torch_mm_us": t_lib * 1e6,
         "cpu_baseline": {"value": 2.0 * 256 * 1024 * 1024 / tc / 1e12, "unit": "TFLOP/s",
                          "cores": cores, "kind": "port", "sample": "256 of the 1024 rows"}}
+    # The column shards of the headline problem (2 / 4 / 8 GPUs) and a one-wave cube,
+    # ours beside the library on the same buffers: bursts of launches, interleaved,
+    # with an idle pause between bursts (the rate depends on the part's temperature).
+    shapes = {}
+    for (m, n, k) in ((8192, 4096, 8192), (8192, 2048, 8192), (8192, 1024, 8192), (2048, 2048, 2048)):
+        As = (torch.randn(m, k, generator=g) * k ** -0.5).to(torch.bfloat16).cuda()
+        Bs = torch.randn(k, n, generator=g).to(torch.bfloat16).cuda()
+        bs = torch.randn(n, generator=g).to(torch.bfloat16).cuda()
+        Cs = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+        fns = {"ours": lambda: h.matmul(As, Bs, out=Cs, bias=bs),
+               "library": lambda: torch.addmm(bs, As, Bs, out=Cs)}
+        iters = max(5, min(50, int(2e-2 / (2.0 * m * n * k / 1.4e15))))
+        ts = {kk: [] for kk in fns}
+        for f in fns.values():
+            for _ in range(3):
+                f()
+        for _ in range(5):
+            for kk, f in fns.items():
+                s0, e0 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                s0.record()
+                for _ in range(iters):
+                    f()
+                e0.record()
+                e0.synchronize()
+                ts[kk].append(s0.elapsed_time(e0) * 1e-3 / iters)
+                torch.cuda._sleep(50_000_000)
+                torch.cuda.synchronize()
+        to, tl = statistics.median(ts["ours"]), statistics.median(ts["library"])
+        shapes[f"{m}x{n}x{k}"] = {"TFLOP/s": 2.0 * m * n * k / to / 1e12,
+                                  "library_torch_addmm_TFLOP/s": 2.0 * m * n * k / tl / 1e12,
+                                  "ours_over_library": tl / to, "us": to * 1e6, "kernel": h.last_kernel}
+        del As, Bs, bs, Cs
+    out["bf16_gemm_bias_other_shapes"] = shapes
     h.check()
     return out
 
