@@ -22,7 +22,9 @@
 //
 // 512-wide tiles (pairs only) hold two 256-column halves that fill TMEM; the MMA
 // role skews the halves at tile boundaries and the epilogue drains them through
-// registers (see epilogue_two_halves and the MMA role below).
+// registers (see epilogue_two_halves and the MMA role below).  The drain is
+// instruction-bound, so it is compiled per output type (the kernel's DRAIN
+// parameter), and a CTA's last tile stages its stores through the operand ring.
 //
 // CTAS == 2 pairs two CTAs of a cluster on one 256-row tile
 // (tcgen05.mma.cta_group::2): each CTA loads its own 128 rows of A and its own
@@ -768,6 +770,10 @@ __device__ __forceinline__ void issue_kblock(uint32_t d_tmem, uint32_t a_lo, uin
   }
 }
 
+// BN: tile width; CTAS: CTAs per tile (2 = a pair on a 256-row tile); EPI: epilogue
+// warps; REDUCE: kapy.reduce fused after the epilogue; SK: the K blocks of the last
+// wave's tiles are dealt out as spans (GemmParams::sk_*); DRAIN: the 16-bit output
+// type the register drain of the 512-wide tile is compiled for (1 bf16, 2 f16).
 template <int BN, int CTAS, int EPI, bool REDUCE = false, bool SK = false, int DRAIN = 1>
 __global__ void __launch_bounds__(64 + 32 * EPI, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,

@@ -1850,12 +1850,22 @@ extern "C" KAPYB_API kapyb_status kapyb_matmul_host_sharded(
     CUDA_TRY(h, cudaEventRecord(h->ev[2 * j + 1], stream));
     trace.mark("piece multiplied", stream, j);
     CUDA_TRY(h, cudaStreamWaitEvent(h->copy_out, h->ev[2 * j + 1], 0));
-    for (int r = 0; r < world; ++r) {
-      // staging rows of (rank r, piece j) -> rows r * R + j * P of the caller's output
-      const size_t src = (static_cast<size_t>(first) + static_cast<size_t>(r) * P) * out_row_bytes;
-      const size_t dst = (static_cast<size_t>(r) * R + static_cast<size_t>(j) * P) * out_row_bytes;
-      CUDA_TRY(h, cudaMemcpyAsync(hc + dst, dc + src, static_cast<size_t>(P) * out_row_bytes,
-                                  cudaMemcpyDeviceToHost, h->copy_out));
+    // staging rows of (rank r, piece j) -> rows r * R + j * P of the caller's output
+    if (out->stride0 == out->size1) {
+      // the P rows of a rank are one contiguous block on both sides: all ranks'
+      // blocks of the piece go home as one pitched copy (one block per "row")
+      // instead of `world` small ones
+      const size_t block = static_cast<size_t>(P) * out_row_bytes;
+      CUDA_TRY(h, cudaMemcpy2DAsync(hc + static_cast<size_t>(j) * block, static_cast<size_t>(R) * out_row_bytes,
+                                    dc + static_cast<size_t>(first) * out_row_bytes, block, block,
+                                    static_cast<size_t>(world), cudaMemcpyDeviceToHost, h->copy_out));
+    } else {
+      for (int r = 0; r < world; ++r) {
+        const size_t src = (static_cast<size_t>(first) + static_cast<size_t>(r) * P) * out_row_bytes;
+        const size_t dst = (static_cast<size_t>(r) * R + static_cast<size_t>(j) * P) * out_row_bytes;
+        CUDA_TRY(h, cudaMemcpyAsync(hc + dst, dc + src, static_cast<size_t>(P) * out_row_bytes,
+                                    cudaMemcpyDeviceToHost, h->copy_out));
+      }
     }
     trace.mark("piece downloaded", h->copy_out, j);
   }
