@@ -53,4 +53,35 @@ __global__ void gather_wait_kernel(const uint32_t *my_flags, int n_ranks, uint32
   __threadfence_system();
 }
 
+// Forwards `n16` 16-byte words from this GPU's memory to the same offset of up to
+// kMaxGatherRanks - 1 peers: read once, stored once per peer (plain stores through
+// peer-mapped pointers; nothing is loaded from a peer).  The copy engines, which
+// could do the same, are busy with the host traffic of the call this serves: seven
+// engine copies of 4 MB each took 0.42 ms per piece there, this kernel's NVLink
+// time is a tenth of that.
+struct ForwardPeers {
+  uint4 *dst[kMaxGatherRanks];
+  int n;
+};
+
+__global__ void __launch_bounds__(256) forward_to_peers_kernel(const uint4 *__restrict__ src,
+                                                               size_t n16, const ForwardPeers peers) {
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  // four independent loads in flight per thread
+  for (; i + 3 * stride < n16; i += 4 * stride) {
+    uint4 v[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) v[u] = __ldcs(src + i + u * stride);
+    for (int p = 0; p < peers.n; ++p) {
+#pragma unroll
+      for (int u = 0; u < 4; ++u) peers.dst[p][i + u * stride] = v[u];
+    }
+  }
+  for (; i < n16; i += stride) {
+    const uint4 v = __ldcs(src + i);
+    for (int p = 0; p < peers.n; ++p) peers.dst[p][i] = v;
+  }
+}
+
 }  // namespace kapyb

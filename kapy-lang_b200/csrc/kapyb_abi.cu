@@ -1102,6 +1102,12 @@ static kapyb_status plan_decide(const PlanOptions &o, const MatmulProblem &p, vo
       // less than half a wave of 256-wide pair tiles: 128-wide ones put more SMs to work
       const long long t256 = static_cast<long long>((p.M + 255) / 256) * ((p.N + 255) / 256) * p.batch;
       if (bn == 256 && t256 * 2 <= pairs) bn = 128;
+      // Push epilogue: a tile's stores to the peers can only leave when its K loop is
+      // over, so more, smaller tiles start the NVLink traffic earlier.  With three
+      // waves or more of 256-wide tiles that outweighs their slower main loop
+      // (full output on every rank, 8192^3: 2 GPUs 0.409 against 0.419 ms, 4 GPUs
+      // 0.289 against 0.312; at 8 GPUs, 1.7 waves, the wide tile wins 0.278 : 0.288).
+      if (n_peers > 0 && bn == 512 && t256 >= 3 * pairs) bn = 256;
     }
     if (bn == 64) bn = 128;
     if (group_cols(bn, 2) < min_cols) bn = 512;
@@ -1810,10 +1816,26 @@ extern "C" KAPYB_API kapyb_status kapyb_matmul_host_sharded(
     CUDA_TRY(h, cudaEventRecord(h->ev_push[j], h->copy_in));
     trace.mark("own piece uploaded", h->copy_in, j);
     CUDA_TRY(h, cudaStreamWaitEvent(h->push, h->ev_push[j], 0));
-    for (int i = 1; i < world; ++i) {
-      const int peer = (rank + i) % world;  // ranks start with different peers
-      CUDA_TRY(h, cudaMemcpyAsync(static_cast<char *>(ctx->peer_lhs[peer]) + half + off, da + off,
-                                  piece_bytes, cudaMemcpyDeviceToDevice, h->push));
+    if (piece_bytes % 16 == 0 && world - 1 < kMaxGatherRanks) {
+      ForwardPeers fw;
+      fw.n = world - 1;
+      for (int i = 1; i < world; ++i) {
+        const int peer = (rank + i) % world;  // ranks start with different peers
+        fw.dst[i - 1] = reinterpret_cast<uint4 *>(static_cast<char *>(ctx->peer_lhs[peer]) + half + off);
+      }
+      // a quarter of the SMs: NVLink, not the SMs, bounds it, and the products of the
+      // pieces before run beside it
+      const int grid = std::max(8, h->sm_count / 4);
+      forward_to_peers_kernel<<<grid, 256, 0, h->push>>>(reinterpret_cast<const uint4 *>(da + off),
+                                                         piece_bytes / 16, fw);
+      CUDA_TRY(h, cudaGetLastError());
+      h->launches++;
+    } else {
+      for (int i = 1; i < world; ++i) {
+        const int peer = (rank + i) % world;
+        CUDA_TRY(h, cudaMemcpyAsync(static_cast<char *>(ctx->peer_lhs[peer]) + half + off, da + off,
+                                    piece_bytes, cudaMemcpyDeviceToDevice, h->push));
+      }
     }
     st = kapyb_gather_signal(h, ctx->peer_flags, world, rank, flag_value(j), h->push);
     if (st != KAPYB_OK) return st;
