@@ -302,22 +302,6 @@ __device__ __forceinline__ void add_bias32(float (&f)[32], const uint4 *bp) {
   }
 }
 
-// The same from four 128-bit words already in registers.
-template <int DT>
-__device__ __forceinline__ void add_bias32_regs(float (&f)[32], const uint4 (&b)[4]) {
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const uint32_t ws[4] = {b[j].x, b[j].y, b[j].z, b[j].w};
-#pragma unroll
-    for (int t = 0; t < 4; ++t) {
-      float lo, hi;
-      unpack2_16<DT>(ws[t], lo, hi);
-      f[8 * j + 2 * t] += lo;
-      f[8 * j + 2 * t + 1] += hi;
-    }
-  }
-}
-
 // What one epilogue warp needs to drain its share of one accumulator tile.
 struct EpiTile {
   int b, m0, n0, row, lane, cpart;
@@ -328,6 +312,12 @@ struct EpiTile {
   uint8_t *stg;     // this warp's two 4 KB staging buffers
   bool bias_col, bias_fast;
   float bias_row;
+  // A 16-bit column bias fetched before the accumulator was awaited (so its latency
+  // hides behind the main loop): lane l holds the eight values of tile columns
+  // 8 l .. 8 l + 7; the pieces pick theirs up by shuffle.  Kernels with four epilogue
+  // warps and one accumulator per tile (a warp then drains up to 256 adjacent columns).
+  bool bias_lanes;
+  uint4 bias8;
   uint32_t *prof;   // profiling (debug bit 7, one warp of the first CTA): shared words that
                     // collect clocks spent per phase of the chunk loop; else nullptr
 };
@@ -335,11 +325,9 @@ struct EpiTile {
 // The fused arithmetic on 32 consecutive accumulator columns of one row
 // (columns col0 .. col0+31 of row t.row): scale, bias, addend, activation.
 // LEVEL 0: scale only; 1: scale and bias; 2: scale, bias, addend, activation.
-// `pre`: the 32 column-bias values (16-bit, as fetched ahead of the accumulator
-// wait), or nullptr to fetch them here.
 template <int LEVEL, bool REDUCE = false>
 __device__ __forceinline__ void finish32(const GemmParams &p, const EpiTile &t, float (&f)[32],
-                                         int col0, const uint4 (*pre)[4] = nullptr) {
+                                         int col0) {
   const int lane = t.lane;
   if (p.ep.alpha != 1.0f) {
 #pragma unroll
@@ -347,11 +335,26 @@ __device__ __forceinline__ void finish32(const GemmParams &p, const EpiTile &t, 
   }
   if constexpr (LEVEL >= 1) {
     if (t.bias_col) {
-      if (pre != nullptr) {
-        if (p.ep.bias_dtype == KAPYB_BF16)
-          add_bias32_regs<KAPYB_BF16>(f, *pre);
-        else
-          add_bias32_regs<KAPYB_F16>(f, *pre);
+      if (t.bias_lanes) {
+        const int src0 = (col0 - t.n0) >> 3;  // the lane that holds the piece's first eight values
+        const bool bf16 = p.ep.bias_dtype == KAPYB_BF16;
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj) {
+          const uint32_t ws[4] = {__shfl_sync(0xffffffffu, t.bias8.x, src0 + jj),
+                                  __shfl_sync(0xffffffffu, t.bias8.y, src0 + jj),
+                                  __shfl_sync(0xffffffffu, t.bias8.z, src0 + jj),
+                                  __shfl_sync(0xffffffffu, t.bias8.w, src0 + jj)};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            float lo, hi;
+            if (bf16)
+              unpack2_16<KAPYB_BF16>(ws[e], lo, hi);
+            else
+              unpack2_16<KAPYB_F16>(ws[e], lo, hi);
+            f[8 * jj + 2 * e] += lo;
+            f[8 * jj + 2 * e + 1] += hi;
+          }
+        }
       } else if (t.bias_fast && col0 + 32 <= p.N) {
         const uint4 *bp =
             reinterpret_cast<const uint4 *>(static_cast<const uint16_t *>(p.ep.bias) + col0);
@@ -446,19 +449,6 @@ __device__ __forceinline__ bool epilogue_tile(const GemmParams &p, const TmapArr
     const int nc = t.n0 + c * CW;
     if (nc >= p.N) break;
     uint8_t *sbuf = t.stg + (C_BUFS == 2 ? buf : 0) * 4096;
-    // A 16-bit column bias is fetched first: its latency hides behind the
-    // accumulator loads and the wait for the staging buffer.  (Only where the
-    // registers are there: 192-thread CTAs; with eight epilogue warps a thread has
-    // 168 and the extra 32 spilled.)
-    const bool bias_ahead = EPI == 4 && !PLAIN && t.bias_col && t.bias_fast && nc + CW <= p.N;
-    uint4 braw[EPI == 4 ? NH : 1][4];
-    if (bias_ahead) {
-      const uint4 *bp = reinterpret_cast<const uint4 *>(static_cast<const uint16_t *>(p.ep.bias) + nc);
-#pragma unroll
-      for (int h = 0; h < NH; ++h)
-#pragma unroll
-        for (int j = 0; j < 4; ++j) braw[h][j] = __ldg(bp + h * 4 + j);
-    }
     // All loads of the chunk are in flight before the one wait.
     uint32_t v[NH][32];
     const bool probing = kEpilogueProbes && t.prof != nullptr;
@@ -493,7 +483,7 @@ __device__ __forceinline__ bool epilogue_tile(const GemmParams &p, const TmapArr
       float f[32];
 #pragma unroll
       for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(v[h][i]);
-      finish32<PLAIN ? 0 : 2, REDUCE>(p, t, f, col0, bias_ahead ? &braw[EPI == 4 ? h : 0] : nullptr);
+      finish32<PLAIN ? 0 : 2, REDUCE>(p, t, f, col0);
       // Row `lane` of the staging tile, 128-byte swizzle: 16-byte chunk j of row
       // r lives at chunk position j ^ (r & 7).
       if constexpr (OUTK == 0) stage_half_f32(srow, f, lane);
@@ -1340,6 +1330,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
           et.bias_col = bias_col;
           et.bias_fast = bias_fast;
           et.bias_row = 0.0f;
+          et.bias_lanes = false;
+          et.bias8 = make_uint4(0u, 0u, 0u, 0u);
           et.prof = (kEpilogueProbes && timeline && blockIdx.x == 0 && e == 0) ? p.status + 9 : nullptr;
           if (p.ep.bias != nullptr && p.ep.bias_axis == 0 && row < p.M)
             et.bias_row = load_as_f32(p.ep.bias, p.ep.bias_dtype, row);
@@ -1352,6 +1344,24 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
           if (!alive) break;
           acc_phase ^= 1u;
           continue;
+        }
+      }
+      bool bias_lanes = false;
+      uint4 bias8 = make_uint4(0u, 0u, 0u, 0u);
+      if constexpr (Cfg::HALVES == 1 && EPI == 4) {
+        if (bias_col && bias_fast && m0 < p.M) {
+          bias_lanes = true;
+          const int col = n0 + lane * 8;
+          const uint16_t *bp = static_cast<const uint16_t *>(p.ep.bias);
+          if (lane * 8 < BN && col + 8 <= p.N) {
+            bias8 = __ldg(reinterpret_cast<const uint4 *>(bp + col));
+          } else if (lane * 8 < BN) {
+            uint32_t wv[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+            for (int k = 0; k < 8; ++k)
+              if (col + k < p.N) wv[k >> 1] |= static_cast<uint32_t>(__ldg(bp + col + k)) << (16 * (k & 1));
+            bias8 = make_uint4(wv[0], wv[1], wv[2], wv[3]);
+          }
         }
       }
 #pragma unroll 1
@@ -1388,6 +1398,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
           et.bias_col = bias_col;
           et.bias_fast = bias_fast;
           et.bias_row = 0.0f;
+          et.bias_lanes = bias_lanes;
+          et.bias8 = bias8;
           et.prof = prof;
           if (p.ep.bias != nullptr && p.ep.bias_axis == 0 && row < p.M)
             et.bias_row = load_as_f32(p.ep.bias, p.ep.bias_dtype, row);

@@ -1103,11 +1103,11 @@ static kapyb_status plan_decide(const PlanOptions &o, const MatmulProblem &p, vo
       const long long t256 = static_cast<long long>((p.M + 255) / 256) * ((p.N + 255) / 256) * p.batch;
       if (bn == 256 && t256 * 2 <= pairs) bn = 128;
       // Push epilogue: a tile's stores to the peers can only leave when its K loop is
-      // over, so more, smaller tiles start the NVLink traffic earlier.  With three
-      // waves or more of 256-wide tiles that outweighs their slower main loop
-      // (full output on every rank, 8192^3: 2 GPUs 0.409 against 0.419 ms, 4 GPUs
-      // 0.289 against 0.312; at 8 GPUs, 1.7 waves, the wide tile wins 0.278 : 0.288).
-      if (n_peers > 0 && bn == 512 && t256 >= 3 * pairs) bn = 256;
+      // over, so more, smaller tiles start the NVLink traffic earlier, which outweighs
+      // their slower main loop once there is a wave of them (full output on every rank,
+      // 8192^3, 256-wide against 512-wide: 2 GPUs 0.410 : 0.422 ms, 4 GPUs 0.289 : 0.312,
+      // 8 GPUs 0.268 : 0.278; 128-wide tiles are slower again: 0.303 at 8 GPUs).
+      if (n_peers > 0 && bn == 512 && t256 >= pairs) bn = 256;
     }
     if (bn == 64) bn = 128;
     if (group_cols(bn, 2) < min_cols) bn = 512;
