@@ -1461,6 +1461,56 @@ static kapyb_status ensure_pipe(kapyb_handle h) {
   return KAPYB_OK;
 }
 
+// KAPYB_TRACE=1 in the environment makes the host-buffer calls record a timing
+// event on the stream of each phase as the phase is issued and, when the call is
+// over, print when each one completed on the device (milliseconds after the
+// call's first event) next to the host time at which it had been issued.
+// Nothing is synchronised while the call runs, so the overlap is the real one.
+// A diagnosis aid: events are created per call, so leave it off in timed runs.
+struct HostTrace {
+  bool on;
+  int rank;
+  std::chrono::steady_clock::time_point t0;
+  struct Mark {
+    const char *what;
+    int index;
+    cudaEvent_t ev;
+    double issued_ms;
+  };
+  std::vector<Mark> marks;
+  explicit HostTrace(int rank_) : rank(rank_), t0(std::chrono::steady_clock::now()) {
+    const char *e = getenv("KAPYB_TRACE");
+    on = e && e[0] && e[0] != '0';
+  }
+  double ms() const {
+    return std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
+  }
+  void mark(const char *what, cudaStream_t s, int index = -1) {
+    if (!on) return;
+    cudaEvent_t ev;
+    if (cudaEventCreate(&ev) != cudaSuccess) return;
+    cudaEventRecord(ev, s);
+    marks.push_back(Mark{what, index, ev, ms()});
+  }
+  // call after everything has completed
+  void report() {
+    if (!on || marks.empty()) return;
+    for (const Mark &m : marks) {
+      float dev_ms = 0.0f;
+      cudaEventElapsedTime(&dev_ms, marks[0].ev, m.ev);
+      if (m.index >= 0)
+        fprintf(stderr, "[kapyb trace r%d] %-22s %d  issued %7.3f ms, done on device %7.3f ms\n", rank,
+                m.what, m.index, m.issued_ms, dev_ms);
+      else
+        fprintf(stderr, "[kapyb trace r%d] %-24s issued %7.3f ms, done on device %7.3f ms\n", rank,
+                m.what, m.issued_ms, dev_ms);
+    }
+    fprintf(stderr, "[kapyb trace r%d] call returns at %7.3f ms (host)\n", rank, ms());
+    for (const Mark &m : marks) cudaEventDestroy(m.ev);
+    marks.clear();
+  }
+};
+
 extern "C" KAPYB_API kapyb_status kapyb_matmul_host(kapyb_handle h, const kapyb_tensor2d *lhs,
                                                     const kapyb_tensor2d *rhs,
                                                     const kapyb_tensor2d *out,
@@ -1522,33 +1572,52 @@ extern "C" KAPYB_API kapyb_status kapyb_matmul_host(kapyb_handle h, const kapyb_
     st = ensure_pipe(h);
     if (st != KAPYB_OK) return st;
     const int M = lhs->size0;
-    // 1024-row chunks: what is left exposed at the end is one chunk's GEMM and
-    // download; smaller chunks lose more in copy and event overhead than they save
-    // there (8192^3 bf16: 5.87 ms with 1024 rows, 6.05 with 512, 6.00 with 2048;
-    // the upload alone takes 4.92 ms)
-    const int chunks = std::min(kMaxChunks, std::max(2, M / 1024));
+    // 1024-row chunks (8192^3 bf16: 5.87 ms with 1024 rows, 6.05 with 512, 6.00 with
+    // 2048: smaller chunks lose more in copy and event overhead than they save; the
+    // upload alone takes 4.92 ms, and each direction runs about 20 % slower while
+    // the other is busy).  What stays exposed at the end is the last chunk's GEMM
+    // and download, so the LAST chunk's rows go as a half and two quarters.
+    const int chunks = std::min(kMaxChunks - 2, std::max(2, M / 1024));
     const int rows_per = ((M + chunks - 1) / chunks + 255) / 256 * 256;
+    int plan_rows[kMaxChunks + 2];
+    int n_plan = 0;
+    {
+      int r0 = 0;
+      while (M - r0 > rows_per + 255) {   // whole chunks while more than one is left
+        plan_rows[n_plan++] = rows_per;
+        r0 += rows_per;
+      }
+      int left = M - r0;                  // the last chunk: 256 .. rows_per + 255 rows
+      for (int div = 2; div <= 4 && left >= 512; div += 2) {
+        const int part = (left / 2 + 255) / 256 * 256;
+        if (left - part < 256) break;
+        plan_rows[n_plan++] = part;
+        left -= part;
+      }
+      plan_rows[n_plan++] = left;         // never fewer than 256 rows (no decode-kernel chunk,
+                                          // whose sums run in another order than the tiles')
+    }
     cudaEvent_t ev_start = h->ev[2 * kMaxChunks], ev_done = h->ev[2 * kMaxChunks + 1];
+    HostTrace trace(0);
+    trace.mark("start", stream);
     // B and the bias are already on their way on `stream`; A goes up chunk by chunk
     CUDA_TRY(h, cudaEventRecord(ev_start, stream));
+    trace.mark("rhs uploaded", stream);
     CUDA_TRY(h, cudaStreamWaitEvent(h->copy_in, ev_start, 0));
     CUDA_TRY(h, cudaStreamWaitEvent(h->copy_out, ev_start, 0));
     const size_t esz_a = dtype_size(lhs->dtype), esz_c = dtype_size(out->dtype);
     const char *ha = static_cast<const char *>(elem_ptr(lhs));
     char *hc = static_cast<char *>(const_cast<void *>(elem_ptr(out)));
     int n_chunks = 0;
-    for (int r0 = 0, rows = 0; r0 < M; r0 += rows, ++n_chunks) {
-      rows = std::min(rows_per, M - r0);
-      // a last chunk of a few rows would go to the decode kernel, whose sums run in
-      // another order than the tiles': it joins the chunk before it, so the result has
-      // the bits of the device-resident call
-      if (M - (r0 + rows) < 256) rows = M - r0;
+    for (int r0 = 0, rows = 0; n_chunks < n_plan; r0 += rows, ++n_chunks) {
+      rows = plan_rows[n_chunks];
       const size_t a_off = static_cast<size_t>(r0) * lhs->stride0 * esz_a;
       const size_t c_off = static_cast<size_t>(r0) * out->stride0 * esz_c;
       CUDA_TRY(h, cudaMemcpyAsync(da + a_off, ha + a_off,
                                   static_cast<size_t>(rows) * lhs->stride0 * esz_a,
                                   cudaMemcpyHostToDevice, h->copy_in));
       CUDA_TRY(h, cudaEventRecord(h->ev[2 * n_chunks], h->copy_in));
+      trace.mark("chunk uploaded", h->copy_in, n_chunks);
       CUDA_TRY(h, cudaStreamWaitEvent(stream, h->ev[2 * n_chunks], 0));
       kapyb_tensor2d cl = dl, co = dout;
       cl.offset_elems = static_cast<int64_t>(r0) * lhs->stride0;
@@ -1561,14 +1630,21 @@ extern "C" KAPYB_API kapyb_status kapyb_matmul_host(kapyb_handle h, const kapyb_
       st = run_matmul(h, make_problem(&cl, &dr, nullptr, &co, &cep), nullptr, 0, stream);
       if (st != KAPYB_OK) return st;
       CUDA_TRY(h, cudaEventRecord(h->ev[2 * n_chunks + 1], stream));
+      trace.mark("chunk multiplied", stream, n_chunks);
       CUDA_TRY(h, cudaStreamWaitEvent(h->copy_out, h->ev[2 * n_chunks + 1], 0));
       CUDA_TRY(h, cudaMemcpyAsync(hc + c_off, dc + c_off,
                                   static_cast<size_t>(rows) * out->stride0 * esz_c,
                                   cudaMemcpyDeviceToHost, h->copy_out));
+      trace.mark("chunk downloaded", h->copy_out, n_chunks);
     }
     CUDA_TRY(h, cudaEventRecord(ev_done, h->copy_out));
     CUDA_TRY(h, cudaStreamWaitEvent(stream, ev_done, 0));
-    return kapyb_check(h, stream);
+    const kapyb_status done = kapyb_check(h, stream);
+    if (trace.on) {
+      cudaDeviceSynchronize();
+      trace.report();
+    }
+    return done;
   }
   st = run_matmul(h, make_problem(&dl, &dr, nullptr, &dout, &ep), nullptr, 0, stream);
   if (st != KAPYB_OK) return st;
@@ -1636,55 +1712,6 @@ extern "C" KAPYB_API kapyb_status kapyb_gather_wait(kapyb_handle h, const void *
 
 // ------------------------------------------- host buffers, rows of A sharded
 
-// KAPYB_TRACE=1 in the environment makes the sharded host call record a timing
-// event on the stream of each phase as the phase is issued and, when the call is
-// over, print when each one completed on the device (milliseconds after the
-// call's first event) next to the host time at which it had been issued.
-// Nothing is synchronised while the call runs, so the overlap is the real one.
-// A diagnosis aid: events are created per call, so leave it off in timed runs.
-struct HostTrace {
-  bool on;
-  int rank;
-  std::chrono::steady_clock::time_point t0;
-  struct Mark {
-    const char *what;
-    int index;
-    cudaEvent_t ev;
-    double issued_ms;
-  };
-  std::vector<Mark> marks;
-  explicit HostTrace(int rank_) : rank(rank_), t0(std::chrono::steady_clock::now()) {
-    const char *e = getenv("KAPYB_TRACE");
-    on = e && e[0] && e[0] != '0';
-  }
-  double ms() const {
-    return std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
-  }
-  void mark(const char *what, cudaStream_t s, int index = -1) {
-    if (!on) return;
-    cudaEvent_t ev;
-    if (cudaEventCreate(&ev) != cudaSuccess) return;
-    cudaEventRecord(ev, s);
-    marks.push_back(Mark{what, index, ev, ms()});
-  }
-  // call after everything has completed
-  void report() {
-    if (!on || marks.empty()) return;
-    for (const Mark &m : marks) {
-      float dev_ms = 0.0f;
-      cudaEventElapsedTime(&dev_ms, marks[0].ev, m.ev);
-      if (m.index >= 0)
-        fprintf(stderr, "[kapyb trace r%d] %-22s %d  issued %7.3f ms, done on device %7.3f ms\n", rank,
-                m.what, m.index, m.issued_ms, dev_ms);
-      else
-        fprintf(stderr, "[kapyb trace r%d] %-24s issued %7.3f ms, done on device %7.3f ms\n", rank,
-                m.what, m.issued_ms, dev_ms);
-    }
-    fprintf(stderr, "[kapyb trace r%d] call returns at %7.3f ms (host)\n", rank, ms());
-    for (const Mark &m : marks) cudaEventDestroy(m.ev);
-    marks.clear();
-  }
-};
 
 extern "C" KAPYB_API kapyb_status kapyb_matmul_host_sharded(
     kapyb_handle h, const kapyb_tensor2d *lhs_rows, int32_t m_total, int32_t row_begin,
