@@ -49,6 +49,16 @@ __device__ __forceinline__ float gelu_tanh_f32(float u) {
   return div_full(u, __fadd_rn(1.0f, e));
 }
 
+// The same with the activation known at compile time (callers that finish many
+// values at once branch once per group, not once per value).
+template <int ACT>
+__device__ __forceinline__ float apply_activation_t(float v) {
+  if constexpr (ACT == KAPYB_ACT_RELU) return v > 0.0f ? v : (v != v ? v : 0.0f);
+  if constexpr (ACT == KAPYB_ACT_GELU_TANH) return gelu_tanh_f32(v);
+  if constexpr (ACT == KAPYB_ACT_SILU) return div_full(v, __fadd_rn(1.0f, kapy_exp(-v)));
+  return v;
+}
+
 __device__ __forceinline__ float apply_activation(int act, float v) {
   switch (act) {
   case KAPYB_ACT_RELU: return v > 0.0f ? v : (v != v ? v : 0.0f);

@@ -383,9 +383,23 @@ __device__ __forceinline__ void finish32(const GemmParams &p, const EpiTile &t, 
           f[i] += load_as_f32(p.ep.acc, p.ep.acc_dtype,
                               base + static_cast<long long>(col0 + i) * p.ep.acc_stride1);
     }
-    if (p.ep.activation != KAPYB_ACT_NONE) {
+    // one branch per 32 values: with the choice inside the unrolled loop a fused
+    // relu made a 4096 x 4096 x 1024 product three times slower
+    switch (p.ep.activation) {
+    case KAPYB_ACT_RELU:
 #pragma unroll
-      for (int i = 0; i < 32; ++i) f[i] = apply_activation(p.ep.activation, f[i]);
+      for (int i = 0; i < 32; ++i) f[i] = apply_activation_t<KAPYB_ACT_RELU>(f[i]);
+      break;
+    case KAPYB_ACT_GELU_TANH:
+#pragma unroll
+      for (int i = 0; i < 32; ++i) f[i] = apply_activation_t<KAPYB_ACT_GELU_TANH>(f[i]);
+      break;
+    case KAPYB_ACT_SILU:
+#pragma unroll
+      for (int i = 0; i < 32; ++i) f[i] = apply_activation_t<KAPYB_ACT_SILU>(f[i]);
+      break;
+    default:
+      break;
     }
   }
   if constexpr (REDUCE) {
@@ -524,9 +538,9 @@ __device__ __forceinline__ bool epilogue_tile(const GemmParams &p, const TmapArr
 // hands each half back as soon as its last load has landed, and stores from the
 // registers afterwards, under the next tile's main loop.  Covers the epilogues
 // that are a scale and an optional bias, rounded to nearest; anything more goes
-// chunk by chunk.  Returns false when a wait ran out.
-// One copy serves bf16 and f16 outputs, with or without a bias: separate copies
-// inlined into one kernel made the register allocator spill.
+// chunk by chunk.  `spare`: 12 KB of the operand ring when this is the CTA's last
+// tile (its three register-held chunks are then staged there and stored together),
+// else nullptr.  Returns false when a wait ran out.
 // MODE 1 / 2: the output is bf16 / f16, known at compile time, and a column bias
 // kept in registers is of the same type (one type throughout, the usual case).
 // The drain is bound by the instructions these warps issue, and choosing the

@@ -1099,6 +1099,13 @@ static kapyb_status plan_decide(const PlanOptions &o, const MatmulProblem &p, vo
         return static_cast<double>(t) / static_cast<double>((t + pairs - 1) / pairs * pairs);
       };
       bn = (p.N >= 512 && p.K >= 1024 && wave_eff(512) >= 0.8 * wave_eff(256)) ? 512 : 256;
+      // The wide tile's drain is not hidden behind the next tile's main loop, which
+      // costs the more the shorter the K loop and the fewer the waves: measured
+      // 256-wide against 512-wide, 4096 x 4096 x 1024 30.7 : 34.0 us, 4096 x 2048 x 2048
+      // 29.6 : 32.3, 2048 x 4096 x 4096 51.3 : 53.3; the other way round 8192 x 8192 x 2048
+      // 190 : 184, 4096^3 99.5 : 97.5, 8192 x 1024 x 8192 102 : 96.
+      const long long t512 = static_cast<long long>((p.M + 255) / 256) * ((p.N + 511) / 512) * p.batch;
+      if (bn == 512 && ((p.K <= 2048 && t512 < 3 * pairs) || (p.K <= 4096 && t512 <= pairs))) bn = 256;
       // less than half a wave of 256-wide pair tiles: 128-wide ones put more SMs to work
       const long long t256 = static_cast<long long>((p.M + 255) / 256) * ((p.N + 255) / 256) * p.batch;
       if (bn == 256 && t256 * 2 <= pairs) bn = 128;
