@@ -303,7 +303,10 @@ KAPYB_API kapyb_status kapyb_reserve_workspace(kapyb_handle h, size_t bytes);
  * one of the two fp8 types (Kapy.cpp:484-487, :530-564); either may be row- or
  * column-major (one unit stride, CoalesceAccess.cpp:32-40).  `acc` may be NULL
  * (= zero accumulator, the arith.constant dense<0.0> of matmul.mlir:6) or an
- * f16/f32 [M,N] tensor added in fp32.  out: f16, bf16 or f32.
+ * f16/f32 [M,N] tensor added in fp32 (fastest when it has out's element type,
+ * unit stride on its columns, a 16-byte aligned base and a leading dimension
+ * that is a multiple of 16 bytes: the epilogue then fetches it tile by tile;
+ * anything else is read element by element, same result).  out: f16, bf16 or f32.
  * Returns KAPYB_INVALID_ARG for the shape/dtype violations MatmulOp::verify
  * rejects (Kapy.cpp:459-487). */
 KAPYB_API kapyb_status kapyb_matmul(kapyb_handle h, const kapyb_tensor2d *lhs,

@@ -139,6 +139,10 @@ struct GemmParams {
   // L2 policy of the TMA traffic per tensor (from the descriptors' eviction
   // priority): 0 default, 1 evict_first, 2 evict_last
   int a_l2, b_l2, c_l2;
+  // 1: the addend (ep.acc) has the output's type and a TMA-describable layout; its
+  // tensor map sits in the last slot of the output maps and the epilogue fetches it
+  // tile by tile into the staging buffer.  0: element by element (any type, any strides).
+  int acc_tma;
   // SPLIT instantiations only.  Tiles below sk_first_tile are dealt to the CTAs
   // (pairs) whole, round-robin; the K blocks of the tiles from there on, sk_total in
   // all, are dealt out as one contiguous span per CTA (pair), so a last wave that
@@ -318,6 +322,7 @@ struct EpiTile {
   // warps and one accumulator per tile (a warp then drains up to 256 adjacent columns).
   bool bias_lanes;
   uint4 bias8;
+  volatile uint32_t *abort_flag;
   uint32_t *prof;   // profiling (debug bit 7, one warp of the first CTA): shared words that
                     // collect clocks spent per phase of the chunk loop; else nullptr
 };
@@ -325,9 +330,11 @@ struct EpiTile {
 // The fused arithmetic on 32 consecutive accumulator columns of one row
 // (columns col0 .. col0+31 of row t.row): scale, bias, addend, activation.
 // LEVEL 0: scale only; 1: scale and bias; 2: scale, bias, addend, activation.
-template <int LEVEL, bool REDUCE = false>
+// `acc_srow` (ACCK >= 0): this lane's row of the addend tile in the staging buffer
+// (128-byte swizzle), piece `acc_h` of it; ACCK 0 f32, 1 bf16, 2 f16.
+template <int LEVEL, bool REDUCE = false, int ACCK = -1>
 __device__ __forceinline__ void finish32(const GemmParams &p, const EpiTile &t, float (&f)[32],
-                                         int col0) {
+                                         int col0, const uint8_t *acc_srow = nullptr, int acc_h = 0) {
   const int lane = t.lane;
   if (p.ep.alpha != 1.0f) {
 #pragma unroll
@@ -374,7 +381,31 @@ __device__ __forceinline__ void finish32(const GemmParams &p, const EpiTile &t, 
     }
   }
   if constexpr (LEVEL >= 2) {
-    if (p.ep.acc != nullptr && t.row < p.M) {
+    if (ACCK >= 0 && acc_srow != nullptr) {
+      if constexpr (ACCK == 0) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const uint4 q = *reinterpret_cast<const uint4 *>(acc_srow + ((j ^ (lane & 7)) << 4));
+          f[4 * j] += __uint_as_float(q.x);
+          f[4 * j + 1] += __uint_as_float(q.y);
+          f[4 * j + 2] += __uint_as_float(q.z);
+          f[4 * j + 3] += __uint_as_float(q.w);
+        }
+      } else if constexpr (ACCK > 0) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const uint4 q = *reinterpret_cast<const uint4 *>(acc_srow + (((acc_h * 4 + j) ^ (lane & 7)) << 4));
+          const uint32_t ws[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            float lo, hi;
+            unpack2_16<ACCK == 1 ? KAPYB_BF16 : KAPYB_F16>(ws[e], lo, hi);
+            f[8 * j + 2 * e] += lo;
+            f[8 * j + 2 * e + 1] += hi;
+          }
+        }
+      }
+    } else if (p.ep.acc != nullptr && t.row < p.M) {
       const long long base = static_cast<long long>(t.b) * p.ep.acc_batch_stride +
                              static_cast<long long>(t.row) * p.ep.acc_stride0;
 #pragma unroll
@@ -451,8 +482,11 @@ __device__ __forceinline__ void stage_packed16(uint8_t *srow, const uint32_t (&w
 // Returns whether the slot was handed back (false when this warp had no chunk).
 template <int BN, int EPI, int OUTK, bool PLAIN, bool REDUCE = false>
 __device__ __forceinline__ bool epilogue_tile(const GemmParams &p, const TmapArray &tmC,
-                                              const EpiTile &t, int &buf) {
+                                              const EpiTile &t, int &buf, uint32_t acc_bar,
+                                              uint32_t &acc_parity) {
   constexpr bool OUT32 = OUTK == 0;
+  constexpr int ACCK = PLAIN ? -1 : (OUTK == 0 ? 0 : (OUTK <= 2 ? 1 : 2));
+  const bool acc_tma = !PLAIN && p.acc_tma != 0;
   constexpr int CW = OUT32 ? 32 : 64;  // output columns per 128-byte staging row
   constexpr int NH = CW / 32;
   constexpr int CSTEP = EPI / 4;
@@ -472,7 +506,15 @@ __device__ __forceinline__ bool epilogue_tile(const GemmParams &p, const TmapArr
       ptx::tmem_ld_32x32(t.t_row + static_cast<uint32_t>(c * CW + h * 32), v[h]);
     // The store that last read this buffer (two chunks ago, or the previous one
     // with a single buffer) must have finished reading it.
-    if (lane == 0) ptx::tma_store_wait_read<C_BUFS - 1>();
+    if (lane == 0) {
+      ptx::tma_store_wait_read<C_BUFS - 1>();
+      if (acc_tma) {
+        // the addend's tile of this chunk comes into the buffer the result will leave
+        // from (each lane then reads and rewrites its own row)
+        ptx::mbar_arrive_expect_tx(acc_bar, 4096u);
+        ptx::tma_load_3d(ptx::smem_u32(sbuf), &tmC.m[kMaxOutputs - 1], acc_bar, nc, t.m0, t.b);
+      }
+    }
     __syncwarp();
     const uint32_t c1 = probing ? static_cast<uint32_t>(clock()) : 0u;
     ptx::tmem_ld_wait();
@@ -491,13 +533,20 @@ __device__ __forceinline__ bool epilogue_tile(const GemmParams &p, const TmapArr
       }
     }
     uint8_t *srow = sbuf + lane * 128;
+    bool acc_here = false;
+    if (acc_tma) {
+      // (a wait that runs out has raised the abort flag: the kernel is on its way out
+      // and the status word will say so; the sums below then go without the addend)
+      acc_here = __all_sync(0xffffffffu, ptx::mbar_wait(acc_bar, acc_parity, t.abort_flag)) != 0;
+      acc_parity ^= 1u;
+    }
 #pragma unroll
     for (int h = 0; h < NH; ++h) {
       const int col0 = nc + h * 32;
       float f[32];
 #pragma unroll
       for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(v[h][i]);
-      finish32<PLAIN ? 0 : 2, REDUCE>(p, t, f, col0);
+      finish32<PLAIN ? 0 : 2, REDUCE, ACCK>(p, t, f, col0, acc_here ? srow : nullptr, h);
       // Row `lane` of the staging tile, 128-byte swizzle: 16-byte chunk j of row
       // r lives at chunk position j ^ (r & 7).
       if constexpr (OUTK == 0) stage_half_f32(srow, f, lane);
@@ -800,6 +849,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tempty_bar + 2);
   volatile uint32_t *abort_flag = tmem_slot + 1;
   uint32_t *prof_words = tmem_slot + 8;  // [5] clocks per epilogue phase (debug bit 7)
+  uint64_t *acc_bars = bars + 64;        // [EPI] one per epilogue warp: its addend tile has landed
 
   // the shuffle makes the warp index provably uniform for the compiler
   const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0);
@@ -823,6 +873,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       ptx::mbar_init(ptx::smem_u32(&tfull_bar[a]), 1);          // one tcgen05.commit
       ptx::mbar_init(ptx::smem_u32(&tempty_bar[a]), EPI * CTAS);  // one arrival per epilogue warp
     }
+    for (int w = 0; w < EPI; ++w) ptx::mbar_init(ptx::smem_u32(&acc_bars[w]), 1);  // one TMA load of an addend tile
     abort_flag[0] = 0u;
     abort_flag[1] = p.wait_limit_us;
     for (int i = 0; i < 5; ++i) prof_words[i] = 0u;
@@ -1181,6 +1232,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
     int acc = 0;
     uint32_t acc_phase = 0;
     int buf = 0;
+    const uint32_t acc_bar = ptx::smem_u32(&acc_bars[e]);
+    uint32_t acc_parity = 0;
     uint32_t *prof = (kEpilogueProbes && timeline && blockIdx.x == 0 && e == 0) ? prof_words : nullptr;
     for (WorkIter<SK> w(p, unit, unit_step); w.next(p);) {
       const uint32_t s0 = prof ? static_cast<uint32_t>(clock()) : 0u;
@@ -1346,6 +1399,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
           et.bias_row = 0.0f;
           et.bias_lanes = false;
           et.bias8 = make_uint4(0u, 0u, 0u, 0u);
+          et.abort_flag = abort_flag;
           et.prof = (kEpilogueProbes && timeline && blockIdx.x == 0 && e == 0) ? p.status + 9 : nullptr;
           if (p.ep.bias != nullptr && p.ep.bias_axis == 0 && row < p.M)
             et.bias_row = load_as_f32(p.ep.bias, p.ep.bias_dtype, row);
@@ -1414,22 +1468,23 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
           et.bias_row = 0.0f;
           et.bias_lanes = bias_lanes;
           et.bias8 = bias8;
+          et.abort_flag = abort_flag;
           et.prof = prof;
           if (p.ep.bias != nullptr && p.ep.bias_axis == 0 && row < p.M)
             et.bias_row = load_as_f32(p.ep.bias, p.ep.bias_dtype, row);
           // One specialised copy of the chunk loop per (output kind, plain/full
           // epilogue): the switch runs once per slot, the loops inside are tight.
           switch (out_kind * 2 + (plain ? 1 : 0)) {
-          case 0: handed_back = epilogue_tile<BN, EPI, 0, false, REDUCE>(p, tmC, et, buf); break;
-          case 1: handed_back = epilogue_tile<BN, EPI, 0, true>(p, tmC, et, buf); break;
-          case 2: handed_back = epilogue_tile<BN, EPI, 1, false, REDUCE>(p, tmC, et, buf); break;
-          case 3: handed_back = epilogue_tile<BN, EPI, 1, true>(p, tmC, et, buf); break;
-          case 4: handed_back = epilogue_tile<BN, EPI, 2, false, REDUCE>(p, tmC, et, buf); break;
-          case 5: handed_back = epilogue_tile<BN, EPI, 2, true>(p, tmC, et, buf); break;
-          case 6: handed_back = epilogue_tile<BN, EPI, 3, false, REDUCE>(p, tmC, et, buf); break;
-          case 7: handed_back = epilogue_tile<BN, EPI, 3, true>(p, tmC, et, buf); break;
-          case 8: handed_back = epilogue_tile<BN, EPI, 4, false, REDUCE>(p, tmC, et, buf); break;
-          default: handed_back = epilogue_tile<BN, EPI, 4, true>(p, tmC, et, buf); break;
+          case 0: handed_back = epilogue_tile<BN, EPI, 0, false, REDUCE>(p, tmC, et, buf, acc_bar, acc_parity); break;
+          case 1: handed_back = epilogue_tile<BN, EPI, 0, true>(p, tmC, et, buf, acc_bar, acc_parity); break;
+          case 2: handed_back = epilogue_tile<BN, EPI, 1, false, REDUCE>(p, tmC, et, buf, acc_bar, acc_parity); break;
+          case 3: handed_back = epilogue_tile<BN, EPI, 1, true>(p, tmC, et, buf, acc_bar, acc_parity); break;
+          case 4: handed_back = epilogue_tile<BN, EPI, 2, false, REDUCE>(p, tmC, et, buf, acc_bar, acc_parity); break;
+          case 5: handed_back = epilogue_tile<BN, EPI, 2, true>(p, tmC, et, buf, acc_bar, acc_parity); break;
+          case 6: handed_back = epilogue_tile<BN, EPI, 3, false, REDUCE>(p, tmC, et, buf, acc_bar, acc_parity); break;
+          case 7: handed_back = epilogue_tile<BN, EPI, 3, true>(p, tmC, et, buf, acc_bar, acc_parity); break;
+          case 8: handed_back = epilogue_tile<BN, EPI, 4, false, REDUCE>(p, tmC, et, buf, acc_bar, acc_parity); break;
+          default: handed_back = epilogue_tile<BN, EPI, 4, true>(p, tmC, et, buf, acc_bar, acc_parity); break;
           }
         }
         if (!handed_back) {

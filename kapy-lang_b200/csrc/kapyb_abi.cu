@@ -755,6 +755,16 @@ static kapyb_status launch_tcgen05(kapyb_handle h, const MatmulProblem &p, bool 
   gp.b_l2 = p.b_l2;
   gp.c_l2 = p.c_l2;
 
+  gp.acc_tma = 0;
+  if (p.ep.acc != nullptr && n_out < kMaxOutputs && p.ep.acc_dtype == p.out_dtype &&
+      (p.ep.acc_stride1 == 1 || p.N == 1) &&
+      tma_ok(p.ep.acc, p.ep.acc_dtype, p.N, p.M, p.ep.acc_stride0, p.batch, p.ep.acc_batch_stride)) {
+    // the addend as tiles of the output's shape: fetched by TMA in the epilogue
+    st = make_tmap(h, &tmC.m[kMaxOutputs - 1], p.ep.acc, p.ep.acc_dtype, p.N, p.M, p.batch,
+                   p.ep.acc_stride0, p.ep.acc_batch_stride, cw, 32);
+    if (st != KAPYB_OK) return st;
+    gp.acc_tma = 1;
+  }
   gp.sk_first_tile = gp.num_tiles;
   gp.sk_total = 0;
   gp.sk_scratch = nullptr;

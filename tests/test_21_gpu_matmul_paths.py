@@ -200,3 +200,28 @@ def test_eviction_priorities_become_l2_policies(handle, pkg, path):
         handle.set_matmul_path("auto")
     with pytest.raises(ValueError, match="cache operator or eviction priority"):
         handle.matmul(X, W, cache=(A_.cache_hints(0, 7), 0, 0))
+
+
+@pytest.mark.parametrize("path", ["2cta:512", "2cta:256", "2cta:128", "1cta:256", "1cta:256:e8", "1cta:64"])
+def test_addend_fetched_by_tiles(handle, ko, path):
+    """kapy.matmul's third operand.  An addend of the output's type with a layout
+    TMA can describe comes into the epilogue tile by tile; any other (here: unit
+    stride on the rows) element by element.  Same arithmetic, same bits; ragged
+    edges, f16 and f32."""
+    M, N, K = 600, 1096, 320
+    for dt, odt in ((torch.float16, torch.float16), (torch.bfloat16, torch.float32)):
+        A, B = normal((M, K), 71, K ** -0.5, dt), normal((K, N), 72, 1.0, dt)
+        acc = normal((M, N), 73, 1.0, odt)
+        bias = uniform((N,), 74, -0.1, 0.1, dt)
+        handle.set_matmul_path(path)
+        try:
+            fast = handle.matmul(A.cuda(), B.cuda(), acc=acc.cuda(), bias=bias.cuda(), alpha=0.75,
+                                 activation=1, out_dtype=odt)
+            by_element = handle.matmul(A.cuda(), B.cuda(), acc=acc.t().contiguous().cuda().t(),
+                                       bias=bias.cuda(), alpha=0.75, activation=1, out_dtype=odt)
+            handle.check()
+        finally:
+            handle.set_matmul_path("auto")
+        check(ko, fast, A, B, acc=acc, bias=bias, alpha=0.75, activation=1)
+        assert torch.equal(fast, by_element)
+
