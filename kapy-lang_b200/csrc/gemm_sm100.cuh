@@ -321,7 +321,8 @@ struct EpiTile {
   // 8 l .. 8 l + 7; the pieces pick theirs up by shuffle.  Kernels with four epilogue
   // warps and one accumulator per tile (a warp then drains up to 256 adjacent columns).
   bool bias_lanes;
-  uint4 bias8;
+  uint4 bias8;      // eight 16-bit values, or the first four of eight f32 values
+  uint4 bias8_hi;   // f32 bias: the other four
   volatile uint32_t *abort_flag;
   uint32_t *prof;   // profiling (debug bit 7, one warp of the first CTA): shared words that
                     // collect clocks spent per phase of the chunk loop; else nullptr
@@ -342,7 +343,20 @@ __device__ __forceinline__ void finish32(const GemmParams &p, const EpiTile &t, 
   }
   if constexpr (LEVEL >= 1) {
     if (t.bias_col) {
-      if (t.bias_lanes) {
+      if (t.bias_lanes && p.ep.bias_dtype == KAPYB_F32) {
+        const int src0 = (col0 - t.n0) >> 3;  // the lane that holds the piece's first eight values
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj) {
+          f[8 * jj + 0] += __uint_as_float(__shfl_sync(0xffffffffu, t.bias8.x, src0 + jj));
+          f[8 * jj + 1] += __uint_as_float(__shfl_sync(0xffffffffu, t.bias8.y, src0 + jj));
+          f[8 * jj + 2] += __uint_as_float(__shfl_sync(0xffffffffu, t.bias8.z, src0 + jj));
+          f[8 * jj + 3] += __uint_as_float(__shfl_sync(0xffffffffu, t.bias8.w, src0 + jj));
+          f[8 * jj + 4] += __uint_as_float(__shfl_sync(0xffffffffu, t.bias8_hi.x, src0 + jj));
+          f[8 * jj + 5] += __uint_as_float(__shfl_sync(0xffffffffu, t.bias8_hi.y, src0 + jj));
+          f[8 * jj + 6] += __uint_as_float(__shfl_sync(0xffffffffu, t.bias8_hi.z, src0 + jj));
+          f[8 * jj + 7] += __uint_as_float(__shfl_sync(0xffffffffu, t.bias8_hi.w, src0 + jj));
+        }
+      } else if (t.bias_lanes) {
         const int src0 = (col0 - t.n0) >> 3;  // the lane that holds the piece's first eight values
         const bool bf16 = p.ep.bias_dtype == KAPYB_BF16;
 #pragma unroll
@@ -1399,6 +1413,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
           et.bias_row = 0.0f;
           et.bias_lanes = false;
           et.bias8 = make_uint4(0u, 0u, 0u, 0u);
+          et.bias8_hi = make_uint4(0u, 0u, 0u, 0u);
           et.abort_flag = abort_flag;
           et.prof = (kEpilogueProbes && timeline && blockIdx.x == 0 && e == 0) ? p.status + 9 : nullptr;
           if (p.ep.bias != nullptr && p.ep.bias_axis == 0 && row < p.M)
@@ -1415,9 +1430,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
         }
       }
       bool bias_lanes = false;
-      uint4 bias8 = make_uint4(0u, 0u, 0u, 0u);
+      uint4 bias8 = make_uint4(0u, 0u, 0u, 0u), bias8_hi = make_uint4(0u, 0u, 0u, 0u);
       if constexpr (Cfg::HALVES == 1 && EPI == 4) {
-        if (bias_col && bias_fast && m0 < p.M) {
+        if (bias_col && p.ep.bias_dtype == KAPYB_F32 && m0 < p.M) {
+          // an f32 bias: eight values per lane in two words of four
+          bias_lanes = true;
+          const int col = n0 + lane * 8;
+          const float *bp = static_cast<const float *>(p.ep.bias);
+          uint32_t wv[8];
+#pragma unroll
+          for (int k = 0; k < 8; ++k)
+            wv[k] = (lane * 8 < BN && col + k < p.N) ? __float_as_uint(__ldg(bp + col + k)) : 0u;
+          bias8 = make_uint4(wv[0], wv[1], wv[2], wv[3]);
+          bias8_hi = make_uint4(wv[4], wv[5], wv[6], wv[7]);
+        } else if (bias_col && bias_fast && m0 < p.M) {
           bias_lanes = true;
           const int col = n0 + lane * 8;
           const uint16_t *bp = static_cast<const uint16_t *>(p.ep.bias);
@@ -1468,6 +1494,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
           et.bias_row = 0.0f;
           et.bias_lanes = bias_lanes;
           et.bias8 = bias8;
+          et.bias8_hi = bias8_hi;
           et.abort_flag = abort_flag;
           et.prof = prof;
           if (p.ep.bias != nullptr && p.ep.bias_axis == 0 && row < p.M)
