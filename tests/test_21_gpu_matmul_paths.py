@@ -224,4 +224,14 @@ def test_addend_fetched_by_tiles(handle, ko, path):
             handle.set_matmul_path("auto")
         check(ko, fast, A, B, acc=acc, bias=bias, alpha=0.75, activation=1)
         assert torch.equal(fast, by_element)
+        # in place (C = act(alpha * A.B + bias + C)): every tile is read before it is written
+        handle.set_matmul_path(path)
+        try:
+            inplace = acc.cuda()
+            handle.matmul(A.cuda(), B.cuda(), acc=inplace, out=inplace, bias=bias.cuda(), alpha=0.75,
+                          activation=1)
+            handle.check()
+        finally:
+            handle.set_matmul_path("auto")
+        assert torch.equal(inplace, fast)
 
