@@ -647,9 +647,21 @@ __device__ __forceinline__ bool epilogue_two_halves(const GemmParams &p, const T
   constexpr bool bias_bf16 = MODE == 1;
   const bool bias_regs = t.bias_col && t.bias_fast &&
                          p.ep.bias_dtype == (MODE == 1 ? KAPYB_BF16 : KAPYB_F16);
+  // an f32 column bias (the usual companion of 16-bit operands) the same way, eight
+  // values per lane in two words
+  const bool bias_regs32 = t.bias_col && p.ep.bias_dtype == KAPYB_F32;
   const float alpha = p.ep.alpha;
-  uint4 bv = make_uint4(0u, 0u, 0u, 0u);
-  if (bias_regs) {
+  uint4 bv = make_uint4(0u, 0u, 0u, 0u), bv_hi = make_uint4(0u, 0u, 0u, 0u);
+  if (bias_regs32) {
+    const int ci = lane >> 3;
+    const int col = t.n0 + ((ci >> 1) * 4 + t.cpart + 2 * (ci & 1)) * 64 + (lane & 7) * 8;
+    const float *bp = static_cast<const float *>(p.ep.bias);
+    uint32_t w[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) w[e] = col + e < p.N ? __float_as_uint(__ldg(bp + col + e)) : 0u;
+    bv = make_uint4(w[0], w[1], w[2], w[3]);
+    bv_hi = make_uint4(w[4], w[5], w[6], w[7]);
+  } else if (bias_regs) {
     const int ci = lane >> 3;
     const int col = t.n0 + ((ci >> 1) * 4 + t.cpart + 2 * (ci & 1)) * 64 + (lane & 7) * 8;
     const uint16_t *bp = static_cast<const uint16_t *>(p.ep.bias);
@@ -749,6 +761,19 @@ __device__ __forceinline__ bool epilogue_two_halves(const GemmParams &p, const T
               f[8 * jj + 2 * e] = fmaf(f[8 * jj + 2 * e], alpha, lo);
               f[8 * jj + 2 * e + 1] = fmaf(f[8 * jj + 2 * e + 1], alpha, hi);
             }
+          }
+        } else if (bias_regs32) {
+#pragma unroll
+          for (int jj = 0; jj < 4; ++jj) {
+            const int src = i * 8 + h * 4 + jj;
+            f[8 * jj + 0] = fmaf(f[8 * jj + 0], alpha, __uint_as_float(__shfl_sync(0xffffffffu, bv.x, src)));
+            f[8 * jj + 1] = fmaf(f[8 * jj + 1], alpha, __uint_as_float(__shfl_sync(0xffffffffu, bv.y, src)));
+            f[8 * jj + 2] = fmaf(f[8 * jj + 2], alpha, __uint_as_float(__shfl_sync(0xffffffffu, bv.z, src)));
+            f[8 * jj + 3] = fmaf(f[8 * jj + 3], alpha, __uint_as_float(__shfl_sync(0xffffffffu, bv.w, src)));
+            f[8 * jj + 4] = fmaf(f[8 * jj + 4], alpha, __uint_as_float(__shfl_sync(0xffffffffu, bv_hi.x, src)));
+            f[8 * jj + 5] = fmaf(f[8 * jj + 5], alpha, __uint_as_float(__shfl_sync(0xffffffffu, bv_hi.y, src)));
+            f[8 * jj + 6] = fmaf(f[8 * jj + 6], alpha, __uint_as_float(__shfl_sync(0xffffffffu, bv_hi.z, src)));
+            f[8 * jj + 7] = fmaf(f[8 * jj + 7], alpha, __uint_as_float(__shfl_sync(0xffffffffu, bv_hi.w, src)));
           }
         } else {
           finish32<1>(p, t, f, nc + h * 32);
