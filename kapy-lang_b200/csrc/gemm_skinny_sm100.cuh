@@ -130,15 +130,28 @@ struct SkinnyWork {
 // optional per-column bias, 16-bit output rounded to nearest): a multiply-add, a
 // conversion and a store per element.  One warp per scheduler runs this, so every
 // instruction saved comes off the kernel's tail.
-template <int DT>
+template <int DT, int ACT = KAPYB_ACT_NONE>
 __device__ __forceinline__ void skinny_store16(uint16_t *col, long long row_stride, int rows,
                                                const float (&v)[16], float alpha, float bias_n) {
 #pragma unroll
   for (int i = 0; i < 16; ++i) {
     if (i < rows) {
-      const float r = fmaf(v[i], alpha, bias_n);
+      const float r = apply_activation_t<ACT>(fmaf(v[i], alpha, bias_n));
       col[i * row_stride] = static_cast<uint16_t>(cvt_pack2_t<DT, 1>(r, 0.0f) & 0xffffu);
     }
+  }
+}
+
+// The same with the activation picked once per 16 values.
+template <int DT>
+__device__ __forceinline__ void skinny_store16_act(int act, uint16_t *col, long long row_stride,
+                                                   int rows, const float (&v)[16], float alpha,
+                                                   float bias_n) {
+  switch (act) {
+  case KAPYB_ACT_RELU: skinny_store16<DT, KAPYB_ACT_RELU>(col, row_stride, rows, v, alpha, bias_n); break;
+  case KAPYB_ACT_GELU_TANH: skinny_store16<DT, KAPYB_ACT_GELU_TANH>(col, row_stride, rows, v, alpha, bias_n); break;
+  case KAPYB_ACT_SILU: skinny_store16<DT, KAPYB_ACT_SILU>(col, row_stride, rows, v, alpha, bias_n); break;
+  default: skinny_store16<DT>(col, row_stride, rows, v, alpha, bias_n); break;
   }
 }
 
@@ -379,8 +392,8 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   } else if (warp >= 2) {
     // ------------------------------------------------------------ epilogue
     const int q = warp & 3;
-    // scale + optional per-column bias into a 16-bit output, rounded to nearest
-    const bool fast16 = p.ep.acc == nullptr && p.ep.activation == KAPYB_ACT_NONE &&
+    // scale, optional per-column bias and activation into a 16-bit output, rounded to nearest
+    const bool fast16 = p.ep.acc == nullptr &&
                         (p.ep.bias == nullptr || p.ep.bias_axis == 1) &&
                         p.out_dtype != KAPYB_F32 && p.ep.rounding == KAPYB_RN;
     int acc = 0;
@@ -489,9 +502,11 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         if (n < p.N && !skinny_debug_on<16>(p.debug)) {
           if (fast16) {
             if (p.out_dtype == KAPYB_BF16)
-              skinny_store16<KAPYB_BF16>(col16 + mc * p.c_s0, p.c_s0, p.M - mc, f, p.ep.alpha, bias_n);
+              skinny_store16_act<KAPYB_BF16>(p.ep.activation, col16 + mc * p.c_s0, p.c_s0, p.M - mc, f,
+                                             p.ep.alpha, bias_n);
             else
-              skinny_store16<KAPYB_F16>(col16 + mc * p.c_s0, p.c_s0, p.M - mc, f, p.ep.alpha, bias_n);
+              skinny_store16_act<KAPYB_F16>(p.ep.activation, col16 + mc * p.c_s0, p.c_s0, p.M - mc, f,
+                                            p.ep.alpha, bias_n);
           } else {
 #pragma unroll
             for (int i = 0; i < 16; ++i)
