@@ -2494,6 +2494,68 @@ extern "C" KAPYB_API kapyb_status kapyb_reduce(kapyb_handle h, const kapyb_tenso
   const bool vec = unit_inner && (reinterpret_cast<uintptr_t>(p.src) & 31u) == 0 &&
                    (p.src_row_stride * esz) % 32 == 0;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  // Results on the unit-stride axis (column sums of a row-major tensor), long
+  // enough to be worth two passes: slabs of the reduced axis first, then the slabs.
+  const bool slabs = !unit_inner && p.src_row_stride == 1 && length >= 256 && results >= 64 &&
+                     results % (esz == 4 ? 4 : 8) == 0 && (esz == 2 || esz == 4) &&
+                     (reinterpret_cast<uintptr_t>(p.src) & 15u) == 0 && p.src_col_stride > 0 &&
+                     (p.src_col_stride * esz) % 16 == 0;
+  if (slabs) {
+    const int epl = esz == 4 ? 4 : 8;
+    const int blocks_x = (results + 32 * epl - 1) / (32 * epl);
+    int n_slabs = std::max(1, std::min({64, h->sm_count * 4 / blocks_x, length / 64}));
+    const int slab_len = ((length + n_slabs - 1) / n_slabs + 7) / 8 * 8;
+    n_slabs = (length + slab_len - 1) / slab_len;
+    const size_t skinny_ws = skinny_workspace_bytes();
+    kapyb_status st = kapyb_reserve_workspace(h, skinny_ws + static_cast<size_t>(n_slabs) * results * sizeof(float));
+    if (st != KAPYB_OK) return st;
+    float *partial = reinterpret_cast<float *>(static_cast<char *>(h->workspace) + skinny_ws);
+    const dim3 grid(blocks_x, n_slabs);
+    const long long step_bytes = p.src_col_stride * esz;
+    const bool narrow = p.dst_dtype != KAPYB_F32;
+    ReduceParams q = p;
+    q.src = partial;
+    q.src_dtype = KAPYB_F32;
+    q.cols = n_slabs;
+    q.src_row_stride = 1;
+    q.src_col_stride = results;
+    const int grid2 = (results + 31) / 32;
+#define KAPYB_SLAB(COMB)                                                                             \
+  do {                                                                                               \
+    if (p.src_dtype == KAPYB_F32) {                                                                  \
+      reduce_cols_slab_kernel<COMB, KAPYB_F32, KAPYB_F32><<<grid, 256, 0, stream>>>(                 \
+          p.src, step_bytes, results, length, slab_len, partial);                                    \
+      reduce_cols_kernel<COMB><<<grid2, 256, 0, stream>>>(q);                                        \
+    } else if (p.src_dtype == KAPYB_BF16 && narrow) {                                                \
+      reduce_cols_slab_kernel<COMB, KAPYB_BF16, KAPYB_BF16><<<grid, 256, 0, stream>>>(               \
+          p.src, step_bytes, results, length, slab_len, partial);                                    \
+      reduce_cols_kernel<COMB, KAPYB_BF16><<<grid2, 256, 0, stream>>>(q);                            \
+    } else if (p.src_dtype == KAPYB_BF16) {                                                          \
+      reduce_cols_slab_kernel<COMB, KAPYB_BF16, KAPYB_F32><<<grid, 256, 0, stream>>>(                \
+          p.src, step_bytes, results, length, slab_len, partial);                                    \
+      reduce_cols_kernel<COMB><<<grid2, 256, 0, stream>>>(q);                                        \
+    } else if (narrow) {                                                                             \
+      reduce_cols_slab_kernel<COMB, KAPYB_F16, KAPYB_F16><<<grid, 256, 0, stream>>>(                 \
+          p.src, step_bytes, results, length, slab_len, partial);                                    \
+      reduce_cols_kernel<COMB, KAPYB_F16><<<grid2, 256, 0, stream>>>(q);                             \
+    } else {                                                                                         \
+      reduce_cols_slab_kernel<COMB, KAPYB_F16, KAPYB_F32><<<grid, 256, 0, stream>>>(                 \
+          p.src, step_bytes, results, length, slab_len, partial);                                    \
+      reduce_cols_kernel<COMB><<<grid2, 256, 0, stream>>>(q);                                        \
+    }                                                                                                \
+  } while (0)
+    switch (combiner) {
+    case KAPYB_RED_ADD: KAPYB_SLAB(KAPYB_RED_ADD); break;
+    case KAPYB_RED_MUL: KAPYB_SLAB(KAPYB_RED_MUL); break;
+    case KAPYB_RED_MAX: KAPYB_SLAB(KAPYB_RED_MAX); break;
+    default: KAPYB_SLAB(KAPYB_RED_MIN); break;
+    }
+#undef KAPYB_SLAB
+    CUDA_TRY(h, cudaGetLastError());
+    h->launches += 2;
+    h->last_kernel = "reduce_cols_slabs";
+    return KAPYB_OK;
+  }
   switch (combiner) {
   case KAPYB_RED_ADD: launch_reduce<KAPYB_RED_ADD>(p, unit_inner, vec, h->sm_count, stream); break;
   case KAPYB_RED_MUL: launch_reduce<KAPYB_RED_MUL>(p, unit_inner, vec, h->sm_count, stream); break;

@@ -86,7 +86,8 @@ def test_axis0_and_strided(handle, ko, shape):
     out = handle.reduce(X.cuda(), axis=0, out_dtype=torch.float32)
     handle.check()
     assert out.shape == (1, shape[1])
-    assert handle.last_kernel == ("reduce_cols" if shape[1] > 1 else "reduce_rows")
+    assert handle.last_kernel == ("reduce_rows" if shape[1] == 1 else
+                                  "reduce_cols_slabs" if shape == (4096, 64) else "reduce_cols")
     check_sum(ko, out.cpu().numpy().ravel().astype(np.float64), X, torch.bfloat16, 0,
               torch.float32)
     # a column-major view reduced along axis 1 is the same computation
@@ -133,3 +134,30 @@ def test_shape_rules(handle, pkg):
         handle.reduce(X, axis=1, out=torch.zeros((4, 1), dtype=torch.float16, device="cuda"))
     e = handle.reduce(torch.zeros((0, 8), dtype=torch.bfloat16, device="cuda"), axis=1)
     assert e.shape == (0, 1)
+
+
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("comb", ["ADD", "MAX", "MIN"])
+def test_column_reduction_in_slabs(handle, ko, pkg, dt, comb):
+    """Results on the unit-stride axis of a tall source: the reduced axis is cut into
+    slabs (first pass) that a second pass combines.  f32 results and, for 16-bit
+    sources, results at the source's type (a rounding per combination)."""
+    shape = (3000, 520)
+    X = normal(shape, 91, dtype=dt)
+    c = getattr(pkg.abi, "RED_" + comb)
+    for od in ([torch.float32] if dt == torch.float32 else [torch.float32, dt]):
+        out = handle.reduce(X.cuda(), axis=0, combiner=c, out_dtype=od)
+        handle.check()
+        assert handle.last_kernel == "reduce_cols_slabs" and out.shape == (1, shape[1])
+        got = out.cpu().double().numpy().ravel()
+        if comb == "ADD":
+            check_sum(ko, got, X, dt, 0, od)
+        else:
+            ref, _ = ko.reduce_f64(bits(X), code(dt), 0, c)
+            assert np.array_equal(got, ref)
+    # a NaN reaches its column's result whatever slab it sits in
+    if comb != "ADD":
+        Xn = X.clone()
+        Xn[2999, 7] = float("nan")
+        o = handle.reduce(Xn.cuda(), axis=0, combiner=c, out_dtype=torch.float32).cpu().ravel()
+        assert torch.isnan(o[7]) and not torch.isnan(o[8])
