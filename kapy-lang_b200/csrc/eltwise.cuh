@@ -557,6 +557,11 @@ template <int OP>
 __device__ __forceinline__ float binop_at(float a, float b, int dt) {
   if (OP == KAPYB_OP_ADD) return dt == KAPYB_F32 ? __fadd_rn(a, b) : fma_at(a, 1.0f, b, dt);
   if (OP == KAPYB_OP_SUB) return dt == KAPYB_F32 ? __fsub_rn(a, b) : fma_at(b, -1.0f, a, dt);
+  if (OP == KAPYB_OP_DIV) return dt == KAPYB_F32 ? div_full(a, b) : round_to_dtype(__fdiv_rn(a, b), dt, 1);
+  if (OP == KAPYB_OP_MAXIMUM) return maximum_f(a, b);
+  if (OP == KAPYB_OP_MINIMUM) return minimum_f(a, b);
+  if (OP == KAPYB_OP_MAXNUM) return fmaxf(a, b);
+  if (OP == KAPYB_OP_MINNUM) return fminf(a, b);
   return dt == KAPYB_F32 ? __fmul_rn(a, b) : fma_at(a, b, -0.0f, dt);
 }
 
@@ -564,6 +569,19 @@ template <int OP>
 __device__ __forceinline__ uint32_t binop_word(uint32_t wa, uint32_t wb, int dt) {
   if (dt == KAPYB_F32)
     return __float_as_uint(binop_at<OP>(__uint_as_float(wa), __uint_as_float(wb), dt));
+  if constexpr (OP != KAPYB_OP_ADD && OP != KAPYB_OP_SUB && OP != KAPYB_OP_MUL) {
+    // the interpreter's own arithmetic on each half (results are values of the type:
+    // the repacking conversion is exact)
+    float alo, ahi, blo, bhi;
+    if (dt == KAPYB_BF16) {
+      unpack2_16<KAPYB_BF16>(wa, alo, ahi);
+      unpack2_16<KAPYB_BF16>(wb, blo, bhi);
+    } else {
+      unpack2_16<KAPYB_F16>(wa, alo, ahi);
+      unpack2_16<KAPYB_F16>(wb, blo, bhi);
+    }
+    return cvt_pack2(binop_at<OP>(alo, blo, dt), binop_at<OP>(ahi, bhi, dt), dt, 1);
+  }
   if (dt == KAPYB_BF16) {
     const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162 *>(&wa);
     const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162 *>(&wb);

@@ -2341,10 +2341,12 @@ extern "C" KAPYB_API kapyb_status kapyb_elementwise(kapyb_handle h, const kapyb_
       return KAPYB_OK;
     }
   }
-  // Fused path 2: z = a (add|sub|mul) b, one element type, contiguous.
+  // Fused path 2: z = a (add|sub|mul|div|maximum|minimum|maxnum|minnum) b, one element type, contiguous.
   if (!in_place && root >= 0 && n_inputs >= 2) {
     const ExprNode &r = nodes[root];
-    if ((r.op == KAPYB_OP_ADD || r.op == KAPYB_OP_SUB || r.op == KAPYB_OP_MUL) && r.a >= 0 &&
+    if ((r.op == KAPYB_OP_ADD || r.op == KAPYB_OP_SUB || r.op == KAPYB_OP_MUL ||
+         r.op == KAPYB_OP_DIV || r.op == KAPYB_OP_MAXIMUM || r.op == KAPYB_OP_MINIMUM ||
+         r.op == KAPYB_OP_MAXNUM || r.op == KAPYB_OP_MINNUM) && r.a >= 0 &&
         r.b >= 0 && nodes[r.a].op == KAPYB_OP_LOAD && nodes[r.b].op == KAPYB_OP_LOAD &&
         r.dtype == out->dtype) {
       const kapyb_tensor2d &ta = inputs[nodes[r.a].flags], &tb = inputs[nodes[r.b].flags];
@@ -2359,12 +2361,15 @@ extern "C" KAPYB_API kapyb_status kapyb_elementwise(kapyb_handle h, const kapyb_
         const uint4 *pa = static_cast<const uint4 *>(elem_ptr(&ta));
         const uint4 *pb = static_cast<const uint4 *>(elem_ptr(&tb));
         uint4 *pz = static_cast<uint4 *>(const_cast<void *>(elem_ptr(out)));
-        if (r.op == KAPYB_OP_ADD)
-          elt_binary_kernel<KAPYB_OP_ADD><<<grid, 256, 0, stream>>>(pa, pb, pz, n_vec, total, r.dtype);
-        else if (r.op == KAPYB_OP_SUB)
-          elt_binary_kernel<KAPYB_OP_SUB><<<grid, 256, 0, stream>>>(pa, pb, pz, n_vec, total, r.dtype);
-        else
-          elt_binary_kernel<KAPYB_OP_MUL><<<grid, 256, 0, stream>>>(pa, pb, pz, n_vec, total, r.dtype);
+        switch (r.op) {
+#define KAPYB_BIN(OP) \
+  case OP: elt_binary_kernel<OP><<<grid, 256, 0, stream>>>(pa, pb, pz, n_vec, total, r.dtype); break;
+          KAPYB_BIN(KAPYB_OP_ADD) KAPYB_BIN(KAPYB_OP_SUB) KAPYB_BIN(KAPYB_OP_DIV)
+          KAPYB_BIN(KAPYB_OP_MAXIMUM) KAPYB_BIN(KAPYB_OP_MINIMUM) KAPYB_BIN(KAPYB_OP_MAXNUM)
+          KAPYB_BIN(KAPYB_OP_MINNUM)
+#undef KAPYB_BIN
+        default: elt_binary_kernel<KAPYB_OP_MUL><<<grid, 256, 0, stream>>>(pa, pb, pz, n_vec, total, r.dtype); break;
+        }
         CUDA_TRY(h, cudaGetLastError());
         h->launches++;
         h->last_kernel = "elt_binary";

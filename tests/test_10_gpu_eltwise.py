@@ -62,7 +62,7 @@ def test_fused_equals_interpreter(handle, ko, pkg):
     assert torch.equal(y_fused, y_interp)
 
 
-@pytest.mark.parametrize("op", ["ADD", "SUB", "MUL"])
+@pytest.mark.parametrize("op", ["ADD", "SUB", "MUL", "DIV", "MAXIMUM", "MINIMUM", "MAXNUM", "MINNUM"])
 @pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16, torch.float32])
 def test_binary_bit_exact(handle, ko, pkg, op, dt):
     """elementwise_add.mlir:17-23 at whole-tensor scope: [1,n] f16 add, and its
@@ -72,7 +72,11 @@ def test_binary_bit_exact(handle, ko, pkg, op, dt):
     prog = pkg.programs.binary(getattr(pkg.abi, "OP_" + op), pkg.runtime.dtype_code(dt))
     got, want = run_both(handle, ko, prog, [a, b], (1, n), dt)
     assert handle.last_kernel == "elt_binary"
-    if dt == torch.float32:
+    if dt == torch.float32 and op == "DIV":
+        # div.full.f32 (ElementwiseOpToLLVM.cpp:730-769) is good to 2 ulp, not correctly rounded
+        g, w = got.view(np.uint32).astype(np.int64), want.view(np.uint32).astype(np.int64)
+        assert np.abs(g - w).max() <= 2
+    elif dt == torch.float32:
         assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
     else:
         assert np.array_equal(got, want)
